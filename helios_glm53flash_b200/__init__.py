@@ -1,0 +1,289 @@
+"""helios_glm53flash_b200 - B200 (sm_100a) kernels for the GLM-5.3-Flash trunk-attention hot path.
+
+The product is ``libhelios_b200.so`` (hand-written CUDA behind a C ABI, see ``include/helios_b200.h``)
+plus the reference-named C++ launchers (``include/helios_b200_shim.hpp``).  This module is the
+Python host side used by the tests and the benchmark: it loads the library with ctypes and exposes
+one function per reference launcher, under the reference's names and argument order
+(``helios::attn::*`` in src/cuda/attn/attn.cuh, ``helios::aux::*`` in src/cuda/aux/gdn.cuh and
+dsa_topk.cuh of the reference tree), taking torch CUDA tensors as device buffers.
+
+There is no CPU path: calling a compute entry point without the library or without a CUDA device
+raises.  PyTorch is used for device memory and streams only.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhelios_b200.so")
+
+HK_OK, HK_ERR_INVALID, HK_ERR_UNSUPPORTED, HK_ERR_CUDA, HK_ERR_WORKSPACE, HK_ERR_TIMEOUT = range(6)
+HK_F16, HK_BF16 = 0, 1
+
+_c = ctypes
+_vp, _i, _f, _sz, _i64 = _c.c_void_p, _c.c_int, _c.c_float, _c.c_size_t, _c.c_int64
+
+# name -> (restype, argtypes): every symbol declared in include/helios_b200.h
+SIGNATURES = {
+    "hk_status_string": (_c.c_char_p, [_i]),
+    "hk_abi_version": (_i, []),
+    "hk_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
+    "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
+    "hk_kda_chunked_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "hk_kpool_write": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
+    "hk_indexer_score": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "hk_indexer_score_legacy": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hk_dsa_topk": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "hk_pool_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "hk_mla_partial_bytes": (_sz, [_i, _i64]),
+    "hk_mla_auto_splits": (_i, [_i, _i]),
+    "hk_mla_sparse": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "hk_mla_dense": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "hk_mla_dense_partial": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
+    "hk_lse_combine_ptrs": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
+    "hk_q_latent": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "hk_o_absorb": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "hk_wuv_transpose": (_i, [_vp, _vp, _vp]),
+    "hk_o_absorb_t": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "hk_read_device_status": (_i, [_vp, _i]),
+    "hk_tc05_selftest": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+}
+
+_lib = None
+
+
+class HeliosB200Error(RuntimeError):
+    """Raised when an hk_* entry point returns a non-zero status."""
+
+    def __init__(self, name, status):
+        self.status = status
+        super().__init__("%s failed with status %d (%s)" % (name, status, status_string(status)))
+
+
+def load_library():
+    """Load libhelios_b200.so (built in-tree by ``build.py``); raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libhelios_b200.so is not built (run `python -m helios_glm53flash_b200.build` or "
+                "__graft_entry__.build()); this package has no fallback path")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def status_string(status):
+    return load_library().hk_status_string(int(status)).decode()
+
+
+def _require_cuda():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("helios_glm53flash_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    return torch
+
+
+def _ptr(t):
+    return None if t is None else _c.c_void_p(t.data_ptr())
+
+
+def _stream(stream=None):
+    torch = _require_cuda()
+    s = torch.cuda.current_stream() if stream is None else stream
+    return _c.c_void_p(s.cuda_stream)
+
+
+def _call(name, *args):
+    st = getattr(load_library(), name)(*args)
+    if st != HK_OK:
+        raise HeliosB200Error(name, st)
+
+
+def _scratch(nbytes, device):
+    """A torch-owned scratch buffer (256-byte aligned by the caching allocator)."""
+    torch = _require_cuda()
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# ---------------------------------------------------------------------------------------------
+# helios::aux
+# ---------------------------------------------------------------------------------------------
+def cuda_causal_conv1d_update(x, conv_state, slots, weight, bias, out, bsz, dim, seqlen, state_size,
+                              K, activation, history, stream=None):
+    """helios::aux::cuda_causal_conv1d_update (src/cuda/aux/gdn.cuh:67-83)."""
+    _call("hk_conv1d_update", _ptr(x), _ptr(conv_state), _ptr(slots), _ptr(weight), _ptr(bias),
+          _ptr(out), bsz, dim, seqlen, state_size, K, int(bool(activation)), int(bool(history)),
+          _stream(stream))
+
+
+def cuda_recurrent_gated_delta_rule(mixed_qkv, g, beta, recurrent_state, core_attn_out, bsz, seqlen,
+                                    num_k_heads, num_v_heads, k_head_dim, v_head_dim,
+                                    history_stride, slots, channelwise, history, stream=None,
+                                    out_f32=None, force_recurrent=False, workspace=None):
+    """helios::aux::cuda_recurrent_gated_delta_rule (src/cuda/aux/gdn.cuh:47-65).
+
+    As the C++ launcher of this library does, long channelwise calls go to the chunked tensor-core
+    kernel; ``force_recurrent`` keeps the per-token kernel.  ``out_f32`` optionally receives the
+    output before bf16 rounding."""
+    chunked = (channelwise and not history and seqlen >= 64 and k_head_dim == 128 and
+               v_head_dim == 128 and num_k_heads == num_v_heads and history_stride == 1 and
+               not force_recurrent)
+    if chunked:
+        nbytes = load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_v_heads)
+        ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device)
+        st = load_library().hk_kda_chunked_prefill(
+            _ptr(mixed_qkv), _ptr(g), _ptr(beta), _ptr(recurrent_state), _ptr(core_attn_out),
+            _ptr(out_f32), bsz, seqlen, num_v_heads, _ptr(slots), _ptr(ws), ws.numel(),
+            _stream(stream))
+        if st == HK_OK:
+            return "chunked"
+        if st != HK_ERR_UNSUPPORTED:
+            raise HeliosB200Error("hk_kda_chunked_prefill", st)
+    _call("hk_kda_recurrent", _ptr(mixed_qkv), _ptr(g), _ptr(beta), _ptr(recurrent_state),
+          _ptr(core_attn_out), _ptr(out_f32), bsz, seqlen, num_k_heads, num_v_heads, k_head_dim,
+          v_head_dim, history_stride, _ptr(slots), int(bool(channelwise)), int(bool(history)),
+          _stream(stream))
+    return "recurrent"
+
+
+def kda_chunked_workspace_bytes(bsz, seqlen, num_heads):
+    return load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)
+
+
+def dsa_topk(scores, s_stride, indices, R, T, k, k_pad, t_ptr=None, t_seq=0, stream=None):
+    """helios::aux::dsa_topk (src/cuda/aux/dsa_topk.cuh:15-27)."""
+    _call("hk_dsa_topk", _ptr(scores), s_stride, _ptr(indices), R, T, k, k_pad, _ptr(t_ptr), t_seq,
+          _stream(stream))
+
+
+# ---------------------------------------------------------------------------------------------
+# helios::attn
+# ---------------------------------------------------------------------------------------------
+def kpool_write(idx_k, idx_g, raw_ring, raw_rows, pool_k_nt, ape, pos_start, n_new, stream=None):
+    """helios::attn::kpool_write (src/cuda/attn/attn.cuh:80-87)."""
+    _call("hk_kpool_write", _ptr(idx_k), _ptr(idx_g), _ptr(raw_ring), raw_rows, _ptr(pool_k_nt),
+          _ptr(ape), pos_start, n_new, _stream(stream))
+
+
+def indexer_score(q_idx, pool_k_nt, w, q_pos, scores, m, npools, stream=None, score_stride=None,
+                  n_heads=32):
+    """helios::attn::indexer_score (src/cuda/attn/attn.cuh:49-55); fp16 or bf16 keys by tensor dtype."""
+    torch = _require_cuda()
+    dtype = HK_BF16 if q_idx.dtype == torch.bfloat16 else HK_F16
+    _call("hk_indexer_score", _ptr(q_idx), _ptr(pool_k_nt), _ptr(w), _ptr(q_pos), _ptr(scores), m,
+          npools, npools if score_stride is None else score_stride, n_heads, dtype, _stream(stream))
+
+
+indexer_score_mma = indexer_score
+
+
+def indexer_score_legacy(q_idx, pool_k, w, q_pos, scores, m, npools, pk_stride, stream=None):
+    """helios::attn::indexer_score_legacy (src/cuda/attn/attn.cuh:46-48)."""
+    _call("hk_indexer_score_legacy", _ptr(q_idx), _ptr(pool_k), _ptr(w), _ptr(q_pos), _ptr(scores),
+          m, npools, pk_stride, _stream(stream))
+
+
+def pool_expand(pool_idx, q_pos, raw_idx, m, cur_pos, stream=None, n_sel=512):
+    """helios::attn::pool_expand (src/cuda/attn/attn.cuh:60-65): one cur_pos for every row."""
+    _call("hk_pool_expand", _ptr(pool_idx), None, _ptr(raw_idx), m, cur_pos, n_sel, _stream(stream))
+
+
+def pool_expand_row(pool_idx, q_pos, raw_idx, m, stream=None, n_sel=512):
+    """helios::attn::pool_expand_row (src/cuda/attn/attn.cuh:67-72)."""
+    _call("hk_pool_expand", _ptr(pool_idx), _ptr(q_pos), _ptr(raw_idx), m, 0, n_sel, _stream(stream))
+
+
+def mla_auto_splits(m, n_keys):
+    return load_library().hk_mla_auto_splits(m, n_keys)
+
+
+def mla_partial_bytes(n_split, rows):
+    return load_library().hk_mla_partial_bytes(n_split, rows)
+
+
+def mla_sparse_decode(q_lat, ckv, raw_idx, kidx, lat_out, m, stream=None, scale=0.0625, n_heads=64,
+                      n_split=0, workspace=None):
+    """helios::attn::mla_sparse_decode (src/cuda/attn/attn.cuh:93-99) with explicit scale / heads."""
+    if n_split <= 0:
+        n_split = mla_auto_splits(m, kidx)
+    ws = workspace
+    if n_split > 1 and ws is None:
+        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device)
+    _call("hk_mla_sparse", _ptr(q_lat), _ptr(ckv), _ptr(raw_idx), kidx, _ptr(lat_out), m, n_heads,
+          float(scale), n_split, _ptr(ws), 0 if ws is None else ws.numel(), _stream(stream))
+
+
+def mla_dense_prefill(q_lat, ckv, lat_out, qlen, pos_start, stream=None, scale=0.0625, n_heads=64,
+                      kv_base=None, kv_len=None, n_split=0, workspace=None, n_keys_hint=None):
+    """helios::attn::mla_dense_prefill (src/cuda/attn/attn.cuh:104-108); qlen = 1 is dense decode.
+    kv_base / kv_len (device int64 / int32 per row) select per-row cache ranges (batched decode)."""
+    if n_split <= 0:
+        n_split = mla_auto_splits(qlen, n_keys_hint if n_keys_hint else pos_start + qlen)
+    ws = workspace
+    if n_split > 1 and ws is None:
+        ws = _scratch(mla_partial_bytes(n_split, qlen * n_heads), q_lat.device)
+    _call("hk_mla_dense", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start,
+          _ptr(lat_out), qlen, n_heads, float(scale), n_split, _ptr(ws),
+          0 if ws is None else ws.numel(), _stream(stream))
+
+
+def mla_dense_partial(q_lat, ckv, kv_base, kv_len, pos_start, part_m, part_l, part_acc, m,
+                      n_heads=64, scale=0.0625, stream=None):
+    """One split's un-normalised (m, l, acc) partial - the unit of split-KV across GPUs."""
+    _call("hk_mla_dense_partial", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start,
+          _ptr(part_m), _ptr(part_l), _ptr(part_acc), m, n_heads, float(scale), _stream(stream))
+
+
+def lse_combine(part_m, part_l, part_acc, n_split, rows, out, stream=None):
+    """Standalone split-KV log-sum-exp combine (the reference merges in-kernel, attn.cu:462-481)."""
+    _call("hk_lse_combine", _ptr(part_m), _ptr(part_l), _ptr(part_acc), n_split, rows, _ptr(out),
+          _stream(stream))
+
+
+def lse_combine_ptrs(ptrs_m, ptrs_l, ptrs_acc, n_split, rows, out, stream=None):
+    """Combine over per-split pointers (device int64 tensors of addresses, e.g. peer buffers)."""
+    _call("hk_lse_combine_ptrs", _ptr(ptrs_m), _ptr(ptrs_l), _ptr(ptrs_acc), n_split, rows,
+          _ptr(out), _stream(stream))
+
+
+def q_latent(q_nope, kv_b, q_lat, m, stream=None):
+    _call("hk_q_latent", _ptr(q_nope), _ptr(kv_b), _ptr(q_lat), m, _stream(stream))
+
+
+q_latent_t = q_latent
+
+
+def o_absorb(lat_out, kv_b, o, m, stream=None):
+    _call("hk_o_absorb", _ptr(lat_out), _ptr(kv_b), _ptr(o), m, _stream(stream))
+
+
+def wuv_transpose(kv_b, wuv_t, stream=None):
+    _call("hk_wuv_transpose", _ptr(kv_b), _ptr(wuv_t), _stream(stream))
+
+
+def o_absorb_t(lat_out, wuv_t, o, nrows, stream=None):
+    _call("hk_o_absorb_t", _ptr(lat_out), _ptr(wuv_t), _ptr(o), nrows, _stream(stream))
+
+
+def read_device_status(reset=True):
+    """0 unless a bounded device-side wait expired since the last reset (synchronises)."""
+    _require_cuda()
+    v = _c.c_int(0)
+    _call("hk_read_device_status", _c.byref(v), int(reset))
+    return v.value
+
+
+def tc05_selftest(a, b, M, N, K, b_layout, stream=None):
+    """Raw TMEM accumulator [128][N] of D = A * B through the tcgen05 helper layer."""
+    torch = _require_cuda()
+    d = torch.zeros(128, N, dtype=torch.float32, device=a.device)
+    status = torch.zeros(4, dtype=torch.int32, device=a.device)
+    _call("hk_tc05_selftest", _ptr(a), _ptr(b), _ptr(d), M, N, K, b_layout, _ptr(status),
+          _stream(stream))
+    return d, status

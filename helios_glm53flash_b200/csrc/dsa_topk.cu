@@ -1,0 +1,203 @@
+// Exact top-k selection over fp16 score rows for the DSA indexer.
+// Interface and output contract of helios::aux::dsa_topk (reference: src/cuda/aux/dsa_topk.cu:73-273,
+// :668-732): on the order-preserving 16-bit key of the fp16 bit pattern (:21-24) find the k-th
+// largest value v*; emit every entry above v* in ascending index order, then entries equal to v*
+// in ascending index order until k are out; -inf (and anything below it) is never selected; if a
+// row holds fewer than k selectable entries all of them are emitted; the rest of the k_pad-wide
+// output row is -1.  Integer work: results are bit-exact by construction.
+//
+// One CTA of 1024 threads per row, three sweeps of the row (the reference makes four: two
+// histogram sweeps and two compaction sweeps).  Sweep 1 histograms the top 11 key bits, sweep 2 the
+// low 5 bits inside the crossing bucket, sweep 3 is a single ordered compaction that places the
+// "above" entries and the tie entries at once (their final offsets are known after sweep 2).
+#include "hk_common.cuh"
+
+namespace hk {
+
+constexpr int TK_THREADS = 1024;
+constexpr int TK_WARPS = TK_THREADS / 32;
+constexpr uint32_t KEY_NEG_INF = 0x03ffu;  // key of fp16 -inf (0xfc00)
+
+__device__ __forceinline__ uint32_t topk_key(uint32_t u16) {
+  return (u16 & 0x8000u) ? (~u16 & 0xffffu) : (u16 | 0x8000u);
+}
+
+// Exclusive block scan of one int per thread; returns the exclusive prefix, *total = block sum.
+// `scratch` holds TK_WARPS + 1 ints.  Contains two barriers.
+__device__ __forceinline__ int block_exscan(int v, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int wv = scratch[lane];
+    int wi = wv;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += n;
+    }
+    scratch[lane] = wi - wv;
+    if (lane == 31) scratch[TK_WARPS] = wi;
+  }
+  __syncthreads();
+  *total = scratch[TK_WARPS];
+  return scratch[warp] + incl - v;
+}
+
+// load 8 consecutive keys starting at element i8*8 (VEC: one 16-byte load), invalid ones as 0
+template <bool VEC>
+__device__ __forceinline__ void load8(const uint16_t* row, int i8, int T, uint32_t (&key)[8]) {
+  const int base = i8 * 8;
+  if (VEC && base + 8 <= T) {
+    uint4 v = *reinterpret_cast<const uint4*>(row + base);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      key[2 * j] = topk_key(w[j] & 0xffffu);
+      key[2 * j + 1] = topk_key(w[j] >> 16);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; j++) key[j] = (base + j < T) ? topk_key(row[base + j]) : 0u;
+  }
+}
+
+template <bool VEC>
+__global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
+    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k,
+    int k_pad, const int* __restrict__ t_ptr, int t_seq) {
+  if (t_ptr) T = t_seq > 0 ? t_ptr[blockIdx.x / t_seq] : *t_ptr;
+  const uint16_t* row = scores + (size_t)blockIdx.x * s_stride;
+  int* row_o = out + (size_t)blockIdx.x * k_pad;
+  const int t = threadIdx.x;
+  const int n_slots = (T + 7) >> 3;
+
+  __shared__ int hist[2048];
+  __shared__ int scan_ws[TK_WARPS + 1];
+  __shared__ int sh_sel[3];  // crossing bucket, count above it, (sweep 2) low bits
+
+  // ---- sweep 1: histogram of key >> 5 over selectable entries (bucket >= 32 <=> key > -inf) ----
+  for (int i = t; i < 2048; i += TK_THREADS) hist[i] = 0;
+  __syncthreads();
+  for (int i8 = t; i8 < n_slots; i8 += TK_THREADS) {
+    uint32_t key[8];
+    load8<VEC>(row, i8, T, key);
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if (key[j] > KEY_NEG_INF) atomicAdd(&hist[key[j] >> 5], 1);
+  }
+  __syncthreads();
+  // thread t owns buckets 2047-2t and 2046-2t (descending); find where the running count crosses k
+  int h_hi = hist[2047 - 2 * t], h_lo = hist[2046 - 2 * t];
+  int total_sel;
+  int excl = block_exscan(h_hi + h_lo, scan_ws, &total_sel);
+  if (t == 0) sh_sel[0] = -1;
+  __syncthreads();
+  if (total_sel >= k && k > 0) {
+    if (excl < k && excl + h_hi >= k) { sh_sel[0] = 2047 - 2 * t; sh_sel[1] = excl; }
+    else if (excl + h_hi < k && excl + h_hi + h_lo >= k) { sh_sel[0] = 2046 - 2 * t; sh_sel[1] = excl + h_hi; }
+  }
+  __syncthreads();
+  const int b1 = sh_sel[0];
+  uint32_t thresh;
+  int cnt_gt, n_eq_take;
+  if (b1 < 0) {
+    // fewer than k selectable entries (or k == 0): take them all, no ties
+    thresh = KEY_NEG_INF;
+    cnt_gt = k > 0 ? total_sel : 0;
+    n_eq_take = 0;
+    if (k == 0) thresh = 0xffffu;
+  } else {
+    const int above1 = sh_sel[1];
+    // ---- sweep 2: low 5 bits inside bucket b1 ----
+    if (t < 32) hist[t] = 0;
+    __syncthreads();
+    for (int i8 = t; i8 < n_slots; i8 += TK_THREADS) {
+      uint32_t key[8];
+      load8<VEC>(row, i8, T, key);
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if ((int)(key[j] >> 5) == b1) atomicAdd(&hist[key[j] & 31u], 1);
+    }
+    __syncthreads();
+    if (t < 32) {
+      // lane l owns low value 31-l (descending)
+      const int hv = hist[31 - t];
+      int incl = hv;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (t >= o) incl += n;
+      }
+      const int need = k - above1;
+      if (incl - hv < need && incl >= need) { sh_sel[2] = 31 - t; sh_sel[1] = above1 + incl - hv; }
+    }
+    __syncthreads();
+    thresh = ((uint32_t)b1 << 5) | (uint32_t)sh_sel[2];
+    cnt_gt = sh_sel[1];
+    n_eq_take = k - cnt_gt;
+  }
+
+  // ---- sweep 3: ordered compaction, 8 consecutive elements per thread per tile ----
+  int base_gt = 0, base_eq = 0;
+  const int n_tiles = (n_slots + TK_THREADS - 1) / TK_THREADS;
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (base_gt >= cnt_gt && base_eq >= n_eq_take) break;  // block-uniform
+    const int i8 = tile * TK_THREADS + t;
+    uint32_t m_gt = 0, m_eq = 0;
+    if (i8 < n_slots) {
+      uint32_t key[8];
+      load8<VEC>(row, i8, T, key);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        if (key[j] > thresh && key[j] > KEY_NEG_INF) m_gt |= 1u << j;
+        if (key[j] == thresh && n_eq_take > 0) m_eq |= 1u << j;
+      }
+    }
+    const int packed = __popc(m_gt) | (__popc(m_eq) << 16);
+    int tot;
+    const int ex = block_exscan(packed, scan_ws, &tot);
+    int o_gt = base_gt + (ex & 0xffff);
+    int o_eq = base_eq + (ex >> 16);
+    const int ibase = i8 * 8;
+    while (m_gt) {
+      const int j = __ffs((int)m_gt) - 1;
+      m_gt &= m_gt - 1;
+      row_o[o_gt++] = ibase + j;
+    }
+    while (m_eq) {
+      const int j = __ffs((int)m_eq) - 1;
+      m_eq &= m_eq - 1;
+      if (o_eq < n_eq_take) row_o[cnt_gt + o_eq] = ibase + j;
+      o_eq++;
+    }
+    base_gt += tot & 0xffff;
+    base_eq += tot >> 16;
+  }
+  const int emitted = cnt_gt + min(base_eq, n_eq_take);
+  for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
+}
+
+}  // namespace hk
+
+HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, int T, int k,
+                       int k_pad, const int* t_ptr, int t_seq, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(scores && indices && R >= 0 && T >= 0 && k >= 0 && k <= k_pad && s_stride >= 0);
+  HK_REQUIRE(k <= 32767);  // packed 16-bit counters in the compaction scan
+  if (R == 0) return HK_OK;
+  const bool vec = (s_stride % 8 == 0) && aligned(scores, 16);
+  cudaStream_t s = as_stream(stream);
+  if (vec)
+    dsa_topk_kernel<true><<<R, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad, t_ptr, t_seq);
+  else
+    dsa_topk_kernel<false><<<R, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad, t_ptr, t_seq);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

@@ -1,0 +1,202 @@
+// DSA indexer scores on the 5th-generation tensor cores.
+//   S[r][p] = 32^-1/2 * sum_h w[r][h] * relu(128^-1/2 * q[r][h] . pk[p]),  -inf where 4p+3 > q_pos[r]
+// Interface of helios::attn::indexer_score (reference: src/cuda/attn/attn.cu:182-273, an
+// mma.sync.m16n8k16 kernel with queries as M).
+//
+// Orientation: POOLS are the MMA M dimension (128 pooled keys per tile = 128 TMEM lanes) and
+// (query row, head) pairs are N (up to 8 rows x 32 heads = 256 columns), K = 128.  That way the
+// relu / head-weight / head-sum epilogue reads one TMEM lane per thread and never crosses lanes,
+// and a decode step (one query row) is a single M128 N32 K128 tile per 32 KB of pooled keys: the
+// kernel streams the key plane once from HBM (256 B per pool).  Both operands are K-major exactly
+// as they sit in memory ([pool][128] and [row][head][128]); they are staged with 16-byte cp.async
+// into the no-swizzle core-matrix layout (8 rows x 16 B contiguous per lane group: conflict-free).
+#include <cuda_pipeline_primitives.h>
+
+#include "hk_common.cuh"
+#include "tc05.cuh"
+
+namespace hk {
+
+constexpr int IX_TILE_P = 128;   // pools per tile (MMA M)
+constexpr int IX_RG = 8;         // query rows per MMA group (N = 32 * rows)
+constexpr int IX_HEADS = 32;
+constexpr uint32_t IX_LBO = 128;           // K-chunk stride: core matrices adjacent along K
+constexpr uint32_t IX_SBO = 16 * 128;      // 8-row group stride: 16 K-chunks of 128 B
+constexpr size_t IX_SMEM_A = (size_t)IX_TILE_P * IDX_DIM * 2;            // 32 KB
+constexpr size_t IX_SMEM_B = (size_t)IX_RG * IX_HEADS * IDX_DIM * 2;     // 64 KB
+constexpr size_t IX_SMEM = IX_SMEM_A + IX_SMEM_B + IX_RG * IX_HEADS * 4 + IX_RG * 4 + 64;
+
+// Stage `nrows` rows of 128 16-bit elements (256 B each, contiguous in global memory) as a K-major
+// tile.  Lane l of a warp handles row (l % 8) of an 8-row group and K-chunk (l / 8) + 4*j, so every
+// quarter-warp writes one contiguous 128-byte core matrix.  Rows >= valid_rows are zero-filled.
+__device__ __forceinline__ void stage_kmajor_rows(uint8_t* smem_tile, const uint16_t* gsrc,
+                                                  int nrows, int valid_rows, int tid, int nthreads) {
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+  const int r_in = lane & 7, kc0 = lane >> 3;
+  // one warp-iteration covers 8 rows x 4 chunks; a row group needs 4 of them (16 chunks)
+  const int items = (nrows / 8) * 4;
+  for (int it = warp; it < items; it += nwarps) {
+    const int grp = it >> 2, kc = kc0 + (it & 3) * 4;
+    const int row = grp * 8 + r_in;
+    uint8_t* dst = smem_tile + grp * IX_SBO + kc * IX_LBO + r_in * 16;
+    if (row < valid_rows) {
+      __pipeline_memcpy_async(dst, gsrc + (size_t)row * IDX_DIM + kc * 8, 16);
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+template <int FMT>
+__global__ __launch_bounds__(128) void indexer_tc_kernel(
+    const uint16_t* __restrict__ q, const uint16_t* __restrict__ pk, const uint16_t* __restrict__ w,
+    const int* __restrict__ q_pos, __half* __restrict__ scores, int m, int npools, int score_stride,
+    int rows_per_cta, int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + IX_SMEM_A;
+  float* w_sm = reinterpret_cast<float*>(sB + IX_SMEM_B);
+  int* pos_sm = reinterpret_cast<int*>(w_sm + IX_RG * IX_HEADS);
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int p0 = blockIdx.x * IX_TILE_P;
+  const int r_begin = blockIdx.y * rows_per_cta;
+  const int r_end = min(m, r_begin + rows_per_cta);
+
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
+  stage_kmajor_rows(sA, pk + (size_t)p0 * IDX_DIM, IX_TILE_P, min(IX_TILE_P, npools - p0), tid, 128);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t a_addr = tc::smem_u32(sA), b_addr = tc::smem_u32(sB);
+  const int p = p0 + tid;  // this thread's pool (TMEM lane tid)
+  uint32_t parity = 0;
+
+  for (int rg0 = r_begin; rg0 < r_end; rg0 += IX_RG) {
+    const int nr = min(IX_RG, r_end - rg0);
+    const int nb = nr * IX_HEADS;  // N of this group
+    stage_kmajor_rows(sB, q + (size_t)rg0 * IX_HEADS * IDX_DIM, nb, nb, tid, 128);
+    for (int i = tid; i < nb; i += 128) {
+      const uint16_t wb = w[(size_t)rg0 * IX_HEADS + i];
+      w_sm[i] = FMT == tc::FMT_BF16 ? bf16_bits_to_f(wb) : __half2float(__ushort_as_half(wb));
+    }
+    if (tid < nr) pos_sm[tid] = q_pos[rg0 + tid];
+    __pipeline_commit();
+    __pipeline_wait_prior(0);
+    tc::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t idesc = tc::make_idesc(IX_TILE_P, nb, FMT, FMT, false, false);
+#pragma unroll
+      for (int kk = 0; kk < IDX_DIM / 16; kk++) {
+        const uint64_t ad = tc::make_sdesc(a_addr + kk * 2 * IX_LBO, IX_LBO, IX_SBO);
+        const uint64_t bd = tc::make_sdesc(b_addr + kk * 2 * IX_LBO, IX_LBO, IX_SBO);
+        tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
+      }
+      tc::mma_commit(&bar);
+    }
+    const bool ok = tc::mbar_wait(&bar, parity, &abort_flag, 1);
+    parity ^= 1;
+    tc::fence_after_sync();
+    if (ok) {
+      for (int rr = 0; rr < nr; rr++) {
+        uint32_t c[32];
+        tc::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + rr * IX_HEADS, c);
+        tc::tmem_ld_wait();
+        float tot = 0.f;
+#pragma unroll
+        for (int h = 0; h < IX_HEADS; h++) {
+          const float d = __uint_as_float(c[h]) * 0.08838834764f;
+          tot = fmaf(w_sm[rr * IX_HEADS + h], fmaxf(d, 0.f), tot);
+        }
+        if (p < npools) {
+          const bool vis = p * POOL + POOL - 1 <= pos_sm[rr];
+          scores[(size_t)(rg0 + rr) * score_stride + p] =
+              vis ? __float2half_rn(tot * 0.17677669530f) : __ushort_as_half((unsigned short)0xfc00);
+        }
+      }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+  }
+  if (warp == 0) tc::tmem_dealloc(tmem, 256);
+  if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
+}
+
+}  // namespace hk
+
+// device word that records a bounded wait giving up (read with hk_read_device_status)
+__device__ int hk_g_status = 0;
+
+HK_API int hk_read_device_status(int* host_out, int reset) {
+  if (!host_out) return HK_ERR_INVALID;
+  if (cudaMemcpyFromSymbol(host_out, hk_g_status, sizeof(int)) != cudaSuccess) return HK_ERR_CUDA;
+  if (reset) {
+    int z = 0;
+    if (cudaMemcpyToSymbol(hk_g_status, &z, sizeof(int)) != cudaSuccess) return HK_ERR_CUDA;
+  }
+  return HK_OK;
+}
+
+namespace hk {
+int* device_status_ptr() {
+  static int* ptr[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, hk_g_status) != cudaSuccess) return nullptr;
+    ptr[dev] = (int*)p;
+  }
+  return ptr[dev];
+}
+}  // namespace hk
+
+HK_API int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void* w,
+                            const int* q_pos, void* scores, int m, int npools, int score_stride,
+                            int n_heads, int dtype, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_idx && pool_k_nt && w && q_pos && scores);
+  HK_REQUIRE(m >= 0 && npools >= 0 && score_stride >= npools);
+  HK_REQUIRE(dtype == HK_F16 || dtype == HK_BF16);
+  HK_REQUIRE(aligned(q_idx, 16) && aligned(pool_k_nt, 16));
+  if (n_heads != IX_HEADS) return HK_ERR_UNSUPPORTED;
+  if (m == 0 || npools == 0) return HK_OK;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(indexer_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IX_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(indexer_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IX_SMEM) != cudaSuccess)
+      return HK_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  const int tiles = (npools + IX_TILE_P - 1) / IX_TILE_P;
+  // enough row groups per CTA to amortise the key tile, enough CTAs to cover the GPU twice
+  int row_groups = (m + IX_RG - 1) / IX_RG;
+  int want_y = (2 * sm_count() + tiles - 1) / tiles;
+  if (want_y < 1) want_y = 1;
+  if (want_y > row_groups) want_y = row_groups;
+  int groups_per_cta = (row_groups + want_y - 1) / want_y;
+  int rows_per_cta = groups_per_cta * IX_RG;
+  dim3 grid(tiles, (m + rows_per_cta - 1) / rows_per_cta);
+  cudaStream_t s = as_stream(stream);
+  int* st = device_status_ptr();
+  if (dtype == HK_F16)
+    indexer_tc_kernel<0><<<grid, 128, IX_SMEM, s>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, rows_per_cta, st);
+  else
+    indexer_tc_kernel<1><<<grid, 128, IX_SMEM, s>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, rows_per_cta, st);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

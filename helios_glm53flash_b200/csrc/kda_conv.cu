@@ -1,0 +1,209 @@
+// KDA short convolution: depthwise causal conv (window K) + SiLU over channel-major input, with a
+// rolling window state.  Interface and arithmetic of helios::aux::cuda_causal_conv1d_update
+// (reference: src/cuda/aux/gdn.cu:880-1023): fp32 fma chain k ascending, SiLU as a * 1/(1+exp(-a)),
+// bf16 round-to-nearest output, state = last K inputs.
+//
+// Two kernels:
+//   conv4_tile_kernel  prefill: K = 4, no history.  A CTA transposes a [64 channel][128 token] tile
+//                      through shared memory: 16-byte coalesced reads along tokens (the input is
+//                      channel-major), 128-byte coalesced writes along channels (the output is
+//                      token-major).  HBM-bound: 2 B read + 2 B written per channel-token.
+//   conv_generic_kernel decode and every other case (any K <= 16, history, ragged shapes): one
+//                      thread per channel; with seqlen = 1 its accesses are contiguous in channels.
+#include "hk_common.cuh"
+
+namespace hk {
+
+constexpr int CONV_MAX_K = 16;
+constexpr int CT_CH = 64;       // channels per tile
+constexpr int CT_TOK = 128;     // tokens per tile
+constexpr int CT_STRIDE = 138;  // bf16 elements per shared row: 8 halo slots + 128 tokens + 2 pad
+                                // (69 words, odd, so channel-strided reads spread over the banks)
+
+__device__ __forceinline__ float silu_fast(float a) { return a * (1.0f / (1.0f + __expf(-a))); }
+
+template <bool ACT, bool VEC>
+__global__ __launch_bounds__(256) void conv4_tile_kernel(
+    const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ state,
+    const int* __restrict__ slots, const __nv_bfloat16* __restrict__ weight,
+    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int dim, int seqlen,
+    int state_size) {
+  __shared__ __align__(16) __nv_bfloat16 xs[CT_CH * CT_STRIDE];
+  const int d0 = blockIdx.x * CT_CH;
+  const int s0 = blockIdx.y * CT_TOK;
+  const int b = blockIdx.z;
+  const int tid = threadIdx.x;
+  const __nv_bfloat16* xb = x + ((size_t)b * dim + d0) * seqlen;
+
+  // ---- stage the tile: rows = channels, 8 tokens per 16-byte load ----
+  if (VEC) {
+    for (int idx = tid; idx < CT_CH * (CT_TOK / 8); idx += 256) {
+      int r = idx >> 4, c = idx & 15;
+      int s = s0 + c * 8;
+      if (s < seqlen) {
+        uint4 v = ld_stream16(xb + (size_t)r * seqlen + s);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(xs + r * CT_STRIDE + 8 + c * 8);
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+      }
+    }
+  } else {
+    for (int idx = tid; idx < CT_CH * CT_TOK; idx += 256) {
+      int r = idx >> 7, c = idx & 127;
+      int s = s0 + c;
+      if (s < seqlen) xs[r * CT_STRIDE + 8 + c] = xb[(size_t)r * seqlen + s];
+    }
+  }
+  // ---- halo (3 tokens before the tile) and, in the first tile, the state update ----
+  if (tid < CT_CH) {
+    const int r = tid;
+    __nv_bfloat16* hrow = xs + r * CT_STRIDE + 5;
+    if (s0 == 0) {
+      const int slot = slots ? slots[b] : b;
+      __nv_bfloat16* st = state + ((size_t)slot * dim + d0 + r) * state_size;
+      __nv_bfloat16 old[4] = {st[0], st[1], st[2], st[3]};
+      hrow[0] = old[1]; hrow[1] = old[2]; hrow[2] = old[3];
+      // new window = last 4 entries of [old(4) | x(seqlen)]
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        int src_t = seqlen + k;
+        st[k] = (src_t < 4) ? old[src_t] : xb[(size_t)r * seqlen + (src_t - 4)];
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 3; h++) hrow[h] = xb[(size_t)r * seqlen + (s0 - 3 + h)];
+    }
+  }
+  __syncthreads();
+
+  // ---- compute: lane owns 2 adjacent channels, warp owns 16 consecutive tokens ----
+  const int lane = tid & 31, wid = tid >> 5;
+  const int c0 = lane * 2;
+  const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)(d0 + c0) * 4);
+  const float w00 = bf16lo(wv.x), w01 = bf16hi(wv.x), w02 = bf16lo(wv.y), w03 = bf16hi(wv.y);
+  const float w10 = bf16lo(wv.z), w11 = bf16hi(wv.z), w12 = bf16lo(wv.w), w13 = bf16hi(wv.w);
+  float b0 = 0.f, b1 = 0.f;
+  if (bias) {
+    b0 = __bfloat162float(bias[d0 + c0]);
+    b1 = __bfloat162float(bias[d0 + c0 + 1]);
+  }
+  const __nv_bfloat16* r0 = xs + c0 * CT_STRIDE + 8;
+  const __nv_bfloat16* r1 = r0 + CT_STRIDE;
+  const int t0 = wid * 16;
+  float a0 = __bfloat162float(r0[t0 - 3]), a1 = __bfloat162float(r0[t0 - 2]), a2 = __bfloat162float(r0[t0 - 1]);
+  float e0 = __bfloat162float(r1[t0 - 3]), e1 = __bfloat162float(r1[t0 - 2]), e2 = __bfloat162float(r1[t0 - 1]);
+  __nv_bfloat16* ob = out + ((size_t)b * seqlen) * dim + d0 + c0;
+#pragma unroll 4
+  for (int t = t0; t < t0 + 16; t++) {
+    if (s0 + t >= seqlen) break;
+    float a3 = __bfloat162float(r0[t]), e3 = __bfloat162float(r1[t]);
+    float y0 = fmaf(w03, a3, fmaf(w02, a2, fmaf(w01, a1, fmaf(w00, a0, b0))));
+    float y1 = fmaf(w13, e3, fmaf(w12, e2, fmaf(w11, e1, fmaf(w10, e0, b1))));
+    if (ACT) {
+      y0 = silu_fast(y0);
+      y1 = silu_fast(y1);
+    }
+    __nv_bfloat162 pk;
+    pk.x = __float2bfloat16_rn(y0);
+    pk.y = __float2bfloat16_rn(y1);
+    *reinterpret_cast<__nv_bfloat162*>(ob + (size_t)(s0 + t) * dim) = pk;
+    a0 = a1; a1 = a2; a2 = a3;
+    e0 = e1; e1 = e2; e2 = e3;
+  }
+}
+
+template <bool ACT, bool HISTORY>
+__global__ __launch_bounds__(256) void conv_generic_kernel(
+    const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ state,
+    const int* __restrict__ slots, const __nv_bfloat16* __restrict__ weight,
+    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int dim, int seqlen,
+    int state_size, int K) {
+  const int d = blockIdx.x * 256 + threadIdx.x;
+  if (d >= dim) return;
+  const int b = blockIdx.y;
+  const int slot = slots ? slots[b] : b;
+  const __nv_bfloat16* x_d = x + ((size_t)b * dim + d) * seqlen;
+  __nv_bfloat16* st = state + ((size_t)slot * dim + d) * state_size;
+  float w[CONV_MAX_K], old[CONV_MAX_K], win[CONV_MAX_K];
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_K; k++)
+    if (k < K) {
+      w[k] = __bfloat162float(weight[(size_t)d * K + k]);
+      old[k] = __bfloat162float(st[k]);
+    }
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_K - 1; k++)
+    if (k < K - 1) win[k] = old[k + 1];
+  const float bias_d = bias ? __bfloat162float(bias[d]) : 0.0f;
+  for (int s = 0; s < seqlen; s++) {
+    float cur = __bfloat162float(x_d[s]);
+    float acc = bias_d;
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_K; k++)
+      if (k < K) acc = fmaf(w[k], (k == K - 1) ? cur : win[k], acc);
+    if (ACT) acc = silu_fast(acc);
+    out[((size_t)b * seqlen + s) * dim + d] = __float2bfloat16_rn(acc);
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_K - 1; k++)
+      if (k < K - 1) win[k] = (k == K - 2) ? cur : win[k + 1];
+  }
+  if (!HISTORY) {
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_K; k++)
+      if (k < K) {
+        int src_t = seqlen + k;
+        float v = (src_t < K) ? old[src_t] : __bfloat162float(x_d[src_t - K]);
+        st[k] = __float2bfloat16_rn(v);
+      }
+  } else {
+    int total = K + seqlen;
+    int write_size = state_size < total ? state_size : total;
+    int dst_start = state_size - write_size, src_start = total - write_size;
+    for (int j = 0; j < write_size; j++) {
+      int src_t = src_start + j;
+      float v = (src_t < K) ? old[src_t] : __bfloat162float(x_d[src_t - K]);
+      st[dst_start + j] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+}  // namespace hk
+
+HK_API int hk_conv1d_update(const void* x, void* conv_state, const int* slots, const void* weight,
+                            const void* bias, void* out, int bsz, int dim, int seqlen,
+                            int state_size, int K, int activation, int history, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(x && conv_state && weight && out);
+  HK_REQUIRE(bsz > 0 && dim > 0 && seqlen > 0);
+  HK_REQUIRE(K >= 1 && K <= CONV_MAX_K && state_size >= K);
+  auto xs = (const __nv_bfloat16*)x;
+  auto st = (__nv_bfloat16*)conv_state;
+  auto w = (const __nv_bfloat16*)weight;
+  auto bs = (const __nv_bfloat16*)bias;
+  auto o = (__nv_bfloat16*)out;
+  cudaStream_t s = as_stream(stream);
+
+  const bool tile_ok = (K == 4) && !history && (dim % CT_CH == 0) && seqlen >= 16 &&
+                       aligned(weight, 16) && aligned(out, 4);
+  if (tile_ok) {
+    dim3 grid(dim / CT_CH, (seqlen + CT_TOK - 1) / CT_TOK, bsz);
+    const bool vec = (seqlen % 8 == 0) && aligned(x, 16);
+    if (activation) {
+      if (vec) conv4_tile_kernel<true, true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+      else     conv4_tile_kernel<true, false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+    } else {
+      if (vec) conv4_tile_kernel<false, true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+      else     conv4_tile_kernel<false, false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+    }
+  } else {
+    dim3 grid((dim + 255) / 256, bsz);
+    if (activation) {
+      if (history) conv_generic_kernel<true, true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size, K);
+      else         conv_generic_kernel<true, false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size, K);
+    } else {
+      if (history) conv_generic_kernel<false, true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size, K);
+      else         conv_generic_kernel<false, false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size, K);
+    }
+  }
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

@@ -1,0 +1,188 @@
+// KDA / gated-delta-rule recurrence, one token at a time: the decode step, short sequences and the
+// history (rewindable) mode.  Interface and arithmetic of
+// helios::aux::cuda_recurrent_gated_delta_rule (reference: src/cuda/aux/gdn.cu:555-866).
+//
+// Layout of the work: one CTA per (batch item, head, slice of NV value-columns).  The CTA's
+// [D x NV] slice of the fp32 state lives in REGISTERS for the whole call (the reference re-reads and
+// re-writes it from global memory on every token), so a decode step moves each state byte exactly
+// once in and once out - the HBM floor of 2*H*D*D*4 bytes per layer-step - and a multi-token call
+// costs state traffic only once.  Thread (kg, j) owns column j and the D/KG consecutive k-rows of
+// group kg; the k-reduction is the sum of the KG group sums taken in ascending order, which for
+// D = 128, NV = 32 is exactly the reference's 4 x 32 order (gdn.cu:683-705).
+#include "hk_common.cuh"
+
+namespace hk {
+
+template <int D, int NV, bool CW, bool HIST>
+__global__ __launch_bounds__(128) void kda_recurrent_kernel(
+    const __nv_bfloat16* __restrict__ mixed_qkv, const float* __restrict__ g,
+    const __nv_bfloat16* __restrict__ beta, float* __restrict__ state,
+    __nv_bfloat16* __restrict__ out, float* __restrict__ out_f32, int seqlen, int Hk, int Hv,
+    float scale, const int* __restrict__ slots, int history_stride) {
+  constexpr int KG = 128 / NV;   // k-groups per CTA
+  constexpr int RPT = D / KG;    // state rows per thread
+  constexpr int NW = D / 32;     // warps that carry q/k channels
+  const int b = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * NV;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j = tid % NV, kg = tid / NV;
+  const int group = Hv / Hk, k_head = head / group;
+  const size_t row = (size_t)2 * Hk * D + (size_t)Hv * D;
+  const size_t head_state = (size_t)D * D;
+  const size_t state_size = (size_t)Hv * head_state;
+  const int slot = slots ? slots[b] : b;
+  float* slot_state = state + (size_t)slot * history_stride * state_size;
+  float* my_state = slot_state + head * head_state + (size_t)(kg * RPT) * D + v0 + j;
+
+  const __nv_bfloat16* tok = mixed_qkv + (size_t)b * seqlen * row;
+  const float* gp = g + (size_t)b * seqlen * Hv * (CW ? D : 1) + (size_t)head * (CW ? D : 1);
+  const __nv_bfloat16* bp = beta + (size_t)b * seqlen * Hv + head;
+  const size_t out_base = ((size_t)b * seqlen * Hv + head) * D + v0 + j;
+
+  __shared__ float sh_q[D], sh_k[D], sh_d[D];
+  __shared__ float sh_red[2][4];
+  __shared__ float sh_part[2][KG][NV];
+
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; i++) S[i] = my_state[(size_t)i * D];
+
+  // software prefetch of the next token's operands
+  float nq = 0.f, nk = 0.f, ng = 0.f, nv, nb;
+  if (tid < D) {
+    nq = __bfloat162float(tok[(size_t)k_head * D + tid]);
+    nk = __bfloat162float(tok[(size_t)(Hk + k_head) * D + tid]);
+    if (CW) ng = gp[tid];
+  }
+  if (!CW) ng = gp[0];
+  nv = __bfloat162float(tok[(size_t)2 * Hk * D + (size_t)head * D + v0 + j]);
+  nb = __bfloat162float(bp[0]);
+
+  for (int s = 0; s < seqlen; s++) {
+    float q = nq, k = nk, gv = ng, v = nv, beta_h = nb;
+    if (s + 1 < seqlen) {
+      const __nv_bfloat16* nt = tok + (size_t)(s + 1) * row;
+      if (tid < D) {
+        nq = __bfloat162float(nt[(size_t)k_head * D + tid]);
+        nk = __bfloat162float(nt[(size_t)(Hk + k_head) * D + tid]);
+        if (CW) ng = gp[(size_t)(s + 1) * Hv * D + tid];
+      }
+      if (!CW) ng = gp[(size_t)(s + 1) * Hv];
+      nv = __bfloat162float(nt[(size_t)2 * Hk * D + (size_t)head * D + v0 + j]);
+      nb = __bfloat162float(bp[(size_t)(s + 1) * Hv]);
+    }
+    // ---- L2 normalisation of q and k over the D channels ----
+    float sq = warp_sum(q * q), sk = warp_sum(k * k);
+    if (lane == 0 && warp < NW) {
+      sh_red[0][warp] = sq;
+      sh_red[1][warp] = sk;
+    }
+    __syncthreads();
+    if (tid < D) {
+      float tq = 0.f, tk = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; w++) {
+        tq += sh_red[0][w];
+        tk += sh_red[1][w];
+      }
+      sh_q[tid] = q * rsqrtf(tq + 1e-6f);
+      sh_k[tid] = k * rsqrtf(tk + 1e-6f);
+      if (CW) sh_d[tid] = __expf(gv);
+    }
+    __syncthreads();
+    // ---- kv_j = sum_c k_c d_c S[c][j] (the state is read decayed when channelwise) ----
+    const float g_h = CW ? 1.0f : __expf(gv);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+      const int c = kg * RPT + i;
+      if (CW) sum = sum + sh_k[c] * sh_d[c] * S[i];
+      else    sum = sum + sh_k[c] * S[i];
+    }
+    sh_part[0][kg][j] = sum;
+    __syncthreads();
+    float kv = 0.f;
+#pragma unroll
+    for (int p = 0; p < KG; p++) kv = __fadd_rn(kv, sh_part[0][p][j]);
+    const float vp = v - kv * g_h;
+    // ---- S <- S*decay + k v' beta ;  o_j = sum_c q_c S[c][j] ----
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+      const int c = kg * RPT + i;
+      float st = S[i] * (CW ? sh_d[c] : g_h) + sh_k[c] * vp * beta_h;
+      S[i] = st;
+      o = o + sh_q[c] * st;
+    }
+    sh_part[1][kg][j] = o;
+    if (HIST) {
+      // step s writes history slot s+1; the last step writes the final slot 0
+      float* dst = (s == seqlen - 1) ? my_state : my_state + (size_t)(s + 1) * state_size;
+#pragma unroll
+      for (int i = 0; i < RPT; i++) dst[(size_t)i * D] = S[i];
+    }
+    __syncthreads();
+    if (kg == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int p = 0; p < KG; p++) tot = __fadd_rn(tot, sh_part[1][p][j]);
+      tot *= scale;
+      const size_t oi = out_base + (size_t)s * Hv * D;
+      out[oi] = __float2bfloat16_rz(tot);
+      if (out_f32) out_f32[oi] = tot;
+    }
+  }
+  if (!HIST) {
+#pragma unroll
+    for (int i = 0; i < RPT; i++) my_state[(size_t)i * D] = S[i];
+  }
+}
+
+template <int D, int NV>
+static int launch_recurrent(const __nv_bfloat16* qkv, const float* g, const __nv_bfloat16* beta,
+                            float* state, __nv_bfloat16* out, float* out_f32, int bsz, int seqlen,
+                            int Hk, int Hv, int history_stride, const int* slots, bool cw,
+                            bool hist, cudaStream_t s) {
+  dim3 grid(bsz, Hv, D / NV);
+  const float scale = 1.0f / sqrtf((float)D);
+#define HK_RL(CWV, HV)                                                                             \
+  kda_recurrent_kernel<D, NV, CWV, HV><<<grid, 128, 0, s>>>(qkv, g, beta, state, out, out_f32,    \
+                                                            seqlen, Hk, Hv, scale, slots,          \
+                                                            history_stride)
+  if (cw) { if (hist) HK_RL(true, true); else HK_RL(true, false); }
+  else    { if (hist) HK_RL(false, true); else HK_RL(false, false); }
+#undef HK_RL
+  return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+}
+
+}  // namespace hk
+
+HK_API int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* beta, float* state,
+                            void* out, float* out_f32, int bsz, int seqlen, int num_k_heads,
+                            int num_v_heads, int k_head_dim, int v_head_dim, int history_stride,
+                            const int* slots, int channelwise, int history, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(mixed_qkv && g && beta && state && out);
+  HK_REQUIRE(bsz > 0 && seqlen > 0 && num_k_heads > 0 && num_v_heads > 0 && history_stride >= 1);
+  HK_REQUIRE(num_v_heads % num_k_heads == 0);
+  if (history) HK_REQUIRE(history_stride >= seqlen);  // slots 1..seqlen-1 are written
+  if (k_head_dim != v_head_dim) return HK_ERR_UNSUPPORTED;
+  if (channelwise && k_head_dim != 128) return HK_ERR_INVALID;  // as the reference launcher
+  auto q = (const __nv_bfloat16*)mixed_qkv;
+  auto bt = (const __nv_bfloat16*)beta;
+  auto o = (__nv_bfloat16*)out;
+  cudaStream_t s = as_stream(stream);
+  // narrower column slices when the (batch x head) count alone cannot cover the SMs
+  const bool narrow = (long)bsz * num_v_heads * 4 < sm_count();
+  if (k_head_dim == 128) {
+    return narrow ? launch_recurrent<128, 16>(q, g, bt, state, o, out_f32, bsz, seqlen, num_k_heads,
+                                              num_v_heads, history_stride, slots, channelwise,
+                                              history, s)
+                  : launch_recurrent<128, 32>(q, g, bt, state, o, out_f32, bsz, seqlen, num_k_heads,
+                                              num_v_heads, history_stride, slots, channelwise,
+                                              history, s);
+  }
+  if (k_head_dim == 64)
+    return launch_recurrent<64, 32>(q, g, bt, state, o, out_f32, bsz, seqlen, num_k_heads,
+                                    num_v_heads, history_stride, slots, channelwise, history, s);
+  return HK_ERR_UNSUPPORTED;
+}

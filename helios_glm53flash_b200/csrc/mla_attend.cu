@@ -1,0 +1,187 @@
+// Host entry points of absorbed MLA over the latent cache (dense / sparse, final / partial) and of
+// the split-KV log-sum-exp combine.  Replaces helios::attn::mla_sparse_decode and
+// helios::attn::mla_dense_prefill (reference: src/cuda/attn/attn.cu:394-699) and restates the
+// reference's in-kernel merge (:462-481) as a standalone combine.
+//
+// Dispatch: 64-head launches go to the tcgen05 flash kernel (mla_flash_tc.cu); every other head
+// count (multiple of 4) and the HK_MLA_FORCE_SIMT debug switch go to the CUDA-core kernel.
+#include <cstdlib>
+
+#include "mla_simt.cuh"
+
+namespace hk {
+
+// implemented in mla_flash_tc.cu; returns HK_ERR_UNSUPPORTED when the shape is not covered
+int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s);
+int mla_flash_tc_auto_splits(int m, int n_keys);
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct PartialLayout {
+  size_t off_l, off_acc, total;
+};
+static PartialLayout partial_layout(int n_split, int64_t rows) {
+  PartialLayout p;
+  size_t ml = align_up((size_t)n_split * rows * sizeof(float), 256);
+  p.off_l = ml;
+  p.off_acc = 2 * ml;
+  p.total = p.off_acc + (size_t)n_split * rows * LATENT * sizeof(float);
+  return p;
+}
+
+static bool force_simt() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = std::getenv("HK_MLA_FORCE_SIMT");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+static int simt_auto_splits(int m, int n_heads, int n_keys) {
+  long ctas = (long)m * (n_heads / SIMT_HG);
+  int want = (int)((2L * sm_count() + ctas - 1) / ctas);
+  int cap = (n_keys + 63) / 64;
+  int s = want < 1 ? 1 : want;
+  if (s > cap) s = cap < 1 ? 1 : cap;
+  if (s > 64) s = 64;
+  return s;
+}
+
+static int launch_simt(const MlaArgs& a, cudaStream_t s) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(mla_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)MLA_SIMT_SMEM) != cudaSuccess)
+      return HK_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  dim3 grid(a.n_heads / SIMT_HG, a.n_split, a.m);
+  mla_simt_kernel<<<grid, 256, MLA_SIMT_SMEM, s>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+}
+
+static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
+                   __half* out, cudaStream_t s) {
+  lse_combine_kernel<false><<<(unsigned)rows, 128, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
+                                                            n_split, rows, out);
+  return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+}
+
+// common driver: final output, optionally through split partials in the workspace
+static int attend(MlaArgs a, int n_keys_hint, int n_split, void* workspace, size_t workspace_bytes,
+                  cudaStream_t s) {
+  const bool tc = (a.n_heads == 64) && !force_simt();
+  if (n_split <= 0)
+    n_split = tc ? mla_flash_tc_auto_splits(a.m, n_keys_hint)
+                 : simt_auto_splits(a.m, a.n_heads, n_keys_hint);
+  const int64_t rows = (int64_t)a.m * a.n_heads;
+  __half* final_out = a.out;
+  a.n_split = n_split;
+  if (n_split > 1) {
+    PartialLayout pl = partial_layout(n_split, rows);
+    if (!workspace || workspace_bytes < pl.total) return HK_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return HK_ERR_INVALID;
+    char* ws = (char*)workspace;
+    a.part_m = (float*)ws;
+    a.part_l = (float*)(ws + pl.off_l);
+    a.part_acc = (float*)(ws + pl.off_acc);
+    a.out = nullptr;
+  }
+  int st = HK_ERR_UNSUPPORTED;
+  if (tc) st = mla_flash_tc_launch(a, s);
+  if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
+  if (st != HK_OK) return st;
+  if (n_split > 1) return combine(a.part_m, a.part_l, a.part_acc, n_split, rows, final_out, s);
+  return HK_OK;
+}
+
+}  // namespace hk
+
+HK_API size_t hk_mla_partial_bytes(int n_split, int64_t rows) {
+  if (n_split <= 0 || rows <= 0) return 0;
+  return hk::partial_layout(n_split, rows).total;
+}
+
+HK_API int hk_mla_auto_splits(int m, int n_keys) {
+  if (m <= 0 || n_keys <= 0) return 1;
+  return hk::force_simt() ? hk::simt_auto_splits(m, 64, n_keys) : hk::mla_flash_tc_auto_splits(m, n_keys);
+}
+
+HK_API int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx, int kidx,
+                         void* lat_out, int m, int n_heads, float scale, int n_split,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv && raw_idx && lat_out);
+  HK_REQUIRE(m >= 0 && kidx >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(lat_out, 16));
+  if (m == 0) return HK_OK;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.raw_idx = raw_idx; a.kidx = kidx;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  a.out = (__half*)lat_out;
+  return attend(a, kidx, n_split, workspace, workspace_bytes, as_stream(stream));
+}
+
+HK_API int hk_mla_dense(const void* q_lat, const void* ckv, const int64_t* kv_base,
+                        const int* kv_len, int pos_start, void* lat_out, int m, int n_heads,
+                        float scale, int n_split, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv && lat_out);
+  HK_REQUIRE(m >= 0 && pos_start >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(lat_out, 16));
+  if (m == 0) return HK_OK;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = pos_start;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  a.out = (__half*)lat_out;
+  // without host-visible lengths the split heuristic uses the longest causal row
+  const int hint = kv_len ? (pos_start > 0 ? pos_start : 4096) : pos_start + m;
+  return attend(a, hint, n_split, workspace, workspace_bytes, as_stream(stream));
+}
+
+HK_API int hk_mla_dense_partial(const void* q_lat, const void* ckv, const int64_t* kv_base,
+                                const int* kv_len, int pos_start, float* part_m, float* part_l,
+                                float* part_acc, int m, int n_heads, float scale, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv && part_m && part_l && part_acc);
+  HK_REQUIRE(m >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(part_acc, 16));
+  if (m == 0) return HK_OK;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = pos_start;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  a.n_split = 1;
+  a.part_m = part_m; a.part_l = part_l; a.part_acc = part_acc;
+  int st = HK_ERR_UNSUPPORTED;
+  if (n_heads == 64 && !force_simt()) st = mla_flash_tc_launch(a, as_stream(stream));
+  if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, as_stream(stream));
+  return st;
+}
+
+HK_API int hk_lse_combine(const float* part_m, const float* part_l, const float* part_acc,
+                          int n_split, int64_t rows, void* out_f16, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(part_m && part_l && part_acc && out_f16 && n_split >= 1 && rows >= 0);
+  HK_REQUIRE(aligned(part_acc, 16) && aligned(out_f16, 8));
+  if (rows == 0) return HK_OK;
+  return combine(part_m, part_l, part_acc, n_split, rows, (__half*)out_f16, as_stream(stream));
+}
+
+HK_API int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
+                               const float* const* ptrs_acc, int n_split, int64_t rows,
+                               void* out_f16, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && n_split >= 1 && rows >= 0);
+  if (rows == 0) return HK_OK;
+  lse_combine_kernel<true><<<(unsigned)rows, 128, 0, as_stream(stream)>>>(
+      nullptr, nullptr, nullptr, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

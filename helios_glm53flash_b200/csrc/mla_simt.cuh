@@ -1,0 +1,170 @@
+// CUDA-core flash attention over the latent cache: the cross-check / odd-shape path of the MLA
+// entry points (any head count divisible by 4, any key count), and the split-KV combine kernels.
+// fp32 products and accumulation throughout (the reference's scalar kernels use fp16 products,
+// src/cuda/attn/attn.cu:517-533).
+#pragma once
+#include "hk_common.cuh"
+#include "mla_args.cuh"
+
+namespace hk {
+
+constexpr int SIMT_HG = 4;  // heads per CTA
+
+
+
+// grid (n_heads/4, n_split, m), 256 threads.  Warp w walks keys k0+w, k0+w+8, ...; lane owns 16
+// channels; the 8 warps are merged through shared memory at the end.
+__global__ __launch_bounds__(256) void mla_simt_kernel(MlaArgs a) {
+  extern __shared__ float smem[];
+  float* w_acc = smem;                           // [8][4][512]
+  float* w_m = smem + 8 * SIMT_HG * LATENT;      // [8][4]
+  float* w_l = w_m + 8 * SIMT_HG;                // [8][4]
+  const int hg = blockIdx.x, sp = blockIdx.y, r = blockIdx.z;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int h0 = hg * SIMT_HG;
+  const bool sparse = a.raw_idx != nullptr;
+  int n;
+  int64_t base = 0;
+  if (sparse) n = a.kidx;
+  else {
+    n = a.kv_len ? a.kv_len[r] : a.pos_start + r + 1;
+    base = a.kv_base ? a.kv_base[r] : 0;
+  }
+  const int per = (n + a.n_split - 1) / a.n_split;
+  const int k0 = sp * per, k1 = min(n, k0 + per);
+
+  float qf[SIMT_HG][16];
+#pragma unroll
+  for (int h = 0; h < SIMT_HG; h++) {
+    const __half* q = a.q_lat + ((size_t)r * a.n_heads + h0 + h) * LATENT + lane * 16;
+    uint4 u0 = *reinterpret_cast<const uint4*>(q), u1 = *reinterpret_cast<const uint4*>(q + 8);
+    const __half2* p0 = reinterpret_cast<const __half2*>(&u0);
+    const __half2* p1 = reinterpret_cast<const __half2*>(&u1);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float2 f0 = __half22float2(p0[u]), f1 = __half22float2(p1[u]);
+      qf[h][2 * u] = f0.x * a.scale; qf[h][2 * u + 1] = f0.y * a.scale;
+      qf[h][8 + 2 * u] = f1.x * a.scale; qf[h][8 + 2 * u + 1] = f1.y * a.scale;
+    }
+  }
+  float m_i[SIMT_HG], l_i[SIMT_HG], acc[SIMT_HG][16];
+#pragma unroll
+  for (int h = 0; h < SIMT_HG; h++) {
+    m_i[h] = -INFINITY;
+    l_i[h] = 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; u++) acc[h][u] = 0.f;
+  }
+  for (int i = k0 + wid; i < k1; i += 8) {
+    int64_t tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + i] : base + i;
+    if (tok < 0) continue;  // warp-uniform
+    const __half* crow = a.ckv + (size_t)tok * LATENT + lane * 16;
+    uint4 u0 = *reinterpret_cast<const uint4*>(crow), u1 = *reinterpret_cast<const uint4*>(crow + 8);
+    const __half2* p0 = reinterpret_cast<const __half2*>(&u0);
+    const __half2* p1 = reinterpret_cast<const __half2*>(&u1);
+    float kf[16];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float2 f0 = __half22float2(p0[u]), f1 = __half22float2(p1[u]);
+      kf[2 * u] = f0.x; kf[2 * u + 1] = f0.y; kf[8 + 2 * u] = f1.x; kf[8 + 2 * u + 1] = f1.y;
+    }
+#pragma unroll
+    for (int h = 0; h < SIMT_HG; h++) {
+      float d = 0.f;
+#pragma unroll
+      for (int u = 0; u < 16; u++) d = fmaf(qf[h][u], kf[u], d);
+      d = warp_sum(d);
+      if (d > m_i[h]) {
+        const float sc = __expf(m_i[h] - d);
+#pragma unroll
+        for (int u = 0; u < 16; u++) acc[h][u] *= sc;
+        l_i[h] *= sc;
+        m_i[h] = d;
+      }
+      const float p = __expf(d - m_i[h]);
+      l_i[h] += p;
+#pragma unroll
+      for (int u = 0; u < 16; u++) acc[h][u] = fmaf(p, kf[u], acc[h][u]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < SIMT_HG; h++) {
+    if (lane == 0) {
+      w_m[wid * SIMT_HG + h] = m_i[h];
+      w_l[wid * SIMT_HG + h] = l_i[h];
+    }
+#pragma unroll
+    for (int u = 0; u < 16; u++) w_acc[(wid * SIMT_HG + h) * LATENT + lane * 16 + u] = acc[h][u];
+  }
+  __syncthreads();
+  const size_t rows = (size_t)a.m * a.n_heads;
+  for (int idx = threadIdx.x; idx < SIMT_HG * LATENT; idx += 256) {
+    const int h = idx / LATENT, ch = idx % LATENT;
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; w++) gm = fmaxf(gm, w_m[w * SIMT_HG + h]);
+    float gl = 0.f, o = 0.f;
+    if (gm != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 8; w++) {
+        const float mw = w_m[w * SIMT_HG + h];
+        const float sc = mw == -INFINITY ? 0.f : __expf(mw - gm);
+        gl += sc * w_l[w * SIMT_HG + h];
+        o += sc * w_acc[(w * SIMT_HG + h) * LATENT + ch];
+      }
+    }
+    const size_t rh = (size_t)r * a.n_heads + h0 + h;
+    if (a.out) {
+      a.out[rh * LATENT + ch] = __float2half_rn(gl > 0.f ? o / gl : 0.f);
+    } else {
+      a.part_acc[((size_t)sp * rows + rh) * LATENT + ch] = o;
+      if (ch == 0) {
+        a.part_m[(size_t)sp * rows + rh] = gm;
+        a.part_l[(size_t)sp * rows + rh] = gl;
+      }
+    }
+  }
+}
+
+constexpr size_t MLA_SIMT_SMEM = (size_t)(8 * SIMT_HG * LATENT + 2 * 8 * SIMT_HG) * sizeof(float);
+
+// ---- split-KV log-sum-exp combine: one CTA (128 threads x 4 channels) per (row, head) ----
+// gm = max m_s; gl = sum e^{m_s-gm} l_s; o = sum e^{m_s-gm} acc_s / gl; m_s = -inf weighs 0; all
+// -inf (or gl = 0) gives zeros (reference in-kernel merge: src/cuda/attn/attn.cu:462-481).
+template <bool PTRS>
+__global__ __launch_bounds__(128) void lse_combine_kernel(
+    const float* __restrict__ part_m, const float* __restrict__ part_l,
+    const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
+    const float* const* __restrict__ ptrs_l, const float* const* __restrict__ ptrs_acc,
+    int n_split, int64_t rows, __half* __restrict__ out) {
+  const int64_t r = blockIdx.x;
+  const int t = threadIdx.x;
+  float gm = -INFINITY;
+  for (int s = 0; s < n_split; s++) {
+    const float* pm = PTRS ? ptrs_m[s] : part_m + (size_t)s * rows;
+    gm = fmaxf(gm, pm[r]);
+  }
+  float gl = 0.f;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (gm != -INFINITY) {
+    for (int s = 0; s < n_split; s++) {
+      const float* pm = PTRS ? ptrs_m[s] : part_m + (size_t)s * rows;
+      const float* pl = PTRS ? ptrs_l[s] : part_l + (size_t)s * rows;
+      const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
+      const float ms = pm[r];
+      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
+      gl += sc * pl[r];
+      const float4 a = *reinterpret_cast<const float4*>(pa + (size_t)r * LATENT + t * 4);
+      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
+    }
+  }
+  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
+  __half2 h1 = __floats2half2_rn(o.z * inv, o.w * inv);
+  uint2 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+  *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + t * 4) = pk;
+}
+
+}  // namespace hk

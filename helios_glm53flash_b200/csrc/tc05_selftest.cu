@@ -1,0 +1,112 @@
+// Self test of the tcgen05 / TMEM helper layer (tc05.cuh): one CTA computes D = A * B with fp16
+// operands staged in the no-swizzle canonical layouts and dumps the raw TMEM accumulator
+// (all 128 lanes x N columns), so the host can check both the arithmetic and the row <-> lane
+// mapping of each instruction shape.
+#include "hk_common.cuh"
+#include "tc05.cuh"
+
+namespace hk {
+
+__global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __restrict__ A,
+                                                            const __half* __restrict__ B,
+                                                            float* __restrict__ D, int M, int N,
+                                                            int K, int flags, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const bool b_mn = flags & 1, swap_a = flags & 0x100, swap_b = flags & 0x200;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + 128 * 128 * 2;
+  const uint32_t kchunks = K / 8;
+  // K direction contiguous core matrices (LBO = 128 B), M/N groups of 8 rows kchunks*128 B apart
+  const uint32_t lbo_a = 128, sbo_a = kchunks * 128;
+  const uint32_t lbo_b = 128, sbo_b = kchunks * 128;
+
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
+  // zero both operand regions so rows beyond M read as zero
+  for (int i = tid; i < (128 * 128 * 2 + 256 * 128 * 2) / 16; i += 128)
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  for (int i = tid; i < M * (int)kchunks; i += 128) {
+    int r = i / kchunks, kc = i % kchunks;
+    uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)r * K + kc * 8);
+    *reinterpret_cast<uint4*>(sA + tc::kmajor_off(r, kc, lbo_a, sbo_a)) = v;
+  }
+  if (!b_mn) {
+    for (int i = tid; i < N * (int)kchunks; i += 128) {
+      int r = i / kchunks, kc = i % kchunks;
+      uint4 v = *reinterpret_cast<const uint4*>(B + (size_t)r * K + kc * 8);
+      *reinterpret_cast<uint4*>(sB + tc::kmajor_off(r, kc, lbo_b, sbo_b)) = v;
+    }
+  } else {
+    const int nchunks = N / 8;
+    for (int i = tid; i < K * nchunks; i += 128) {
+      int k = i / nchunks, nc = i % nchunks;
+      uint4 v = *reinterpret_cast<const uint4*>(B + (size_t)k * N + nc * 8);
+      *reinterpret_cast<uint4*>(sB + tc::mnmajor_off(k, nc, lbo_b, sbo_b)) = v;
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (tid == 0) {
+    const uint32_t idesc = tc::make_idesc(M, N, tc::FMT_F16, tc::FMT_F16, false, b_mn);
+    for (int kk = 0; kk < K / 16; kk++) {
+      uint64_t ad = swap_a ? tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, sbo_a, lbo_a)
+                           : tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, lbo_a, sbo_a);
+      uint64_t bd = swap_b ? tc::make_sdesc(tc::smem_u32(sB) + kk * 2 * lbo_b, sbo_b, lbo_b)
+                           : tc::make_sdesc(tc::smem_u32(sB) + kk * 2 * lbo_b, lbo_b, sbo_b);
+      tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
+    }
+    tc::mma_commit(&bar);
+  }
+  const bool ok = tc::mbar_wait(&bar, 0, &abort_flag, 1);
+  tc::fence_after_sync();
+  if (ok) {
+    for (int c0 = 0; c0 < N; c0 += 16) {
+      uint32_t r[16];
+      tc::tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; j++) D[(size_t)tid * N + c0 + j] = __uint_as_float(r[j]);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 256);
+  if (tid == 0) status[0] = abort_flag;
+}
+
+}  // namespace hk
+
+HK_API int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,
+                            int b_layout, int* status, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(a_f16 && b_f16 && d && status);
+  HK_REQUIRE((M == 64 || M == 128) && N >= 16 && N <= 256 && N % 16 == 0 && K >= 16 && K <= 128 &&
+             K % 16 == 0);
+  const size_t smem = 128 * 128 * 2 + 256 * 128 * 2;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(tc05_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return HK_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  tc05_selftest_kernel<<<1, 128, smem, as_stream(stream)>>>((const __half*)a_f16,
+                                                            (const __half*)b_f16, d, M, N, K,
+                                                            b_layout, status);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

@@ -1,0 +1,200 @@
+/* helios_b200.h — C ABI of libhelios_b200.so
+ *
+ * sm_100a (B200) implementation of the GLM-5.3-Flash trunk-attention hot path of the Helios engine:
+ * KDA (short conv, recurrent decode, chunked prefill), absorbed MLA over the 512-wide fp16 latent
+ * cache (dense and sparse, decode and chunked prefill), the DSA indexer (pooled keys, scores,
+ * top-k, expansion) and the split-KV log-sum-exp combine.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise;
+ *   - bf16 / fp16 tensors are passed as void* (bit patterns of __nv_bfloat16 / __half);
+ *   - `stream` is a cudaStream_t passed as void*; every call is asynchronous on that stream;
+ *   - nothing is allocated, freed or synchronised behind the caller's back: scratch memory is
+ *     caller-provided and sized by the *_workspace_bytes() queries;
+ *   - every function returns an hk_status (0 = ok).  Argument errors are detected on the host
+ *     before any launch.  The reference's launchers return void and abort() on precondition
+ *     failure; the C++ shim (helios_b200_shim.hpp) keeps that behaviour on top of these codes.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the reference tree).
+ */
+#ifndef HELIOS_B200_H
+#define HELIOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hk_status {
+  HK_OK = 0,
+  HK_ERR_INVALID = 1,      /* bad shape / null pointer / misaligned buffer                        */
+  HK_ERR_UNSUPPORTED = 2,  /* valid request the library has no kernel for (e.g. head dim 96)      */
+  HK_ERR_CUDA = 3,         /* the CUDA runtime reported an error at launch                        */
+  HK_ERR_WORKSPACE = 4,    /* caller-provided workspace too small                                 */
+  HK_ERR_TIMEOUT = 5       /* a bounded device-side wait expired (see hk_read_device_status)      */
+} hk_status;
+
+/* dtype tags for the entry points that accept either 16-bit float format */
+enum { HK_F16 = 0, HK_BF16 = 1 };
+
+const char* hk_status_string(int status);
+int hk_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * (a) KDA
+ * ------------------------------------------------------------------------------------------- */
+
+/* Causal depthwise short convolution (+SiLU) with rolling window state.
+ * Replaces helios::aux::cuda_causal_conv1d_update  (src/cuda/aux/gdn.cuh:67-83, gdn.cu:972-1023).
+ *   x     [bsz][dim][seqlen] bf16 (channel-major)      state [slots][dim][state_size] bf16 (in place)
+ *   w     [dim][K] bf16     bias [dim] bf16 or NULL    out   [bsz][seqlen][dim] bf16
+ *   slots [bsz] or NULL (identity).  K <= 16, state_size >= K.                                  */
+int hk_conv1d_update(const void* x, void* conv_state, const int* slots, const void* weight,
+                     const void* bias, void* out, int bsz, int dim, int seqlen, int state_size,
+                     int K, int activation, int history, void* stream);
+
+/* Gated delta rule recurrence, token by token (decode, short sequences, history mode).
+ * Replaces helios::aux::cuda_recurrent_gated_delta_rule (src/cuda/aux/gdn.cuh:47-65,
+ * gdn.cu:760-866).  Same tensor layouts:
+ *   mixed_qkv [bsz][seqlen][2*Hk*dk + Hv*dv] bf16 = q | k | v      g [bsz][seqlen][Hv][dk] f32
+ *   (channelwise) or [bsz][seqlen][Hv]      beta [bsz][seqlen][Hv] bf16
+ *   state [slots][history_stride][Hv][dk][dv] f32 (in place)   out [bsz][seqlen][Hv][dv] bf16 (rz)
+ *   out_f32: optional (may be NULL) copy of the output before bf16 rounding, same shape.
+ * Supported head dims: (dk,dv) = (128,128) and (64,64).                                          */
+int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* beta, float* state,
+                     void* out, float* out_f32, int bsz, int seqlen, int num_k_heads,
+                     int num_v_heads, int k_head_dim, int v_head_dim, int history_stride,
+                     const int* slots, int channelwise, int history, void* stream);
+
+/* Chunked (64-token) KDA prefill on the tensor cores; numerically equivalent to
+ * hk_kda_recurrent(channelwise=1, history=0) on the same arguments (the reference has no chunked
+ * kernel: prefill calls the recurrence with seqlen = n, src/engine/runner.cpp:468-471).
+ * Requires dk = dv = 128, Hk == Hv.  seqlen may be any positive length (a ragged tail shorter
+ * than a chunk is processed by the same kernels).  `workspace` must hold at least
+ * hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads) bytes, 256-byte aligned.             */
+size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads);
+int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* beta, float* state,
+                           void* out, float* out_f32, int bsz, int seqlen, int num_heads,
+                           const int* slots, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (c) DSA indexer
+ * ------------------------------------------------------------------------------------------- */
+
+/* Ring write of k||gate rows and pooling of every 4-token group completed by this call.
+ * Replaces helios::attn::kpool_write (src/cuda/attn/attn.cuh:74-87, attn.cu:332-390).          */
+int hk_kpool_write(const void* idx_k, const void* idx_g, void* raw_ring, int raw_rows,
+                   void* pool_k_nt, const float* ape, int pos_start, int n_new, void* stream);
+
+/* scores[r][p] = n_heads^-1/2 * sum_h w[r][h] * relu(128^-1/2 * q[r][h] . pool_k[p]),
+ * -inf where 4p+3 > q_pos[r].  Replaces helios::attn::indexer_score / indexer_score_mma
+ * (src/cuda/attn/attn.cuh:44-55, attn.cu:182-273).  Tensor-core (tcgen05) kernel.
+ *   q_idx [m][n_heads][128], pool_k_nt [npools][128], w [m][n_heads]: fp16 or bf16 (`dtype`);
+ *   scores [m][score_stride] fp16.  n_heads must be 32.                                         */
+int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void* w, const int* q_pos,
+                     void* scores, int m, int npools, int score_stride, int n_heads, int dtype,
+                     void* stream);
+
+/* Scalar cross-check kernel reading the transposed [128][pk_stride] plane.
+ * Replaces helios::attn::indexer_score_legacy (src/cuda/attn/attn.cu:134-158, :275-280).        */
+int hk_indexer_score_legacy(const void* q_idx, const void* pool_k, const void* w, const int* q_pos,
+                            void* scores, int m, int npools, int pk_stride, void* stream);
+
+/* Exact top-k over fp16 score rows: every entry above the k-th value in ascending index order,
+ * then ties with the k-th value in ascending index order, -1 padding up to k_pad; -inf is never
+ * selected.  Replaces helios::aux::dsa_topk (src/cuda/aux/dsa_topk.cuh:15-27, dsa_topk.cu:668-732).
+ * If t_ptr != NULL: T = t_seq > 0 ? t_ptr[row / t_seq] : t_ptr[0] (device override, as there).   */
+int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, int T, int k, int k_pad,
+                const int* t_ptr, int t_seq, void* stream);
+
+/* Pool index -> token index expansion plus the 4 tail tokens, clipped to the row's position.
+ * Replaces helios::attn::pool_expand_row (q_pos != NULL) and helios::attn::pool_expand
+ * (q_pos == NULL, cur_pos used for every row)  (src/cuda/attn/attn.cuh:57-72, attn.cu:284-327).
+ *   pool_idx [m][n_sel], raw_idx [m][4*n_sel + 4]                                               */
+int hk_pool_expand(const int* pool_idx, const int* q_pos, int* raw_idx, int m, int cur_pos,
+                   int n_sel, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (b) absorbed MLA, (d) split-KV combine
+ * ------------------------------------------------------------------------------------------- */
+
+/* Partial format of a split: for every (row, head) a running max m, a sum l = sum exp(s - m) and an
+ * un-normalised accumulator acc[512] = sum exp(s - m) * latent.  A workspace for n_split splits of
+ * `rows` (row, head) pairs is laid out as  m[n_split][rows] f32 | l[n_split][rows] f32 |
+ * acc[n_split][rows][512] f32, i.e. n_split * rows * 2056 bytes (+ alignment).                  */
+size_t hk_mla_partial_bytes(int n_split, int64_t rows);
+
+/* Number of KV splits the library would pick for a launch with `m` query rows attending `n_keys`
+ * keys each (so that the grid covers the GPU); 1 means no workspace is needed.                  */
+int hk_mla_auto_splits(int m, int n_keys);
+
+/* Sparse (gathered) attention: row r attends ckv[raw_idx[r][i]] for every i < kidx with
+ * raw_idx >= 0 (duplicates count twice; all skipped -> zeros).
+ * Replaces helios::attn::mla_sparse_decode (src/cuda/attn/attn.cuh:89-99, attn.cu:394-617) with an
+ * explicit softmax scale and head count (the reference pins 0.0625 and 64).
+ *   q_lat [m][n_heads][512] f16, ckv [*][512] f16, lat_out [m][n_heads][512] f16.
+ * n_split = 0 lets the library choose; workspace may be NULL when the choice is 1.             */
+int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx, int kidx, void* lat_out,
+                  int m, int n_heads, float scale, int n_split, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+/* Dense causal attention: row r attends ckv[kv_base[r] .. kv_base[r] + kv_len[r]).
+ * With kv_base == NULL and kv_len == NULL: base 0 and len = pos_start + r + 1, which is
+ * helios::attn::mla_dense_prefill (src/cuda/attn/attn.cuh:101-108, attn.cu:621-699); qlen = 1 is
+ * dense decode, and per-row base/len arrays give batched decode over concatenated caches.       */
+int hk_mla_dense(const void* q_lat, const void* ckv, const int64_t* kv_base, const int* kv_len,
+                 int pos_start, void* lat_out, int m, int n_heads, float scale, int n_split,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same two, but writing un-normalised split partials only (no combine): the building block of
+ * split-KV across GPUs.  part_* point at storage for ONE split: m[rows], l[rows], acc[rows][512]. */
+int hk_mla_dense_partial(const void* q_lat, const void* ckv, const int64_t* kv_base,
+                         const int* kv_len, int pos_start, float* part_m, float* part_l,
+                         float* part_acc, int m, int n_heads, float scale, void* stream);
+
+/* Log-sum-exp combine of n_split partials (layout above; the three arrays may live anywhere,
+ * split stride = `rows` elements for m/l and rows*512 for acc).
+ * Restates the in-kernel merge src/cuda/attn/attn.cu:462-481 as a standalone kernel.           */
+int hk_lse_combine(const float* part_m, const float* part_l, const float* part_acc, int n_split,
+                   int64_t rows, void* out_f16, void* stream);
+
+/* Combine where split s lives at the s-th pointer of device arrays (e.g. peer-mapped buffers of
+ * other GPUs, read with plain loads over NVLink).  ptrs_* are DEVICE arrays of n_split pointers. */
+int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
+                        const float* const* ptrs_acc, int n_split, int64_t rows, void* out_f16,
+                        void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * adjacent projections (kept so the engine's layer loop links unchanged)
+ * Replace helios::attn::q_latent / q_latent_t / o_absorb / o_absorb_t / wuv_transpose
+ * (src/cuda/attn/attn.cuh:24-39, attn.cu:12-130).
+ * ------------------------------------------------------------------------------------------- */
+int hk_q_latent(const void* q_nope, const void* kv_b, void* q_lat, int m, void* stream);
+int hk_o_absorb(const void* lat_out, const void* kv_b, void* o, int m, void* stream);
+int hk_wuv_transpose(const void* kv_b, void* wuv_t, void* stream);
+int hk_o_absorb_t(const void* lat_out, const void* wuv_t, void* o, int nrows, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * diagnostics
+ * ------------------------------------------------------------------------------------------- */
+
+/* Kernels never spin without a bound: a device-side wait (mbarrier, peer flag) that expires makes the
+ * kernel record HK_ERR_TIMEOUT in a per-device status word and finish.  This reads (and optionally
+ * clears) that word on the current device; 0 means no wait has expired since the last reset.
+ * Synchronises with the device.                                                                */
+int hk_read_device_status(int* host_out, int reset);
+
+/* Tensor-core self test: D[M][N] = A[M][K] * B (fp16 in, fp32 out) through the library's tcgen05 /
+ * TMEM helper layer.  b_layout 0: B given as [N][K] (K-major); 1: B given as [K][N] (N-major).
+ * M in {64,128}; N multiple of 16, <= 256; K multiple of 16, <= 256.  D receives the RAW accumulator, float [128 lanes][N].
+ * `status` (device int) is set to 0 on success or records which bounded wait expired.                                   */
+int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,
+                     int b_layout, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELIOS_B200_H */

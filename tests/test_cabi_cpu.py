@@ -1,0 +1,68 @@
+"""No-GPU checks of the boundary: the shared library loads, exports every symbol the public header
+declares (and nothing the header does not), the reference-named C++ launchers are exported, and the
+Python host layer refuses to compute without a device."""
+import os
+import re
+import subprocess
+
+import pytest
+
+import helios_glm53flash_b200 as hk
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built():
+    from helios_glm53flash_b200 import build as hk_build
+    return hk_build.build()
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "helios_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_exactly_the_header(built):
+    out = subprocess.check_output(["nm", "-D", "--defined-only", built], text=True)
+    exported = sorted(l.split()[-1] for l in out.splitlines() if " T " in l and l.split()[-1].startswith("hk_"))
+    declared = _header_symbols()
+    assert exported == declared
+    assert sorted(hk.SIGNATURES) == declared, "ctypes table covers the whole header"
+
+
+def test_library_loads_and_answers_without_a_gpu(built):
+    lib = hk.load_library()
+    assert lib.hk_abi_version() == 1
+    assert hk.status_string(0) == "ok" and "workspace" in hk.status_string(hk.HK_ERR_WORKSPACE)
+    assert lib.hk_mla_partial_bytes(4, 128) >= 4 * 128 * 2056
+    assert lib.hk_kda_chunked_workspace_bytes(1, 512, 32) > 0
+
+
+def test_reference_named_launchers_are_exported(built):
+    out = subprocess.check_output(["nm", "-DC", "--defined-only", built], text=True)
+    for name in ["helios::aux::cuda_recurrent_gated_delta_rule(", "helios::aux::cuda_causal_conv1d_update(",
+                 "helios::aux::dsa_topk(", "helios::attn::kpool_write(", "helios::attn::indexer_score(",
+                 "helios::attn::pool_expand_row(", "helios::attn::mla_sparse_decode(",
+                 "helios::attn::mla_dense_prefill(", "helios::attn::q_latent_t(", "helios::attn::o_absorb_t(",
+                 "helios::attn::o_absorb(", "helios::attn::wuv_transpose("]:
+        assert name in out, name
+
+
+def test_no_cpu_path():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    t = torch.zeros(4)
+    with pytest.raises(RuntimeError):
+        hk.dsa_topk(t, 4, t, 1, 4, 1, 1)
+
+
+def test_product_does_not_reference_the_oracle():
+    pkg = os.path.join(ROOT, "helios_glm53flash_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".hpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "liboracle" not in text and "hk_oracle" not in text and "oracle/" not in text, f

@@ -1,0 +1,139 @@
+"""GPU parity of the KDA kernels (short conv, recurrence) through the C ABI, against the CPU oracle
+and, when it was built, against the reference's own kernels compiled for sm_100a."""
+import numpy as np
+import pytest
+import torch
+
+import hk_oracle as orc
+import hk_ref as ref
+from gpu_util import bf16_ulp_diff, bits, dev, dev_bf16, frob_rel, max_rel
+import helios_glm53flash_b200 as hk
+from helios_glm53flash_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_conv(x, st, w, bsz, dim, T, K=4, act=True, history=False, state_size=None, use_ref=False):
+    state_size = state_size or K
+    dx, dst, dw = dev_bf16(x), dev_bf16(st), dev_bf16(w)
+    out = torch.empty(bsz, T, dim, dtype=torch.bfloat16, device="cuda")
+    fn = ref.conv1d_update if use_ref else hk.cuda_causal_conv1d_update
+    fn(dx, dst, None, dw, None, out, bsz, dim, T, state_size, K, act, history)
+    torch.cuda.synchronize()
+    return bits(out), bits(dst)
+
+
+@pytest.mark.parametrize("dim,T", [(1536, 512), (1536, 1), (1536, 3), (1536, 37), (256, 200), (192, 4099), (12288, 128)])
+def test_conv_vs_oracle_and_reference(dim, T):
+    inp = synth.conv_inputs(T, dim, seed=dim + T)
+    o_out, o_st = orc.conv1d_update(inp["x"], inp["state"], inp["weight"], None, 1, dim, T, 4, 4)
+    g_out, g_st = _run_conv(inp["x"], inp["state"], inp["weight"], 1, dim, T)
+    assert np.array_equal(g_st, o_st), "window state must match exactly"
+    ulp = bf16_ulp_diff(g_out, o_out)
+    assert ulp.max() <= 1 and (ulp > 0).mean() < 2e-3  # exp approximation may flip a rounding
+    if ref.available():
+        r_out, r_st = _run_conv(inp["x"], inp["state"], inp["weight"], 1, dim, T, use_ref=True)
+        assert np.array_equal(g_st, r_st)
+        assert np.array_equal(g_out, r_out), "same arithmetic as the reference kernel: bit-exact"
+
+
+def test_conv_history_and_generic_k():
+    dim, T, K, S = 96, 9, 3, 7
+    inp = synth.conv_inputs(T, dim, K=K, seed=5)
+    st = synth.f32_to_bf16_bits(synth.rng(9).standard_normal((1, dim, S), dtype=np.float32))
+    for history in (False, True):
+        o_out, o_st = orc.conv1d_update(inp["x"], st, inp["weight"], None, 1, dim, T, S, K, True, history)
+        g_out, g_st = _run_conv(inp["x"], st, inp["weight"], 1, dim, T, K=K, history=history, state_size=S)
+        assert np.array_equal(g_st, o_st)
+        assert bf16_ulp_diff(g_out, o_out).max() <= 1
+
+
+def _run_rec(inp, state, bsz, T, H, D, stride=1, cw=True, hist=False, use_ref=False, force_recurrent=True):
+    q, g, b = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"])
+    st = dev(state)
+    out = torch.empty(bsz, T, H, D, dtype=torch.bfloat16, device="cuda")
+    o32 = torch.empty(bsz, T, H, D, dtype=torch.float32, device="cuda")
+    if use_ref:
+        ref.kda_recurrent(q, g, b, st, out, bsz, T, H, H, D, D, stride, None, cw, hist)
+        o32 = None
+    else:
+        hk.cuda_recurrent_gated_delta_rule(q, g, b, st, out, bsz, T, H, H, D, D, stride, None, cw, hist,
+                                           out_f32=o32, force_recurrent=force_recurrent)
+    torch.cuda.synchronize()
+    return bits(out), (None if o32 is None else o32.cpu().numpy()), st.cpu().numpy()
+
+
+@pytest.mark.parametrize("T,H", [(1, 32), (16, 4), (70, 2), (1, 64)])
+def test_recurrent_vs_oracle_and_reference(T, H):
+    D = 128
+    inp = synth.kda_inputs(T, H, D, seed=T)
+    s0 = (0.1 * synth.rng(3).standard_normal((1, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    o_out, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, 1, T, H, H, D, D)
+    g_out, g_32, g_st = _run_rec(inp, s0, 1, T, H, D)
+    assert max_rel(g_32, o_32) < 2e-3 and max_rel(g_32, o_32) < 1e-4
+    assert frob_rel(g_st, o_st) < 1e-5
+    assert bf16_ulp_diff(g_out, o_out).max() <= 1
+    if ref.available():
+        r_out, _, r_st = _run_rec(inp, s0, 1, T, H, D, use_ref=True)
+        assert frob_rel(g_st, r_st) < 1e-5
+        assert bf16_ulp_diff(g_out, r_out).max() <= 1
+        assert frob_rel(o_st, r_st) < 1e-5, "oracle pinned to the reference kernel"
+
+
+@pytest.mark.parametrize("dim,cw,hist,steps", [(64, False, False, 7), (64, False, True, 7), (128, False, True, 1),
+                                               (128, True, True, 7), (128, True, False, 7), (128, False, False, 1)])
+def test_recurrent_determinism_suite_shapes(dim, cw, hist, steps):
+    """the 12-config grid of the reference's bit-repeatability test (test_deterministic_reductions.cu:19-49):
+    same synthetic inputs, here also checked for VALUE against the oracle, then 4 repeats byte-equal."""
+    heads, stride = 2, (steps + 1 if hist else 1)
+    n = steps * 3 * heads * dim
+    i = np.arange(n, dtype=np.float32)
+    qkv = synth.f32_to_bf16_bits(np.sin(i * np.float32(0.019))).reshape(1, steps, 3 * heads * dim)
+    bi = np.arange(steps * heads, dtype=np.float32)
+    beta = synth.f32_to_bf16_bits((0.3 + np.cos(bi) * 0.1).astype(np.float32)).reshape(1, steps, heads)
+    ng = steps * heads * (dim if cw else 1)
+    g = (-0.01 - (np.arange(ng) % 7) * 0.003).astype(np.float32)
+    s0 = (np.sin(np.arange(stride * heads * dim * dim, dtype=np.float32) * np.float32(0.017)) * 0.2).astype(np.float32)
+    s0 = s0.reshape(1, stride, heads, dim, dim)
+    inp = {"mixed_qkv": qkv, "g": g, "beta": beta}
+    o_out, o_32, o_st = orc.kda_recurrent(qkv, g, beta, s0, 1, steps, heads, heads, dim, dim, stride,
+                                          None, cw, hist)
+    first = None
+    for rep in range(4):
+        g_out, g_32, g_st = _run_rec(inp, s0, 1, steps, heads, dim, stride, cw, hist)
+        if first is None:
+            first = (g_out.copy(), g_st.copy())
+            assert max_rel(g_32, o_32) < 1e-4
+            assert frob_rel(g_st, o_st) < 1e-5
+        assert np.array_equal(g_out, first[0]) and np.array_equal(g_st.view(np.uint32), first[1].view(np.uint32))
+    if ref.available():
+        r_out, _, r_st = _run_rec(inp, s0, 1, steps, heads, dim, stride, cw, hist, use_ref=True)
+        assert frob_rel(g_st, r_st) < 1e-5
+        assert bf16_ulp_diff(g_out, r_out).max() <= 1
+
+
+def test_recurrent_slots_and_batch():
+    T, H, D, bsz = 3, 4, 128, 3
+    inp = synth.kda_inputs(T, H, D, bsz=bsz, seed=11)
+    slots = np.array([2, 0, 3], dtype=np.int32)
+    s0 = (0.1 * synth.rng(4).standard_normal((4, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    o_out, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, bsz, T, H, H, D, D, 1, slots)
+    q, g, b, st = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"]), dev(s0)
+    out = torch.empty(bsz, T, H, D, dtype=torch.bfloat16, device="cuda")
+    hk.cuda_recurrent_gated_delta_rule(q, g, b, st, out, bsz, T, H, H, D, D, 1, dev(slots), True, False)
+    torch.cuda.synchronize()
+    assert frob_rel(st.cpu().numpy(), o_st) < 1e-5
+    assert np.array_equal(st.cpu().numpy()[1], s0[1]), "unused slot untouched"
+    assert bf16_ulp_diff(bits(out), o_out).max() <= 1
+
+
+def test_bad_arguments_are_rejected_before_launch():
+    t = torch.zeros(16, device="cuda")
+    with pytest.raises(hk.HeliosB200Error) as e:
+        hk.cuda_recurrent_gated_delta_rule(t, t, t, t, t, 1, 1, 3, 4, 128, 128, 1, None, True, False)
+    assert e.value.status == hk.HK_ERR_INVALID
+    with pytest.raises(hk.HeliosB200Error) as e:
+        hk.cuda_recurrent_gated_delta_rule(t, t, t, t, t, 1, 1, 4, 4, 96, 96, 1, None, False, False)
+    assert e.value.status == hk.HK_ERR_UNSUPPORTED
+    with pytest.raises(hk.HeliosB200Error):
+        hk.cuda_causal_conv1d_update(t, t, None, t, None, t, 1, 64, 8, 2, 4, True, False)

@@ -1,0 +1,174 @@
+"""GPU parity of absorbed MLA (sparse gather / dense causal, decode / prefill rows), the split-KV
+partials and the log-sum-exp combine, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import hk_oracle as orc
+import hk_ref as ref
+from gpu_util import bits, dev, dev_f16, max_rel, sum_rel
+import helios_glm53flash_b200 as hk
+from helios_glm53flash_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3  # max |a-b| / max |b| for attention outputs
+
+
+def _sparse_case(m, kidx, T, scale, seed, holes=True, std=0.5):
+    inp = synth.mla_inputs(T, m, seed=seed, cache_std=std)
+    r = np.random.RandomState(seed)
+    ridx = r.randint(0, T, (m, kidx)).astype(np.int32)
+    if holes:
+        ridx[:, 3::7] = -1
+    return inp, ridx
+
+
+@pytest.mark.parametrize("m,kidx,T,scale,n_split", [
+    (1, 64, 512, 0.0625, 1), (3, 300, 2048, 0.0625, 0), (1, 2052, 8192, 0.0625, 0), (2, 2052, 8192, 512 ** -0.5, 5),
+    (1, 7, 64, 0.0625, 3), (5, 130, 1000, 0.0625, 2)])
+def test_sparse_vs_oracle_and_reference(m, kidx, T, scale, n_split):
+    inp, ridx = _sparse_case(m, kidx, T, scale, seed=kidx)
+    o16, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, scale, raw_idx=ridx, kidx=kidx)
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_sparse_decode(q, c, dev(ridx), kidx, out, m, scale=scale, n_split=n_split)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    g = synth.f16_bits_to_f32(bits(out))
+    assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
+    if ref.available() and scale == 0.0625:
+        out2 = torch.empty_like(out)
+        ref.mla_sparse_decode(q, c, dev(ridx), kidx, out2, m)
+        torch.cuda.synchronize()
+        rr = synth.f16_bits_to_f32(bits(out2))
+        assert max_rel(g, rr) < TOL, "within 2e-3 of the reference's own kernel"
+        assert sum_rel(rr, o32) < 3e-3, "oracle pinned to the reference kernel"
+
+
+def test_sparse_all_skipped_row_gives_zeros_and_duplicates_count_twice():
+    m, kidx, T = 2, 16, 64
+    inp, ridx = _sparse_case(m, kidx, T, 0.0625, seed=1, holes=False)
+    ridx[0, :] = -1
+    ridx[1, :] = np.array([5, 5, 9, -1] * 4, dtype=np.int32)
+    o16, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, raw_idx=ridx, kidx=kidx)
+    out = torch.full((m, 64, 512), 3.0, dtype=torch.float16, device="cuda")
+    hk.mla_sparse_decode(dev_f16(inp["q_lat"]), dev_f16(inp["ckv"]), dev(ridx), kidx, out, m)
+    torch.cuda.synchronize()
+    g = synth.f16_bits_to_f32(bits(out))
+    assert (g[0] == 0).all()
+    assert max_rel(g[1], o32[1]) < TOL
+
+
+@pytest.mark.parametrize("qlen,pos_start,scale,n_split", [(16, 0, 0.0625, 1), (1, 4095, 0.0625, 0), (1, 32767, 512 ** -0.5, 0),
+                                                          (4, 1000, 0.0625, 3), (33, 100, 0.0625, 0)])
+def test_dense_vs_oracle_and_reference(qlen, pos_start, scale, n_split):
+    T = pos_start + qlen
+    inp = synth.mla_inputs(T, qlen, seed=qlen + pos_start, cache_std=0.5)
+    o16, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], qlen, 64, scale, pos_start=pos_start)
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    out = torch.empty(qlen, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_dense_prefill(q, c, out, qlen, pos_start, scale=scale, n_split=n_split)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    g = synth.f16_bits_to_f32(bits(out))
+    assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
+    if ref.available() and scale == 0.0625 and T <= 8192:
+        out2 = torch.empty_like(out)
+        ref.mla_dense_prefill(q, c, out2, qlen, pos_start)
+        torch.cuda.synchronize()
+        rr = synth.f16_bits_to_f32(bits(out2))
+        assert max_rel(g, rr) < TOL
+        assert sum_rel(rr, o32) < 3e-3
+
+
+def test_dense_batched_decode_over_concatenated_caches():
+    B, L = 4, 777
+    inp = synth.mla_inputs(B * L, B, seed=8, cache_std=0.5)
+    base = (np.arange(B) * L).astype(np.int64)
+    lens = np.array([L, L - 5, 1, 300], dtype=np.int32)
+    o16, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], B, 64, 0.0625, kv_base=base, kv_len=lens)
+    out = torch.empty(B, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_dense_prefill(dev_f16(inp["q_lat"]), dev_f16(inp["ckv"]), out, B, 0, kv_base=dev(base), kv_len=dev(lens),
+                         n_keys_hint=L)
+    torch.cuda.synchronize()
+    assert max_rel(synth.f16_bits_to_f32(bits(out)), o32) < TOL
+
+
+def test_partials_and_combine_vs_oracle():
+    m, L, S = 2, 900, 3
+    inp = synth.mla_inputs(L, m, seed=21, cache_std=0.5)
+    rows = m * 64
+    cuts = [0, 250, 251, L]
+    pm = torch.empty(S, rows, dtype=torch.float32, device="cuda")
+    pl = torch.empty(S, rows, dtype=torch.float32, device="cuda")
+    pa = torch.empty(S, rows, 512, dtype=torch.float32, device="cuda")
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    o_parts = []
+    for s in range(S):
+        base = np.full(m, cuts[s], dtype=np.int64)
+        lens = np.full(m, cuts[s + 1] - cuts[s], dtype=np.int32)
+        hk.mla_dense_partial(q, c, dev(base), dev(lens), 0, pm[s], pl[s], pa[s], m)
+        o_parts.append(orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=base, kv_len=lens, partial=True)[2])
+    out = torch.empty(rows, 512, dtype=torch.float16, device="cuda")
+    hk.lse_combine(pm, pl, pa, S, rows, out)
+    torch.cuda.synchronize()
+    # the partial of each split, renormalised, equals the oracle's partial
+    for s in range(S):
+        om, ol, oa = o_parts[s]
+        gm, gl, ga = pm[s].cpu().numpy(), pl[s].cpu().numpy(), pa[s].cpu().numpy()
+        w = np.exp(gm - om)
+        assert np.allclose(gl * w, ol, rtol=2e-3)
+        assert max_rel(ga * w[:, None], oa) < TOL
+    full16, full32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=np.zeros(m, np.int64),
+                                    kv_len=np.full(m, L, np.int32))
+    g = synth.f16_bits_to_f32(bits(out)).reshape(m, 64, 512)
+    assert max_rel(g, full32) < TOL
+    # oracle combine of the GPU partials gives the same
+    c16, c32 = orc.lse_combine(pm.cpu().numpy(), pl.cpu().numpy(), pa.cpu().numpy(), S, rows)
+    assert max_rel(g.reshape(rows, 512), c32) < 1e-3
+
+
+def test_combine_edge_cases_and_pointer_variant():
+    rows, S = 6, 4
+    r = synth.rng(5)
+    pm = r.standard_normal((S, rows), dtype=np.float32)
+    pl = (1 + r.random((S, rows))).astype(np.float32)
+    pa = r.standard_normal((S, rows, 512), dtype=np.float32)
+    pm[:, 0] = -np.inf                    # a row where every split is empty -> zeros
+    pm[1, 2] = -np.inf; pl[1, 2] = 0; pa[1, 2] = 0   # one empty split
+    c16, c32 = orc.lse_combine(pm, pl, pa, S, rows)
+    dm, dl, da = dev(pm), dev(pl), dev(pa)
+    out = torch.empty(rows, 512, dtype=torch.float16, device="cuda")
+    hk.lse_combine(dm, dl, da, S, rows, out)
+    out2 = torch.empty_like(out)
+    pm_ptrs = torch.tensor([dm[s].data_ptr() for s in range(S)], dtype=torch.int64, device="cuda")
+    pl_ptrs = torch.tensor([dl[s].data_ptr() for s in range(S)], dtype=torch.int64, device="cuda")
+    pa_ptrs = torch.tensor([da[s].data_ptr() for s in range(S)], dtype=torch.int64, device="cuda")
+    hk.lse_combine_ptrs(pm_ptrs, pl_ptrs, pa_ptrs, S, rows, out2)
+    torch.cuda.synchronize()
+    g = synth.f16_bits_to_f32(bits(out))
+    assert (g[0] == 0).all()
+    assert max_rel(g, c32) < 1e-3
+    assert np.array_equal(bits(out), bits(out2))
+
+
+def test_absorbed_projections_vs_oracle():
+    m = 2
+    r = synth.rng(9)
+    qn = synth.f32_to_f16_bits(r.uniform(-1, 1, (m, 64, 256)).astype(np.float32))
+    kb = synth.f32_to_f16_bits((0.3 * r.uniform(-1, 1, (32768, 512))).astype(np.float32))
+    lo = synth.f32_to_f16_bits(r.uniform(-1, 1, (m, 64, 512)).astype(np.float32))
+    dq, dkb, dlo = dev_f16(qn), dev_f16(kb), dev_f16(lo)
+    ql = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+    o1 = torch.empty(m, 64, 256, dtype=torch.float16, device="cuda")
+    o2 = torch.empty_like(o1)
+    wt = torch.empty(64, 512, 256, dtype=torch.float16, device="cuda")
+    hk.q_latent(dq, dkb, ql, m)
+    hk.o_absorb(dlo, dkb, o1, m)
+    hk.wuv_transpose(dkb, wt)
+    hk.o_absorb_t(dlo, wt, o2, m)
+    torch.cuda.synchronize()
+    f = synth.f16_bits_to_f32
+    assert sum_rel(f(bits(ql)), f(orc.q_latent(qn, kb, m))) < 2e-3
+    want_o = f(orc.o_absorb(lo, kb, m))
+    assert sum_rel(f(bits(o1)), want_o) < 2e-3 and sum_rel(f(bits(o2)), want_o) < 2e-3
