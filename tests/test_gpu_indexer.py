@@ -143,6 +143,8 @@ def test_topk_bit_exact_vs_oracle_and_reference(R, T, k, k_pad, stride_pad, offs
 
 
 def test_topk_selects_the_true_top_k():
+    """independent of the oracle: the selection is a true top-k, above-threshold entries come out in
+    ascending index order followed by the threshold ties in ascending index order"""
     R, T, k = 3, 5000, 512
     sc = synth.rng(77).standard_normal((R, T), dtype=np.float32)
     scb = synth.f32_to_f16_bits(sc)
@@ -150,9 +152,15 @@ def test_topk_selects_the_true_top_k():
     vals = synth.f16_bits_to_f32(scb)
     for r_ in range(R):
         sel = got[r_]
-        assert (np.diff(sel) > 0).all(), "no ties here, so indices come out ascending"
         kth = np.sort(vals[r_])[-k]
-        assert vals[r_][sel].min() >= kth and len(set(sel.tolist())) == k
+        assert len(set(sel.tolist())) == k and vals[r_][sel].min() == kth
+        above = sel[vals[r_][sel] > kth]
+        ties = sel[vals[r_][sel] == kth]
+        assert (np.diff(above) > 0).all() and (np.diff(ties) > 0).all()
+        assert np.array_equal(sel, np.concatenate([above, ties]))
+        assert len(above) == (vals[r_] > kth).sum()
+        # ties are the FIRST ones by index
+        assert np.array_equal(ties, np.nonzero(vals[r_] == kth)[0][: len(ties)])
 
 
 @pytest.mark.parametrize("per_row", [True, False])

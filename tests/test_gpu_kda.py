@@ -137,3 +137,84 @@ def test_bad_arguments_are_rejected_before_launch():
     assert e.value.status == hk.HK_ERR_UNSUPPORTED
     with pytest.raises(hk.HeliosB200Error):
         hk.cuda_causal_conv1d_update(t, t, None, t, None, t, 1, 64, 8, 2, 4, True, False)
+
+
+# ------------------------------------------------------------------------------------------------
+# chunked tensor-core prefill == the recurrence called with seqlen = T
+# ------------------------------------------------------------------------------------------------
+def _gate_like_reference(T, H, D, seed):
+    """log-decay in the reference engine's range: lb * sigmoid(x), lb = -5 (src/engine/glue2.cu:347-360)"""
+    x = synth.rng(seed).standard_normal((1, T, H, D), dtype=np.float32)
+    return (-5.0 / (1.0 + np.exp(-x))).astype(np.float32)
+
+
+@pytest.mark.parametrize("T,H,gate", [(64, 2, "config"), (65, 2, "config"), (127, 1, "config"), (128, 4, "config"),
+                                      (200, 2, "config"), (512, 32, "config"), (256, 2, "reference"), (192, 2, "weak")])
+def test_chunked_prefill_vs_oracle(T, H, gate):
+    D = 128
+    inp = synth.kda_inputs(T, H, D, seed=100 + T)
+    if gate == "reference":
+        inp["g"] = _gate_like_reference(T, H, D, 7)
+    elif gate == "weak":
+        inp["g"] = (inp["g"] * 0.02).astype(np.float32)      # long memory: state grows over many chunks
+    s0 = (0.1 * synth.rng(3).standard_normal((1, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    o_out, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, 1, T, H, H, D, D)
+    q, g, b, st = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"]), dev(s0)
+    out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+    o32 = torch.empty(1, T, H, D, dtype=torch.float32, device="cuda")
+    path = hk.cuda_recurrent_gated_delta_rule(q, g, b, st, out, 1, T, H, H, D, D, 1, None, True, False, out_f32=o32)
+    torch.cuda.synchronize()
+    assert path == "chunked"
+    assert hk.read_device_status() == 0
+    e_out, e_st = max_rel(o32.cpu().numpy(), o_32), frob_rel(st.cpu().numpy(), o_st)
+    print("chunked T=%d H=%d gate=%s: out max_rel %.2e, state frob %.2e" % (T, H, gate, e_out, e_st))
+    assert e_out < 2e-3, "outputs within 2e-3 (max |a-b| / max |b|) of the recurrence"
+    assert e_st < 1e-2, "state within 1e-2 relative Frobenius"
+    # the rounded output is the round-toward-zero bf16 of the fp32 output
+    want_bits = (o32.cpu().numpy().view(np.uint32) >> 16).astype(np.uint16)
+    assert np.array_equal(bits(out), want_bits)
+
+
+def test_chunked_prefill_then_decode_continues_the_state():
+    T, H, D, extra = 256, 4, 128, 16
+    inp = synth.kda_inputs(T + extra, H, D, seed=9)
+    s0 = np.zeros((1, 1, H, D, D), dtype=np.float32)
+    _, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, 1, T + extra, H, H, D, D)
+    q, g, b, st = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"]), dev(s0)
+    out = torch.empty(1, T + extra, H, D, dtype=torch.bfloat16, device="cuda")
+    o32 = torch.empty(1, T + extra, H, D, dtype=torch.float32, device="cuda")
+    hk.cuda_recurrent_gated_delta_rule(q[:, :T], g[:, :T], b[:, :T], st, out[:, :T], 1, T, H, H, D, D, 1, None, True,
+                                       False, out_f32=o32[:, :T])
+    for s in range(T, T + extra):
+        hk.cuda_recurrent_gated_delta_rule(q[:, s:s + 1], g[:, s:s + 1], b[:, s:s + 1], st, out[:, s:s + 1], 1, 1, H, H,
+                                           D, D, 1, None, True, False, out_f32=o32[:, s:s + 1])
+    torch.cuda.synchronize()
+    assert max_rel(o32.cpu().numpy(), o_32) < 2e-3
+    assert frob_rel(st.cpu().numpy(), o_st) < 1e-2
+
+
+def test_chunked_matches_recurrent_kernel_and_reference_kernel():
+    T, H, D = 320, 3, 128
+    inp = synth.kda_inputs(T, H, D, seed=12)
+    s0 = (0.05 * synth.rng(5).standard_normal((1, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    _, c32, c_st = _run_rec(inp, s0, 1, T, H, D, force_recurrent=False)
+    _, r32, r_st = _run_rec(inp, s0, 1, T, H, D, force_recurrent=True)
+    assert max_rel(c32, r32) < 2e-3 and frob_rel(c_st, r_st) < 1e-2
+    if ref.available():
+        _, _, ref_st = _run_rec(inp, s0, 1, T, H, D, use_ref=True)
+        assert frob_rel(c_st, ref_st) < 1e-2, "state vs the reference's own kernel run with seqlen = T"
+
+
+def test_chunked_batch_and_slots():
+    T, H, D, bsz = 130, 2, 128, 2
+    inp = synth.kda_inputs(T, H, D, bsz=bsz, seed=14)
+    slots = np.array([1, 0], dtype=np.int32)
+    s0 = (0.1 * synth.rng(6).standard_normal((2, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    _, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, bsz, T, H, H, D, D, 1, slots)
+    q, g, b, st = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"]), dev(s0)
+    out = torch.empty(bsz, T, H, D, dtype=torch.bfloat16, device="cuda")
+    o32 = torch.empty(bsz, T, H, D, dtype=torch.float32, device="cuda")
+    assert hk.cuda_recurrent_gated_delta_rule(q, g, b, st, out, bsz, T, H, H, D, D, 1, dev(slots), True, False,
+                                              out_f32=o32) == "chunked"
+    torch.cuda.synchronize()
+    assert max_rel(o32.cpu().numpy(), o_32) < 2e-3 and frob_rel(st.cpu().numpy(), o_st) < 1e-2
