@@ -52,6 +52,14 @@ def kda_inputs(seqlen, heads=32, dim=128, bsz=1, seed=0, normalise=True, g_scale
     return {"mixed_qkv": f32_to_bf16_bits(mixed), "g": g, "beta": f32_to_bf16_bits(beta)}
 
 
+def kda_gates(seqlen, heads=32, dim=128, bsz=1, seed=0):
+    """only the gate tensors of kda_inputs (same distributions): g f32 [bsz][T][H][D], beta bf16 bits"""
+    r = rng(seed + 505)
+    beta = 1.0 / (1.0 + np.exp(-r.standard_normal((bsz, seqlen, heads), dtype=np.float32)))
+    g = -_softplus(r.standard_normal((bsz, seqlen, heads, dim), dtype=np.float32))
+    return {"g": g.astype(np.float32), "beta": f32_to_bf16_bits(beta)}
+
+
 def conv_inputs(seqlen, dim, bsz=1, K=4, seed=0):
     """Short-conv inputs: x ~ N(0,1) channel-major [bsz][dim][T], weights ~ N(0,0.1) [dim][K],
     previous window state ~ N(0,1) [bsz][dim][K]."""
