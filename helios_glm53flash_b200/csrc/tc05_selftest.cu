@@ -15,7 +15,7 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  const bool b_mn = flags & 1, swap_a = flags & 0x100, swap_b = flags & 0x200;
+  const bool b_mn = flags & 1, a_mn = flags & 2, swap_a = flags & 0x100, swap_b = flags & 0x200;
   const int tid = threadIdx.x, warp = tid >> 5;
   uint8_t* sA = smem;
   uint8_t* sB = smem + 128 * 128 * 2;
@@ -34,10 +34,19 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   for (int i = tid; i < (128 * 128 * 2 + 256 * 128 * 2) / 16; i += 128)
     reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
-  for (int i = tid; i < M * (int)kchunks; i += 128) {
-    int r = i / kchunks, kc = i % kchunks;
-    uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)r * K + kc * 8);
-    *reinterpret_cast<uint4*>(sA + tc::kmajor_off(r, kc, lbo_a, sbo_a)) = v;
+  if (!a_mn) {
+    for (int i = tid; i < M * (int)kchunks; i += 128) {
+      int r = i / kchunks, kc = i % kchunks;
+      uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)r * K + kc * 8);
+      *reinterpret_cast<uint4*>(sA + tc::kmajor_off(r, kc, lbo_a, sbo_a)) = v;
+    }
+  } else {  // A given as [K][M]
+    const int mchunks = M / 8;
+    for (int i = tid; i < K * mchunks; i += 128) {
+      int k = i / mchunks, mc = i % mchunks;
+      uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)k * M + mc * 8);
+      *reinterpret_cast<uint4*>(sA + tc::mnmajor_off(k, mc, lbo_a, sbo_a)) = v;
+    }
   }
   if (!b_mn) {
     for (int i = tid; i < N * (int)kchunks; i += 128) {
@@ -59,7 +68,7 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
   if (tid == 0) {
-    const uint32_t idesc = tc::make_idesc(M, N, tc::FMT_F16, tc::FMT_F16, false, b_mn);
+    const uint32_t idesc = tc::make_idesc(M, N, tc::FMT_F16, tc::FMT_F16, a_mn, b_mn);
     for (int kk = 0; kk < K / 16; kk++) {
       uint64_t ad = swap_a ? tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, sbo_a, lbo_a)
                            : tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, lbo_a, sbo_a);

@@ -188,7 +188,7 @@ int hk_o_absorb_t(const void* lat_out, const void* wuv_t, void* o, int nrows, vo
 int hk_read_device_status(int* host_out, int reset);
 
 /* Tensor-core self test: D[M][N] = A[M][K] * B (fp16 in, fp32 out) through the library's tcgen05 /
- * TMEM helper layer.  b_layout 0: B given as [N][K] (K-major); 1: B given as [K][N] (N-major).
+ * TMEM helper layer.  b_layout bit 0: B given as [K][N] instead of [N][K]; bit 1: A given as [K][M] instead of [M][K].
  * M in {64,128}; N multiple of 16, <= 256; K multiple of 16, <= 256.  D receives the RAW accumulator, float [128 lanes][N].
  * `status` (device int) is set to 0 on success or records which bounded wait expired.                                   */
 int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,

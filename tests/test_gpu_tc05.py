@@ -14,14 +14,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.parametrize("M,N,K,b_layout", [(128, 32, 128, 0), (128, 256, 128, 0), (128, 64, 64, 1), (128, 32, 128, 1),
-                                            (128, 16, 128, 0), (128, 128, 16, 1), (128, 256, 64, 1)])
+                                            (128, 16, 128, 0), (128, 128, 16, 1), (128, 256, 64, 1), (128, 64, 64, 2), (128, 64, 128, 3)])
 def test_tc05_gemm_matches_fp32_matmul(M, N, K, b_layout):
     g = torch.Generator(device="cpu").manual_seed(M + N + K + b_layout)
     a = torch.randn(M, K, generator=g).half()
     b = torch.randn(N, K, generator=g).half()
     want = a.float() @ b.float().t()
-    b_in = b if b_layout == 0 else b.t().contiguous()
-    d, status = hk.tc05_selftest(a.cuda(), b_in.cuda(), M, N, K, b_layout)
+    b_in = b if (b_layout & 1) == 0 else b.t().contiguous()
+    a_in = a if (b_layout & 2) == 0 else a.t().contiguous()
+    d, status = hk.tc05_selftest(a_in.cuda(), b_in.cuda(), M, N, K, b_layout)
     torch.cuda.synchronize()
     assert int(status[0]) == 0
     got = d[:M].cpu()
