@@ -36,35 +36,52 @@ def _peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-class ClockSampler(threading.Thread):
-    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
+class ClockSampler:
+    """one `nvidia-smi -lms` process sampling SM clocks and throttle reasons; samples are stamped on
+    arrival so that the ones taken inside the timed region can be picked out"""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        super().__init__(daemon=True)
-        self.index, self.rows, self.stop_flag = index, [], False
+        self.rows, self.proc, self.thread = [], None, None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
 
-    def run(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-        while not self.stop_flag:
+    def _pump(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 6:
+                self.rows.append((time.time(), parts))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
             try:
-                o = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
-                                   capture_output=True, text=True, timeout=5).stdout.strip()
-                if o:
-                    self.rows.append([x.strip() for x in o.split(",")])
+                self.proc.wait(timeout=5)
             except Exception:
-                pass
-            time.sleep(0.1)
+                self.proc.kill()
 
-    def summary(self):
-        if not self.rows:
+    def summary(self, t_begin, t_end):
+        inside = [r for ts, r in self.rows if t_begin <= ts <= t_end]
+        note = "samples inside the timed region"
+        if not inside:
+            inside = [r for _, r in self.rows]
+            note = "no sample fell inside the timed region; all samples of the run (warm-up included)"
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        sm = sorted(int(r[0]) for r in inside if r[0].isdigit())
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in inside)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None,
-                "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None, "reasons": reasons,
-                "samples": len(self.rows)}
+                "sm_max_mhz": int(inside[0][1]) if inside[0][1].isdigit() else None, "reasons": reasons,
+                "samples": len(inside), "note": note}
 
 
 def cpu_baseline(steps=1, sample_t=CPU_SAMPLE_T):
@@ -107,7 +124,7 @@ def run_reference_arm(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=T_FULL, help="sequence length (default: the benchmark's 32768)")
@@ -180,19 +197,20 @@ def main():
     for _ in range(warmup):
         path = step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin = time.time()
     e0.record(stream)
     for i in range(steps):
         step(ev=evs[i])
     e1.record(stream)
     barrier()
+    t_end = time.time()
     ms_total = e0.elapsed_time(e1)
-    sampler.stop_flag = True
+    if sampler:
+        sampler.stop()
     conv_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / steps
     kda_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / steps
     assert hk.read_device_status() == 0, "a bounded device wait expired"
@@ -248,7 +266,7 @@ def main():
             "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": 3 * steps,
-            "clocks": sampler.summary(),
+            "clocks": sampler.summary(t_begin, t_end),
             "extras": extras,
         }
         if not args.no_cpu:
@@ -258,9 +276,11 @@ def main():
         dist.destroy_process_group()
 
 
-def _time_cuda(torch, fn, iters=20, warm=3, flush=None):
+def _time_loop(torch, fns, iters=10, warm=2, flush=None):
+    """median time of running every callable of `fns` back to back (one launch chain), in ms"""
     for _ in range(warm):
-        fn()
+        for f in fns:
+            f()
     torch.cuda.synchronize()
     ts = []
     for _ in range(iters):
@@ -268,7 +288,8 @@ def _time_cuda(torch, fn, iters=20, warm=3, flush=None):
             flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        for f in fns:
+            f()
         b.record()
         torch.cuda.synchronize()
         ts.append(a.elapsed_time(b))
@@ -277,54 +298,74 @@ def _time_cuda(torch, fn, iters=20, warm=3, flush=None):
 
 
 def side_measurements(hk, synth, torch, np):
-    """decode-side figures at 32K / 262K context (median kernel time, L2 flushed between iterations)"""
+    """Decode-side figures.  Each is the median device time of a chain of launches over DISTINCT
+    per-layer buffers (34 KDA layers, 11 MLA layers, as in the hybrid trunk), divided by the number of
+    layers; L2 is flushed (256 MB write) before every chain unless the buffers exceed L2 on their own."""
     from gpu_util import dev, dev_bf16, dev_f16
     res = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     H, D = HEADS, DIM
-    # KDA decode step, one layer (state 2 MiB in + out)
+    # ---- KDA decode step: 34 layers, each its own 2 MiB fp32 state ----
+    n_kda = 34
     kd = synth.kda_inputs(1, H, D, seed=5)
     q, g, b = dev_bf16(kd["mixed_qkv"]), dev(kd["g"]), dev_bf16(kd["beta"])
-    st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+    sts = [torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda") for _ in range(n_kda)]
     o = torch.empty(1, 1, H, D, dtype=torch.bfloat16, device="cuda")
-    ms = _time_cuda(torch, lambda: hk.cuda_recurrent_gated_delta_rule(q, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False), flush=flush)
+    fns = [(lambda st=st: hk.cuda_recurrent_gated_delta_rule(q, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)) for st in sts]
+    ms = _time_loop(torch, fns, flush=flush) / n_kda
     res["kda_decode_us_per_layer"] = ms * 1e3
     res["kda_decode_hbm_gbs"] = (2 * H * D * D * 4 + H * 1538) / (ms * 1e-3) / 1e9
-    # dense MLA decode over a 32K latent cache
-    for B in (1, 8):
-        L = 32768
-        ml = synth.mla_inputs(L * B, B, seed=6)
-        qd, ck = dev_f16(ml["q_lat"]), dev_f16(ml["ckv"])
+    del sts
+    # ---- dense MLA decode over 32K latent caches: 11 layers (B=1), 2 alternating layers (B=8) ----
+    L = 32768
+    for B, n_layers in ((1, 11), (8, 2)):
+        cks = [torch.randn(B * L, 512, dtype=torch.float16, device="cuda") for _ in range(n_layers)]
+        qd = torch.randn(B, 64, 512, dtype=torch.float16, device="cuda")
         base = dev((np.arange(B) * L).astype(np.int64))
         lens = dev(np.full(B, L, dtype=np.int32))
         lo = torch.empty(B, 64, 512, dtype=torch.float16, device="cuda")
         ns = hk.mla_auto_splits(B, L)
         wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, B * 64)), dtype=torch.uint8, device="cuda")
-        ms = _time_cuda(torch, lambda: hk.mla_dense_prefill(qd, ck, lo, B, 0, scale=512 ** -0.5, kv_base=base, kv_len=lens,
-                                                            n_split=ns, workspace=wsb, n_keys_hint=L), flush=flush)
-        res["mla_dense_decode_32k_b%d_us" % B] = ms * 1e3
+        fns = [(lambda ck=ck: hk.mla_dense_prefill(qd, ck, lo, B, 0, scale=512 ** -0.5, kv_base=base, kv_len=lens,
+                                                   n_split=ns, workspace=wsb, n_keys_hint=L)) for ck in cks]
+        ms = _time_loop(torch, fns, flush=flush if B * L * 1024 * n_layers < (200 << 20) else None) / n_layers
+        res["mla_dense_decode_32k_b%d_us_per_layer" % B] = ms * 1e3
         res["mla_dense_decode_32k_b%d_hbm_gbs" % B] = B * L * 1024 / (ms * 1e-3) / 1e9
-    # indexer -> top-512 -> expand -> sparse MLA at 262,144 tokens of context
-    npools, L = 65536, 262144
+        res["mla_dense_decode_32k_b%d_splits" % B] = ns
+        del cks
+    # ---- indexer -> top-512 -> expand -> sparse MLA at 262,144 tokens of context, 11 layers ----
+    npools, L, n_mla = 65536, 262144, 11
     ix = synth.indexer_inputs(npools, 1, seed=7)
-    qi, pk, w = dev_f16(ix["q_idx"]), dev_f16(ix["pool_k"]), dev_f16(ix["w"])
+    qi, w = dev_f16(ix["q_idx"]), dev_f16(ix["w"])
+    pks = [torch.randn(npools, 128, dtype=torch.float16, device="cuda") for _ in range(n_mla)]
+    ckvs = [torch.randn(L, 512, dtype=torch.float16, device="cuda") for _ in range(n_mla)]
     q_pos = dev(np.array([L - 1], dtype=np.int32))
     sc = torch.empty(1, npools, dtype=torch.float16, device="cuda")
     idx = torch.empty(1, 512, dtype=torch.int32, device="cuda")
     raw = torch.empty(1, 2052, dtype=torch.int32, device="cuda")
-    ckv = torch.randn(L, 512, dtype=torch.float16, device="cuda")
     ql = torch.randn(1, 64, 512, dtype=torch.float16, device="cuda")
     lo = torch.empty(1, 64, 512, dtype=torch.float16, device="cuda")
     ns = hk.mla_auto_splits(1, 2052)
     wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=torch.uint8, device="cuda")
-    ms = _time_cuda(torch, lambda: hk.indexer_score(qi, pk, w, q_pos, sc, 1, npools), flush=flush)
-    res["indexer_score_262k_us"] = ms * 1e3
+    f_score = [(lambda pk=pk: hk.indexer_score(qi, pk, w, q_pos, sc, 1, npools)) for pk in pks]
+    ms = _time_loop(torch, f_score, flush=flush) / n_mla
+    res["indexer_score_262k_us_per_layer"] = ms * 1e3
     res["indexer_score_262k_hbm_gbs"] = npools * 256 / (ms * 1e-3) / 1e9
-    res["topk512_262k_us"] = 1e3 * _time_cuda(torch, lambda: hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512), flush=flush)
+    f_topk = [lambda: hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)] * n_mla
+    res["topk512_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_topk, flush=flush) / n_mla
     hk.pool_expand_row(idx, q_pos, raw, 1)
-    ms = _time_cuda(torch, lambda: hk.mla_sparse_decode(ql, ckv, raw, 2052, lo, 1, n_split=ns, workspace=wsb), flush=flush)
-    res["mla_sparse_decode_262k_us"] = ms * 1e3
+    f_sparse = [(lambda ck=ck: hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)) for ck in ckvs]
+    ms = _time_loop(torch, f_sparse, flush=flush) / n_mla
+    res["mla_sparse_decode_262k_us_per_layer"] = ms * 1e3
     res["mla_sparse_decode_262k_hbm_gbs"] = 2052 * 1024 / (ms * 1e-3) / 1e9
+
+    def chain(pk, ck):
+        hk.indexer_score(qi, pk, w, q_pos, sc, 1, npools)
+        hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)
+        hk.pool_expand_row(idx, q_pos, raw, 1)
+        hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
+    f_chain = [(lambda pk=pk, ck=ck: chain(pk, ck)) for pk, ck in zip(pks, ckvs)]
+    res["dsa_sparse_mla_decode_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_chain, flush=flush) / n_mla
     return res
 
 

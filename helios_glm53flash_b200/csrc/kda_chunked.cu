@@ -64,39 +64,54 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 // =================================================================================================
-// kernel 1: per-chunk preparation
+// kernel 1: per-chunk preparation.  256 threads, 104 KB of shared memory: two CTAs per SM, so the
+// serial stages of one chunk overlap with another chunk's.
 // =================================================================================================
-constexpr int P1_LD = 132;                               // padded fp32 row (conflict-free fragments)
-constexpr int P1_LDA = 68;                               // padded row of the 64x64 matrices
-constexpr uint32_t P1_G = 0;                             // f32 [64][132] cumulative log decay
-constexpr uint32_t P1_K = P1_G + KC * P1_LD * 4;         // f32 [64][132] k^
-constexpr uint32_t P1_LK = P1_K + KC * P1_LD * 4;        // tf32 [64][132] k^ e^{G_t - P_blk}
-constexpr uint32_t P1_LQ = P1_LK + KC * P1_LD * 4;       // tf32 [64][132] q^ e^{G_t - P_blk}
-constexpr uint32_t P1_A = P1_LQ + KC * P1_LD * 4;        // f32 [64][68]  A_ts beta_s (strictly lower)
-constexpr uint32_t P1_B = P1_A + KC * P1_LDA * 4;        // f32 [64][68]  B_ts beta_s (lower incl.)
-constexpr uint32_t P1_T = P1_B + KC * P1_LDA * 4;        // fp16 A operand [128 rows][64], 16 KB
-constexpr uint32_t P1_KV = P1_T + 16384;                 // fp16 B operand [64 tokens][256], 32 KB
-constexpr uint32_t P1_P = P1_KV + 32768;                 // f32 [4][128] G before each 16-token block
+constexpr int P1_LD = 132;                               // fp32 row pitch (conflict-free fragment loads)
+constexpr int P1_LDH = 136;                              // 16-bit row pitch of raw k
+constexpr int P1_LDA = 68;                               // fp32 row pitch of the 64x64 matrices
+constexpr uint32_t P1_KP = 0;                            // fp16 K+ = first half of the B operand [K+|V] (16 KB)
+constexpr uint32_t P1_G = 16384;                         // f32 [64][132] cumulative log decay      (later: V half of the B operand)
+constexpr uint32_t P1_KR = P1_G + KC * P1_LD * 4;        // bf16 [64][136] raw k                    (later: X = inverse, f32 [64][68])
+constexpr uint32_t P1_L = P1_KR + KC * P1_LDH * 2;       // tf32 [2][16][132] left operands of ONE 16-row block (later: T operand, 16 KB)
+constexpr uint32_t P1_A = P1_L + 2 * 16 * P1_LD * 4;     // f32 [64][68] N = A beta (strictly lower); upper blocks = scratch
+constexpr uint32_t P1_P = P1_A + KC * P1_LDA * 4;        // f32 [4][128] G before each 16-token block
 constexpr uint32_t P1_EP = P1_P + 2048;                  // f32 [4][128] exp of the above
 constexpr uint32_t P1_BETA = P1_EP + 2048;               // f32 [64]
-constexpr uint32_t P1_SMEM = P1_BETA + 256;
+constexpr uint32_t P1_RK = P1_BETA + 256;                // f32 [64] 1/|k|
+constexpr uint32_t P1_SMEM = P1_RK + 256;
+static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_LDH * 2 == KC * P1_LDA * 4, "aliases");
 
-__global__ __launch_bounds__(256, 1) void kda_chunk_prep_kernel(
+// 16 x 16 block product helper of the blocked triangular inverse: returns sum_k L[r][k] * R[k][c]
+__device__ __forceinline__ float dot16(const float* __restrict__ lrow, const float* __restrict__ rcol) {
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; k += 4) {
+    const float4 l = *reinterpret_cast<const float4*>(lrow + k);
+    a0 = fmaf(l.x, rcol[(k + 0) * P1_LDA], a0);
+    a1 = fmaf(l.y, rcol[(k + 1) * P1_LDA], a1);
+    a0 = fmaf(l.z, rcol[(k + 2) * P1_LDA], a0);
+    a1 = fmaf(l.w, rcol[(k + 3) * P1_LDA], a1);
+  }
+  return a0 + a1;
+}
+
+__global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
     const __nv_bfloat16* __restrict__ beta, uint8_t* __restrict__ ws, int seqlen, int H,
     int n_chunks, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + P1_G);
-  float* sK = reinterpret_cast<float*>(smem + P1_K);
-  float* sLk = reinterpret_cast<float*>(smem + P1_LK);
-  float* sLq = reinterpret_cast<float*>(smem + P1_LQ);
+  uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
+  float* sL = reinterpret_cast<float*>(smem + P1_L);         // [0]: k rows, [1]: q rows of the current block
   float* sA = reinterpret_cast<float*>(smem + P1_A);
-  float* sB = reinterpret_cast<float*>(smem + P1_B);
-  uint8_t* sT = smem + P1_T;
-  uint8_t* sKV = smem + P1_KV;
   float* sP = reinterpret_cast<float*>(smem + P1_P);
   float* sEP = reinterpret_cast<float*>(smem + P1_EP);
   float* sBeta = reinterpret_cast<float*>(smem + P1_BETA);
+  float* sRk = reinterpret_cast<float*>(smem + P1_RK);
+  uint8_t* sKV = smem + P1_KP;                             // [K+ | V]; the V half aliases sG, valid after the A/B stage
+  float* sX = reinterpret_cast<float*>(smem + P1_KR);      // alias, valid after the A/B stage
+  uint8_t* sT = smem + P1_L;                               // alias, valid after the A/B stage
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -117,46 +132,54 @@ __global__ __launch_bounds__(256, 1) void kda_chunk_prep_kernel(
   }
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
 
-  // ---- stage 1: load a token per warp-iteration; lane owns channels 4*lane .. 4*lane+3 ----
-  for (int t = warp; t < KC; t += 8) {
-    float kf[4] = {0.f, 0.f, 0.f, 0.f}, qf[4] = {0.f, 0.f, 0.f, 0.f}, vf[4] = {0.f, 0.f, 0.f, 0.f};
-    float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+  // ---- stage 1: all loads of the chunk in flight at once.  Warp w owns tokens w, w+8, ...; lane owns
+  //      channels 4*lane .. 4*lane+3.  g goes straight to shared memory, q and k stay in registers.
+  float qv[8][4], kv[8][4], rq[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int t = warp + 8 * i;
+    uint2 qr = make_uint2(0, 0), kr = make_uint2(0, 0);
+    float* gdst = sG + t * P1_LD + lane * 4;
     if (t < n_valid) {
       const __nv_bfloat16* tk = tok0 + (size_t)t * row;
-      const uint2 qr = *reinterpret_cast<const uint2*>(tk + (size_t)head * KD + lane * 4);
-      const uint2 kr = *reinterpret_cast<const uint2*>(tk + (size_t)(H + head) * KD + lane * 4);
-      const uint2 vr = *reinterpret_cast<const uint2*>(tk + (size_t)(2 * H + head) * KD + lane * 4);
-      qf[0] = bf16lo(qr.x); qf[1] = bf16hi(qr.x); qf[2] = bf16lo(qr.y); qf[3] = bf16hi(qr.y);
-      kf[0] = bf16lo(kr.x); kf[1] = bf16hi(kr.x); kf[2] = bf16lo(kr.y); kf[3] = bf16hi(kr.y);
-      vf[0] = bf16lo(vr.x); vf[1] = bf16hi(vr.x); vf[2] = bf16lo(vr.y); vf[3] = bf16hi(vr.y);
-      gv = *reinterpret_cast<const float4*>(g0 + (size_t)t * H * KD + lane * 4);
+      qr = *reinterpret_cast<const uint2*>(tk + (size_t)head * KD + lane * 4);
+      kr = *reinterpret_cast<const uint2*>(tk + (size_t)(H + head) * KD + lane * 4);
+      __pipeline_memcpy_async(gdst, g0 + (size_t)t * H * KD + lane * 4, 16);
+    } else {
+      *reinterpret_cast<float4*>(gdst) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float sq = warp_sum(qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3]);
-    const float sk = warp_sum(kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3]);
-    const float rq = rsqrtf(sq + 1e-6f), rk = rsqrtf(sk + 1e-6f);
-    *reinterpret_cast<float4*>(sK + t * P1_LD + lane * 4) = make_float4(kf[0] * rk, kf[1] * rk, kf[2] * rk, kf[3] * rk);
-    *reinterpret_cast<float4*>(sLq + t * P1_LD + lane * 4) = make_float4(qf[0] * rq, qf[1] * rq, qf[2] * rq, qf[3] * rq);
-    *reinterpret_cast<float4*>(sG + t * P1_LD + lane * 4) = gv;
-    // V -> B operand columns 128..255 (MN-major: off = (n/8)*1024 + (t/8)*128 + (t%8)*16 + (n%8)*2)
-    const int n = KD + lane * 4;
-    uint2 pv;
-    pv.x = pack_h2(vf[0], vf[1]);
-    pv.y = pack_h2(vf[2], vf[3]);
-    *reinterpret_cast<uint2*>(sKV + (n >> 3) * 1024 + (t >> 3) * 128 + (t & 7) * 16 + (n & 7) * 2) = pv;
+    qv[i][0] = bf16lo(qr.x); qv[i][1] = bf16hi(qr.x); qv[i][2] = bf16lo(qr.y); qv[i][3] = bf16hi(qr.y);
+    kv[i][0] = bf16lo(kr.x); kv[i][1] = bf16hi(kr.x); kv[i][2] = bf16lo(kr.y); kv[i][3] = bf16hi(kr.y);
+    *reinterpret_cast<uint2*>(sKr + t * P1_LDH + lane * 4) = kr;
+  }
+  __pipeline_commit();
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const float sq = warp_sum(qv[i][0] * qv[i][0] + qv[i][1] * qv[i][1] + qv[i][2] * qv[i][2] + qv[i][3] * qv[i][3]);
+    const float sk = warp_sum(kv[i][0] * kv[i][0] + kv[i][1] * kv[i][1] + kv[i][2] * kv[i][2] + kv[i][3] * kv[i][3]);
+    rq[i] = rsqrtf(sq + 1e-6f);
+    const float rk = rsqrtf(sk + 1e-6f);
+#pragma unroll
+    for (int u = 0; u < 4; u++) kv[i][u] *= rk;
+    if (lane == 0) sRk[warp + 8 * i] = rk;
   }
   if (tid < KC) sBeta[tid] = tid < n_valid ? __bfloat162float(beta[((size_t)b * seqlen + t0 + tid) * H + head]) : 0.f;
-  for (int i = tid; i < KC * P1_LDA; i += 256) {
-    sA[i] = 0.f;
-    sB[i] = 0.f;
+  for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
+  // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
+  if (tid < 192) {
+    const int blk = tid >> 5, e = tid & 31;             // 6 blocks x (16 rows x 2 chunks)
+    const int ib = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+    const int jb = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+    const int t = ib * 16 + (e >> 1), sc = jb * 2 + (e & 1);
+    *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
   }
-  // rows 64..127 of the T operand are never produced: keep them zero so the unused TMEM lanes stay finite
-  for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
+  __pipeline_wait_prior(0);
   __syncthreads();
 
   // ---- stage 2: inclusive cumulative log decay per channel; block bases P and e^P; chunk decay ----
   if (tid < KD) {
     float acc = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int t = 0; t < KC; t++) {
       if ((t & 15) == 0) {
         sP[(t >> 4) * KD + tid] = acc;
@@ -169,28 +192,7 @@ __global__ __launch_bounds__(256, 1) void kda_chunk_prep_kernel(
   }
   __syncthreads();
 
-  // ---- stage 3: left operands (tf32) with the exponent re-based to the start of the row's block;
-  //      K+ into the B operand, Q+ and Kt^T straight to the workspace ----
-  for (int i = tid; i < KC * (KD / 8); i += 256) {
-    const int t = i >> 4, cc = i & 15, c0 = cc * 8, blk = t >> 4;
-    float kp[8], qp[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int c = c0 + u;
-      const float f = __expf(sG[t * P1_LD + c] - sP[blk * KD + c]);
-      const float lk = sK[t * P1_LD + c] * f, lq = sLq[t * P1_LD + c] * f;
-      sLk[t * P1_LD + c] = __uint_as_float(f2tf32(lk));
-      sLq[t * P1_LD + c] = __uint_as_float(f2tf32(lq));
-      const float ep = sEP[blk * KD + c];
-      kp[u] = lk * ep;
-      qp[u] = lq * ep;
-    }
-    uint4 pk, pq;
-    pk.x = pack_h2(kp[0], kp[1]); pk.y = pack_h2(kp[2], kp[3]); pk.z = pack_h2(kp[4], kp[5]); pk.w = pack_h2(kp[6], kp[7]);
-    pq.x = pack_h2(qp[0], qp[1]); pq.y = pack_h2(qp[2], qp[3]); pq.z = pack_h2(qp[4], qp[5]); pq.w = pack_h2(qp[6], qp[7]);
-    *reinterpret_cast<uint4*>(sKV + cc * 1024 + (t >> 3) * 128 + (t & 7) * 16) = pk;
-    *reinterpret_cast<uint4*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + cc * LBO + (t & 7) * 16) = pq;
-  }
+  // ---- stage 3: Kt^T tile (rows = channels, K = tokens) straight to the workspace ----
   for (int i = tid; i < KD * (KC / 8); i += 256) {
     const int c = i & 127, tg = i >> 7;
     const float glast = sG[(KC - 1) * P1_LD + c];
@@ -198,99 +200,151 @@ __global__ __launch_bounds__(256, 1) void kda_chunk_prep_kernel(
 #pragma unroll
     for (int u = 0; u < 8; u++) {
       const int t = tg * 8 + u;
-      kt[u] = sBeta[t] * sK[t * P1_LD + c] * __expf(glast - sG[t * P1_LD + c]);
+      kt[u] = sBeta[t] * sRk[t] * bf16_bits_to_f(sKr[t * P1_LDH + c]) * __expf(glast - sG[t * P1_LD + c]);
     }
     uint4 p;
     p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
     *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
   }
-  __syncthreads();
 
-  // ---- stage 4: A and B on the warp-level tensor cores (TF32), one (row block, column block) pair
-  //      of 16x16 per warp-iteration; right operand k^_s e^{P_rowblk - G_s} is formed on the fly ----
+  // ---- stage 4: A and B on the warp-level tensor cores (TF32), one 16-token ROW block at a time.
+  //      Left operands k^,q^ * e^{G_t - P_ib} of the block come from the registers (fp32 range is
+  //      needed: the factor spans e^{-80}..1); right operand k^_s e^{P_ib - G_s} is formed on the fly.
+  //      The same pass emits K+ = k^ e^{G_t} (shared memory) and Q+ = q^ e^{G_t} (workspace). ----
   {
     const int gq = lane >> 2, tig = lane & 3;
-    for (int pair = warp; pair < 10; pair += 8) {
-      // pairs ordered by decreasing work locality: (3,3)(3,2)(3,1)(3,0)(2,2)(2,1)(2,0)(1,1)(1,0)(0,0)
-      int ib, jb;
-      if (pair < 4) { ib = 3; jb = 3 - pair; }
-      else if (pair < 7) { ib = 2; jb = 6 - pair; }
-      else if (pair < 9) { ib = 1; jb = 8 - pair; }
-      else { ib = 0; jb = 0; }
-      float acc[2][2][4];
 #pragma unroll
-      for (int x = 0; x < 2; x++)
+    for (int ib = 0; ib < 4; ib++) {
 #pragma unroll
-        for (int y = 0; y < 2; y++)
+      for (int half = 0; half < 2; half++) {
+        const int i = 2 * ib + half, t = warp + 8 * i, lr = t - 16 * ib;
+        const float4 gt = *reinterpret_cast<const float4*>(sG + t * P1_LD + lane * 4);
+        const float4 pb = *reinterpret_cast<const float4*>(sP + ib * KD + lane * 4);
+        const float4 ep = *reinterpret_cast<const float4*>(sEP + ib * KD + lane * 4);
+        const float f0 = __expf(gt.x - pb.x), f1 = __expf(gt.y - pb.y), f2 = __expf(gt.z - pb.z), f3 = __expf(gt.w - pb.w);
+        const float k0 = kv[i][0] * f0, k1 = kv[i][1] * f1, k2 = kv[i][2] * f2, k3 = kv[i][3] * f3;
+        const float q0 = qv[i][0] * rq[i] * f0, q1 = qv[i][1] * rq[i] * f1, q2 = qv[i][2] * rq[i] * f2, q3 = qv[i][3] * rq[i] * f3;
+        *reinterpret_cast<uint4*>(sL + lr * P1_LD + lane * 4) = make_uint4(f2tf32(k0), f2tf32(k1), f2tf32(k2), f2tf32(k3));
+        *reinterpret_cast<uint4*>(sL + (16 + lr) * P1_LD + lane * 4) = make_uint4(f2tf32(q0), f2tf32(q1), f2tf32(q2), f2tf32(q3));
+        // chunk-start based copies: 4 channels = half of a 16-byte operand chunk
+        const int c = lane * 4;
+        uint2 kp, qp;
+        kp.x = pack_h2(k0 * ep.x, k1 * ep.y); kp.y = pack_h2(k2 * ep.z, k3 * ep.w);
+        qp.x = pack_h2(q0 * ep.x, q1 * ep.y); qp.y = pack_h2(q2 * ep.z, q3 * ep.w);
+        *reinterpret_cast<uint2*>(sKV + (c >> 3) * 1024 + (t >> 3) * 128 + (t & 7) * 16 + (c & 7) * 2) = kp;
+        *reinterpret_cast<uint2*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (c >> 3) * LBO + (t & 7) * 16 + (c & 7) * 2) = qp;
+      }
+      __syncthreads();
+      // units of this row block: (column block jb <= ib, 8-column half nt)
+      for (int unit_i = warp; unit_i < 2 * (ib + 1); unit_i += 8) {
+        const int jb = unit_i >> 1, nt = unit_i & 1;
+        float acck[4] = {0.f, 0.f, 0.f, 0.f}, accq[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* lk0 = sL + gq * P1_LD;
+        const float* lq0 = sL + (16 + gq) * P1_LD;
+        const float* pb = sP + ib * KD;
+        const int s = jb * 16 + nt * 8 + gq;
+        const float rks = sRk[s];
+        const uint16_t* krow = sKr + s * P1_LDH;
+        const float* grow = sG + s * P1_LD;
+#pragma unroll 4
+        for (int ks = 0; ks < KD / 8; ks++) {
+          const int c = ks * 8 + tig;
+          uint32_t ak[4], aq[4];
+          ak[0] = __float_as_uint(lk0[c]); ak[1] = __float_as_uint(lk0[8 * P1_LD + c]);
+          ak[2] = __float_as_uint(lk0[c + 4]); ak[3] = __float_as_uint(lk0[8 * P1_LD + c + 4]);
+          aq[0] = __float_as_uint(lq0[c]); aq[1] = __float_as_uint(lq0[8 * P1_LD + c]);
+          aq[2] = __float_as_uint(lq0[c + 4]); aq[3] = __float_as_uint(lq0[8 * P1_LD + c + 4]);
+          const uint32_t b0 = f2tf32(bf16_bits_to_f(krow[c]) * rks * __expf(pb[c] - grow[c]));
+          const uint32_t b1 = f2tf32(bf16_bits_to_f(krow[c + 4]) * rks * __expf(pb[c + 4] - grow[c + 4]));
+          mma_tf32(acck, ak, b0, b1);
+          mma_tf32(accq, aq, b0, b1);
+        }
+        // fragment: rows t = 16 ib + gq (+8), columns s = 16 jb + 8 nt + 2 tig (+1)
+        const int s0 = jb * 16 + nt * 8 + tig * 2;
+        const float b0 = sBeta[s0], b1 = sBeta[s0 + 1];
 #pragma unroll
-          for (int z = 0; z < 4; z++) acc[x][y][z] = 0.f;
-      const float* lk0 = sLk + (ib * 16 + gq) * P1_LD;
-      const float* lq0 = sLq + (ib * 16 + gq) * P1_LD;
-      const float* pb = sP + ib * KD;
-#pragma unroll 2
-      for (int ks = 0; ks < KD / 8; ks++) {
-        const int c = ks * 8 + tig;
-        uint32_t ak[4], aq[4];
-        ak[0] = __float_as_uint(lk0[c]); ak[1] = __float_as_uint(lk0[8 * P1_LD + c]);
-        ak[2] = __float_as_uint(lk0[c + 4]); ak[3] = __float_as_uint(lk0[8 * P1_LD + c + 4]);
-        aq[0] = __float_as_uint(lq0[c]); aq[1] = __float_as_uint(lq0[8 * P1_LD + c]);
-        aq[2] = __float_as_uint(lq0[c + 4]); aq[3] = __float_as_uint(lq0[8 * P1_LD + c + 4]);
-        const float p0 = pb[c], p1 = pb[c + 4];
-#pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-          const int s = jb * 16 + nt * 8 + gq;
-          const uint32_t b0 = f2tf32(sK[s * P1_LD + c] * __expf(p0 - sG[s * P1_LD + c]));
-          const uint32_t b1 = f2tf32(sK[s * P1_LD + c + 4] * __expf(p1 - sG[s * P1_LD + c + 4]));
-          mma_tf32(acc[0][nt], ak, b0, b1);
-          mma_tf32(acc[1][nt], aq, b0, b1);
+        for (int hrow = 0; hrow < 2; hrow++) {
+          const int t = ib * 16 + gq + hrow * 8;
+          if (s0 < t) sA[t * P1_LDA + s0] = acck[2 * hrow] * b0;
+          if (s0 + 1 < t) sA[t * P1_LDA + s0 + 1] = acck[2 * hrow + 1] * b1;
+          const float v0 = s0 <= t ? accq[2 * hrow] * b0 : 0.f;
+          const float v1 = s0 + 1 <= t ? accq[2 * hrow + 1] * b1 : 0.f;
+          *reinterpret_cast<uint32_t*>(unit + U_BB + (t >> 3) * SBO_K64 + (s0 >> 3) * LBO + (t & 7) * 16 + (s0 & 7) * 2) =
+              pack_h2(v0, v1);
         }
       }
-#pragma unroll
-      for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-        for (int z = 0; z < 4; z++) {
-          const int t = ib * 16 + gq + ((z & 2) ? 8 : 0);
-          const int s = jb * 16 + nt * 8 + tig * 2 + (z & 1);
-          const float bs = sBeta[s];
-          if (s < t) sA[t * P1_LDA + s] = acc[0][nt][z] * bs;
-          if (s <= t) sB[t * P1_LDA + s] = acc[1][nt][z] * bs;
-        }
+      __syncthreads();
     }
   }
-  __syncthreads();
+  // from here on sG, sKr and sL are dead: the V half of sKV, sX and sT take their place
 
-  // ---- stage 5: warps 0-1 invert (I + A beta) by forward substitution, one column per thread, fp32;
-  //      the other warps ship B beta to the workspace meanwhile ----
-  if (tid < KC) {
-    const int j = tid;
-    float x[KC];
-#pragma unroll
-    for (int t = 0; t < KC; t++) {
-      float a0 = (t == j) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      const float4* nrow = reinterpret_cast<const float4*>(sA + t * P1_LDA);
-#pragma unroll
-      for (int s4 = 0; s4 < (t + 3) / 4; s4++) {
-        const float4 nv = nrow[s4];
-        if (s4 * 4 + 0 < t) a0 = fmaf(-nv.x, x[s4 * 4 + 0], a0);
-        if (s4 * 4 + 1 < t) a1 = fmaf(-nv.y, x[s4 * 4 + 1], a1);
-        if (s4 * 4 + 2 < t) a2 = fmaf(-nv.z, x[s4 * 4 + 2], a2);
-        if (s4 * 4 + 3 < t) a3 = fmaf(-nv.w, x[s4 * 4 + 3], a3);
-      }
-      x[t] = (a0 + a1) + (a2 + a3);
-    }
-    // T[t][j] into the A operand (K-major, K = 64): off = (t/8)*1024 + (j/8)*128 + (t%8)*16 + (j%8)*2
-    __half* tcol = reinterpret_cast<__half*>(sT + (j >> 3) * LBO + (j & 7) * 2);
-#pragma unroll
-    for (int t = 0; t < KC; t++) tcol[((t >> 3) * SBO_K64 + (t & 7) * 16) / 2] = __float2half_rn(x[t]);
-  } else {
-    for (int i = tid - KC; i < KC * (KC / 8); i += 256 - KC) {
-      const int t = i >> 3, sc = i & 7;
-      const float4 v0 = *reinterpret_cast<const float4*>(sB + t * P1_LDA + sc * 8);
-      const float4 v1 = *reinterpret_cast<const float4*>(sB + t * P1_LDA + sc * 8 + 4);
+  // ---- stage 5: V -> B operand columns 128..255, then the blocked
+  //      inverse X = (I + N)^-1 in fp32 and its fp16 copy T as the A operand ----
+  for (int i = tid; i < KC * (KD / 8); i += 256) {
+    const int t = (i & 7) + ((i >> 7) << 3), cc = (i >> 3) & 15;
+    uint8_t* dst = sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16;
+    if (t < n_valid) {
+      // bf16 -> fp16 needs a register pass: load, convert, store
+      const uint4 vr = *reinterpret_cast<const uint4*>(tok0 + (size_t)t * row + (size_t)(2 * H + head) * KD + cc * 8);
       uint4 p;
-      p.x = pack_h2(v0.x, v0.y); p.y = pack_h2(v0.z, v0.w); p.z = pack_h2(v1.x, v1.y); p.w = pack_h2(v1.z, v1.w);
-      *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = p;
+      p.x = pack_h2(bf16lo(vr.x), bf16hi(vr.x)); p.y = pack_h2(bf16lo(vr.y), bf16hi(vr.y));
+      p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
+      *reinterpret_cast<uint4*>(dst) = p;
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
+  }
+  // rows 64..127 of the T operand are never produced: zero, so the unused TMEM lanes stay finite
+  for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < KC * P1_LDA; i += 256) sX[i] = 0.f;
+  __syncthreads();
+  // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
+  if (warp < 4 && lane < 16) {
+    const int ib = warp;
+    float x[16];
+#pragma unroll
+    for (int r = 0; r < 16; r++) {
+      float a0 = (r == lane) ? 1.f : 0.f, a1 = 0.f;
+      const float* nrow = sA + (ib * 16 + r) * P1_LDA + ib * 16;
+#pragma unroll
+      for (int s = 0; s < r; s++) {
+        if (s & 1) a1 = fmaf(-nrow[s], x[s], a1);
+        else a0 = fmaf(-nrow[s], x[s], a0);
+      }
+      x[r] = a0 + a1;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; r++) sX[(ib * 16 + r) * P1_LDA + ib * 16 + lane] = x[r];
+  }
+  __syncthreads();
+  // 5b: off-diagonal blocks by distance d: Y_ij = sum_{m=j}^{i-1} N_im X_mj (kept in the unused
+  //     mirror block (j,i) of sA), then X_ij = -X_ii Y_ij
+#pragma unroll 1
+  for (int d = 1; d < 4; d++) {
+    const int nb = 4 - d;                                 // blocks (i, i-d), i = d..3
+    for (int o = tid; o < nb * 256; o += 256) {
+      const int i = d + (o >> 8), j = i - d, r = (o >> 4) & 15, c = o & 15;
+      float acc = 0.f;
+      for (int m = j; m < i; m++)
+        acc += dot16(sA + (i * 16 + r) * P1_LDA + m * 16, sX + (m * 16) * P1_LDA + j * 16 + c);
+      sA[(j * 16 + r) * P1_LDA + i * 16 + c] = acc;       // mirror block as scratch
+    }
+    __syncthreads();
+    for (int o = tid; o < nb * 256; o += 256) {
+      const int i = d + (o >> 8), j = i - d, r = (o >> 4) & 15, c = o & 15;
+      const float v = dot16(sX + (i * 16 + r) * P1_LDA + i * 16, sA + (j * 16) * P1_LDA + i * 16 + c);
+      sX[(i * 16 + r) * P1_LDA + j * 16 + c] = -v;
+    }
+    __syncthreads();
+  }
+  // 5c: T = fp16(X) as the K-major A operand (K = 64): lanes = 8 rows x 4 chunks
+  for (int i = tid; i < KC * (KC / 8); i += 256) {
+    const int t = (i & 7) + ((i >> 6) << 3), jc = (i >> 3) & 7;
+    const float4 v0 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8);
+    const float4 v1 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8 + 4);
+    uint4 p;
+    p.x = pack_h2(v0.x, v0.y); p.y = pack_h2(v0.z, v0.w); p.z = pack_h2(v1.x, v1.y); p.w = pack_h2(v1.z, v1.w);
+    *reinterpret_cast<uint4*>(sT + (t >> 3) * SBO_K64 + jc * LBO + (t & 7) * 16) = p;
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -578,7 +632,7 @@ HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const v
   using namespace hk;
   HK_REQUIRE(mixed_qkv && g && beta && state && out && workspace);
   HK_REQUIRE(bsz > 0 && seqlen > 0 && num_heads > 0);
-  HK_REQUIRE(aligned(mixed_qkv, 8) && aligned(g, 16) && aligned(state, 16) && aligned(out, 16) &&
+  HK_REQUIRE(aligned(mixed_qkv, 16) && aligned(g, 16) && aligned(state, 16) && aligned(out, 16) &&
              aligned(workspace, 256) && (!out_f32 || aligned(out_f32, 16)));
   if (workspace_bytes < hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)) return HK_ERR_WORKSPACE;
   const int n_chunks = (seqlen + KC - 1) / KC;

@@ -1,0 +1,156 @@
+"""Per-kernel micro-benchmarks of libhelios_b200 on synthetic inputs.
+
+    python -m helios_glm53flash_b200.microbench --case mla_dense_b8 [--iters 20] [--warmup 3]
+
+Each case times one entry point with CUDA events on the current stream (median of --iters, L2 flushed
+by a 256 MB write between iterations unless the working set exceeds L2 by itself) and prints one JSON
+line with the time and the achieved algorithmic bandwidth.  The cases are small enough to be captured
+under a profiler (a few hundred MB on the device).
+"""
+import argparse
+import json
+
+import numpy as np
+
+
+def _bits16(t, dtype):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(t).view(np.int16)).view(dtype).cuda()
+
+
+def build_case(name):
+    """returns (callable, algorithmic_bytes, needs_flush, description)"""
+    import torch
+    import helios_glm53flash_b200 as hk
+    from helios_glm53flash_b200 import synth
+    H, D = 32, 128
+    if name in ("kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512"):
+        T = {"kda_prefill_8k": 8192, "kda_prefill_32k": 32768, "kda_recurrent_512": 512}[name]
+        gates = synth.kda_gates(T, H, D, seed=1)
+        g, beta = torch.from_numpy(gates["g"]).cuda(), _bits16(gates["beta"], torch.bfloat16)
+        qkv = torch.randn(1, T, 3 * H * D, device="cuda").to(torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(hk.kda_chunked_workspace_bytes(1, T, H), dtype=torch.uint8, device="cuda")
+        force = name == "kda_recurrent_512"
+
+        def fn():
+            hk.cuda_recurrent_gated_delta_rule(qkv, g, beta, st, out, 1, T, H, H, D, D, 1, None, True, False,
+                                               workspace=ws, force_recurrent=force)
+        return fn, T * H * 1538 + 2 * H * D * D * 4, T < 8192, "KDA prefill T=%d H=32 (chunked unless 'recurrent')" % T
+    if name in ("conv_8k", "conv_32k"):
+        T = 8192 if name == "conv_8k" else 32768
+        dim = 3 * H * D
+        x = torch.randn(1, dim, T, device="cuda").to(torch.bfloat16)
+        w = (0.1 * torch.randn(dim, 4, device="cuda")).to(torch.bfloat16)
+        st = torch.zeros(1, dim, 4, dtype=torch.bfloat16, device="cuda")
+        out = torch.empty(1, T, dim, dtype=torch.bfloat16, device="cuda")
+
+        def fn():
+            hk.cuda_causal_conv1d_update(x, st, None, w, None, out, 1, dim, T, 4, 4, True, False)
+        return fn, 4 * dim * T, False, "short conv + SiLU, 12288 channels x %d tokens" % T
+    if name == "kda_decode":
+        kd = synth.kda_inputs(1, H, D, seed=5)
+        q, g, b = _bits16(kd["mixed_qkv"], torch.bfloat16), torch.from_numpy(kd["g"]).cuda(), _bits16(kd["beta"], torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        o = torch.empty(1, 1, H, D, dtype=torch.bfloat16, device="cuda")
+
+        def fn():
+            hk.cuda_recurrent_gated_delta_rule(q, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)
+        return fn, 2 * H * D * D * 4 + H * 1538, True, "KDA decode step, 32 heads"
+    if name in ("mla_dense_b1", "mla_dense_b8", "mla_dense_b1_simt"):
+        B = 8 if name == "mla_dense_b8" else 1
+        L = 32768
+        ck = torch.randn(B * L, 512, dtype=torch.float16, device="cuda")
+        qd = torch.randn(B, 64, 512, dtype=torch.float16, device="cuda")
+        base = torch.from_numpy((np.arange(B) * L).astype(np.int64)).cuda()
+        lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        lo = torch.empty(B, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(B, L)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, B * 64)), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.mla_dense_prefill(qd, ck, lo, B, 0, scale=512 ** -0.5, kv_base=base, kv_len=lens, n_split=ns,
+                                 workspace=wsb, n_keys_hint=L)
+        return fn, B * L * 1024, B == 1, "dense MLA decode, batch %d x 32768 latents, %d splits" % (B, ns)
+    if name == "mla_prefill_256":
+        qlen, pos = 256, 32768
+        ck = torch.randn(pos + qlen, 512, dtype=torch.float16, device="cuda")
+        qd = torch.randn(qlen, 64, 512, dtype=torch.float16, device="cuda")
+        lo = torch.empty(qlen, 64, 512, dtype=torch.float16, device="cuda")
+
+        def fn():
+            hk.mla_dense_prefill(qd, ck, lo, qlen, pos, scale=512 ** -0.5, n_split=1)
+        return fn, (pos + qlen) * 1024 + 2 * qlen * 65536, True, "dense causal MLA prefill, 256 rows after 32768"
+    if name in ("indexer_262k", "indexer_prefill_256"):
+        npools = 65536
+        m = 1 if name == "indexer_262k" else 256
+        ix = synth.indexer_inputs(npools, m, seed=7)
+        qi, pk, w = _bits16(ix["q_idx"], torch.float16), _bits16(ix["pool_k"], torch.float16), _bits16(ix["w"], torch.float16)
+        q_pos = torch.full((m,), 4 * npools - 1, dtype=torch.int32, device="cuda")
+        sc = torch.empty(m, npools, dtype=torch.float16, device="cuda")
+
+        def fn():
+            hk.indexer_score(qi, pk, w, q_pos, sc, m, npools)
+        return fn, npools * 256 + m * npools * 2, True, "indexer scores, %d rows x 65536 pools" % m
+    if name == "topk_262k":
+        npools = 65536
+        sc = torch.randn(1, npools, device="cuda").half()
+        idx = torch.empty(1, 512, dtype=torch.int32, device="cuda")
+
+        def fn():
+            hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)
+        return fn, npools * 2, True, "top-512 of 65536 fp16 scores, one row"
+    if name == "sparse_262k":
+        L = 262144
+        ck = torch.randn(L, 512, dtype=torch.float16, device="cuda")
+        ql = torch.randn(1, 64, 512, dtype=torch.float16, device="cuda")
+        raw = torch.randint(0, L, (1, 2052), dtype=torch.int32, device="cuda")
+        lo = torch.empty(1, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(1, 2052)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
+        return fn, 2052 * 1024, True, "sparse MLA decode, 2052 gathered latents of 262144, %d splits" % ns
+    raise SystemExit("unknown case " + name)
+
+
+CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, help="one of: " + ", ".join(CASES) + ", or 'all'")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    import torch
+    import helios_glm53flash_b200 as hk
+    for name in (CASES if args.case == "all" else [args.case]):
+        fn, nbytes, flush, desc = build_case(name)
+        buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.iters):
+            if buf is not None:
+                buf.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        ms = ts[len(ts) // 2]
+        print(json.dumps({"case": name, "desc": desc, "us": ms * 1e3, "algorithmic_GBps": nbytes / (ms * 1e-3) / 1e9,
+                          "device_status": hk.read_device_status()}), flush=True)
+        del fn, buf
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
