@@ -38,6 +38,8 @@ SIGNATURES = {
     "hk_mla_partial_bytes": (_sz, [_i, _i64]),
     "hk_mla_auto_splits": (_i, [_i, _i]),
     "hk_mla_sparse": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "hk_mla_sparse_static_max_slots": (_sz, []),
+    "hk_mla_sparse_static": (_i, [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _vp]),
     "hk_mla_dense": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
     "hk_mla_dense_partial": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
@@ -217,6 +219,15 @@ def mla_sparse_decode(q_lat, ckv, raw_idx, kidx, lat_out, m, stream=None, scale=
         ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device)
     _call("hk_mla_sparse", _ptr(q_lat), _ptr(ckv), _ptr(raw_idx), kidx, _ptr(lat_out), m, n_heads,
           float(scale), n_split, _ptr(ws), 0 if ws is None else ws.numel(), _stream(stream))
+
+
+def mla_sparse_decode_static(q_lat, ckv, raw_idx, kidx, lat_out, m, stream=None, scale=0.0625, n_split=0):
+    """Sparse MLA decode for callers that cannot allocate: same result as mla_sparse_decode, but the
+    split partials use the library's built-in ~8 MiB device array (n_split * m <= 64), so neither
+    this wrapper nor the library allocates anything.  Calls on one device share that array: do not
+    let two of them overlap on the GPU."""
+    _call("hk_mla_sparse_static", _ptr(q_lat), _ptr(ckv), _ptr(raw_idx), kidx, _ptr(lat_out), m, float(scale),
+          n_split, _stream(stream))
 
 
 def mla_dense_prefill(q_lat, ckv, lat_out, qlen, pos_start, stream=None, scale=0.0625, n_heads=64,

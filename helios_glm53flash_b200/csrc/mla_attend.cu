@@ -126,6 +126,75 @@ HK_API int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx,
   return attend(a, kidx, n_split, workspace, workspace_bytes, as_stream(stream));
 }
 
+// ---------------------------------------------------------------------------------------------
+// Sparse MLA decode for callers that cannot allocate device memory.
+//
+// Some hosts of this library own all of their device memory up front and have nothing to hand out
+// at call time: the Helios engine carves every buffer out of one bump allocator at start-up and
+// its launcher signatures carry no workspace pointer, and code running under a memory-pool policy
+// or inside a region where the CUDA allocator must not be entered has the same problem.  For them
+// the split-KV partials of this entry point live in a fixed array in the library's own device
+// image: every GPU that loads the library holds these HK_STATIC_SCRATCH_BYTES (about 8 MiB) until
+// the process exits, whether or not the function is ever called.
+//
+// In host code the array's name is only a handle, not a device address, so it must never be
+// passed to a kernel; the address is obtained once per device with cudaGetSymbolAddress while that
+// device is current.  The first call on a device does this set-up: make that first call outside
+// any stream capture.  All calls on a device share the one array and it keeps whatever the last
+// call left in it; nothing in it needs to start at zero because every launch rewrites every
+// (m, l, acc) slot it later reads, but two calls that overlap on the GPU (different streams,
+// no ordering between them) would overwrite each other's partials: order them.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t HK_STATIC_MAX_SLOTS = 64;   // n_split * m must not exceed this
+constexpr size_t HK_STATIC_SCRATCH_BYTES = 2 * ((HK_STATIC_MAX_SLOTS * 64 * sizeof(float) + 255) / 256 * 256) +
+                                           HK_STATIC_MAX_SLOTS * 64 * hk::LATENT * sizeof(float);
+static __device__ __align__(256) unsigned char hk_static_scratch[HK_STATIC_SCRATCH_BYTES];
+
+static void* static_scratch_address(int* status) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *status = HK_ERR_CUDA;
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, hk_static_scratch) != cudaSuccess || !p) {
+      *status = HK_ERR_CUDA;
+      return nullptr;
+    }
+    cached[dev] = p;
+  }
+  *status = HK_OK;
+  return cached[dev];
+}
+
+HK_API size_t hk_mla_sparse_static_max_slots(void) { return HK_STATIC_MAX_SLOTS; }
+
+HK_API int hk_mla_sparse_static(const void* q_lat, const void* ckv, const int* raw_idx, int kidx,
+                                void* lat_out, int m, float scale, int n_split, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv && raw_idx && lat_out && m >= 0 && kidx >= 0);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(lat_out, 16));
+  if (m == 0) return HK_OK;
+  if ((size_t)m > HK_STATIC_MAX_SLOTS) return HK_ERR_WORKSPACE;  // beyond the built-in scratch: use hk_mla_sparse
+  if (n_split <= 0) {
+    n_split = force_simt() ? simt_auto_splits(m, 64, kidx) : mla_flash_tc_auto_splits(m, kidx);
+    const int cap = (int)(HK_STATIC_MAX_SLOTS / (size_t)m);
+    if (n_split > cap) n_split = cap;
+  }
+  if ((size_t)n_split * (size_t)m > HK_STATIC_MAX_SLOTS) return HK_ERR_WORKSPACE;
+  int st = HK_OK;
+  void* scratch = static_scratch_address(&st);
+  if (st != HK_OK) return st;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.raw_idx = raw_idx; a.kidx = kidx;
+  a.m = m; a.n_heads = 64; a.scale = scale;
+  a.out = (__half*)lat_out;
+  return attend(a, kidx, n_split, scratch, HK_STATIC_SCRATCH_BYTES, as_stream(stream));
+}
+
 HK_API int hk_mla_dense(const void* q_lat, const void* ckv, const int64_t* kv_base,
                         const int* kv_len, int pos_start, void* lat_out, int m, int n_heads,
                         float scale, int n_split, void* workspace, size_t workspace_bytes,

@@ -141,6 +141,20 @@ int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx, int ki
                   int m, int n_heads, float scale, int n_split, void* workspace,
                   size_t workspace_bytes, void* stream);
 
+/* Sparse MLA decode that allocates nothing and takes no workspace: the split partials live in a
+ * fixed ~8 MiB array inside the library's device image (held by every GPU that loads the library
+ * until exit).  For hosts that cannot call an allocator at this point - an engine that owns all
+ * device memory through its own start-up arena and whose launcher signatures have no scratch
+ * argument, or code that must not enter the CUDA allocator.  It has no counterpart in the reference.
+ * Same arguments and result as hk_mla_sparse with n_heads = 64.  Limit: n_split * m <= 64
+ * (hk_mla_sparse_static_max_slots()); larger requests return HK_ERR_WORKSPACE - use hk_mla_sparse
+ * with caller memory instead.  n_split = 0 picks a split count that fits.  The first call on a
+ * device looks the array's address up (make it outside stream capture); calls on one device share
+ * the array, so calls that overlap on the GPU race.                                               */
+size_t hk_mla_sparse_static_max_slots(void);
+int hk_mla_sparse_static(const void* q_lat, const void* ckv, const int* raw_idx, int kidx,
+                         void* lat_out, int m, float scale, int n_split, void* stream);
+
 /* Dense causal attention: row r attends ckv[kv_base[r] .. kv_base[r] + kv_len[r]).
  * With kv_base == NULL and kv_len == NULL: base 0 and len = pos_start + r + 1, which is
  * helios::attn::mla_dense_prefill (src/cuda/attn/attn.cuh:101-108, attn.cu:621-699); qlen = 1 is
