@@ -14,7 +14,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libhelios_b200.so")
+# HELIOS_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("HELIOS_B200_LIB") or os.path.join(_HERE, "libhelios_b200.so")
 
 HK_OK, HK_ERR_INVALID, HK_ERR_UNSUPPORTED, HK_ERR_CUDA, HK_ERR_WORKSPACE, HK_ERR_TIMEOUT = range(6)
 HK_F16, HK_BF16 = 0, 1

@@ -6,7 +6,7 @@
 //
 // Work item = (query row, key split) -> one CTA; all 64 heads of the row share every latent row that
 // is staged, so the cache is read once per row (the reference re-reads it per head pair).
-// Per tile of 64 keys (64 KB, cp.async, double buffered, invalid slots zero-filled):
+// Per tile of 64 keys (64 KB, 16-byte cp.async, double buffered, invalid slots zero-filled):
 //   S  [64 heads x 64 keys]  = Q  K^T   tcgen05 M64  N64 K512: Q and the tile both K-major
 //   softmax: heads are TMEM lanes, keys are columns -> max / exp2 / sum run inside one thread; the
 //            running reference max only moves when a tile exceeds it by 2^8 (lazy rescale of O)
@@ -14,6 +14,11 @@
 //            (the latent row is both key and value), P written K-major by the head threads
 // The no-swizzle core-matrix layout makes the two views of the tile coincide: 8 keys x 16 bytes of
 // channels per core matrix, channel chunks 128 B apart, key groups 8 KB apart.
+//
+// Warp roles (256 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
+// every tcgen05.mma, warps 5-7 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1
+// runs on the tensor pipe while tile i is in the softmax, and the copy of tile i+1 is in flight during
+// both.  All hand-offs are mbarriers with bounded waits.
 // HBM-bound by design: 1 KB per key for 128 K flops (128 flop/B), accumulators never leave TMEM.
 #include <cuda_pipeline_primitives.h>
 
@@ -24,29 +29,50 @@ namespace hk {
 
 constexpr int FT_KEYS = 64;                       // keys per tile
 constexpr int FT_HEADS = 64;
-constexpr uint32_t FT_CS = 128;                   // channel-chunk stride inside a tile
-constexpr uint32_t FT_KS = 64 * 128;              // key-group stride (64 channel chunks)
-constexpr uint32_t FT_TILE = FT_KEYS * LATENT * 2;   // 65536
+constexpr int FT_THREADS = 384;
+constexpr int FT_LOAD_WARPS = 7;                  // warps 5-11
+constexpr int FT_LOADERS = FT_LOAD_WARPS * 32;
+constexpr int FT_ITEMS = (2 * FT_KEYS + FT_LOAD_WARPS - 1) / FT_LOAD_WARPS;   // half-rows per loader warp and tile
+// Channel chunks of one key group are 144 B apart (128 B core matrix + 16 B pad): a warp that copies
+// 32 consecutive 16-byte chunks of ONE latent row (a fully coalesced 512-byte read) then stores them
+// to 32 different core matrices without a shared-memory bank conflict.
+constexpr uint32_t FT_CS = 144;                   // channel-chunk stride inside a tile
+constexpr uint32_t FT_KS = 64 * FT_CS;            // key-group stride (64 channel chunks) = 9216
+constexpr uint32_t FT_TILE = 8 * FT_KS;           // 73728
 constexpr uint32_t FQ_LBO = 128, FQ_SBO = 64 * 128;  // Q operand [64 heads][512] K-major
 constexpr uint32_t FP_LBO = 128, FP_SBO = 8 * 128;   // P operand [64 heads][64 keys] K-major
 constexpr uint32_t FS_Q = 0;                      // 65536
-constexpr uint32_t FS_K = 65536;                  // 2 x 65536
-constexpr uint32_t FS_P = FS_K + 2 * FT_TILE;     // 8192
-constexpr uint32_t FS_MISC = FS_P + 8192;         // alpha[64] f32, m[64], l[64], masks
-constexpr uint32_t FS_SMEM = FS_MISC + 1024;
+constexpr uint32_t FS_K = 65536;                  // 2 x 73728
+constexpr uint32_t FS_P = FS_K + 2 * FT_TILE;     // 2 x 8192
+constexpr uint32_t FS_MISC = FS_P + 2 * 8192;     // alpha[2][64], m[64], l[64], masks, flags
+constexpr uint32_t FS_SMEM = FS_MISC + 1536;
+constexpr int FT_POLL_NS = 40;                    // poll back-off of the waiting warps
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units: P stays below 2^8, fine for fp16
 
-__global__ __launch_bounds__(128, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status) {
+// Optional timeline instrumentation (compile with -DHK_FLASH_TRACE): CTA (0,0) stamps clock64 at the
+// hand-off points of its first 64 tiles; hk_debug_flash_trace copies the stamps to the host.
+#ifdef HK_FLASH_TRACE
+__device__ long long hk_flash_trace[64 * 16];
+#define FT_TRACE(slot, tile)                                                         \
+  do {                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) hk_flash_trace[(tile) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define FT_TRACE(slot, tile) do { } while (0)
+#endif
+
+__device__ __forceinline__ void softmax_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* sQ = smem + FS_Q;
-  uint8_t* sP = smem + FS_P;
-  float* s_alpha = reinterpret_cast<float*>(smem + FS_MISC);
-  float* s_m = s_alpha + 64;
+  float* s_alpha = reinterpret_cast<float*>(smem + FS_MISC);       // [2][64]
+  float* s_m = s_alpha + 128;
   float* s_l = s_m + 64;
   unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_l + 64);  // [2]
-  int* s_flag = reinterpret_cast<int*>(s_mask + 2);
-  __shared__ uint64_t bar;
+  int* s_flag = reinterpret_cast<int*>(s_mask + 2);                // [2]
+  __shared__ uint64_t k_full[2], s_full[2], s_free[2], p_full[2], t_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -67,215 +93,327 @@ __global__ __launch_bounds__(128, 1) void mla_flash_tc_kernel(MlaArgs a, int* __
   const int n_tiles = (k1 - k0 + FT_KEYS - 1) / FT_KEYS;
 
   if (tid == 0) {
-    tc::mbar_init(&bar, 1);
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+      tc::mbar_init(&k_full[b], FT_LOADERS);
+      tc::mbar_init(&s_full[b], 1);
+      tc::mbar_init(&s_free[b], 128);
+      tc::mbar_init(&p_full[b], 128);
+      tc::mbar_init(&t_done[b], 1);
+      s_flag[b] = 0;
+    }
     tc::mbar_fence_init();
     abort_flag = 0;
-    *s_flag = 0;
   }
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 512);
-
-  // ---- Q: 64 heads x 64 chunks of 16 B, K-major operand; octet = 8 heads of one chunk ----
-  {
-    const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
-    for (int it = warp; it < 8 * 16; it += 4) {      // 8 head groups x 16 chunk quads
-      const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
-      __pipeline_memcpy_async(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16, q + (size_t)h * LATENT + ch * 8, 16);
-    }
-  }
-  // key tile loader: 8 key groups x 16 chunk quads per tile
-  auto load_tile = [&](int tile, int buf) {
-    uint8_t* dst0 = smem + FS_K + buf * FT_TILE;
-    const int p0 = k0 + tile * FT_KEYS;
-    for (int it = warp; it < 8 * 16; it += 4) {
-      const int kg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), key = kg * 8 + (lane & 7);
-      const int p = p0 + key;
-      int64_t tok = -1;
-      if (p < k1) tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + p] : base + p;
-      uint8_t* dst = dst0 + kg * FT_KS + ch * FT_CS + (lane & 7) * 16;
-      if (tok >= 0) __pipeline_memcpy_async(dst, a.ckv + (size_t)tok * LATENT + ch * 8, 16);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-    }
-    if (warp == 0) {
-      // validity of the 64 key slots of this tile
-      unsigned long long m = 0;
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
-        const int p = p0 + half * 32 + lane;
-        bool v = p < k1;
-        if (v && sparse) v = a.raw_idx[(size_t)r * a.kidx + p] >= 0;
-        m |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
-      }
-      if (lane == 0) s_mask[buf] = m;
-    }
-  };
-  if (n_tiles > 0) load_tile(0, 0);
-  __pipeline_commit();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 64;   // S: 64 columns; O^T: 4 x 64 columns
-  const uint32_t q_addr = tc::smem_u32(sQ), p_addr = tc::smem_u32(sP);
-  const uint32_t idesc_s = tc::make_idesc(64, FT_KEYS, tc::FMT_F16, tc::FMT_F16, false, false);
-  const uint32_t idesc_o = tc::make_idesc(128, FT_HEADS, tc::FMT_F16, tc::FMT_F16, true, false);
-  const float sc2 = a.scale * LOG2E;
-  const int head = warp * 16 + (lane & 15);   // rows of an M=64 accumulator sit in lanes 0-15 of each quarter
-  const bool head_thread = lane < 16;
-  float m_ref = -INFINITY, l_run = 0.f;
-  uint32_t parity = 0;
+  const uint32_t tS = tmem, tO = tmem + 128;   // S: 2 x 64 columns; O^T: 4 x 64 columns
   bool ok = true;
 
-  for (int tile = 0; tile < n_tiles; tile++) {
-    const int buf = tile & 1;
-    if (tile + 1 < n_tiles) load_tile(tile + 1, buf ^ 1);
-    __pipeline_commit();
-    __pipeline_wait_prior(1);
-    tc::fence_async_smem();
-    __syncthreads();
-    const uint32_t k_addr = tc::smem_u32(smem + FS_K + buf * FT_TILE);
-    // ---- S = Q K^T ----
-    if (tid == 0) {
-#pragma unroll 4
-      for (int kk = 0; kk < LATENT / 16; kk++) {
-        const uint64_t ad = tc::make_sdesc(q_addr + kk * 2 * FQ_LBO, FQ_LBO, FQ_SBO);
-        const uint64_t bd = tc::make_sdesc(k_addr + kk * 2 * FT_CS, FT_CS, FT_KS);
-        tc::mma_f16(tS, ad, bd, idesc_s, kk > 0);
+  if (warp >= 5) {
+    // =========================== loaders: Q once, then the key tiles ===========================
+    // Register-staged copies: every loader warp first issues all of its 16-byte loads of the NEXT
+    // tile (they fly while the tensor pipe still owns the buffer), then waits for the buffer, then
+    // stores.  Plain vector loads: the per-thread cp.async path sustains far fewer bytes in flight.
+    const int lw = warp - 5;
+    uint4 stage[FT_ITEMS];
+    if (n_tiles > 0) {
+      // Q: item = (head group, chunk quad); lanes = 8 heads x 4 chunks -> one 128-byte core matrix per octet
+      const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
+#pragma unroll
+      for (int j = 0; j < FT_ITEMS; j++) {
+        const int it = lw + j * FT_LOAD_WARPS;
+        if (it < 128) {
+          const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
+          stage[j] = *reinterpret_cast<const uint4*>(q + (size_t)h * LATENT + ch * 8);
+        }
       }
-      tc::mma_commit(&bar);
+#pragma unroll
+      for (int j = 0; j < FT_ITEMS; j++) {
+        const int it = lw + j * FT_LOAD_WARPS;
+        if (it < 128) {
+          const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3);
+          *reinterpret_cast<uint4*>(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16) = stage[j];
+        }
+      }
     }
-    ok = tc::mbar_wait(&bar, parity, &abort_flag, 1) && ok;
-    parity ^= 1;
-    tc::fence_after_sync();
-    // ---- softmax of this tile: one thread per head ----
-    {
-      uint32_t s0[32], s1[32];
-      tc::tmem_ld32(tS + ((uint32_t)(warp * 32) << 16), s0);
-      tc::tmem_ld32(tS + ((uint32_t)(warp * 32) << 16) + 32, s1);
+    // L2 prefetch of the tiles ahead keeps HBM busy while this CTA computes: the register-staged
+    // loads below then hit L2.  Dense: one contiguous range per tile; sparse: one 1 KB row per lane.
+    auto prefetch_tile = [&](int t) {
+      if (lw != 0 || t >= n_tiles) return;
+      const int q0 = k0 + t * FT_KEYS;
+      if (!sparse) {
+        const int cnt = min(FT_KEYS, k1 - q0);
+        if (lane == 0 && cnt > 0) tc::prefetch_l2(a.ckv + (size_t)(base + q0) * LATENT, (uint32_t)cnt * LATENT * 2);
+      } else {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const int pp = q0 + half * 32 + lane;
+          if (pp < k1) {
+            const int tk = a.raw_idx[(size_t)r * a.kidx + pp];
+            if (tk >= 0) tc::prefetch_l2(a.ckv + (size_t)tk * LATENT, LATENT * 2);
+          }
+        }
+      }
+    };
+    prefetch_tile(1);
+    prefetch_tile(2);
+    prefetch_tile(3);
+    for (int tile = 0; tile < n_tiles; tile++) {
+      const int buf = tile & 1;
+      const int p0 = k0 + tile * FT_KEYS;
+      prefetch_tile(tile + 4);
+      // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
+#pragma unroll
+      for (int j = 0; j < FT_ITEMS; j++) {
+        const int it = lw + j * FT_LOAD_WARPS;
+        stage[j] = make_uint4(0, 0, 0, 0);
+        if (it < 2 * FT_KEYS) {
+          const int p = p0 + (it >> 1);
+          int64_t tok = -1;
+          if (p < k1) tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + p] : base + p;
+          if (tok >= 0) stage[j] = ld_stream16(a.ckv + (size_t)tok * LATENT + ((it & 1) * 32 + lane) * 8);
+        }
+      }
+      unsigned long long mk = 0;                       // validity of the 64 key slots of this tile
+      if (lw == 0) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const int p = p0 + half * 32 + lane;
+          bool v = p < k1;
+          if (v && sparse) v = a.raw_idx[(size_t)r * a.kidx + p] >= 0;
+          mk |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
+        }
+      }
+      if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - 2) >> 1) & 1, &abort_flag, 5) && ok;
+      if (tid == 160) FT_TRACE(0, tile);               // buffer free, stores start
+      uint8_t* dst0 = smem + FS_K + buf * FT_TILE;
+#pragma unroll
+      for (int j = 0; j < FT_ITEMS; j++) {
+        const int it = lw + j * FT_LOAD_WARPS;
+        if (it < 2 * FT_KEYS) {
+          const int key = it >> 1, ch = (it & 1) * 32 + lane;
+          *reinterpret_cast<uint4*>(dst0 + (key >> 3) * FT_KS + ch * FT_CS + (key & 7) * 16) = stage[j];
+        }
+      }
+      if (lw == 0 && lane == 0) s_mask[buf] = mk;
+      tc::fence_async_smem();
+      tc::mbar_arrive(&k_full[buf]);
+      if (tid == 160) FT_TRACE(1, tile);               // tile published
+    }
+  } else if (warp == 4) {
+    // =========================== tensor-core issue (one thread) ===========================
+    if (lane == 0) {
+      const uint32_t q_addr = tc::smem_u32(sQ);
+      const uint32_t idesc_s = tc::make_idesc(64, FT_KEYS, tc::FMT_F16, tc::FMT_F16, false, false);
+      const uint32_t idesc_o = tc::make_idesc(128, FT_HEADS, tc::FMT_F16, tc::FMT_F16, true, false);
+      auto gemm2 = [&](int t) {                        // O^T += V^T P^T of tile t
+        const int b = t & 1;
+        const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
+        const uint32_t p_addr = tc::smem_u32(smem + FS_P + b * 8192);
+        const uint64_t ad0 = tc::make_sdesc(k_addr, FT_KS, FT_CS);
+        const uint64_t bd0 = tc::make_sdesc(p_addr, FP_LBO, FP_SBO);
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+          for (int kk = 0; kk < FT_KEYS / 16; kk++)
+            tc::mma_f16(tO + mt * 64, tc::sdesc_advance(ad0, mt * 16 * FT_CS + kk * 2 * FT_KS),
+                        tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
+        tc::mma_commit(&t_done[b]);
+      };
+      for (int tile = 0; tile < n_tiles; tile++) {
+        const int b = tile & 1;
+        // If the previous tile's P is already published, retire that tile first: its key buffer is
+        // then refilled while this tile's QK^T runs.  Otherwise QK^T goes first and hides the softmax.
+        bool g2_issued_early = false;
+        if (tile >= 1 && tc::mbar_try_wait(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
+          tc::fence_after_sync();
+          FT_TRACE(5, tile - 1);
+          gemm2(tile - 1);
+          FT_TRACE(6, tile - 1);
+          g2_issued_early = true;
+        }
+        ok = tc::mbar_wait<FT_POLL_NS>(&k_full[b], (tile >> 1) & 1, &abort_flag, 1) && ok;
+        if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&s_free[b], ((tile - 2) >> 1) & 1, &abort_flag, 2) && ok;
+        tc::fence_after_sync();
+        FT_TRACE(3, tile);                             // operands ready, QK^T issue starts
+        const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
+        const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
+        const uint64_t bd0 = tc::make_sdesc(k_addr, FT_CS, FT_KS);
+#pragma unroll
+        for (int kk = 0; kk < LATENT / 16; kk++)       // S = Q K^T
+          tc::mma_f16(tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO), tc::sdesc_advance(bd0, kk * 2 * FT_CS),
+                      idesc_s, kk > 0);
+        tc::mma_commit(&s_full[b]);
+        FT_TRACE(4, tile);                             // QK^T issued
+        if (tile >= 1 && !g2_issued_early) {
+          ok = tc::mbar_wait<FT_POLL_NS>(&p_full[b ^ 1], ((tile - 1) >> 1) & 1, &abort_flag, 3) && ok;
+          tc::fence_after_sync();
+          FT_TRACE(5, tile - 1);                       // P ready
+          gemm2(tile - 1);
+          FT_TRACE(6, tile - 1);                       // V^T P^T issued
+        }
+      }
+      if (n_tiles > 0) {
+        ok = tc::mbar_wait<FT_POLL_NS>(&p_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, &abort_flag, 3) && ok;
+        tc::fence_after_sync();
+        gemm2(n_tiles - 1);
+      }
+    }
+  } else {
+    // =========================== softmax warps ===========================
+    // The S accumulator (M = 64) keeps head 16w + i in TMEM lane 32w + i, i < 16.  It is read with the
+    // 16x256b shape so that all 32 lanes work: thread t owns heads hA = 16w + t/4 and hB = hA + 8 and,
+    // of every 8 keys, keys 2(t%4) and 2(t%4)+1; the four threads of a quad share their row maxima by
+    // shuffle and keep partial row sums that are added up once at the end.
+    const float sc2 = a.scale * LOG2E;
+    const int quad = lane & 3;
+    const int hA = warp * 16 + (lane >> 2), hB = hA + 8;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+    for (int tile = 0; tile < n_tiles; tile++) {
+      const int b = tile & 1;
+      ok = tc::mbar_wait<FT_POLL_NS>(&k_full[b], (tile >> 1) & 1, &abort_flag, 6) && ok;   // makes the tile's mask visible
+      ok = tc::mbar_wait<FT_POLL_NS>(&s_full[b], (tile >> 1) & 1, &abort_flag, 7) && ok;
+      tc::fence_after_sync();
+      if (tid == 0) FT_TRACE(7, tile);                 // S ready
+      uint32_t sv[32];
+      tc::tmem_ld_16x256b_x8(tS + b * 64 + ((uint32_t)(warp * 32) << 16), sv);
       tc::tmem_ld_wait();
-      const unsigned long long mask = s_mask[buf];
-      float tmax = -INFINITY;
+      tc::fence_before_sync();
+      tc::mbar_arrive(&s_free[b]);
+      const unsigned long long mask = s_mask[b] >> (2 * quad);
+      float tA = -INFINITY, tB = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; j++) {
-        const float v0 = ((mask >> j) & 1ull) ? __uint_as_float(s0[j]) * sc2 : -INFINITY;
-        const float v1 = ((mask >> (32 + j)) & 1ull) ? __uint_as_float(s1[j]) * sc2 : -INFINITY;
-        s0[j] = __float_as_uint(v0);
-        s1[j] = __float_as_uint(v1);
-        tmax = fmaxf(tmax, fmaxf(v0, v1));
-      }
-      float alpha = 1.f;
-      if (tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && tmax > -INFINITY)) {
-        alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - tmax);
-        m_ref = tmax;
-        l_run *= alpha;
-        if (head_thread && tile > 0) *s_flag = 1;
-      }
-      if (head_thread) s_alpha[head] = alpha;
-      float lsum = 0.f;
-      uint8_t* prow = sP + (head >> 3) * FP_SBO + (head & 7) * 16;
+      for (int j = 0; j < 8; j++) {
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        float p[8];
-#pragma unroll
-        for (int e = 0; e < 8; e++) {
-          const int j = c * 8 + e;
-          const float sv = __uint_as_float(j < 32 ? s0[j] : s1[j - 32]);
-          p[e] = (m_ref == -INFINITY) ? 0.f : exp2f(sv - m_ref);
-          lsum += p[e];
-        }
-        if (head_thread) {
-          __half2 h0 = __floats2half2_rn(p[0], p[1]), h1 = __floats2half2_rn(p[2], p[3]);
-          __half2 h2 = __floats2half2_rn(p[4], p[5]), h3 = __floats2half2_rn(p[6], p[7]);
-          uint4 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-          pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-          *reinterpret_cast<uint4*>(prow + c * FP_LBO) = pk;
+        for (int e = 0; e < 2; e++) {
+          const bool valid = (mask >> (8 * j + e)) & 1ull;
+          const float vA = valid ? __uint_as_float(sv[4 * j + e]) * sc2 : -INFINITY;
+          const float vB = valid ? __uint_as_float(sv[4 * j + 2 + e]) * sc2 : -INFINITY;
+          sv[4 * j + e] = __float_as_uint(vA);
+          sv[4 * j + 2 + e] = __float_as_uint(vB);
+          tA = fmaxf(tA, vA);
+          tB = fmaxf(tB, vB);
         }
       }
-      l_run += lsum;
+      tA = fmaxf(tA, __shfl_xor_sync(0xffffffffu, tA, 1)); tA = fmaxf(tA, __shfl_xor_sync(0xffffffffu, tA, 2));
+      tB = fmaxf(tB, __shfl_xor_sync(0xffffffffu, tB, 1)); tB = fmaxf(tB, __shfl_xor_sync(0xffffffffu, tB, 2));
+      float alA = 1.f, alB = 1.f;
+      bool moved = false;
+      if (tA > mA + RESCALE_THRESHOLD || (mA == -INFINITY && tA > -INFINITY)) {
+        alA = (mA == -INFINITY) ? 0.f : exp2f(mA - tA);
+        mA = tA; lA *= alA; moved = true;
+      }
+      if (tB > mB + RESCALE_THRESHOLD || (mB == -INFINITY && tB > -INFINITY)) {
+        alB = (mB == -INFINITY) ? 0.f : exp2f(mB - tB);
+        mB = tB; lB *= alB; moved = true;
+      }
+      if (quad == 0) {
+        s_alpha[b * 64 + hA] = alA;
+        s_alpha[b * 64 + hB] = alB;
+        if (moved && tile > 0) s_flag[b] = tile + 1;   // stamped with the tile: never needs a reset
+      }
+      if (tid == 0) FT_TRACE(8, tile);                 // max done
+      softmax_group_sync();
+      if (tid == 0) FT_TRACE(9, tile);                 // group barrier passed
+      const bool rescale = s_flag[b] == tile + 1;
+      if (rescale) {
+        // rare: a head's reference max moved.  O^T (columns = heads) is rescaled after the previous
+        // tile's V^T P^T has completed and before this tile's is issued (it waits for p_full below).
+        ok = tc::mbar_wait<FT_POLL_NS>(&t_done[b ^ 1], ((tile - 1) >> 1) & 1, &abort_flag, 8) && ok;
+        tc::fence_after_sync();
+#pragma unroll 1
+        for (int mt = 0; mt < 4; mt++) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < FT_HEADS; c0 += 32) {
+            uint32_t o[32];
+            const uint32_t addr = tO + mt * 64 + c0 + ((uint32_t)(warp * 32) << 16);
+            tc::tmem_ld32(addr, o);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[b * 64 + c0 + j]);
+            tc::tmem_st32(addr, o);
+          }
+        }
+        tc::tmem_st_wait();
+      }
+      // the P buffer of this parity was last read by the V^T P^T of tile-2
+      if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[b], ((tile - 2) >> 1) & 1, &abort_flag, 9) && ok;
+      // P operand [64 heads][64 keys] K-major: chunk j of a head's row holds keys 8j..8j+7; this thread
+      // writes its two keys (4 bytes) of every chunk, for both of its heads
+      uint8_t* pA = smem + FS_P + b * 8192 + (hA >> 3) * FP_SBO + (hA & 7) * 16 + quad * 4;
+      uint8_t* pB = smem + FS_P + b * 8192 + (hB >> 3) * FP_SBO + (hB & 7) * 16 + quad * 4;
+      const bool liveA = mA != -INFINITY, liveB = mB != -INFINITY;
+      float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float a0 = liveA ? exp2f(__uint_as_float(sv[4 * j]) - mA) : 0.f;
+        const float a1 = liveA ? exp2f(__uint_as_float(sv[4 * j + 1]) - mA) : 0.f;
+        const float b0 = liveB ? exp2f(__uint_as_float(sv[4 * j + 2]) - mB) : 0.f;
+        const float b1 = liveB ? exp2f(__uint_as_float(sv[4 * j + 3]) - mB) : 0.f;
+        sumA += a0 + a1;
+        sumB += b0 + b1;
+        __half2 ha = __floats2half2_rn(a0, a1), hb = __floats2half2_rn(b0, b1);
+        *reinterpret_cast<uint32_t*>(pA + j * FP_LBO) = *reinterpret_cast<uint32_t*>(&ha);
+        *reinterpret_cast<uint32_t*>(pB + j * FP_LBO) = *reinterpret_cast<uint32_t*>(&hb);
+      }
+      lA += sumA;
+      lB += sumB;
+      if (tid == 0) FT_TRACE(10, tile);                // P written
+      tc::fence_async_smem();
+      tc::fence_before_sync();
+      tc::mbar_arrive(&p_full[b]);
+      if (tid == 0) FT_TRACE(11, tile);                // P published
     }
-    tc::fence_async_smem();
-    tc::fence_before_sync();
-    __syncthreads();
+    // per-head totals: add the partial row sums of the four threads of each quad
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (quad == 0) {
+      s_m[hA] = mA; s_l[hA] = lA;
+      s_m[hB] = mB; s_l[hB] = lB;
+    }
+    // ---- epilogue (softmax warps): wait for the last V^T P^T, then write the result ----
+    if (n_tiles > 0) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, &abort_flag, 10) && ok;
     tc::fence_after_sync();
-    // ---- rare: a head's reference max moved, rescale the O^T accumulators (columns = heads) ----
-    if (*s_flag) {
+    softmax_group_sync();
+    const size_t rows = (size_t)a.m * FT_HEADS;
+    const size_t rh0 = (size_t)r * FT_HEADS;
+    if (ok && !abort_flag) {
 #pragma unroll 1
       for (int mt = 0; mt < 4; mt++) {
+        const int ch = mt * 128 + tid;   // TMEM lane = channel inside the M tile
 #pragma unroll 1
         for (int c0 = 0; c0 < FT_HEADS; c0 += 32) {
           uint32_t o[32];
-          const uint32_t addr = tO + mt * 64 + c0 + ((uint32_t)(warp * 32) << 16);
-          tc::tmem_ld32(addr, o);
-          tc::tmem_ld_wait();
+          if (n_tiles > 0) {
+            tc::tmem_ld32(tO + mt * 64 + c0 + ((uint32_t)(warp * 32) << 16), o);
+            tc::tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[c0 + j]);
-          tc::tmem_st32(addr, o);
-        }
-      }
-      tc::tmem_st_wait();
-      tc::fence_before_sync();
-      __syncthreads();
-      tc::fence_after_sync();
-      if (tid == 0) *s_flag = 0;
-    }
-    // ---- O^T += V^T P^T ----
-    if (tid == 0) {
-#pragma unroll
-      for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-        for (int kk = 0; kk < FT_KEYS / 16; kk++) {
-          const uint64_t ad = tc::make_sdesc(k_addr + mt * 16 * FT_CS + kk * 2 * FT_KS, FT_KS, FT_CS);
-          const uint64_t bd = tc::make_sdesc(p_addr + kk * 2 * FP_LBO, FP_LBO, FP_SBO);
-          tc::mma_f16(tO + mt * 64, ad, bd, idesc_o, tile > 0 || kk > 0);
-        }
-      tc::mma_commit(&bar);
-    }
-    ok = tc::mbar_wait(&bar, parity, &abort_flag, 2) && ok;
-    parity ^= 1;
-    tc::fence_after_sync();
-  }
-  __pipeline_wait_prior(0);
-
-  // ---- epilogue ----
-  if (head_thread) {
-    s_m[head] = m_ref;
-    s_l[head] = l_run;
-  }
-  __syncthreads();
-  const size_t rows = (size_t)a.m * FT_HEADS;
-  const size_t rh0 = (size_t)r * FT_HEADS;
-  if (ok) {
-#pragma unroll 1
-    for (int mt = 0; mt < 4; mt++) {
-      const int ch = mt * 128 + tid;   // TMEM lane = channel inside the M tile
-#pragma unroll 1
-      for (int c0 = 0; c0 < FT_HEADS; c0 += 32) {
-        uint32_t o[32];
-        if (n_tiles > 0) {
-          tc::tmem_ld32(tO + mt * 64 + c0 + ((uint32_t)(warp * 32) << 16), o);
-          tc::tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; j++) o[j] = 0u;
-        }
-        if (a.out) {
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const float l = s_l[c0 + j];
-            const float v = l > 0.f ? __uint_as_float(o[j]) / l : 0.f;
-            a.out[(rh0 + c0 + j) * LATENT + ch] = __float2half_rn(v);
+            for (int j = 0; j < 32; j++) o[j] = 0u;
           }
-        } else {
+          if (a.out) {
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            a.part_acc[((size_t)sp * rows + rh0 + c0 + j) * LATENT + ch] = s_l[c0 + j] > 0.f ? __uint_as_float(o[j]) : 0.f;
+            for (int j = 0; j < 32; j++) {
+              const float l = s_l[c0 + j];
+              const float v = l > 0.f ? __uint_as_float(o[j]) / l : 0.f;
+              a.out[(rh0 + c0 + j) * LATENT + ch] = __float2half_rn(v);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              a.part_acc[((size_t)sp * rows + rh0 + c0 + j) * LATENT + ch] = s_l[c0 + j] > 0.f ? __uint_as_float(o[j]) : 0.f;
+          }
         }
       }
-    }
-    if (!a.out && tid < FT_HEADS) {
-      const float mr = s_m[tid];
-      a.part_m[(size_t)sp * rows + rh0 + tid] = (mr == -INFINITY || !(s_l[tid] > 0.f)) ? -INFINITY : mr / LOG2E;
-      a.part_l[(size_t)sp * rows + rh0 + tid] = s_l[tid];
+      if (!a.out && tid < FT_HEADS) {
+        const float mr = s_m[tid];
+        a.part_m[(size_t)sp * rows + rh0 + tid] = (mr == -INFINITY || !(s_l[tid] > 0.f)) ? -INFINITY : mr / LOG2E;
+        a.part_l[(size_t)sp * rows + rh0 + tid] = s_l[tid];
+      }
     }
   }
   tc::fence_before_sync();
@@ -284,11 +422,20 @@ __global__ __launch_bounds__(128, 1) void mla_flash_tc_kernel(MlaArgs a, int* __
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
 
+#ifdef HK_FLASH_TRACE
+}  // namespace hk
+extern "C" __attribute__((visibility("default"))) int hk_debug_flash_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, hk::hk_flash_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : 3;
+}
+namespace hk {
+#endif
+
 int mla_flash_tc_auto_splits(int m, int n_keys) {
-  // about one CTA per SM, at least two 64-key tiles per split, splits of equal tile counts
+  // at most one CTA per SM (a second wave would double the time), at least two 64-key tiles per
+  // split, splits of equal tile counts
   const int sms = sm_count();
   const int tiles = (n_keys + FT_KEYS - 1) / FT_KEYS;
-  int want = (sms + m - 1) / m;
+  int want = sms / (m > 0 ? m : 1);
   if (want > 256) want = 256;
   if (want < 1) want = 1;
   int tiles_per = (tiles + want - 1) / want;
@@ -308,7 +455,7 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
     attr_set[dev] = true;
   }
   dim3 grid(a.n_split, a.m);
-  mla_flash_tc_kernel<<<grid, 128, FS_SMEM, s>>>(a, device_status_ptr());
+  mla_flash_tc_kernel<<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr());
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 

@@ -52,6 +52,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // with a broken dependency still terminates within about one budget and reports where it gave up.
 constexpr long long MBAR_WAIT_CYCLES = 2000000000LL;
 
+// SLEEP_NS > 0 backs the poll off with nanosleep: for long waits of warps that share an SM with
+// copy-issuing warps (every poll is a shared-memory pipeline operation).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -59,6 +62,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   for (;;) {
     if (*abort_flag) return false;
     if (mbar_try_wait(bar, parity)) return true;
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (clock64() - t0 > MBAR_WAIT_CYCLES) {
       *abort_flag = code;
       return false;
@@ -77,6 +81,24 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
           smem_u32(smem_dst)),
       "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
+}
+
+// Ask the TMA engine to pull a contiguous global range into L2 (no destination, no completion to wait
+// for): address 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
+// 16-byte asynchronous copy global -> shared that bypasses L1 (cp.async.cg).  The .ca form allocates
+// an L1 line per request; in kernels that give almost all of the SM's 256 KB to shared memory the few
+// KB left for L1 cap the bytes in flight and with them the copy rate.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operand reads)
@@ -117,6 +139,24 @@ __device__ __forceinline__ void tmem_st_wait() {
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 lanes x 64 consecutive 32-bit columns spread over the WHOLE warp (shape 16x256b, 8 repeats): the
+// natural read-back of an M = 64 accumulator, whose rows occupy lanes 0-15 of each lane quarter.
+// Thread t holds rows t/4 and t/4 + 8; in repeat j (columns 8j .. 8j+7) it holds columns
+// 8j + 2(t%4) and 8j + 2(t%4) + 1:  r[4j] = (row t/4, col), r[4j+1] = (row t/4, col+1),
+// r[4j+2] = (row t/4+8, col), r[4j+3] = (row t/4+8, col+1).
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
       "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
@@ -174,6 +214,12 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
   d |= (uint64_t)1 << 46;
   return d;
+}
+
+// descriptor of the same tile advanced by `bytes` (start-address field only; no carry into LBO for
+// the offsets used here: shared addresses stay below 256 KB = 14 bits of 16-byte units)
+__device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) {
+  return desc + (uint64_t)(bytes >> 4);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
