@@ -45,6 +45,8 @@ SIGNATURES = {
     "hk_mla_dense_partial": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_lse_combine_ptrs": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
+    "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
+    "hk_lse_combine_peers": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _i, _vp]),
     "hk_q_latent": (_i, [_vp, _vp, _vp, _i, _vp]),
     "hk_o_absorb": (_i, [_vp, _vp, _vp, _i, _vp]),
     "hk_wuv_transpose": (_i, [_vp, _vp, _vp]),
@@ -262,6 +264,18 @@ def lse_combine_ptrs(ptrs_m, ptrs_l, ptrs_acc, n_split, rows, out, stream=None):
     """Combine over per-split pointers (device int64 tensors of addresses, e.g. peer buffers)."""
     _call("hk_lse_combine_ptrs", _ptr(ptrs_m), _ptr(ptrs_l), _ptr(ptrs_acc), n_split, rows,
           _ptr(out), _stream(stream))
+
+
+def peer_signal(flag_ptrs, n_ranks, my_rank, epoch, stream=None):
+    """Publish `epoch` into slot my_rank of every rank's flag array (flag_ptrs: device int64 tensor)."""
+    _call("hk_peer_signal", _ptr(flag_ptrs), n_ranks, my_rank, epoch, _stream(stream))
+
+
+def lse_combine_peers(ptrs_m, ptrs_l, ptrs_acc, n_split, rows, out, local_flags, epoch, max_wait_ms=1000,
+                      stream=None):
+    """Bounded wait on this GPU's flag array, then combine over peer-mapped partial buffers."""
+    _call("hk_lse_combine_peers", _ptr(ptrs_m), _ptr(ptrs_l), _ptr(ptrs_acc), n_split, rows, _ptr(out),
+          _ptr(local_flags), epoch, max_wait_ms, _stream(stream))
 
 
 def q_latent(q_nope, kv_b, q_lat, m, stream=None):

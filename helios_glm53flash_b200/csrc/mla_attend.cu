@@ -254,3 +254,26 @@ HK_API int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* p
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
+
+HK_API int hk_peer_signal(int* const* flag_ptrs, int n_ranks, int my_rank, int epoch, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(flag_ptrs && n_ranks >= 1 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks);
+  peer_signal_kernel<<<1, 32, 0, as_stream(stream)>>>(flag_ptrs, n_ranks, my_rank, epoch);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}
+
+HK_API int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* ptrs_l,
+                                const float* const* ptrs_acc, int n_split, int64_t rows, void* out_f16,
+                                const int* local_flags, int epoch, int max_wait_ms, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && local_flags && n_split >= 1 && n_split <= 32 && rows >= 0);
+  HK_REQUIRE(max_wait_ms > 0 && max_wait_ms <= 10000);
+  if (rows == 0) return HK_OK;
+  const long long cycles = (long long)max_wait_ms * 2000000LL;   // ~2 GHz
+  lse_combine_peers_kernel<<<(unsigned)rows, 128, 0, as_stream(stream)>>>(
+      ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16, local_flags, epoch, cycles,
+      device_status_ptr());
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}

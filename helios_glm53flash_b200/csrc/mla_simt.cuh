@@ -167,4 +167,66 @@ __global__ __launch_bounds__(128) void lse_combine_kernel(
   *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + t * 4) = pk;
 }
 
+// ---- split-KV across GPUs: peer signal + combine over peer-mapped partial buffers ----
+// Rank g publishes "my partial of step `epoch` is complete" by storing `epoch` into slot g of every
+// rank's flag array (its own included).  The stores are system-scope releases issued after a
+// system-scope fence, in a kernel launched behind the partial kernel on the same stream.
+__global__ void peer_signal_kernel(int* const* __restrict__ flag_ptrs, int n_ranks, int my_rank, int epoch) {
+  const int s = threadIdx.x;
+  if (s < n_ranks) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag_ptrs[s] + my_rank), "r"(epoch) : "memory");
+  }
+}
+
+// Combine that first waits (bounded) until every rank's flag in THIS GPU's flag array has reached
+// `epoch`, then reads the S partial sets through their pointers (peer memory: plain cache-volatile
+// loads over NVLink, nothing else).  On expiry the CTA writes nothing and reports a timeout.
+__global__ __launch_bounds__(128) void lse_combine_peers_kernel(
+    const float* const* __restrict__ ptrs_m, const float* const* __restrict__ ptrs_l,
+    const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows, __half* __restrict__ out,
+    const int* __restrict__ flags, int epoch, long long max_wait_cycles, int* __restrict__ status) {
+  __shared__ int ready;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int s = 0; s < n_split; s++) {
+      for (;;) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
+        if (v >= epoch) break;
+        if (clock64() - t0 > max_wait_cycles) { ok = 0; break; }
+        __nanosleep(200);
+      }
+      if (!ok) break;
+    }
+    ready = ok;
+    if (!ok && status) atomicExch(status, HK_ERR_TIMEOUT);
+  }
+  __syncthreads();
+  if (!ready) return;
+  const int64_t r = blockIdx.x;
+  const int t = threadIdx.x;
+  float gm = -INFINITY;
+  for (int s = 0; s < n_split; s++) gm = fmaxf(gm, __ldcv(ptrs_m[s] + r));
+  float gl = 0.f;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (gm != -INFINITY) {
+    for (int s = 0; s < n_split; s++) {
+      const float ms = __ldcv(ptrs_m[s] + r);
+      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
+      gl += sc * __ldcv(ptrs_l[s] + r);
+      const float4 a = __ldcv(reinterpret_cast<const float4*>(ptrs_acc[s] + (size_t)r * LATENT + t * 4));
+      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
+    }
+  }
+  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
+  __half2 h1 = __floats2half2_rn(o.z * inv, o.w * inv);
+  uint2 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+  *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + t * 4) = pk;
+}
+
 }  // namespace hk

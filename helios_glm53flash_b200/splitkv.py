@@ -1,0 +1,101 @@
+"""Long-context MLA decode split over the GPUs of one node (split-KV), one process per GPU.
+
+Rank g owns a contiguous slice of the latent cache.  A decode step is, on every rank:
+  1. ``hk_mla_dense_partial`` over the local slice -> un-normalised (m, l, acc) partial in a buffer that
+     every peer has mapped (CUDA IPC; NVLink peer access),
+  2. ``hk_peer_signal``: store the step's epoch into this rank's slot of every rank's flag array,
+  3. ``hk_lse_combine_peers``: bounded wait until all slots of the local flag array show the epoch,
+     then read the G partial sets through their peer pointers (plain loads over NVLink) and write the
+     normalised output.  Every rank ends up with the full [m, 64, 512] result.
+There is no collective library call on the data path and nothing but plain peer loads and stores; torch.distributed is used once,
+at set-up, to exchange the IPC handles.  Waits are bounded: a rank that never signals makes the
+others' combine give up after ``max_wait_ms`` with HK_ERR_TIMEOUT in the device status word.
+"""
+import numpy as np
+
+from . import synth
+
+PARTIAL_FLOATS_PER_ROW = 2 + 512      # m, l, acc[512] per (row, head)
+
+
+def shard_tokens(n_tokens, rank, world):
+    """[begin, end) of the cache rows owned by `rank`; slices differ by at most one row"""
+    return synth.shard_range(n_tokens, rank, world)
+
+
+def region_layout(rows, world):
+    """byte offsets inside one rank's exchange region: flags | m | l | acc"""
+    off_flags = 0
+    off_m = 256
+    off_l = off_m + ((rows * 4 + 255) // 256) * 256
+    off_acc = off_l + ((rows * 4 + 255) // 256) * 256
+    total = off_acc + rows * 512 * 4
+    assert world * 4 <= 256
+    return {"flags": off_flags, "m": off_m, "l": off_l, "acc": off_acc, "total": total}
+
+
+class SplitKVDecoder:
+    """Owns the peer-mapped exchange region of this rank and the pointer tables of all ranks."""
+
+    def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000):
+        import torch
+        import torch.distributed as dist
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.torch, self.dist = torch, dist
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.m, self.n_heads, self.rows = m, n_heads, m * n_heads
+        self.max_wait_ms = max_wait_ms
+        self.lay = region_layout(self.rows, self.world)
+        self.local = torch.zeros(self.lay["total"], dtype=torch.uint8, device="cuda")
+        # exchange CUDA IPC handles (set-up only); keep the rebuilt peer tensors alive
+        fn, args = reduce_tensor(self.local)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (fn, args), group=group)
+        self.peers = []
+        for r, (f, a) in enumerate(gathered):
+            self.peers.append(self.local if r == self.rank else f(*a))
+        bases = [p.data_ptr() for p in self.peers]
+
+        def table(key):
+            return torch.tensor([b + self.lay[key] for b in bases], dtype=torch.int64, device="cuda")
+
+        self.flag_ptrs, self.m_ptrs, self.l_ptrs, self.acc_ptrs = table("flags"), table("m"), table("l"), table("acc")
+        self.epoch = 0
+        self._views()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def _views(self):
+        t, lay, rows = self.torch, self.lay, self.rows
+        self.flags = self.local[lay["flags"]:lay["flags"] + 4 * self.world].view(t.int32)
+        self.part_m = self.local[lay["m"]:lay["m"] + rows * 4].view(t.float32)
+        self.part_l = self.local[lay["l"]:lay["l"] + rows * 4].view(t.float32)
+        self.part_acc = self.local[lay["acc"]:lay["acc"] + rows * 2048].view(t.float32)
+
+    def step(self, q_lat, ckv_shard, n_local_keys, out, scale, signal=True):
+        """one decode step; q_lat [m, 64, 512] f16 (same on every rank), ckv_shard = this rank's rows,
+        out [m, 64, 512] f16.  signal=False withholds this rank's flag (failure-injection in tests)."""
+        import helios_glm53flash_b200 as hk
+        t = self.torch
+        self.epoch += 1
+        base = t.zeros(self.m, dtype=t.int64, device="cuda")
+        lens = t.full((self.m,), int(n_local_keys), dtype=t.int32, device="cuda")
+        hk.mla_dense_partial(q_lat, ckv_shard, base, lens, 0, self.part_m, self.part_l, self.part_acc, self.m,
+                             n_heads=self.n_heads, scale=scale)
+        if signal:
+            hk.peer_signal(self.flag_ptrs, self.world, self.rank, self.epoch)
+        hk.lse_combine_peers(self.m_ptrs, self.l_ptrs, self.acc_ptrs, self.world, self.rows, out, self.flags,
+                             self.epoch, max_wait_ms=self.max_wait_ms)
+
+
+def merge_partials_numpy(parts):
+    """host restatement of the combine, for the CPU multi-process test: parts = list of (m, l, acc)"""
+    m = np.stack([p[0] for p in parts]).astype(np.float64)
+    l_ = np.stack([p[1] for p in parts]).astype(np.float64)
+    acc = np.stack([p[2] for p in parts]).astype(np.float64)
+    gm = m.max(axis=0)
+    w = np.where(np.isinf(m), 0.0, np.exp(m - np.where(np.isinf(gm), 0.0, gm)))
+    gl = (w * l_).sum(axis=0)
+    o = (w[..., None] * acc).sum(axis=0)
+    return np.where(gl[:, None] > 0, o / np.maximum(gl[:, None], 1e-300), 0.0)

@@ -181,6 +181,19 @@ int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
                         const float* const* ptrs_acc, int n_split, int64_t rows, void* out_f16,
                         void* stream);
 
+/* Split-KV across GPUs (one process per GPU, partial buffers and flag arrays mapped into every
+ * peer).  After its hk_mla_dense_partial, rank g calls hk_peer_signal: it stores `epoch` into slot g
+ * of every rank's flag array (flag_ptrs: DEVICE array of n_ranks pointers to int[n_ranks]).
+ * hk_lse_combine_peers then waits on THIS GPU's flag array until all n_split slots have reached
+ * `epoch` - a bounded wait of at most max_wait_ms (1..10000); on expiry nothing is written and the
+ * device status word reports HK_ERR_TIMEOUT - and combines the partial sets through their pointers
+ * with plain loads over NVLink.  Epochs must increase from call to call; flags are never reset.
+ * No counterpart in the reference (it is single-GPU for this path).                              */
+int hk_peer_signal(int* const* flag_ptrs, int n_ranks, int my_rank, int epoch, void* stream);
+int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* ptrs_l,
+                         const float* const* ptrs_acc, int n_split, int64_t rows, void* out_f16,
+                         const int* local_flags, int epoch, int max_wait_ms, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * adjacent projections (kept so the engine's layer loop links unchanged)
  * Replace helios::attn::q_latent / q_latent_t / o_absorb / o_absorb_t / wuv_transpose

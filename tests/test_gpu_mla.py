@@ -172,3 +172,37 @@ def test_absorbed_projections_vs_oracle():
     assert sum_rel(f(bits(ql)), f(orc.q_latent(qn, kb, m))) < 2e-3
     want_o = f(orc.o_absorb(lo, kb, m))
     assert sum_rel(f(bits(o1)), want_o) < 2e-3 and sum_rel(f(bits(o2)), want_o) < 2e-3
+
+
+def test_peer_combine_on_one_gpu_and_bounded_wait_times_out_cleanly():
+    """the cross-GPU combine path with every 'peer' on this GPU: flags set by hk_peer_signal release the
+    wait; a slot that nothing sets makes the bounded wait expire - the kernel returns, the status word
+    says so, the output is untouched and the context stays usable"""
+    m, L, S = 1, 640, 2
+    inp = synth.mla_inputs(L, m, seed=31, cache_std=0.5)
+    rows = m * 64
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    pm = torch.empty(S, rows, dtype=torch.float32, device="cuda")
+    pl = torch.empty(S, rows, dtype=torch.float32, device="cuda")
+    pa = torch.empty(S, rows, 512, dtype=torch.float32, device="cuda")
+    for s, (b, e) in enumerate([(0, 300), (300, L)]):
+        hk.mla_dense_partial(q, c, dev(np.full(m, b, np.int64)), dev(np.full(m, e - b, np.int32)), 0, pm[s], pl[s], pa[s], m)
+    flags = torch.zeros(S, dtype=torch.int32, device="cuda")
+    ptr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device="cuda")
+    flag_ptrs = ptr([flags, flags])
+    out = torch.full((rows, 512), 5.0, dtype=torch.float16, device="cuda")
+    # only "rank 0" signals: slot 1 never arrives -> timeout after 50 ms, nothing written
+    hk.peer_signal(flag_ptrs[:1], 1, 0, 1)
+    hk.lse_combine_peers(ptr(list(pm)), ptr(list(pl)), ptr(list(pa)), S, rows, out, flags, 1, max_wait_ms=50)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == hk.HK_ERR_TIMEOUT
+    assert (out == 5.0).all()
+    # now both signal (as rank 0 and rank 1 of a 2-rank group whose flag arrays are this one array)
+    hk.peer_signal(flag_ptrs, 2, 0, 2)
+    hk.peer_signal(flag_ptrs, 2, 1, 2)
+    hk.lse_combine_peers(ptr(list(pm)), ptr(list(pl)), ptr(list(pa)), S, rows, out, flags, 2, max_wait_ms=1000)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    _, full32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=np.zeros(m, np.int64),
+                               kv_len=np.full(m, L, np.int32))
+    assert max_rel(synth.f16_bits_to_f32(bits(out)).reshape(m, 64, 512), full32) < TOL
