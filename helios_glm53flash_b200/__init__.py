@@ -43,6 +43,7 @@ SIGNATURES = {
     "hk_mla_sparse_static": (_i, [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _vp]),
     "hk_mla_dense": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
     "hk_mla_dense_partial": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "hk_mla_dense_partial_ws": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_lse_combine_ptrs": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
@@ -252,6 +253,19 @@ def mla_dense_partial(q_lat, ckv, kv_base, kv_len, pos_start, part_m, part_l, pa
     """One split's un-normalised (m, l, acc) partial - the unit of split-KV across GPUs."""
     _call("hk_mla_dense_partial", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start,
           _ptr(part_m), _ptr(part_l), _ptr(part_acc), m, n_heads, float(scale), _stream(stream))
+
+
+def mla_dense_partial_ws(q_lat, ckv, kv_base, kv_len, pos_start, part_m, part_l, part_acc, m, n_keys_hint,
+                         n_heads=64, scale=0.0625, n_split=0, workspace=None, stream=None):
+    """One partial set computed with every SM of this GPU (local splits merged on the GPU)."""
+    if n_split <= 0:
+        n_split = mla_auto_splits(m, n_keys_hint)
+    ws = workspace
+    if n_split > 1 and ws is None:
+        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device)
+    _call("hk_mla_dense_partial_ws", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start, _ptr(part_m),
+          _ptr(part_l), _ptr(part_acc), m, n_heads, float(scale), n_split, n_keys_hint, _ptr(ws),
+          0 if ws is None else ws.numel(), _stream(stream))
 
 
 def lse_combine(part_m, part_l, part_acc, n_split, rows, out, stream=None):

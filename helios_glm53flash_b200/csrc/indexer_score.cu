@@ -133,6 +133,128 @@ __global__ __launch_bounds__(128) void indexer_tc_kernel(
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Decode form (at most 8 query rows = one N group): persistent CTAs stream the pooled-key plane.
+// The query operand is staged once; key tiles of 128 pools (32 KB) are double buffered, fetched with
+// fully coalesced 16-byte loads into registers while the previous tile is in the tensor pipe and the
+// epilogue, then stored into a padded core-matrix layout (channel chunks 144 B apart, so the 8
+// chunks a quarter-warp writes fall into different banks).
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t IXD_LBO = 144;                // K-chunk stride (128 B core matrix + 16 B pad)
+constexpr uint32_t IXD_SBO = 16 * IXD_LBO;       // 8-row group stride = 2304
+constexpr uint32_t IXD_TILE = 16 * IXD_SBO;      // 128 rows = 36864 B
+
+template <int FMT>
+__global__ __launch_bounds__(128) void indexer_tc_decode_kernel(
+    const uint16_t* __restrict__ q, const uint16_t* __restrict__ pk, const uint16_t* __restrict__ w,
+    const int* __restrict__ q_pos, __half* __restrict__ scores, int m, int npools, int score_stride,
+    int n_tiles, uint32_t tmem_cols, int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sA = smem;                              // 2 x IXD_TILE
+  uint8_t* sB = smem + 2 * IXD_TILE;               // (4 m) groups x IXD_SBO
+  const int nb = m * IX_HEADS;                     // N
+  float* w_sm = reinterpret_cast<float*>(sB + (nb / 8) * IXD_SBO);
+  int* pos_sm = reinterpret_cast<int*>(w_sm + IX_RG * IX_HEADS);
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane >> 4, chunk = lane & 15;    // a warp instruction covers 2 rows x 16 chunks
+
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, tmem_cols);
+  // query rows -> B operand
+  for (int r2 = warp; r2 < nb / 2; r2 += 4) {
+    const int row = r2 * 2 + sub;
+    const uint4 v = *reinterpret_cast<const uint4*>(q + (size_t)row * IDX_DIM + chunk * 8);
+    *reinterpret_cast<uint4*>(sB + (row >> 3) * IXD_SBO + chunk * IXD_LBO + (row & 7) * 16) = v;
+  }
+  for (int i = tid; i < nb; i += 128) {
+    const uint16_t wb = w[i];
+    w_sm[i] = FMT == tc::FMT_BF16 ? bf16_bits_to_f(wb) : __half2float(__ushort_as_half(wb));
+  }
+  if (tid < m) pos_sm[tid] = q_pos[tid];
+
+  uint4 stage[16];
+  auto fetch = [&](int tile) {                     // 128 rows x 256 B of one tile into registers
+    const int p0 = tile * IX_TILE_P;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int row = (warp + 4 * j) * 2 + sub;
+      stage[j] = (p0 + row < npools) ? ld_stream16(pk + (size_t)(p0 + row) * IDX_DIM + chunk * 8)
+                                     : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto stash = [&](int buf) {
+    uint8_t* dst = sA + buf * IXD_TILE;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int row = (warp + 4 * j) * 2 + sub;
+      *reinterpret_cast<uint4*>(dst + (row >> 3) * IXD_SBO + chunk * IXD_LBO + (row & 7) * 16) = stage[j];
+    }
+  };
+  int tile = blockIdx.x;
+  if (tile < n_tiles) {
+    fetch(tile);
+    stash(0);
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t b_addr = tc::smem_u32(sB);
+  const uint32_t idesc = tc::make_idesc(IX_TILE_P, nb, FMT, FMT, false, false);
+  uint32_t parity = 0;
+  int buf = 0;
+  for (; tile < n_tiles; tile += gridDim.x, buf ^= 1) {
+    const int next = tile + gridDim.x;
+    if (next < n_tiles) fetch(next);               // in flight during the MMA and the epilogue below
+    if (tid == 0) {
+      const uint64_t ad0 = tc::make_sdesc(tc::smem_u32(sA + buf * IXD_TILE), IXD_LBO, IXD_SBO);
+      const uint64_t bd0 = tc::make_sdesc(b_addr, IXD_LBO, IXD_SBO);
+#pragma unroll
+      for (int kk = 0; kk < IDX_DIM / 16; kk++)
+        tc::mma_f16(tmem, tc::sdesc_advance(ad0, kk * 2 * IXD_LBO), tc::sdesc_advance(bd0, kk * 2 * IXD_LBO), idesc, kk > 0);
+      tc::mma_commit(&bar);
+    }
+    const bool ok = tc::mbar_wait(&bar, parity, &abort_flag, 1);
+    parity ^= 1;
+    tc::fence_after_sync();
+    const int p = tile * IX_TILE_P + tid;          // this thread's pool (TMEM lane tid)
+    if (ok) {
+      for (int rr = 0; rr < m; rr++) {
+        uint32_t c[32];
+        tc::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + rr * IX_HEADS, c);
+        tc::tmem_ld_wait();
+        float tot = 0.f;
+#pragma unroll
+        for (int h = 0; h < IX_HEADS; h++) {
+          const float d = __uint_as_float(c[h]) * 0.08838834764f;
+          tot = fmaf(w_sm[rr * IX_HEADS + h], fmaxf(d, 0.f), tot);
+        }
+        if (p < npools) {
+          const bool vis = p * POOL + POOL - 1 <= pos_sm[rr];
+          scores[(size_t)rr * score_stride + p] =
+              vis ? __float2half_rn(tot * 0.17677669530f) : __ushort_as_half((unsigned short)0xfc00);
+        }
+      }
+    }
+    if (next < n_tiles) stash(buf ^ 1);            // the other buffer was last read two MMAs ago
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+  }
+  if (warp == 0) tc::tmem_dealloc(tmem, tmem_cols);
+  if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
+}
+
 }  // namespace hk
 
 // device word that records a bounded wait giving up (read with hk_read_device_status)
@@ -183,6 +305,32 @@ HK_API int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void
     attr_set[dev] = true;
   }
   const int tiles = (npools + IX_TILE_P - 1) / IX_TILE_P;
+  if (m <= IX_RG) {
+    // decode form: persistent CTAs over the pool tiles
+    const int nb = m * IX_HEADS;
+    const size_t smem = 2 * IXD_TILE + (size_t)(nb / 8) * IXD_SBO + IX_RG * IX_HEADS * 4 + IX_RG * 4 + 64;
+    uint32_t cols = 32;
+    while ((int)cols < nb) cols <<= 1;
+    static bool dattr[64] = {false};
+    if (dev >= 0 && dev < 64 && !dattr[dev]) {
+      const int max_smem = (int)(2 * IXD_TILE + 32 * IXD_SBO + IX_RG * IX_HEADS * 4 + IX_RG * 4 + 64);
+      if (cudaFuncSetAttribute(indexer_tc_decode_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess ||
+          cudaFuncSetAttribute(indexer_tc_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+        return HK_ERR_CUDA;
+      dattr[dev] = true;
+    }
+    const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+    int grid_x = per_sm * sm_count();
+    if (grid_x > tiles) grid_x = tiles;
+    cudaStream_t sd = as_stream(stream);
+    int* std_ = device_status_ptr();
+    if (dtype == HK_F16)
+      indexer_tc_decode_kernel<0><<<grid_x, 128, smem, sd>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, tiles, cols, std_);
+    else
+      indexer_tc_decode_kernel<1><<<grid_x, 128, smem, sd>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, tiles, cols, std_);
+    HK_LAUNCH_CHECK();
+    return HK_OK;
+  }
   // enough row groups per CTA to amortise the key tile, enough CTAs to cover the GPU twice
   int row_groups = (m + IX_RG - 1) / IX_RG;
   int want_y = (2 * sm_count() + tiles - 1) / tiles;

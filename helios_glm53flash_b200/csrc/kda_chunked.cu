@@ -20,7 +20,7 @@
 // shared-memory layout kernel 2 needs (74,240 bytes).
 // Kernel 2 (kda_chunk_scan_kernel) walks the chunks of one (batch, head, 32-column value slice) in
 // order.  The fp32 state slice stays in registers; per chunk it pulls the 60 KB of operands with TMA
-// bulk copies (double buffered) and issues three tcgen05 contractions with TMEM accumulators:
+// bulk copies (three stages in flight) and issues three tcgen05 contractions with TMEM accumulators:
 // [W;Q+] S0 (M128 N32 K128), [0;B beta] U (accumulated onto the Q+ S0 rows) and Kt^T U (M128 N32 K64).
 #include <cuda_pipeline_primitives.h>
 
@@ -78,9 +78,21 @@ constexpr uint32_t P1_A = P1_L + 2 * 16 * P1_LD * 4;     // f32 [64][68] N = A b
 constexpr uint32_t P1_P = P1_A + KC * P1_LDA * 4;        // f32 [4][128] G before each 16-token block
 constexpr uint32_t P1_EP = P1_P + 2048;                  // f32 [4][128] exp of the above
 constexpr uint32_t P1_BETA = P1_EP + 2048;               // f32 [64]
-constexpr uint32_t P1_RK = P1_BETA + 256;                // f32 [64] 1/|k|
-constexpr uint32_t P1_SMEM = P1_RK + 256;
+constexpr uint32_t P1_RK = P1_BETA + 256;                // f32 [64] beta_t / |k_t|
+constexpr uint32_t P1_DD = P1_RK + 256;                  // f32 [4][128] e^{P_ib - P_(ib-1)}: decay across one 16-token block
+constexpr uint32_t P1_SMEM = P1_DD + 2048;
 static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_LDH * 2 == KC * P1_LDA * 4, "aliases");
+
+// Optional stage timeline (compile with -DHK_KDA_TRACE): one CTA in the middle of the grid stamps clock64
+// at its stage boundaries; hk_debug_kda_trace copies the stamps to the host.
+#ifdef HK_KDA_TRACE
+__device__ long long hk_kda_trace[64];
+#define KT_TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.y == 200 && blockIdx.x == 3) hk_kda_trace[slot] = clock64(); } while (0)
+#define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 3 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
+#else
+#define KT_TRACE(slot) do { } while (0)
+#define KS_TRACE(slot, ch) do { } while (0)
+#endif
 
 // 16 x 16 block product helper of the blocked triangular inverse: returns sum_k L[r][k] * R[k][c]
 __device__ __forceinline__ float dot16(const float* __restrict__ lrow, const float* __restrict__ rcol) {
@@ -99,7 +111,7 @@ __device__ __forceinline__ float dot16(const float* __restrict__ lrow, const flo
 __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
     const __nv_bfloat16* __restrict__ beta, uint8_t* __restrict__ ws, int seqlen, int H,
-    int n_chunks, int* __restrict__ status) {
+    int n_chunks, int prefetch_dist, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + P1_G);
   uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
@@ -109,6 +121,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   float* sEP = reinterpret_cast<float*>(smem + P1_EP);
   float* sBeta = reinterpret_cast<float*>(smem + P1_BETA);
   float* sRk = reinterpret_cast<float*>(smem + P1_RK);
+  float* sDD = reinterpret_cast<float*>(smem + P1_DD);
   uint8_t* sKV = smem + P1_KP;                             // [K+ | V]; the V half aliases sG, valid after the A/B stage
   float* sX = reinterpret_cast<float*>(smem + P1_KR);      // alias, valid after the A/B stage
   uint8_t* sT = smem + P1_L;                               // alias, valid after the A/B stage
@@ -117,7 +130,9 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int chunk = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  // heads are the fastest grid dimension: CTAs that run together read the same tokens, i.e. whole
+  // contiguous rows of the activations
+  const int head = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
   const int t0 = chunk * KC;
   const int n_valid = min(KC, seqlen - t0);
   const size_t row = (size_t)3 * H * KD;
@@ -132,6 +147,21 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
 
+  KT_TRACE(0);
+  // L2 prefetch for the CTA that will run `prefetch_dist` blocks later (about one wave ahead: blocks are
+  // scheduled in linear order, heads fastest): its q, k, v rows (256 B each) and g rows (512 B), one
+  // request per thread.  This CTA's own loads below then mostly hit L2.
+  {
+    const long long lin = (long long)blockIdx.y * H + blockIdx.x + prefetch_dist;
+    const int phead = (int)(lin % H), pchunk = (int)(lin / H);
+    const int pt = pchunk * KC + (tid & 63);
+    if (prefetch_dist > 0 && pchunk < n_chunks && pt < seqlen) {
+      const __nv_bfloat16* ptok = qkv + ((size_t)b * seqlen + pt) * row;
+      const int part = tid >> 6;                          // 0: q, 1: k, 2: v, 3: g
+      if (part < 3) tc::prefetch_l2(ptok + (size_t)(part * H + phead) * KD, KD * 2);
+      else tc::prefetch_l2(g + (((size_t)b * seqlen + pt) * H + phead) * KD, KD * 4);
+    }
+  }
   // ---- stage 1: all loads of the chunk in flight at once.  Warp w owns tokens w, w+8, ...; lane owns
   //      channels 4*lane .. 4*lane+3.  g goes straight to shared memory, q and k stay in registers.
   float qv[8][4], kv[8][4], rq[8];
@@ -173,15 +203,18 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     const int t = ib * 16 + (e >> 1), sc = jb * 2 + (e & 1);
     *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
   }
+  KT_TRACE(1);
   __pipeline_wait_prior(0);
   __syncthreads();
 
+  KT_TRACE(2);
   // ---- stage 2: inclusive cumulative log decay per channel; block bases P and e^P; chunk decay ----
   if (tid < KD) {
     float acc = 0.f;
 #pragma unroll 8
     for (int t = 0; t < KC; t++) {
       if ((t & 15) == 0) {
+        sDD[(t >> 4) * KD + tid] = (t == 0) ? 1.f : __expf(acc - sP[((t >> 4) - 1) * KD + tid]);
         sP[(t >> 4) * KD + tid] = acc;
         sEP[(t >> 4) * KD + tid] = __expf(acc);
       }
@@ -192,6 +225,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   __syncthreads();
 
+  KT_TRACE(3);
   // ---- stage 3: Kt^T tile (rows = channels, K = tokens) straight to the workspace ----
   for (int i = tid; i < KD * (KC / 8); i += 256) {
     const int c = i & 127, tg = i >> 7;
@@ -207,10 +241,31 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
   }
 
+  __syncthreads();
+  KT_TRACE(4);
+  // ---- stage 3b: every (token, channel) gets its two exponentials, once: e = e^{G_t - P_blk} scales
+  //      the LEFT operands k^,q^ (kept in registers), 1/e scales the RIGHT operand
+  //      R[s][c] = k^_s e^{P_blk(s) - G_s}, which overwrites G in place (fp32: up to e^85 inside a block)
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int t = warp + 8 * i, blk = t >> 4;
+    float4* gp = reinterpret_cast<float4*>(sG + t * P1_LD + lane * 4);
+    const float4 gt = *gp;
+    const float4 pb = *reinterpret_cast<const float4*>(sP + blk * KD + lane * 4);
+    const float x0 = fmaxf(gt.x - pb.x, -85.f), x1 = fmaxf(gt.y - pb.y, -85.f);
+    const float x2 = fmaxf(gt.z - pb.z, -85.f), x3 = fmaxf(gt.w - pb.w, -85.f);
+    const float e0 = __expf(x0), e1 = __expf(x1), e2 = __expf(x2), e3 = __expf(x3);
+    *gp = make_float4(kv[i][0] * __expf(-x0), kv[i][1] * __expf(-x1), kv[i][2] * __expf(-x2), kv[i][3] * __expf(-x3));
+    kv[i][0] *= e0; kv[i][1] *= e1; kv[i][2] *= e2; kv[i][3] *= e3;
+    qv[i][0] *= rq[i] * e0; qv[i][1] *= rq[i] * e1; qv[i][2] *= rq[i] * e2; qv[i][3] *= rq[i] * e3;
+  }
+
+  KT_TRACE(5);
   // ---- stage 4: A and B on the warp-level tensor cores (TF32), one 16-token ROW block at a time.
-  //      Left operands k^,q^ * e^{G_t - P_ib} of the block come from the registers (fp32 range is
-  //      needed: the factor spans e^{-80}..1); right operand k^_s e^{P_ib - G_s} is formed on the fly.
-  //      The same pass emits K+ = k^ e^{G_t} (shared memory) and Q+ = q^ e^{G_t} (workspace). ----
+  //      Per block ib: its left operands go from the registers to shared memory (fp32 range is needed:
+  //      the factor spans e^{-85}..1), the right operand rows of all earlier blocks are advanced from
+  //      reference P_(ib-1) to P_ib by one multiplication, and the 16x16 blocks (ib, jb <= ib) are
+  //      plain TF32 products.  The same pass emits K+ = k^ e^{G_t} and Q+ = q^ e^{G_t}. ----
   {
     const int gq = lane >> 2, tig = lane & 3;
 #pragma unroll
@@ -218,12 +273,9 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
 #pragma unroll
       for (int half = 0; half < 2; half++) {
         const int i = 2 * ib + half, t = warp + 8 * i, lr = t - 16 * ib;
-        const float4 gt = *reinterpret_cast<const float4*>(sG + t * P1_LD + lane * 4);
-        const float4 pb = *reinterpret_cast<const float4*>(sP + ib * KD + lane * 4);
         const float4 ep = *reinterpret_cast<const float4*>(sEP + ib * KD + lane * 4);
-        const float f0 = __expf(gt.x - pb.x), f1 = __expf(gt.y - pb.y), f2 = __expf(gt.z - pb.z), f3 = __expf(gt.w - pb.w);
-        const float k0 = kv[i][0] * f0, k1 = kv[i][1] * f1, k2 = kv[i][2] * f2, k3 = kv[i][3] * f3;
-        const float q0 = qv[i][0] * rq[i] * f0, q1 = qv[i][1] * rq[i] * f1, q2 = qv[i][2] * rq[i] * f2, q3 = qv[i][3] * rq[i] * f3;
+        const float k0 = kv[i][0], k1 = kv[i][1], k2 = kv[i][2], k3 = kv[i][3];
+        const float q0 = qv[i][0], q1 = qv[i][1], q2 = qv[i][2], q3 = qv[i][3];
         *reinterpret_cast<uint4*>(sL + lr * P1_LD + lane * 4) = make_uint4(f2tf32(k0), f2tf32(k1), f2tf32(k2), f2tf32(k3));
         *reinterpret_cast<uint4*>(sL + (16 + lr) * P1_LD + lane * 4) = make_uint4(f2tf32(q0), f2tf32(q1), f2tf32(q2), f2tf32(q3));
         // chunk-start based copies: 4 channels = half of a 16-byte operand chunk
@@ -234,6 +286,17 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
         *reinterpret_cast<uint2*>(sKV + (c >> 3) * 1024 + (t >> 3) * 128 + (t & 7) * 16 + (c & 7) * 2) = kp;
         *reinterpret_cast<uint2*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (c >> 3) * LBO + (t & 7) * 16 + (c & 7) * 2) = qp;
       }
+      if (ib > 0) {
+        // rows of the earlier blocks (this thread's own tokens below 16*ib): reference P_(ib-1) -> P_ib
+        const float4 dd = *reinterpret_cast<const float4*>(sDD + ib * KD + lane * 4);
+#pragma unroll
+        for (int i = 0; i < 2 * ib; i++) {
+          float4* rp = reinterpret_cast<float4*>(sG + (warp + 8 * i) * P1_LD + lane * 4);
+          float4 rv = *rp;
+          rv.x *= dd.x; rv.y *= dd.y; rv.z *= dd.z; rv.w *= dd.w;
+          *rp = rv;
+        }
+      }
       __syncthreads();
       // units of this row block: (column block jb <= ib, 8-column half nt)
       for (int unit_i = warp; unit_i < 2 * (ib + 1); unit_i += 8) {
@@ -241,11 +304,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
         float acck[4] = {0.f, 0.f, 0.f, 0.f}, accq[4] = {0.f, 0.f, 0.f, 0.f};
         const float* lk0 = sL + gq * P1_LD;
         const float* lq0 = sL + (16 + gq) * P1_LD;
-        const float* pb = sP + ib * KD;
-        const int s = jb * 16 + nt * 8 + gq;
-        const float rks = sRk[s];
-        const uint16_t* krow = sKr + s * P1_LDH;
-        const float* grow = sG + s * P1_LD;
+        const float* rrow = sG + (jb * 16 + nt * 8 + gq) * P1_LD;
 #pragma unroll 4
         for (int ks = 0; ks < KD / 8; ks++) {
           const int c = ks * 8 + tig;
@@ -254,8 +313,8 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
           ak[2] = __float_as_uint(lk0[c + 4]); ak[3] = __float_as_uint(lk0[8 * P1_LD + c + 4]);
           aq[0] = __float_as_uint(lq0[c]); aq[1] = __float_as_uint(lq0[8 * P1_LD + c]);
           aq[2] = __float_as_uint(lq0[c + 4]); aq[3] = __float_as_uint(lq0[8 * P1_LD + c + 4]);
-          const uint32_t b0 = f2tf32(bf16_bits_to_f(krow[c]) * rks * __expf(pb[c] - grow[c]));
-          const uint32_t b1 = f2tf32(bf16_bits_to_f(krow[c + 4]) * rks * __expf(pb[c + 4] - grow[c + 4]));
+          const uint32_t b0 = f2tf32(rrow[c]);
+          const uint32_t b1 = f2tf32(rrow[c + 4]);
           mma_tf32(acck, ak, b0, b1);
           mma_tf32(accq, aq, b0, b1);
         }
@@ -276,6 +335,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       __syncthreads();
     }
   }
+  KT_TRACE(6);
   // from here on sG, sKr and sL are dead: the V half of sKV, sX and sT take their place
 
   // ---- stage 5: V -> B operand columns 128..255, then the blocked
@@ -298,6 +358,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < KC * P1_LDA; i += 256) sX[i] = 0.f;
   __syncthreads();
+  KT_TRACE(7);
   // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
   if (warp < 4 && lane < 16) {
     const int ib = warp;
@@ -317,6 +378,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     for (int r = 0; r < 16; r++) sX[(ib * 16 + r) * P1_LDA + ib * 16 + lane] = x[r];
   }
   __syncthreads();
+  KT_TRACE(8);
   // 5b: off-diagonal blocks by distance d: Y_ij = sum_{m=j}^{i-1} N_im X_mj (kept in the unused
   //     mirror block (j,i) of sA), then X_ij = -X_ii Y_ij
 #pragma unroll 1
@@ -337,6 +399,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     }
     __syncthreads();
   }
+  KT_TRACE(9);
   // 5c: T = fp16(X) as the K-major A operand (K = 64): lanes = 8 rows x 4 chunks
   for (int i = tid; i < KC * (KC / 8); i += 256) {
     const int t = (i & 7) + ((i >> 6) << 3), jc = (i >> 3) & 7;
@@ -351,6 +414,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   __syncthreads();
   tc::fence_after_sync();
 
+  KT_TRACE(10);
   // ---- stage 6: [W | Uloc] = T [K+ | V] : tcgen05 M128 N256 K64, fp16 in, fp32 TMEM accumulators ----
   const uint32_t tmem = tmem_slot;
   if (tid == 0) {
@@ -366,6 +430,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   const bool ok = tc::mbar_wait(&bar, 0, &abort_flag, 1);
   tc::fence_after_sync();
+  KT_TRACE(11);
   // ---- stage 7: epilogue. Lanes 0-63 are the tokens; warps 0,1 take W, warps 4,5 take Uloc ----
   if (ok && (warp & 3) < 2) {
     const int t = (warp & 3) * 32 + lane;
@@ -397,6 +462,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   tc::fence_before_sync();
   __syncthreads();
+  KT_TRACE(12);
   if (warp == 0) tc::tmem_dealloc(tmem, 256);
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
@@ -411,7 +477,8 @@ constexpr uint32_t S_UL = 65536;          // 4096
 constexpr uint32_t S_DEC = 69632;         // 512
 constexpr uint32_t S_STAGE = 70144;
 constexpr uint32_t S_TX = 32768 + 8192 + 16384 + 4096 + 512;  // bytes landing per stage
-constexpr uint32_t P2_S = 2 * S_STAGE;    // fp16 B operand: state slice [128 k][32], MN-major, 8 KB
+constexpr int S_NSTAGE = 3;               // operand stages in flight: two chunks of lead time for the bulk copies
+constexpr uint32_t P2_S = S_NSTAGE * S_STAGE;  // fp16 B operand: state slice [128 k][32], MN-major, 8 KB
 constexpr uint32_t P2_U = P2_S + 8192;    // fp16 B operand: U [64 tokens][32], MN-major, 4 KB
 constexpr uint32_t P2_SMEM = P2_U + 4096;
 
@@ -420,7 +487,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     float* __restrict__ out_f32, int seqlen, int H, int n_chunks, const int* __restrict__ slots,
     float scale, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ uint64_t full_bar[2];
+  __shared__ uint64_t full_bar[S_NSTAGE];
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -433,8 +500,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   float* st = state + ((size_t)slot * H + head) * KD * KD + (size_t)tid * KD + v0;  // row k = tid
 
   if (tid == 0) {
-    tc::mbar_init(&full_bar[0], 1);
-    tc::mbar_init(&full_bar[1], 1);
+    for (int i = 0; i < S_NSTAGE; i++) tc::mbar_init(&full_bar[i], 1);
     tc::mbar_init(&mma_bar, 1);
     tc::mbar_fence_init();
     abort_flag = 0;
@@ -442,8 +508,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 64);
   // zero halves of the [0 ; B beta] operands
   for (int i = tid; i < 8192 / 16; i += 128) {
-    reinterpret_cast<uint4*>(smem + S_BB)[i] = make_uint4(0, 0, 0, 0);
-    reinterpret_cast<uint4*>(smem + S_STAGE + S_BB)[i] = make_uint4(0, 0, 0, 0);
+    for (int st_i = 0; st_i < S_NSTAGE; st_i++) reinterpret_cast<uint4*>(smem + st_i * S_STAGE + S_BB)[i] = make_uint4(0, 0, 0, 0);
   }
   // state slice: thread = k row, 32 fp32 values in registers; fp16 copy as the B operand
   float S[KNV];
@@ -469,9 +534,9 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   const uint32_t d1 = tmem, d2 = tmem + 32;
 
   auto issue_loads = [&](int chunk) {
-    uint8_t* stg = smem + (chunk & 1) * S_STAGE;
+    uint8_t* stg = smem + (chunk % S_NSTAGE) * S_STAGE;
     const uint8_t* u = unit0 + (size_t)chunk * U_BYTES;
-    uint64_t* bar = &full_bar[chunk & 1];
+    uint64_t* bar = &full_bar[chunk % S_NSTAGE];
     tc::mbar_arrive_expect_tx(bar, S_TX);
     tc::bulk_g2s(stg + S_WQ, u + U_WQ, 32768, bar);
     tc::bulk_g2s(stg + S_BB + 8192, u + U_BB, 8192, bar);
@@ -480,8 +545,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     tc::bulk_g2s(stg + S_DEC, u + U_DEC, 512, bar);
   };
   if (tid == 0) {
-    issue_loads(0);
-    if (n_chunks > 1) issue_loads(1);
+    for (int c = 0; c < S_NSTAGE && c < n_chunks; c++) issue_loads(c);
   }
 
   const uint32_t idesc = tc::make_idesc(128, KNV, tc::FMT_F16, tc::FMT_F16, false, true);
@@ -489,10 +553,12 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   uint32_t mma_parity = 0;
 
   for (int chunk = 0; chunk < n_chunks; chunk++) {
-    const int sidx = chunk & 1;
+    const int sidx = chunk % S_NSTAGE;
     uint8_t* stg = smem + sidx * S_STAGE;
     const uint32_t stg_addr = tc::smem_u32(stg);
-    bool ok = tc::mbar_wait(&full_bar[sidx], (chunk >> 1) & 1, &abort_flag, 2);
+    KS_TRACE(0, chunk);
+    bool ok = tc::mbar_wait(&full_bar[sidx], (chunk / S_NSTAGE) & 1, &abort_flag, 2);
+    KS_TRACE(1, chunk);
     // ---- [W ; Q+] S0 -> D1 (128 x 32) ----
     if (tid == 0) {
 #pragma unroll
@@ -506,6 +572,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 3) && ok;
     mma_parity ^= 1;
     tc::fence_after_sync();
+    KS_TRACE(2, chunk);
     // ---- U = Uloc - W S0 (token rows = TMEM lanes 0-63) ----
     if (warp < 2) {
       const int t = tid;
@@ -534,6 +601,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
+    KS_TRACE(3, chunk);
     // ---- D1 rows 64-127 += (B beta) U ;  D2 = Kt^T U ----
     if (tid == 0) {
 #pragma unroll
@@ -553,6 +621,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 4) && ok;
     mma_parity ^= 1;
     tc::fence_after_sync();
+    KS_TRACE(4, chunk);
     // ---- outputs (TMEM lanes 64-127 = tokens) ----
     if (warp >= 2) {
       const int t = tid - 64;
@@ -584,6 +653,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
         }
       }
     }
+    KS_TRACE(5, chunk);
     // ---- state: S <- S e^{G_last} + Kt^T U (lane = k row), refresh the fp16 operand copy ----
     {
       uint32_t r[32];
@@ -604,7 +674,8 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
-    if (tid == 0 && chunk + 2 < n_chunks) issue_loads(chunk + 2);
+    KS_TRACE(6, chunk);
+    if (tid == 0 && chunk + S_NSTAGE < n_chunks) issue_loads(chunk + S_NSTAGE);
   }
   if (!abort_flag) {
 #pragma unroll
@@ -619,6 +690,12 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
 
 }  // namespace hk
 
+#ifdef HK_KDA_TRACE
+extern "C" __attribute__((visibility("default"))) int hk_debug_kda_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, hk::hk_kda_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
+}
+#endif
+
 HK_API size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads) {
   if (bsz <= 0 || seqlen <= 0 || num_heads <= 0) return 0;
   const size_t n_chunks = ((size_t)seqlen + hk::KC - 1) / hk::KC;
@@ -632,6 +709,7 @@ HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const v
   using namespace hk;
   HK_REQUIRE(mixed_qkv && g && beta && state && out && workspace);
   HK_REQUIRE(bsz > 0 && seqlen > 0 && num_heads > 0);
+  HK_REQUIRE(bsz <= 65535 && (seqlen + KC - 1) / KC <= 65535);   // grid limits
   HK_REQUIRE(aligned(mixed_qkv, 16) && aligned(g, 16) && aligned(state, 16) && aligned(out, 16) &&
              aligned(workspace, 256) && (!out_f32 || aligned(out_f32, 16)));
   if (workspace_bytes < hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)) return HK_ERR_WORKSPACE;
@@ -647,9 +725,9 @@ HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const v
   }
   cudaStream_t s = as_stream(stream);
   int* st = device_status_ptr();
-  kda_chunk_prep_kernel<<<dim3(n_chunks, num_heads, bsz), 256, P1_SMEM, s>>>(
+  kda_chunk_prep_kernel<<<dim3(num_heads, n_chunks, bsz), 256, P1_SMEM, s>>>(
       (const __nv_bfloat16*)mixed_qkv, g, (const __nv_bfloat16*)beta, (uint8_t*)workspace, seqlen,
-      num_heads, n_chunks, st);
+      num_heads, n_chunks, 2 * sm_count(), st);
   HK_LAUNCH_CHECK();
   kda_chunk_scan_kernel<<<dim3(KVS, num_heads, bsz), 128, P2_SMEM, s>>>(
       (const uint8_t*)workspace, state, (__nv_bfloat16*)out, out_f32, seqlen, num_heads, n_chunks,

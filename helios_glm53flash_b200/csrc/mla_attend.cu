@@ -234,6 +234,43 @@ HK_API int hk_mla_dense_partial(const void* q_lat, const void* ckv, const int64_
   return st;
 }
 
+HK_API int hk_mla_dense_partial_ws(const void* q_lat, const void* ckv, const int64_t* kv_base,
+                                   const int* kv_len, int pos_start, float* part_m, float* part_l,
+                                   float* part_acc, int m, int n_heads, float scale, int n_split,
+                                   int n_keys_hint, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv && part_m && part_l && part_acc);
+  HK_REQUIRE(m >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(part_acc, 16));
+  if (m == 0) return HK_OK;
+  const bool tc = (n_heads == 64) && !force_simt();
+  if (n_split <= 0)
+    n_split = tc ? mla_flash_tc_auto_splits(m, n_keys_hint > 0 ? n_keys_hint : 4096)
+                 : simt_auto_splits(m, n_heads, n_keys_hint > 0 ? n_keys_hint : 4096);
+  if (n_split == 1)
+    return hk_mla_dense_partial(q_lat, ckv, kv_base, kv_len, pos_start, part_m, part_l, part_acc, m, n_heads, scale, stream);
+  const int64_t rows = (int64_t)m * n_heads;
+  PartialLayout pl = partial_layout(n_split, rows);
+  if (!workspace || workspace_bytes < pl.total) return HK_ERR_WORKSPACE;
+  if (!aligned(workspace, 256)) return HK_ERR_INVALID;
+  char* ws = (char*)workspace;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = pos_start;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  a.n_split = n_split;
+  a.part_m = (float*)ws; a.part_l = (float*)(ws + pl.off_l); a.part_acc = (float*)(ws + pl.off_acc);
+  cudaStream_t s = as_stream(stream);
+  int st = HK_ERR_UNSUPPORTED;
+  if (tc) st = mla_flash_tc_launch(a, s);
+  if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
+  if (st != HK_OK) return st;
+  lse_merge_partials_kernel<<<(unsigned)rows, 128, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows,
+                                                           part_m, part_l, part_acc);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}
+
 HK_API int hk_lse_combine(const float* part_m, const float* part_l, const float* part_acc,
                           int n_split, int64_t rows, void* out_f16, void* stream) {
   using namespace hk;

@@ -6,23 +6,30 @@
 //
 // Work item = (query row, key split) -> one CTA; all 64 heads of the row share every latent row that
 // is staged, so the cache is read once per row (the reference re-reads it per head pair).
-// Per tile of 64 keys (64 KB, 16-byte cp.async, double buffered, invalid slots zero-filled):
+// Per tile of 64 keys (64 KB, double buffered, invalid slots zero-filled):
 //   S  [64 heads x 64 keys]  = Q  K^T   tcgen05 M64  N64 K512: Q and the tile both K-major
 //   softmax: heads are TMEM lanes, keys are columns -> max / exp2 / sum run inside one thread; the
 //            running reference max only moves when a tile exceeds it by 2^8 (lazy rescale of O)
 //   O^T[512 ch x 64 heads] += V^T P^T   4 x tcgen05 M128 N64 K64: the SAME tile read MN-major as A
 //            (the latent row is both key and value), P written K-major by the head threads
-// The no-swizzle core-matrix layout makes the two views of the tile coincide: 8 keys x 16 bytes of
-// channels per core matrix, channel chunks 128 B apart, key groups 8 KB apart.
+// The key tile sits in the 128-byte-swizzle layout: 8 blocks of 64 channels, each block = 64 key rows
+// of 128 bytes with 16-byte chunk c of row r stored at c ^ (r % 8).  Read K-major (rows = keys) it is
+// the B operand of Q K^T; the same bytes read MN-major (64 contiguous channels per key) are the A
+// operand V^T.  Whole 64-key tiles of a dense range arrive with ONE TMA tensor copy each (3-D box
+// {64 channels, 64 keys, 8 blocks} over the cache viewed as [row][block][64], 128-byte swizzle);
+// gathered rows and ragged tails go through register-staged vector loads into the same layout.
 //
-// Warp roles (256 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
-// every tcgen05.mma, warps 5-7 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1
+// Warp roles (384 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
+// every tcgen05.mma, warps 5-11 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1
 // runs on the tensor pipe while tile i is in the softmax, and the copy of tile i+1 is in flight during
 // both.  All hand-offs are mbarriers with bounded waits.
 // HBM-bound by design: 1 KB per key for 128 K flops (128 flop/B), accumulators never leave TMEM.
+#include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime at first use)
 #include <cuda_pipeline_primitives.h>
 
 #include "mla_args.cuh"
+#include <cstring>
+
 #include "tc05.cuh"
 
 namespace hk {
@@ -33,19 +40,15 @@ constexpr int FT_THREADS = 384;
 constexpr int FT_LOAD_WARPS = 7;                  // warps 5-11
 constexpr int FT_LOADERS = FT_LOAD_WARPS * 32;
 constexpr int FT_ITEMS = (2 * FT_KEYS + FT_LOAD_WARPS - 1) / FT_LOAD_WARPS;   // half-rows per loader warp and tile
-// Channel chunks of one key group are 144 B apart (128 B core matrix + 16 B pad): a warp that copies
-// 32 consecutive 16-byte chunks of ONE latent row (a fully coalesced 512-byte read) then stores them
-// to 32 different core matrices without a shared-memory bank conflict.
-constexpr uint32_t FT_CS = 144;                   // channel-chunk stride inside a tile
-constexpr uint32_t FT_KS = 64 * FT_CS;            // key-group stride (64 channel chunks) = 9216
-constexpr uint32_t FT_TILE = 8 * FT_KS;           // 73728
+constexpr uint32_t FT_BLK = 64 * 128;             // one block of 64 channels: 64 key rows x 128 B
+constexpr uint32_t FT_TILE = 8 * FT_BLK;          // 65536
 constexpr uint32_t FQ_LBO = 128, FQ_SBO = 64 * 128;  // Q operand [64 heads][512] K-major
 constexpr uint32_t FP_LBO = 128, FP_SBO = 8 * 128;   // P operand [64 heads][64 keys] K-major
 constexpr uint32_t FS_Q = 0;                      // 65536
-constexpr uint32_t FS_K = 65536;                  // 2 x 73728
+constexpr uint32_t FS_K = 65536;                  // 2 x 65536, 1 KB aligned
 constexpr uint32_t FS_P = FS_K + 2 * FT_TILE;     // 2 x 8192
 constexpr uint32_t FS_MISC = FS_P + 2 * 8192;     // alpha[2][64], m[64], l[64], masks, flags
-constexpr uint32_t FS_SMEM = FS_MISC + 1536;
+constexpr uint32_t FS_SMEM = FS_MISC + 1536 + 1024;   // + slack to align the base to 1 KB (swizzle atoms)
 constexpr int FT_POLL_NS = 40;                    // poll back-off of the waiting warps
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units: P stays below 2^8, fine for fp16
@@ -64,8 +67,19 @@ __device__ long long hk_flash_trace[64 * 16];
 
 __device__ __forceinline__ void softmax_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-__global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status) {
-  extern __shared__ __align__(128) uint8_t smem[];
+__device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap* tmap, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          tc::smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(0), "r"(row), "r"(0), "r"(tc::smem_u32(bar))
+      : "memory");
+}
+
+__global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status,
+                                                                     const __grid_constant__ CUtensorMap tmap,
+                                                                     int use_tma) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem + FS_Q;
   float* s_alpha = reinterpret_cast<float*>(smem + FS_MISC);       // [2][64]
   float* s_m = s_alpha + 128;
@@ -91,6 +105,8 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const int tiles_per = (tiles_total + a.n_split - 1) / a.n_split;
   const int k0 = min(n, sp * tiles_per * FT_KEYS), k1 = min(n, (sp + 1) * tiles_per * FT_KEYS);
   const int n_tiles = (k1 - k0 + FT_KEYS - 1) / FT_KEYS;
+  // a tile goes through TMA when it is a whole tile of a dense range
+  auto tile_is_tma = [&](int t) { return use_tma && !sparse && (k0 + (t + 1) * FT_KEYS <= k1); };
 
   if (tid == 0) {
 #pragma unroll
@@ -165,13 +181,14 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     for (int tile = 0; tile < n_tiles; tile++) {
       const int buf = tile & 1;
       const int p0 = k0 + tile * FT_KEYS;
+      const bool via_tma = tile_is_tma(tile);
       prefetch_tile(tile + 4);
       // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
 #pragma unroll
       for (int j = 0; j < FT_ITEMS; j++) {
         const int it = lw + j * FT_LOAD_WARPS;
         stage[j] = make_uint4(0, 0, 0, 0);
-        if (it < 2 * FT_KEYS) {
+        if (!via_tma && it < 2 * FT_KEYS) {
           const int p = p0 + (it >> 1);
           int64_t tok = -1;
           if (p < k1) tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + p] : base + p;
@@ -191,17 +208,26 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - 2) >> 1) & 1, &abort_flag, 5) && ok;
       if (tid == 160) FT_TRACE(0, tile);               // buffer free, stores start
       uint8_t* dst0 = smem + FS_K + buf * FT_TILE;
+      if (!via_tma) {
 #pragma unroll
-      for (int j = 0; j < FT_ITEMS; j++) {
-        const int it = lw + j * FT_LOAD_WARPS;
-        if (it < 2 * FT_KEYS) {
-          const int key = it >> 1, ch = (it & 1) * 32 + lane;
-          *reinterpret_cast<uint4*>(dst0 + (key >> 3) * FT_KS + ch * FT_CS + (key & 7) * 16) = stage[j];
+        for (int j = 0; j < FT_ITEMS; j++) {
+          const int it = lw + j * FT_LOAD_WARPS;
+          if (it < 2 * FT_KEYS) {
+            const int key = it >> 1, ch = (it & 1) * 32 + lane;
+            *reinterpret_cast<uint4*>(dst0 + tc::sw128_off(key, ch, FT_BLK)) = stage[j];
+          }
         }
       }
       if (lw == 0 && lane == 0) s_mask[buf] = mk;
-      tc::fence_async_smem();
-      tc::mbar_arrive(&k_full[buf]);
+      if (via_tma && lw == 0 && lane == 0) {
+        // one thread arms the barrier with the byte count and fires the tensor copy; the other loader
+        // threads just arrive, the phase completes when the 64 KB have landed
+        tc::mbar_arrive_expect_tx(&k_full[buf], FT_KEYS * LATENT * 2);
+        tma_load_tile(dst0, &tmap, (int)(base + p0), &k_full[buf]);
+      } else {
+        tc::fence_async_smem();
+        tc::mbar_arrive(&k_full[buf]);
+      }
       if (tid == 160) FT_TRACE(1, tile);               // tile published
     }
   } else if (warp == 4) {
@@ -214,13 +240,14 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         const int b = t & 1;
         const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
         const uint32_t p_addr = tc::smem_u32(smem + FS_P + b * 8192);
-        const uint64_t ad0 = tc::make_sdesc(k_addr, FT_KS, FT_CS);
+        // V^T: M = 128 channels = two 64-channel blocks (leading offset), K = keys in 8-row atoms of 1 KB
+        const uint64_t ad0 = tc::make_sdesc_sw128(k_addr, FT_BLK, 1024);
         const uint64_t bd0 = tc::make_sdesc(p_addr, FP_LBO, FP_SBO);
 #pragma unroll
         for (int mt = 0; mt < 4; mt++)
 #pragma unroll
           for (int kk = 0; kk < FT_KEYS / 16; kk++)
-            tc::mma_f16(tO + mt * 64, tc::sdesc_advance(ad0, mt * 16 * FT_CS + kk * 2 * FT_KS),
+            tc::mma_f16(tO + mt * 64, tc::sdesc_advance(ad0, mt * 2 * FT_BLK + kk * 2048),
                         tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
         tc::mma_commit(&t_done[b]);
       };
@@ -242,10 +269,11 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         FT_TRACE(3, tile);                             // operands ready, QK^T issue starts
         const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
         const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
-        const uint64_t bd0 = tc::make_sdesc(k_addr, FT_CS, FT_KS);
+        // keys as N in 1 KB atoms; 16 channels = 32 B inside the 128-byte row, 64 channels per block
+        const uint64_t bd0 = tc::make_sdesc_sw128(k_addr, 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < LATENT / 16; kk++)       // S = Q K^T
-          tc::mma_f16(tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO), tc::sdesc_advance(bd0, kk * 2 * FT_CS),
+          tc::mma_f16(tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO), tc::sdesc_advance(bd0, (kk >> 2) * FT_BLK + (kk & 3) * 32),
                       idesc_s, kk > 0);
         tc::mma_commit(&s_full[b]);
         FT_TRACE(4, tile);                             // QK^T issued
@@ -454,8 +482,39 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
       return HK_ERR_CUDA;
     attr_set[dev] = true;
   }
+  // tensor map over the latent cache for the dense path: [row][block 8][64 x fp16]; the row extent is
+  // only an upper bound for the copy engine's bounds check (rows are addressed by coordinate)
+  alignas(64) CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  int use_tma = 0;
+  static const bool tma_disabled = getenv("HK_MLA_NO_TMA") != nullptr;   // debug switch: vector-load path only
+  if (!a.raw_idx && !tma_disabled) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+          qres == cudaDriverEntryPointSuccess)
+        encode = (EncodeFn)fn;
+      looked_up = true;
+    }
+    if (encode) {
+      const cuuint64_t dims[3] = {64, (cuuint64_t)1 << 31, 8};
+      const cuuint64_t strides[2] = {LATENT * 2, 128};
+      const cuuint32_t box[3] = {64, FT_KEYS, 8};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void*)a.ckv, dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        use_tma = 1;
+    }
+  }
   dim3 grid(a.n_split, a.m);
-  mla_flash_tc_kernel<<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr());
+  mla_flash_tc_kernel<<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 

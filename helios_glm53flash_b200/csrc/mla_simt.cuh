@@ -167,6 +167,33 @@ __global__ __launch_bounds__(128) void lse_combine_kernel(
   *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + t * 4) = pk;
 }
 
+// ---- merge of S partial sets into ONE partial set (still un-normalised): the per-GPU reduction before
+// the cross-GPU exchange, so that only 2,056 B per (row, head) cross NVLink ----
+__global__ __launch_bounds__(128) void lse_merge_partials_kernel(
+    const float* __restrict__ part_m, const float* __restrict__ part_l, const float* __restrict__ part_acc,
+    int n_split, int64_t rows, float* __restrict__ out_m, float* __restrict__ out_l, float* __restrict__ out_acc) {
+  const int64_t r = blockIdx.x;
+  const int t = threadIdx.x;
+  float gm = -INFINITY;
+  for (int s = 0; s < n_split; s++) gm = fmaxf(gm, part_m[(size_t)s * rows + r]);
+  float gl = 0.f;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (gm != -INFINITY) {
+    for (int s = 0; s < n_split; s++) {
+      const float ms = part_m[(size_t)s * rows + r];
+      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
+      gl += sc * part_l[(size_t)s * rows + r];
+      const float4 a = *reinterpret_cast<const float4*>(part_acc + ((size_t)s * rows + r) * LATENT + t * 4);
+      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
+    }
+  }
+  *reinterpret_cast<float4*>(out_acc + (size_t)r * LATENT + t * 4) = o;
+  if (t == 0) {
+    out_m[r] = gm;
+    out_l[r] = gl;
+  }
+}
+
 // ---- split-KV across GPUs: peer signal + combine over peer-mapped partial buffers ----
 // Rank g publishes "my partial of step `epoch` is complete" by storing `epoch` into slot g of every
 // rank's flag array (its own included).  The stores are system-scope releases issued after a

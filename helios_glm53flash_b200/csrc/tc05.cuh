@@ -216,6 +216,19 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
   return d;
 }
 
+// 128-byte-swizzle descriptor (layout type 2 in bits [61,64)): rows of 128 bytes, atoms of 8 rows
+// (1 KB, the stride offset); the tile base must be 1 KB aligned.  K-major operands ignore the leading
+// offset; MN-major operands use it as the distance between blocks of 64 M/N elements.
+__device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return make_sdesc(smem_addr, lbo_bytes, sbo_bytes) | ((uint64_t)2 << 61);
+}
+
+// byte offset of 16-byte chunk `c` of 128-byte row `r` in a 128-byte-swizzled tile whose blocks of
+// 8 chunks (64 elements of the contiguous dimension) are `block_bytes` apart
+__device__ __forceinline__ uint32_t sw128_off(int r, int c, uint32_t block_bytes) {
+  return (uint32_t)(c >> 3) * block_bytes + (uint32_t)r * 128 + (uint32_t)(((c & 7) ^ (r & 7)) << 4);
+}
+
 // descriptor of the same tile advanced by `bytes` (start-address field only; no carry into LBO for
 // the offsets used here: shared addresses stay below 256 KB = 14 bits of 16-byte units)
 __device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) {

@@ -1,5 +1,6 @@
 // Self test of the tcgen05 / TMEM helper layer (tc05.cuh): one CTA computes D = A * B with fp16
-// operands staged in the no-swizzle canonical layouts and dumps the raw TMEM accumulator
+// operands staged in the no-swizzle canonical layouts (or, per operand, the 128-byte-swizzle layouts
+// a TMA tensor copy with 128-byte rows produces) and dumps the raw TMEM accumulator
 // (all 128 lanes x N columns), so the host can check both the arithmetic and the row <-> lane
 // mapping of each instruction shape.
 #include "hk_common.cuh"
@@ -11,11 +12,12 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
                                                             const __half* __restrict__ B,
                                                             float* __restrict__ D, int M, int N,
                                                             int K, int flags, int* status) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const bool b_mn = flags & 1, a_mn = flags & 2, swap_a = flags & 0x100, swap_b = flags & 0x200;
+  const bool a_sw = flags & 4, b_sw = flags & 8;   // 128-byte swizzle: rows of 128 B, 16-byte chunk c of row r at c ^ (r % 8)
   const int tid = threadIdx.x, warp = tid >> 5;
   uint8_t* sA = smem;
   uint8_t* sB = smem + 128 * 128 * 2;
@@ -34,7 +36,17 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   for (int i = tid; i < (128 * 128 * 2 + 256 * 128 * 2) / 16; i += 128)
     reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
-  if (!a_mn) {
+  // swizzled forms: K-major = [K block of 64][row][128 B], block stride rows*128; MN-major =
+  // [MN block of 64][k][128 B], block stride K*128 (the leading-dimension byte offset of the descriptor)
+  const uint32_t blk_a = a_mn ? K * 128 : 128 * 128, blk_b = b_mn ? K * 128 : 256 * 128;
+  if (a_sw) {
+    const int inner = a_mn ? M / 8 : (int)kchunks, outer = a_mn ? K : M;   // outer = 128-byte row index
+    for (int i = tid; i < outer * inner; i += 128) {
+      const int r = i / inner, c = i % inner;
+      const uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)r * inner * 8 + c * 8);
+      *reinterpret_cast<uint4*>(sA + tc::sw128_off(r, c, blk_a)) = v;
+    }
+  } else if (!a_mn) {
     for (int i = tid; i < M * (int)kchunks; i += 128) {
       int r = i / kchunks, kc = i % kchunks;
       uint4 v = *reinterpret_cast<const uint4*>(A + (size_t)r * K + kc * 8);
@@ -48,7 +60,14 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
       *reinterpret_cast<uint4*>(sA + tc::mnmajor_off(k, mc, lbo_a, sbo_a)) = v;
     }
   }
-  if (!b_mn) {
+  if (b_sw) {
+    const int inner = b_mn ? N / 8 : (int)kchunks, outer = b_mn ? K : N;
+    for (int i = tid; i < outer * inner; i += 128) {
+      const int r = i / inner, c = i % inner;
+      const uint4 v = *reinterpret_cast<const uint4*>(B + (size_t)r * inner * 8 + c * 8);
+      *reinterpret_cast<uint4*>(sB + tc::sw128_off(r, c, blk_b)) = v;
+    }
+  } else if (!b_mn) {
     for (int i = tid; i < N * (int)kchunks; i += 128) {
       int r = i / kchunks, kc = i % kchunks;
       uint4 v = *reinterpret_cast<const uint4*>(B + (size_t)r * K + kc * 8);
@@ -74,6 +93,16 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
                            : tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, lbo_a, sbo_a);
       uint64_t bd = swap_b ? tc::make_sdesc(tc::smem_u32(sB) + kk * 2 * lbo_b, sbo_b, lbo_b)
                            : tc::make_sdesc(tc::smem_u32(sB) + kk * 2 * lbo_b, lbo_b, sbo_b);
+      // swizzled: K-major steps 32 B inside the 128-byte row and one block per 64 K; MN-major steps
+      // two 8-row atoms (2 KB) per 16 K.  Leading offset = block stride, stride offset = 1 KB atom.
+      if (a_sw) {
+        const uint32_t st = tc::smem_u32(sA) + (a_mn ? kk * 2048 : (kk >> 2) * blk_a + (kk & 3) * 32);
+        ad = swap_a ? tc::make_sdesc_sw128(st, 1024, blk_a) : tc::make_sdesc_sw128(st, blk_a, 1024);
+      }
+      if (b_sw) {
+        const uint32_t st = tc::smem_u32(sB) + (b_mn ? kk * 2048 : (kk >> 2) * blk_b + (kk & 3) * 32);
+        bd = swap_b ? tc::make_sdesc_sw128(st, 1024, blk_b) : tc::make_sdesc_sw128(st, blk_b, 1024);
+      }
       tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
     }
     tc::mma_commit(&bar);

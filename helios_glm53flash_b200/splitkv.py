@@ -62,6 +62,7 @@ class SplitKVDecoder:
 
         self.flag_ptrs, self.m_ptrs, self.l_ptrs, self.acc_ptrs = table("flags"), table("m"), table("l"), table("acc")
         self.epoch = 0
+        self.workspace = None
         self._views()
         torch.cuda.synchronize()
         dist.barrier(group=group)
@@ -79,10 +80,16 @@ class SplitKVDecoder:
         import helios_glm53flash_b200 as hk
         t = self.torch
         self.epoch += 1
-        base = t.zeros(self.m, dtype=t.int64, device="cuda")
-        lens = t.full((self.m,), int(n_local_keys), dtype=t.int32, device="cuda")
-        hk.mla_dense_partial(q_lat, ckv_shard, base, lens, 0, self.part_m, self.part_l, self.part_acc, self.m,
-                             n_heads=self.n_heads, scale=scale)
+        if getattr(self, "_n_keys", None) != int(n_local_keys):
+            self._n_keys = int(n_local_keys)
+            self._base = t.zeros(self.m, dtype=t.int64, device="cuda")
+            self._lens = t.full((self.m,), self._n_keys, dtype=t.int32, device="cuda")
+            self._n_split = hk.mla_auto_splits(self.m, max(1, self._n_keys))
+            nbytes = hk.mla_partial_bytes(self._n_split, self.rows) if self._n_split > 1 else 256
+            self.workspace = t.empty(max(256, nbytes), dtype=t.uint8, device="cuda")
+        hk.mla_dense_partial_ws(q_lat, ckv_shard, self._base, self._lens, 0, self.part_m, self.part_l, self.part_acc,
+                                self.m, self._n_keys, n_heads=self.n_heads, scale=scale, n_split=self._n_split,
+                                workspace=self.workspace)
         if signal:
             hk.peer_signal(self.flag_ptrs, self.world, self.rank, self.epoch)
         hk.lse_combine_peers(self.m_ptrs, self.l_ptrs, self.acc_ptrs, self.world, self.rows, out, self.flags,

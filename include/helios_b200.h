@@ -169,6 +169,15 @@ int hk_mla_dense_partial(const void* q_lat, const void* ckv, const int64_t* kv_b
                          const int* kv_len, int pos_start, float* part_m, float* part_l,
                          float* part_acc, int m, int n_heads, float scale, void* stream);
 
+/* The same single partial set, computed with n_split splits over this GPU's SMs (workspace as for
+ * hk_mla_dense: hk_mla_partial_bytes(n_split, m*n_heads)) and merged on the GPU, so that a rank of a
+ * multi-GPU split-KV decode uses every SM yet exports only one (m, l, acc) set.  n_split = 0: the
+ * library picks from n_keys_hint (keys per row on this GPU).                                     */
+int hk_mla_dense_partial_ws(const void* q_lat, const void* ckv, const int64_t* kv_base,
+                            const int* kv_len, int pos_start, float* part_m, float* part_l,
+                            float* part_acc, int m, int n_heads, float scale, int n_split,
+                            int n_keys_hint, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Log-sum-exp combine of n_split partials (layout above; the three arrays may live anywhere,
  * split stride = `rows` elements for m/l and rows*512 for acc).
  * Restates the in-kernel merge src/cuda/attn/attn.cu:462-481 as a standalone kernel.           */

@@ -86,6 +86,9 @@ def main():
         torch.cuda.synchronize()
         err = max(err, float((out.float() - ref.float()).abs().max() / ref.float().abs().max()))
     flags = [err < 2e-3, status == 0, timeout_seen in (None, True), hk.read_device_status() == 0]
+    if not all(flags):
+        print(f"rank {rank}: err={err:.3e} first_status={status} timeout_seen={timeout_seen} checks={flags}",
+              file=sys.stderr, flush=True)
     ok = torch.tensor([int(all(flags))], device="cuda")
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
