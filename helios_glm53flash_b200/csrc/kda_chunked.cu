@@ -75,12 +75,13 @@ constexpr uint32_t P1_G = 16384;                         // f32 [64][132] cumula
 constexpr uint32_t P1_KR = P1_G + KC * P1_LD * 4;        // bf16 [64][136] raw k                    (later: X = inverse, f32 [64][68])
 constexpr uint32_t P1_L = P1_KR + KC * P1_LDH * 2;       // tf32 [2][16][132] left operands of ONE 16-row block (later: T operand, 16 KB)
 constexpr uint32_t P1_A = P1_L + 2 * 16 * P1_LD * 4;     // f32 [64][68] N = A beta (strictly lower); upper blocks = scratch
-constexpr uint32_t P1_P = P1_A + KC * P1_LDA * 4;        // f32 [4][128] G before each 16-token block
-constexpr uint32_t P1_EP = P1_P + 2048;                  // f32 [4][128] exp of the above
+constexpr uint32_t P1_P = P1_A + KC * P1_LDA * 4;     // f32 [4][128] G_last - (sum before each 16-token block)
+constexpr uint32_t P1_EP = P1_P + 2048;                  // f32 [4][128] e^{sum before the block}
 constexpr uint32_t P1_BETA = P1_EP + 2048;               // f32 [64]
-constexpr uint32_t P1_RK = P1_BETA + 256;                // f32 [64] beta_t / |k_t|
-constexpr uint32_t P1_DD = P1_RK + 256;                  // f32 [4][128] e^{P_ib - P_(ib-1)}: decay across one 16-token block
-constexpr uint32_t P1_SMEM = P1_DD + 2048;
+constexpr uint32_t P1_RK = P1_BETA + 256;                // f32 [64] 1 / |k_t|
+constexpr uint32_t P1_DD = P1_RK + 256;                  // f32 [6][128] decay between the starts of two blocks
+constexpr uint32_t P1_TOT = P1_DD + 3072;                // f32 [4][128] log-decay total of each block
+constexpr uint32_t P1_SMEM = P1_TOT + 2048;
 static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_LDH * 2 == KC * P1_LDA * 4, "aliases");
 
 // Optional stage timeline (compile with -DHK_KDA_TRACE): one CTA in the middle of the grid stamps clock64
@@ -94,18 +95,98 @@ __device__ long long hk_kda_trace[64];
 #define KS_TRACE(slot, ch) do { } while (0)
 #endif
 
-// 16 x 16 block product helper of the blocked triangular inverse: returns sum_k L[r][k] * R[k][c]
-__device__ __forceinline__ float dot16(const float* __restrict__ lrow, const float* __restrict__ rcol) {
-  float a0 = 0.f, a1 = 0.f;
+// 16 x 16 block product on the warp-level tensor cores: acc += L R with L, R fp32 in shared memory (row
+// pitch P1_LDA).  Each operand is split into a TF32 head and a TF32 tail and the three significant
+// partial products are accumulated in fp32, which keeps the result at fp32-class accuracy.
+__device__ __forceinline__ void block16_mma(const float* __restrict__ L, const float* __restrict__ R,
+                                            float (&acc)[2][4], int lane) {
+  const int g8 = lane >> 2, tig = lane & 3;
 #pragma unroll
-  for (int k = 0; k < 16; k += 4) {
-    const float4 l = *reinterpret_cast<const float4*>(lrow + k);
-    a0 = fmaf(l.x, rcol[(k + 0) * P1_LDA], a0);
-    a1 = fmaf(l.y, rcol[(k + 1) * P1_LDA], a1);
-    a0 = fmaf(l.z, rcol[(k + 2) * P1_LDA], a0);
-    a1 = fmaf(l.w, rcol[(k + 3) * P1_LDA], a1);
+  for (int ks = 0; ks < 2; ks++) {
+    const float af[4] = {L[g8 * P1_LDA + 8 * ks + tig], L[(g8 + 8) * P1_LDA + 8 * ks + tig],
+                         L[g8 * P1_LDA + 8 * ks + tig + 4], L[(g8 + 8) * P1_LDA + 8 * ks + tig + 4]};
+    uint32_t ah[4], al[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      ah[e] = f2tf32(af[e]);
+      al[e] = f2tf32(af[e] - __uint_as_float(ah[e]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+      const float b0 = R[(8 * ks + tig) * P1_LDA + 8 * nt + g8], b1 = R[(8 * ks + tig + 4) * P1_LDA + 8 * nt + g8];
+      const uint32_t b0h = f2tf32(b0), b1h = f2tf32(b1);
+      const uint32_t b0l = f2tf32(b0 - __uint_as_float(b0h)), b1l = f2tf32(b1 - __uint_as_float(b1h));
+      mma_tf32(acc[nt], al, b0h, b1h);
+      mma_tf32(acc[nt], ah, b0l, b1l);
+      mma_tf32(acc[nt], ah, b0h, b1h);
+    }
   }
-  return a0 + a1;
+}
+
+// writes sign * acc (fragment rows g8, g8 + 8; columns 8 nt + 2 tig, + 1) to a 16 x 16 block
+__device__ __forceinline__ void block16_store(float* __restrict__ D, const float (&acc)[2][4], float sign, int lane) {
+  const int g8 = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < 2; nt++) {
+    *reinterpret_cast<float2*>(D + g8 * P1_LDA + 8 * nt + 2 * tig) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+    *reinterpret_cast<float2*>(D + (g8 + 8) * P1_LDA + 8 * nt + 2 * tig) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+  }
+}
+
+// Stage 4 of the preparation kernel for one warp: rows 16 IB .. 16 IB + 15 of A (k warps) or B (q warps)
+// against the column blocks jb <= IB.  v = this thread's left-operand fragment values (rows g8, g8 + 8;
+// channel 32 m + 8 tig + j at index 8 m + j).  k-step ks of the m16n8k8 product contracts the channel
+// pairs (32 m + 8 tig + j, + 1), j = 2 (ks % 4), m = ks / 4, in MMA k slots tig and tig + 4.
+template <int IB>
+__device__ __forceinline__ void prep_ab_block(const float (&v)[2][32], bool is_q, const float* __restrict__ sR,
+                                              const float* __restrict__ sDD, const float* __restrict__ sBeta,
+                                              float* __restrict__ sA, uint8_t* __restrict__ unit, int g8, int tig) {
+  float acc[IB + 1][2][4];
+#pragma unroll
+  for (int jb = 0; jb <= IB; jb++)
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) acc[jb][nt][e] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < 16; ks++) {
+    const int m = ks >> 2, j = (ks & 3) * 2;
+    const int c0 = 32 * m + 8 * tig + j;
+    uint32_t a[4];
+    a[0] = f2tf32(v[0][8 * m + j]); a[1] = f2tf32(v[1][8 * m + j]);
+    a[2] = f2tf32(v[0][8 * m + j + 1]); a[3] = f2tf32(v[1][8 * m + j + 1]);
+#pragma unroll
+    for (int jb = 0; jb <= IB; jb++) {
+      float2 dd = make_float2(1.f, 1.f);
+      if (jb < IB) dd = *reinterpret_cast<const float2*>(sDD + (IB * (IB - 1) / 2 + jb) * KD + c0);
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) {
+        const float2 r2 = *reinterpret_cast<const float2*>(sR + (jb * 16 + nt * 8 + g8) * P1_LD + c0);
+        mma_tf32(acc[jb][nt], a, f2tf32(r2.x * dd.x), f2tf32(r2.y * dd.y));
+      }
+    }
+  }
+  // accumulator fragment: rows t = 16 IB + g8 (+8), columns s = 16 jb + 8 nt + 2 tig (+1)
+#pragma unroll
+  for (int jb = 0; jb <= IB; jb++)
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+      const int s0 = jb * 16 + nt * 8 + tig * 2;
+      const float b0 = sBeta[s0], b1 = sBeta[s0 + 1];
+#pragma unroll
+      for (int hrow = 0; hrow < 2; hrow++) {
+        const int t = IB * 16 + g8 + hrow * 8;
+        if (!is_q) {            // N = A beta, strictly lower
+          if (s0 < t) sA[t * P1_LDA + s0] = acc[jb][nt][2 * hrow] * b0;
+          if (s0 + 1 < t) sA[t * P1_LDA + s0 + 1] = acc[jb][nt][2 * hrow + 1] * b1;
+        } else {                // B beta, lower including the diagonal, fp16 operand tile
+          const float v0 = s0 <= t ? acc[jb][nt][2 * hrow] * b0 : 0.f;
+          const float v1 = s0 + 1 <= t ? acc[jb][nt][2 * hrow + 1] * b1 : 0.f;
+          *reinterpret_cast<uint32_t*>(unit + U_BB + (t >> 3) * SBO_K64 + (s0 >> 3) * LBO + (t & 7) * 16 + (s0 & 7) * 2) =
+              pack_h2(v0, v1);
+        }
+      }
+    }
 }
 
 __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
@@ -115,9 +196,9 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   extern __shared__ __align__(128) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + P1_G);
   uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
-  float* sL = reinterpret_cast<float*>(smem + P1_L);         // [0]: k rows, [1]: q rows of the current block
   float* sA = reinterpret_cast<float*>(smem + P1_A);
-  float* sP = reinterpret_cast<float*>(smem + P1_P);
+  float* sGLP = reinterpret_cast<float*>(smem + P1_P);
+  float* sTot = reinterpret_cast<float*>(smem + P1_TOT);
   float* sEP = reinterpret_cast<float*>(smem + P1_EP);
   float* sBeta = reinterpret_cast<float*>(smem + P1_BETA);
   float* sRk = reinterpret_cast<float*>(smem + P1_RK);
@@ -162,200 +243,222 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       else tc::prefetch_l2(g + (((size_t)b * seqlen + pt) * H + phead) * KD, KD * 4);
     }
   }
-  // ---- stage 1: all loads of the chunk in flight at once.  Warp w owns tokens w, w+8, ...; lane owns
-  //      channels 4*lane .. 4*lane+3.  g goes straight to shared memory, q and k stay in registers.
-  float qv[8][4], kv[8][4], rq[8];
+  // ---- stage 1: loads.  Ownership for stages 1-4 is the TF32 MMA fragment layout, so that the left
+  //      operands of the A/B products never pass through shared memory: warp -> (16-token row block ib,
+  //      k or q), lane = 4*g8 + tig owns rows 16 ib + g8 and + 8 and, of every 32 channels, the 8
+  //      starting at 8 tig (one 16-byte piece).  The row blocks are paired over the four scheduler
+  //      partitions as (0,3) and (1,2): block ib has ib+1 column blocks of work.
+  const int g8 = lane >> 2, tig = lane & 3;
+  const int ib = (0x22331100u >> (4 * warp)) & 3;
+  const bool is_q = warp & 1;
+  float v[2][32];                                           // [row half][4 pieces x 8 channels]
+  {
+    uint4 raw[2][4];
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int t = warp + 8 * i;
-    uint2 qr = make_uint2(0, 0), kr = make_uint2(0, 0);
-    float* gdst = sG + t * P1_LD + lane * 4;
-    if (t < n_valid) {
-      const __nv_bfloat16* tk = tok0 + (size_t)t * row;
-      qr = *reinterpret_cast<const uint2*>(tk + (size_t)head * KD + lane * 4);
-      kr = *reinterpret_cast<const uint2*>(tk + (size_t)(H + head) * KD + lane * 4);
-      __pipeline_memcpy_async(gdst, g0 + (size_t)t * H * KD + lane * 4, 16);
-    } else {
-      *reinterpret_cast<float4*>(gdst) = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int h = 0; h < 2; h++) {
+      const int t = 16 * ib + g8 + 8 * h;
+      const __nv_bfloat16* src = tok0 + (size_t)t * row + (size_t)(is_q ? head : H + head) * KD + 8 * tig;
+#pragma unroll
+      for (int m = 0; m < 4; m++)
+        raw[h][m] = t < n_valid ? *reinterpret_cast<const uint4*>(src + 32 * m) : make_uint4(0, 0, 0, 0);
     }
-    qv[i][0] = bf16lo(qr.x); qv[i][1] = bf16hi(qr.x); qv[i][2] = bf16lo(qr.y); qv[i][3] = bf16hi(qr.y);
-    kv[i][0] = bf16lo(kr.x); kv[i][1] = bf16hi(kr.x); kv[i][2] = bf16lo(kr.y); kv[i][3] = bf16hi(kr.y);
-    *reinterpret_cast<uint2*>(sKr + t * P1_LDH + lane * 4) = kr;
-  }
-  __pipeline_commit();
+    // g rows straight to shared memory (warp w: tokens w, w+8, ...; lane: 4 channels)
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const float sq = warp_sum(qv[i][0] * qv[i][0] + qv[i][1] * qv[i][1] + qv[i][2] * qv[i][2] + qv[i][3] * qv[i][3]);
-    const float sk = warp_sum(kv[i][0] * kv[i][0] + kv[i][1] * kv[i][1] + kv[i][2] * kv[i][2] + kv[i][3] * kv[i][3]);
-    rq[i] = rsqrtf(sq + 1e-6f);
-    const float rk = rsqrtf(sk + 1e-6f);
+    for (int i = 0; i < 8; i++) {
+      const int t = warp + 8 * i;
+      float* gdst = sG + t * P1_LD + lane * 4;
+      if (t < n_valid) __pipeline_memcpy_async(gdst, g0 + (size_t)t * H * KD + lane * 4, 16);
+      else *reinterpret_cast<float4*>(gdst) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __pipeline_commit();
+    // v rows (raw bf16) are parked where the T operand goes later; chunk cc of row t sits at cc ^ (t % 8)
+    // so that the conversion pass (8 rows of one chunk per quarter-warp) is free of bank conflicts
 #pragma unroll
-    for (int u = 0; u < 4; u++) kv[i][u] *= rk;
-    if (lane == 0) sRk[warp + 8 * i] = rk;
-  }
-  if (tid < KC) sBeta[tid] = tid < n_valid ? __bfloat162float(beta[((size_t)b * seqlen + t0 + tid) * H + head]) : 0.f;
-  for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
-  // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
-  if (tid < 192) {
-    const int blk = tid >> 5, e = tid & 31;             // 6 blocks x (16 rows x 2 chunks)
-    const int ib = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
-    const int jb = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
-    const int t = ib * 16 + (e >> 1), sc = jb * 2 + (e & 1);
-    *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < 4; j++) {
+      const int i = tid + 256 * j, t = i >> 4, cc = i & 15;
+      uint8_t* vdst = sT + t * 256 + ((cc ^ (t & 7)) << 4);
+      if (t < n_valid) __pipeline_memcpy_async(vdst, tok0 + (size_t)t * row + (size_t)(2 * H + head) * KD + cc * 8, 16);
+      else *reinterpret_cast<uint4*>(vdst) = make_uint4(0, 0, 0, 0);
+    }
+    __pipeline_commit();
+    if (tid < KC) sBeta[tid] = tid < n_valid ? __bfloat162float(beta[((size_t)b * seqlen + t0 + tid) * H + head]) : 0.f;
+    for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
+    // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
+    if (tid < 192) {
+      const int blk = tid >> 5, e = tid & 31;             // 6 blocks x (16 rows x 2 chunks)
+      const int zi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+      const int zj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+      const int t = zi * 16 + (e >> 1), sc = zj * 2 + (e & 1);
+      *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int t = 16 * ib + g8 + 8 * h;
+      float ss = 0.f;
+#pragma unroll
+      for (int m = 0; m < 4; m++) {
+        if (!is_q) *reinterpret_cast<uint4*>(sKr + t * P1_LDH + 32 * m + 8 * tig) = raw[h][m];
+        const uint32_t w4[4] = {raw[h][m].x, raw[h][m].y, raw[h][m].z, raw[h][m].w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float lo = bf16lo(w4[e]), hi = bf16hi(w4[e]);
+          v[h][8 * m + 2 * e] = lo;
+          v[h][8 * m + 2 * e + 1] = hi;
+          ss = fmaf(lo, lo, fmaf(hi, hi, ss));
+        }
+      }
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float rn = rsqrtf(ss + 1e-6f);                  // L2 normalisation of the q / k row
+      if (!is_q && tig == 0) sRk[t] = rn;
+#pragma unroll
+      for (int e = 0; e < 32; e++) v[h][e] *= rn;
+    }
   }
   KT_TRACE(1);
-  __pipeline_wait_prior(0);
+  __pipeline_wait_prior(1);                                 // g has landed; the v rows may still be in flight
   __syncthreads();
 
   KT_TRACE(2);
-  // ---- stage 2: inclusive cumulative log decay per channel; block bases P and e^P; chunk decay ----
-  if (tid < KD) {
-    float acc = 0.f;
-#pragma unroll 8
-    for (int t = 0; t < KC; t++) {
-      if ((t & 15) == 0) {
-        sDD[(t >> 4) * KD + tid] = (t == 0) ? 1.f : __expf(acc - sP[((t >> 4) - 1) * KD + tid]);
-        sP[(t >> 4) * KD + tid] = acc;
-        sEP[(t >> 4) * KD + tid] = __expf(acc);
-      }
-      acc += sG[t * P1_LD + tid];
-      sG[t * P1_LD + tid] = acc;
+  // ---- stage 2: log-decay sums per channel.  x_t = inclusive sum INSIDE the 16-token block (in place
+  //      over g), block totals, then the per-block tables: e^{P_blk} (P = sum before the block),
+  //      G_last - P_blk, the decay between two block starts, and the chunk decay e^{G_last}. ----
+  {
+    const int c = tid & 127, b0 = (tid >> 7) * 2;
+    float a0 = 0.f, a1 = 0.f;
+    float* p0 = sG + (16 * b0) * P1_LD + c;
+    float* p1 = p0 + 16 * P1_LD;
+#pragma unroll
+    for (int t = 0; t < 16; t++) {
+      a0 += p0[t * P1_LD]; p0[t * P1_LD] = a0;
+      a1 += p1[t * P1_LD]; p1[t * P1_LD] = a1;
     }
-    reinterpret_cast<float*>(unit + U_DEC)[tid] = __expf(acc);
+    sTot[b0 * KD + c] = a0;
+    sTot[(b0 + 1) * KD + c] = a1;
+  }
+  __syncthreads();
+  if (tid < KD) {
+    const float t0s = sTot[tid], t1s = sTot[KD + tid], t2s = sTot[2 * KD + tid], t3s = sTot[3 * KD + tid];
+    const float P1v = t0s, P2v = P1v + t1s, P3v = P2v + t2s, GL = P3v + t3s;
+    sGLP[tid] = GL; sGLP[KD + tid] = GL - P1v; sGLP[2 * KD + tid] = GL - P2v; sGLP[3 * KD + tid] = GL - P3v;
+    sEP[tid] = 1.f; sEP[KD + tid] = __expf(P1v); sEP[2 * KD + tid] = __expf(P2v); sEP[3 * KD + tid] = __expf(P3v);
+    // pair (ib, jb < ib) at index ib (ib - 1) / 2 + jb: e^{P_ib - P_jb}
+    sDD[tid] = __expf(t0s);
+    sDD[KD + tid] = __expf(t0s + t1s); sDD[2 * KD + tid] = __expf(t1s);
+    sDD[3 * KD + tid] = __expf(t0s + t1s + t2s); sDD[4 * KD + tid] = __expf(t1s + t2s); sDD[5 * KD + tid] = __expf(t2s);
+    reinterpret_cast<float*>(unit + U_DEC)[tid] = __expf(GL);
   }
   __syncthreads();
 
   KT_TRACE(3);
-  // ---- stage 3: Kt^T tile (rows = channels, K = tokens) straight to the workspace ----
-  for (int i = tid; i < KD * (KC / 8); i += 256) {
-    const int c = i & 127, tg = i >> 7;
-    const float glast = sG[(KC - 1) * P1_LD + c];
-    float kt[8];
+  // ---- stage 3 (two phases; k and q warps swap jobs so that x is read before it is overwritten) ----
+  // phase A: k warps write the Kt^T tile (rows = channels, K = tokens) straight to the workspace;
+  //          q warps scale their rows by e^{x}
+  if (!is_q) {
+    for (int i = (warp >> 1) * 32 + lane; i < KD * (KC / 8); i += 128) {
+      const int c = i & 127, tg = i >> 7;
+      const float glp = sGLP[(tg >> 1) * KD + c];
+      float kt[8];
 #pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int t = tg * 8 + u;
-      kt[u] = sBeta[t] * sRk[t] * bf16_bits_to_f(sKr[t * P1_LDH + c]) * __expf(glast - sG[t * P1_LD + c]);
+      for (int u = 0; u < 8; u++) {
+        const int t = tg * 8 + u;
+        kt[u] = sBeta[t] * sRk[t] * bf16_bits_to_f(sKr[t * P1_LDH + c]) * __expf(glp - sG[t * P1_LD + c]);
+      }
+      uint4 p;
+      p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
+      *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
     }
-    uint4 p;
-    p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
-    *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const float* xr = sG + (16 * ib + g8 + 8 * h) * P1_LD + 8 * tig;
+#pragma unroll
+      for (int m = 0; m < 4; m++) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xr + 32 * m), x1 = *reinterpret_cast<const float4*>(xr + 32 * m + 4);
+        v[h][8 * m + 0] *= __expf(fmaxf(x0.x, -85.f)); v[h][8 * m + 1] *= __expf(fmaxf(x0.y, -85.f));
+        v[h][8 * m + 2] *= __expf(fmaxf(x0.z, -85.f)); v[h][8 * m + 3] *= __expf(fmaxf(x0.w, -85.f));
+        v[h][8 * m + 4] *= __expf(fmaxf(x1.x, -85.f)); v[h][8 * m + 5] *= __expf(fmaxf(x1.y, -85.f));
+        v[h][8 * m + 6] *= __expf(fmaxf(x1.z, -85.f)); v[h][8 * m + 7] *= __expf(fmaxf(x1.w, -85.f));
+      }
+    }
   }
-
   __syncthreads();
   KT_TRACE(4);
-  // ---- stage 3b: every (token, channel) gets its two exponentials, once: e = e^{G_t - P_blk} scales
-  //      the LEFT operands k^,q^ (kept in registers), 1/e scales the RIGHT operand
-  //      R[s][c] = k^_s e^{P_blk(s) - G_s}, which overwrites G in place (fp32: up to e^85 inside a block)
+  // phase B: k warps turn x into the RIGHT operand R[s][c] = k^_s e^{-x_s} (in place, fp32: up to e^85)
+  //          and scale their own rows by e^{x}; q warps emit Q+ = q^ e^{G_t} (fp16 tile rows 64..127)
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int t = warp + 8 * i, blk = t >> 4;
-    float4* gp = reinterpret_cast<float4*>(sG + t * P1_LD + lane * 4);
-    const float4 gt = *gp;
-    const float4 pb = *reinterpret_cast<const float4*>(sP + blk * KD + lane * 4);
-    const float x0 = fmaxf(gt.x - pb.x, -85.f), x1 = fmaxf(gt.y - pb.y, -85.f);
-    const float x2 = fmaxf(gt.z - pb.z, -85.f), x3 = fmaxf(gt.w - pb.w, -85.f);
-    const float e0 = __expf(x0), e1 = __expf(x1), e2 = __expf(x2), e3 = __expf(x3);
-    *gp = make_float4(kv[i][0] * __expf(-x0), kv[i][1] * __expf(-x1), kv[i][2] * __expf(-x2), kv[i][3] * __expf(-x3));
-    kv[i][0] *= e0; kv[i][1] *= e1; kv[i][2] *= e2; kv[i][3] *= e3;
-    qv[i][0] *= rq[i] * e0; qv[i][1] *= rq[i] * e1; qv[i][2] *= rq[i] * e2; qv[i][3] *= rq[i] * e3;
-  }
-
-  KT_TRACE(5);
-  // ---- stage 4: A and B on the warp-level tensor cores (TF32), one 16-token ROW block at a time.
-  //      Per block ib: its left operands go from the registers to shared memory (fp32 range is needed:
-  //      the factor spans e^{-85}..1), the right operand rows of all earlier blocks are advanced from
-  //      reference P_(ib-1) to P_ib by one multiplication, and the 16x16 blocks (ib, jb <= ib) are
-  //      plain TF32 products.  The same pass emits K+ = k^ e^{G_t} and Q+ = q^ e^{G_t}. ----
-  {
-    const int gq = lane >> 2, tig = lane & 3;
+  for (int h = 0; h < 2; h++) {
+    const int t = 16 * ib + g8 + 8 * h;
+    float* xr = sG + t * P1_LD + 8 * tig;
 #pragma unroll
-    for (int ib = 0; ib < 4; ib++) {
+    for (int m = 0; m < 4; m++) {
+      if (!is_q) {
+        float4 x0 = *reinterpret_cast<const float4*>(xr + 32 * m), x1 = *reinterpret_cast<const float4*>(xr + 32 * m + 4);
+        float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w}, r8[8];
 #pragma unroll
-      for (int half = 0; half < 2; half++) {
-        const int i = 2 * ib + half, t = warp + 8 * i, lr = t - 16 * ib;
-        const float4 ep = *reinterpret_cast<const float4*>(sEP + ib * KD + lane * 4);
-        const float k0 = kv[i][0], k1 = kv[i][1], k2 = kv[i][2], k3 = kv[i][3];
-        const float q0 = qv[i][0], q1 = qv[i][1], q2 = qv[i][2], q3 = qv[i][3];
-        *reinterpret_cast<uint4*>(sL + lr * P1_LD + lane * 4) = make_uint4(f2tf32(k0), f2tf32(k1), f2tf32(k2), f2tf32(k3));
-        *reinterpret_cast<uint4*>(sL + (16 + lr) * P1_LD + lane * 4) = make_uint4(f2tf32(q0), f2tf32(q1), f2tf32(q2), f2tf32(q3));
-        // chunk-start based copies: 4 channels = half of a 16-byte operand chunk
-        const int c = lane * 4;
-        uint2 kp, qp;
-        kp.x = pack_h2(k0 * ep.x, k1 * ep.y); kp.y = pack_h2(k2 * ep.z, k3 * ep.w);
-        qp.x = pack_h2(q0 * ep.x, q1 * ep.y); qp.y = pack_h2(q2 * ep.z, q3 * ep.w);
-        *reinterpret_cast<uint2*>(sKV + (c >> 3) * 1024 + (t >> 3) * 128 + (t & 7) * 16 + (c & 7) * 2) = kp;
-        *reinterpret_cast<uint2*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (c >> 3) * LBO + (t & 7) * 16 + (c & 7) * 2) = qp;
-      }
-      if (ib > 0) {
-        // rows of the earlier blocks (this thread's own tokens below 16*ib): reference P_(ib-1) -> P_ib
-        const float4 dd = *reinterpret_cast<const float4*>(sDD + ib * KD + lane * 4);
-#pragma unroll
-        for (int i = 0; i < 2 * ib; i++) {
-          float4* rp = reinterpret_cast<float4*>(sG + (warp + 8 * i) * P1_LD + lane * 4);
-          float4 rv = *rp;
-          rv.x *= dd.x; rv.y *= dd.y; rv.z *= dd.z; rv.w *= dd.w;
-          *rp = rv;
+        for (int e = 0; e < 8; e++) {
+          const float xc = fmaxf(xs[e], -85.f);
+          r8[e] = v[h][8 * m + e] * __expf(-xc);
+          v[h][8 * m + e] *= __expf(xc);
         }
+        *reinterpret_cast<float4*>(xr + 32 * m) = make_float4(r8[0], r8[1], r8[2], r8[3]);
+        *reinterpret_cast<float4*>(xr + 32 * m + 4) = make_float4(r8[4], r8[5], r8[6], r8[7]);
+      } else {
+        const float* ep = sEP + ib * KD + 32 * m + 8 * tig;
+        const float4 e0 = *reinterpret_cast<const float4*>(ep), e1 = *reinterpret_cast<const float4*>(ep + 4);
+        uint4 p;
+        p.x = pack_h2(v[h][8 * m + 0] * e0.x, v[h][8 * m + 1] * e0.y); p.y = pack_h2(v[h][8 * m + 2] * e0.z, v[h][8 * m + 3] * e0.w);
+        p.z = pack_h2(v[h][8 * m + 4] * e1.x, v[h][8 * m + 5] * e1.y); p.w = pack_h2(v[h][8 * m + 6] * e1.z, v[h][8 * m + 7] * e1.w);
+        *reinterpret_cast<uint4*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (4 * m + tig) * LBO + (t & 7) * 16) = p;
       }
-      __syncthreads();
-      // units of this row block: (column block jb <= ib, 8-column half nt)
-      for (int unit_i = warp; unit_i < 2 * (ib + 1); unit_i += 8) {
-        const int jb = unit_i >> 1, nt = unit_i & 1;
-        float acck[4] = {0.f, 0.f, 0.f, 0.f}, accq[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* lk0 = sL + gq * P1_LD;
-        const float* lq0 = sL + (16 + gq) * P1_LD;
-        const float* rrow = sG + (jb * 16 + nt * 8 + gq) * P1_LD;
-#pragma unroll 4
-        for (int ks = 0; ks < KD / 8; ks++) {
-          const int c = ks * 8 + tig;
-          uint32_t ak[4], aq[4];
-          ak[0] = __float_as_uint(lk0[c]); ak[1] = __float_as_uint(lk0[8 * P1_LD + c]);
-          ak[2] = __float_as_uint(lk0[c + 4]); ak[3] = __float_as_uint(lk0[8 * P1_LD + c + 4]);
-          aq[0] = __float_as_uint(lq0[c]); aq[1] = __float_as_uint(lq0[8 * P1_LD + c]);
-          aq[2] = __float_as_uint(lq0[c + 4]); aq[3] = __float_as_uint(lq0[8 * P1_LD + c + 4]);
-          const uint32_t b0 = f2tf32(rrow[c]);
-          const uint32_t b1 = f2tf32(rrow[c + 4]);
-          mma_tf32(acck, ak, b0, b1);
-          mma_tf32(accq, aq, b0, b1);
-        }
-        // fragment: rows t = 16 ib + gq (+8), columns s = 16 jb + 8 nt + 2 tig (+1)
-        const int s0 = jb * 16 + nt * 8 + tig * 2;
-        const float b0 = sBeta[s0], b1 = sBeta[s0 + 1];
-#pragma unroll
-        for (int hrow = 0; hrow < 2; hrow++) {
-          const int t = ib * 16 + gq + hrow * 8;
-          if (s0 < t) sA[t * P1_LDA + s0] = acck[2 * hrow] * b0;
-          if (s0 + 1 < t) sA[t * P1_LDA + s0 + 1] = acck[2 * hrow + 1] * b1;
-          const float v0 = s0 <= t ? accq[2 * hrow] * b0 : 0.f;
-          const float v1 = s0 + 1 <= t ? accq[2 * hrow + 1] * b1 : 0.f;
-          *reinterpret_cast<uint32_t*>(unit + U_BB + (t >> 3) * SBO_K64 + (s0 >> 3) * LBO + (t & 7) * 16 + (s0 & 7) * 2) =
-              pack_h2(v0, v1);
-        }
-      }
-      __syncthreads();
     }
   }
+  __syncthreads();
+
+  KT_TRACE(5);
+  // ---- stage 4: A and B on the warp-level tensor cores (TF32).  Every warp multiplies its own 16
+  //      rows (fragments from registers) with the R rows of the column blocks jb <= ib; R of an earlier
+  //      block is moved from its own reference P_jb to P_ib by the pair decay while it is loaded.  The
+  //      contraction runs over the channels in the order the registers hold them. ----
+  switch (ib) {
+    case 0: prep_ab_block<0>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
+    case 1: prep_ab_block<1>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
+    case 2: prep_ab_block<2>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
+    default: prep_ab_block<3>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
+  }
+  if (!is_q) {
+    // K+ = k^ e^{G_t}: first half of the [K+ | V] operand
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int t = 16 * ib + g8 + 8 * h;
+#pragma unroll
+      for (int m = 0; m < 4; m++) {
+        const float* ep = sEP + ib * KD + 32 * m + 8 * tig;
+        const float4 e0 = *reinterpret_cast<const float4*>(ep), e1 = *reinterpret_cast<const float4*>(ep + 4);
+        uint4 p;
+        p.x = pack_h2(v[h][8 * m + 0] * e0.x, v[h][8 * m + 1] * e0.y); p.y = pack_h2(v[h][8 * m + 2] * e0.z, v[h][8 * m + 3] * e0.w);
+        p.z = pack_h2(v[h][8 * m + 4] * e1.x, v[h][8 * m + 5] * e1.y); p.w = pack_h2(v[h][8 * m + 6] * e1.z, v[h][8 * m + 7] * e1.w);
+        *reinterpret_cast<uint4*>(sKV + (4 * m + tig) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
+      }
+    }
+  }
+  __pipeline_wait_prior(0);                                 // v rows
+  __syncthreads();
   KT_TRACE(6);
   // from here on sG, sKr and sL are dead: the V half of sKV, sX and sT take their place
 
   // ---- stage 5: V -> B operand columns 128..255, then the blocked
   //      inverse X = (I + N)^-1 in fp32 and its fp16 copy T as the A operand ----
-  for (int i = tid; i < KC * (KD / 8); i += 256) {
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = tid + 256 * j;
     const int t = (i & 7) + ((i >> 7) << 3), cc = (i >> 3) & 15;
-    uint8_t* dst = sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16;
-    if (t < n_valid) {
-      // bf16 -> fp16 needs a register pass: load, convert, store
-      const uint4 vr = *reinterpret_cast<const uint4*>(tok0 + (size_t)t * row + (size_t)(2 * H + head) * KD + cc * 8);
-      uint4 p;
-      p.x = pack_h2(bf16lo(vr.x), bf16hi(vr.x)); p.y = pack_h2(bf16lo(vr.y), bf16hi(vr.y));
-      p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
-      *reinterpret_cast<uint4*>(dst) = p;
-    } else {
-      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-    }
+    const uint4 vr = *reinterpret_cast<const uint4*>(sT + t * 256 + ((cc ^ (t & 7)) << 4));   // bf16 -> fp16
+    uint4 p;
+    p.x = pack_h2(bf16lo(vr.x), bf16hi(vr.x)); p.y = pack_h2(bf16lo(vr.y), bf16hi(vr.y));
+    p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
+    *reinterpret_cast<uint4*>(sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
   }
-  // rows 64..127 of the T operand are never produced: zero, so the unused TMEM lanes stay finite
-  for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < KC * P1_LDA; i += 256) sX[i] = 0.f;
   __syncthreads();
   KT_TRACE(7);
@@ -379,28 +482,31 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   __syncthreads();
   KT_TRACE(8);
-  // 5b: off-diagonal blocks by distance d: Y_ij = sum_{m=j}^{i-1} N_im X_mj (kept in the unused
-  //     mirror block (j,i) of sA), then X_ij = -X_ii Y_ij
+  // 5b: off-diagonal blocks.  M_im = X_ii N_im for the six pairs i > m (kept in the unused mirror block
+  //     (m, i) of sA), then by distance d = i - j: X_ij = - sum_{m=j}^{i-1} M_im X_mj.  One warp per
+  //     16x16 block, products on the warp-level tensor cores with split operands (fp32-class accuracy).
+  if (warp < 6) {
+    const int i = warp < 1 ? 1 : (warp < 3 ? 2 : 3), m = warp - (i * (i - 1)) / 2;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    block16_mma(sX + (i * 16) * P1_LDA + i * 16, sA + (i * 16) * P1_LDA + m * 16, acc, lane);
+    block16_store(sA + (m * 16) * P1_LDA + i * 16, acc, 1.f, lane);
+  }
+  __syncthreads();
 #pragma unroll 1
   for (int d = 1; d < 4; d++) {
-    const int nb = 4 - d;                                 // blocks (i, i-d), i = d..3
-    for (int o = tid; o < nb * 256; o += 256) {
-      const int i = d + (o >> 8), j = i - d, r = (o >> 4) & 15, c = o & 15;
-      float acc = 0.f;
+    if (warp < 4 - d) {
+      const int i = d + warp, j = warp;
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       for (int m = j; m < i; m++)
-        acc += dot16(sA + (i * 16 + r) * P1_LDA + m * 16, sX + (m * 16) * P1_LDA + j * 16 + c);
-      sA[(j * 16 + r) * P1_LDA + i * 16 + c] = acc;       // mirror block as scratch
-    }
-    __syncthreads();
-    for (int o = tid; o < nb * 256; o += 256) {
-      const int i = d + (o >> 8), j = i - d, r = (o >> 4) & 15, c = o & 15;
-      const float v = dot16(sX + (i * 16 + r) * P1_LDA + i * 16, sA + (j * 16) * P1_LDA + i * 16 + c);
-      sX[(i * 16 + r) * P1_LDA + j * 16 + c] = -v;
+        block16_mma(sA + (m * 16) * P1_LDA + i * 16, sX + (m * 16) * P1_LDA + j * 16, acc, lane);
+      block16_store(sX + (i * 16) * P1_LDA + j * 16, acc, -1.f, lane);
     }
     __syncthreads();
   }
   KT_TRACE(9);
-  // 5c: T = fp16(X) as the K-major A operand (K = 64): lanes = 8 rows x 4 chunks
+  // 5c: T = fp16(X) as the K-major A operand (K = 64): lanes = 8 rows x 4 chunks.  Rows 64..127 of the
+  //     operand are never produced: zero, so the unused TMEM lanes stay finite
+  for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < KC * (KC / 8); i += 256) {
     const int t = (i & 7) + ((i >> 6) << 3), jc = (i >> 3) & 7;
     const float4 v0 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8);

@@ -34,20 +34,22 @@
 
 namespace hk {
 
-constexpr int FT_KEYS = 64;                       // keys per tile
+constexpr int FT_KEYS = 48;                       // keys per tile
+constexpr int FT_NBUF = 3;                        // key tiles in flight
 constexpr int FT_HEADS = 64;
 constexpr int FT_THREADS = 384;
 constexpr int FT_LOAD_WARPS = 7;                  // warps 5-11
 constexpr int FT_LOADERS = FT_LOAD_WARPS * 32;
 constexpr int FT_ITEMS = (2 * FT_KEYS + FT_LOAD_WARPS - 1) / FT_LOAD_WARPS;   // half-rows per loader warp and tile
-constexpr uint32_t FT_BLK = 64 * 128;             // one block of 64 channels: 64 key rows x 128 B
-constexpr uint32_t FT_TILE = 8 * FT_BLK;          // 65536
+constexpr uint32_t FT_BLK = FT_KEYS * 128;        // one block of 64 channels: one 128-byte row per key
+constexpr uint32_t FT_TILE = 8 * FT_BLK;          // 49152
 constexpr uint32_t FQ_LBO = 128, FQ_SBO = 64 * 128;  // Q operand [64 heads][512] K-major
-constexpr uint32_t FP_LBO = 128, FP_SBO = 8 * 128;   // P operand [64 heads][64 keys] K-major
+constexpr uint32_t FP_LBO = 128, FP_SBO = (FT_KEYS / 8) * 128;   // P operand [64 heads][keys] K-major
+constexpr uint32_t FP_BYTES = FT_HEADS * FT_KEYS * 2;
 constexpr uint32_t FS_Q = 0;                      // 65536
-constexpr uint32_t FS_K = 65536;                  // 2 x 65536, 1 KB aligned
-constexpr uint32_t FS_P = FS_K + 2 * FT_TILE;     // 2 x 8192
-constexpr uint32_t FS_MISC = FS_P + 2 * 8192;     // alpha[2][64], m[64], l[64], masks, flags
+constexpr uint32_t FS_K = 65536;                  // FT_NBUF tiles, 1 KB aligned
+constexpr uint32_t FS_P = FS_K + FT_NBUF * FT_TILE; // 2 x FP_BYTES
+constexpr uint32_t FS_MISC = FS_P + 2 * FP_BYTES;  // alpha[2][64], m[64], l[64], masks, flags
 constexpr uint32_t FS_SMEM = FS_MISC + 1536 + 1024;   // + slack to align the base to 1 KB (swizzle atoms)
 constexpr int FT_POLL_NS = 40;                    // poll back-off of the waiting warps
 constexpr float LOG2E = 1.4426950408889634f;
@@ -84,9 +86,11 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   float* s_alpha = reinterpret_cast<float*>(smem + FS_MISC);       // [2][64]
   float* s_m = s_alpha + 128;
   float* s_l = s_m + 64;
-  unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_l + 64);  // [2]
-  int* s_flag = reinterpret_cast<int*>(s_mask + 2);                // [2]
-  __shared__ uint64_t k_full[2], s_full[2], s_free[2], p_full[2], t_done[2];
+  unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(s_l + 64);  // [FT_NBUF]
+  int* s_flag = reinterpret_cast<int*>(s_mask + 4);                // [2]
+  // per key tile buffer: k_full (tile landed), t_done (its V^T P^T finished); per S / P buffer (two):
+  // s_full, s_free, p_full
+  __shared__ uint64_t k_full[FT_NBUF], t_done[FT_NBUF], s_full[2], s_free[2], p_full[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -110,12 +114,15 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
 
   if (tid == 0) {
 #pragma unroll
-    for (int b = 0; b < 2; b++) {
+    for (int b = 0; b < FT_NBUF; b++) {
       tc::mbar_init(&k_full[b], FT_LOADERS);
+      tc::mbar_init(&t_done[b], 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
       tc::mbar_init(&s_full[b], 1);
       tc::mbar_init(&s_free[b], 128);
       tc::mbar_init(&p_full[b], 128);
-      tc::mbar_init(&t_done[b], 1);
       s_flag[b] = 0;
     }
     tc::mbar_fence_init();
