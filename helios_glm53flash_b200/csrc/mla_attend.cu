@@ -65,7 +65,8 @@ static int launch_simt(const MlaArgs& a, cudaStream_t s) {
 
 static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
                    __half* out, cudaStream_t s) {
-  lse_combine_kernel<false><<<(unsigned)rows, 128, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
+  if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
+  lse_combine_kernel<false><<<(unsigned)rows, 256, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
                                                             n_split, rows, out);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
@@ -265,7 +266,8 @@ HK_API int hk_mla_dense_partial_ws(const void* q_lat, const void* ckv, const int
   if (tc) st = mla_flash_tc_launch(a, s);
   if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
   if (st != HK_OK) return st;
-  lse_merge_partials_kernel<<<(unsigned)rows, 128, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows,
+  if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
+  lse_merge_partials_kernel<<<(unsigned)rows, 256, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows,
                                                            part_m, part_l, part_acc);
   HK_LAUNCH_CHECK();
   return HK_OK;
@@ -284,9 +286,9 @@ HK_API int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* p
                                const float* const* ptrs_acc, int n_split, int64_t rows,
                                void* out_f16, void* stream) {
   using namespace hk;
-  HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && n_split >= 1 && rows >= 0);
+  HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && n_split >= 1 && n_split <= LSE_MAX_SPLITS && rows >= 0);
   if (rows == 0) return HK_OK;
-  lse_combine_kernel<true><<<(unsigned)rows, 128, 0, as_stream(stream)>>>(
+  lse_combine_kernel<true><<<(unsigned)rows, 256, 0, as_stream(stream)>>>(
       nullptr, nullptr, nullptr, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16);
   HK_LAUNCH_CHECK();
   return HK_OK;

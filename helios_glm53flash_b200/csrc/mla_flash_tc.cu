@@ -146,20 +146,24 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     if (n_tiles > 0) {
       // Q: item = (head group, chunk quad); lanes = 8 heads x 4 chunks -> one 128-byte core matrix per octet
       const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
+#pragma unroll 1
+      for (int it0 = lw; it0 < 128; it0 += 4 * FT_LOAD_WARPS) {      // 128 items, four in flight per warp
+        uint4 qs[4];
 #pragma unroll
-      for (int j = 0; j < FT_ITEMS; j++) {
-        const int it = lw + j * FT_LOAD_WARPS;
-        if (it < 128) {
-          const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
-          stage[j] = *reinterpret_cast<const uint4*>(q + (size_t)h * LATENT + ch * 8);
+        for (int u = 0; u < 4; u++) {
+          const int it = it0 + u * FT_LOAD_WARPS;
+          if (it < 128) {
+            const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
+            qs[u] = *reinterpret_cast<const uint4*>(q + (size_t)h * LATENT + ch * 8);
+          }
         }
-      }
 #pragma unroll
-      for (int j = 0; j < FT_ITEMS; j++) {
-        const int it = lw + j * FT_LOAD_WARPS;
-        if (it < 128) {
-          const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3);
-          *reinterpret_cast<uint4*>(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16) = stage[j];
+        for (int u = 0; u < 4; u++) {
+          const int it = it0 + u * FT_LOAD_WARPS;
+          if (it < 128) {
+            const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3);
+            *reinterpret_cast<uint4*>(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16) = qs[u];
+          }
         }
       }
     }
@@ -175,21 +179,21 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int pp = q0 + half * 32 + lane;
-          if (pp < k1) {
+          if (half * 32 + lane < FT_KEYS && pp < k1) {
             const int tk = a.raw_idx[(size_t)r * a.kidx + pp];
             if (tk >= 0) tc::prefetch_l2(a.ckv + (size_t)tk * LATENT, LATENT * 2);
           }
         }
       }
     };
-    prefetch_tile(1);
-    prefetch_tile(2);
-    prefetch_tile(3);
+    prefetch_tile(FT_NBUF - 1);
+    prefetch_tile(FT_NBUF);
+    prefetch_tile(FT_NBUF + 1);
     for (int tile = 0; tile < n_tiles; tile++) {
-      const int buf = tile & 1;
+      const int buf = tile % FT_NBUF;
       const int p0 = k0 + tile * FT_KEYS;
       const bool via_tma = tile_is_tma(tile);
-      prefetch_tile(tile + 4);
+      prefetch_tile(tile + FT_NBUF + 2);
       // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
 #pragma unroll
       for (int j = 0; j < FT_ITEMS; j++) {
@@ -207,12 +211,12 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int p = p0 + half * 32 + lane;
-          bool v = p < k1;
+          bool v = half * 32 + lane < FT_KEYS && p < k1;
           if (v && sparse) v = a.raw_idx[(size_t)r * a.kidx + p] >= 0;
           mk |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
         }
       }
-      if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - 2) >> 1) & 1, &abort_flag, 5) && ok;
+      if (tile >= FT_NBUF) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - FT_NBUF) / FT_NBUF) & 1, &abort_flag, 5) && ok;
       if (tid == 160) FT_TRACE(0, tile);               // buffer free, stores start
       uint8_t* dst0 = smem + FS_K + buf * FT_TILE;
       if (!via_tma) {
@@ -244,9 +248,9 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       const uint32_t idesc_s = tc::make_idesc(64, FT_KEYS, tc::FMT_F16, tc::FMT_F16, false, false);
       const uint32_t idesc_o = tc::make_idesc(128, FT_HEADS, tc::FMT_F16, tc::FMT_F16, true, false);
       auto gemm2 = [&](int t) {                        // O^T += V^T P^T of tile t
-        const int b = t & 1;
-        const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
-        const uint32_t p_addr = tc::smem_u32(smem + FS_P + b * 8192);
+        const int b = t & 1, kb = t % FT_NBUF;
+        const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
+        const uint32_t p_addr = tc::smem_u32(smem + FS_P + b * FP_BYTES);
         // V^T: M = 128 channels = two 64-channel blocks (leading offset), K = keys in 8-row atoms of 1 KB
         const uint64_t ad0 = tc::make_sdesc_sw128(k_addr, FT_BLK, 1024);
         const uint64_t bd0 = tc::make_sdesc(p_addr, FP_LBO, FP_SBO);
@@ -256,10 +260,10 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
           for (int kk = 0; kk < FT_KEYS / 16; kk++)
             tc::mma_f16(tO + mt * 64, tc::sdesc_advance(ad0, mt * 2 * FT_BLK + kk * 2048),
                         tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
-        tc::mma_commit(&t_done[b]);
+        tc::mma_commit(&t_done[kb]);
       };
       for (int tile = 0; tile < n_tiles; tile++) {
-        const int b = tile & 1;
+        const int b = tile & 1, kb = tile % FT_NBUF;
         // If the previous tile's P is already published, retire that tile first: its key buffer is
         // then refilled while this tile's QK^T runs.  Otherwise QK^T goes first and hides the softmax.
         bool g2_issued_early = false;
@@ -270,11 +274,11 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
           FT_TRACE(6, tile - 1);
           g2_issued_early = true;
         }
-        ok = tc::mbar_wait<FT_POLL_NS>(&k_full[b], (tile >> 1) & 1, &abort_flag, 1) && ok;
+        ok = tc::mbar_wait<FT_POLL_NS>(&k_full[kb], (tile / FT_NBUF) & 1, &abort_flag, 1) && ok;
         if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&s_free[b], ((tile - 2) >> 1) & 1, &abort_flag, 2) && ok;
         tc::fence_after_sync();
         FT_TRACE(3, tile);                             // operands ready, QK^T issue starts
-        const uint32_t k_addr = tc::smem_u32(smem + FS_K + b * FT_TILE);
+        const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
         const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
         // keys as N in 1 KB atoms; 16 channels = 32 B inside the 128-byte row, 64 channels per block
         const uint64_t bd0 = tc::make_sdesc_sw128(k_addr, 16, 1024);
@@ -309,20 +313,22 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     const int hA = warp * 16 + (lane >> 2), hB = hA + 8;
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     for (int tile = 0; tile < n_tiles; tile++) {
-      const int b = tile & 1;
-      ok = tc::mbar_wait<FT_POLL_NS>(&k_full[b], (tile >> 1) & 1, &abort_flag, 6) && ok;   // makes the tile's mask visible
+      const int b = tile & 1, kb = tile % FT_NBUF;
+      ok = tc::mbar_wait<FT_POLL_NS>(&k_full[kb], (tile / FT_NBUF) & 1, &abort_flag, 6) && ok;   // makes the tile's mask visible
       ok = tc::mbar_wait<FT_POLL_NS>(&s_full[b], (tile >> 1) & 1, &abort_flag, 7) && ok;
       tc::fence_after_sync();
       if (tid == 0) FT_TRACE(7, tile);                 // S ready
-      uint32_t sv[32];
-      tc::tmem_ld_16x256b_x8(tS + b * 64 + ((uint32_t)(warp * 32) << 16), sv);
+      uint32_t sv[FT_KEYS / 2];
+      static_assert(FT_KEYS == 48, "the S read below is 32 + 16 columns");
+      tc::tmem_ld_16x256b_x4(tS + b * 64 + ((uint32_t)(warp * 32) << 16), sv);
+      tc::tmem_ld_16x256b_x2(tS + b * 64 + 32 + ((uint32_t)(warp * 32) << 16), sv + 16);
       tc::tmem_ld_wait();
       tc::fence_before_sync();
       tc::mbar_arrive(&s_free[b]);
-      const unsigned long long mask = s_mask[b] >> (2 * quad);
+      const unsigned long long mask = s_mask[kb] >> (2 * quad);
       float tA = -INFINITY, tB = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
+      for (int j = 0; j < FT_KEYS / 8; j++) {
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const bool valid = (mask >> (8 * j + e)) & 1ull;
@@ -358,7 +364,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       if (rescale) {
         // rare: a head's reference max moved.  O^T (columns = heads) is rescaled after the previous
         // tile's V^T P^T has completed and before this tile's is issued (it waits for p_full below).
-        ok = tc::mbar_wait<FT_POLL_NS>(&t_done[b ^ 1], ((tile - 1) >> 1) & 1, &abort_flag, 8) && ok;
+        ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(tile - 1) % FT_NBUF], ((tile - 1) / FT_NBUF) & 1, &abort_flag, 8) && ok;
         tc::fence_after_sync();
 #pragma unroll 1
         for (int mt = 0; mt < 4; mt++) {
@@ -376,15 +382,15 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         tc::tmem_st_wait();
       }
       // the P buffer of this parity was last read by the V^T P^T of tile-2
-      if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[b], ((tile - 2) >> 1) & 1, &abort_flag, 9) && ok;
+      if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(tile - 2) % FT_NBUF], ((tile - 2) / FT_NBUF) & 1, &abort_flag, 9) && ok;
       // P operand [64 heads][64 keys] K-major: chunk j of a head's row holds keys 8j..8j+7; this thread
       // writes its two keys (4 bytes) of every chunk, for both of its heads
-      uint8_t* pA = smem + FS_P + b * 8192 + (hA >> 3) * FP_SBO + (hA & 7) * 16 + quad * 4;
-      uint8_t* pB = smem + FS_P + b * 8192 + (hB >> 3) * FP_SBO + (hB & 7) * 16 + quad * 4;
+      uint8_t* pA = smem + FS_P + b * FP_BYTES + (hA >> 3) * FP_SBO + (hA & 7) * 16 + quad * 4;
+      uint8_t* pB = smem + FS_P + b * FP_BYTES + (hB >> 3) * FP_SBO + (hB & 7) * 16 + quad * 4;
       const bool liveA = mA != -INFINITY, liveB = mB != -INFINITY;
       float sumA = 0.f, sumB = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
+      for (int j = 0; j < FT_KEYS / 8; j++) {
         const float a0 = liveA ? exp2f(__uint_as_float(sv[4 * j]) - mA) : 0.f;
         const float a1 = liveA ? exp2f(__uint_as_float(sv[4 * j + 1]) - mA) : 0.f;
         const float b0 = liveB ? exp2f(__uint_as_float(sv[4 * j + 2]) - mB) : 0.f;
@@ -411,7 +417,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       s_m[hB] = mB; s_l[hB] = lB;
     }
     // ---- epilogue (softmax warps): wait for the last V^T P^T, then write the result ----
-    if (n_tiles > 0) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, &abort_flag, 10) && ok;
+    if (n_tiles > 0) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(n_tiles - 1) % FT_NBUF], ((n_tiles - 1) / FT_NBUF) & 1, &abort_flag, 10) && ok;
     tc::fence_after_sync();
     softmax_group_sync();
     const size_t rows = (size_t)a.m * FT_HEADS;

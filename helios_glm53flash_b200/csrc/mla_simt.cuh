@@ -131,64 +131,100 @@ constexpr size_t MLA_SIMT_SMEM = (size_t)(8 * SIMT_HG * LATENT + 2 * 8 * SIMT_HG
 // ---- split-KV log-sum-exp combine: one CTA (128 threads x 4 channels) per (row, head) ----
 // gm = max m_s; gl = sum e^{m_s-gm} l_s; o = sum e^{m_s-gm} acc_s / gl; m_s = -inf weighs 0; all
 // -inf (or gl = 0) gives zeros (reference in-kernel merge: src/cuda/attn/attn.cu:462-481).
+// One CTA of 256 threads per (row, head).  The split weights e^{m_s-gm} are computed once into shared
+// memory (splits strided over the threads); the accumulators are then summed by two thread groups (even
+// and odd splits), thread = one float4 of the 512 channels, several independent loads in flight each.
+constexpr int LSE_MAX_SPLITS = 1024;
+
 template <bool PTRS>
-__global__ __launch_bounds__(128) void lse_combine_kernel(
+__device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                               const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
+                                               const float* const* __restrict__ ptrs_l,
+                                               const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows,
+                                               int64_t r, float& gm_out, float& gl_out, float4& o_out) {
+  __shared__ float s_w[LSE_MAX_SPLITS];
+  __shared__ float s_red[8];
+  __shared__ float4 s_o[128];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  float mloc = -INFINITY;
+  for (int s = t; s < n_split; s += 256) {
+    const float m = (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
+    s_w[s] = m;
+    mloc = fmaxf(mloc, m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+  if (lane == 0) s_red[warp] = mloc;
+  __syncthreads();
+  float gm = s_red[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) gm = fmaxf(gm, s_red[w]);
+  __syncthreads();
+  float lloc = 0.f;
+  for (int s = t; s < n_split; s += 256) {
+    const float m = s_w[s];
+    const float w = (m == -INFINITY) ? 0.f : __expf(m - gm);
+    s_w[s] = w;
+    lloc += w * (PTRS ? ptrs_l[s] : part_l + (size_t)s * rows)[r];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+  if (lane == 0) s_red[warp] = lloc;
+  __syncthreads();
+  float gl = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; w++) gl += s_red[w];
+  const int cq = t & 127, sg = t >> 7;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int s = sg; s < n_split; s += 2) {
+    const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
+    const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
+    const float4 a = PTRS ? __ldcv(ap) : __ldg(ap);   // peer memory: never through the read-only cache
+    const float w = s_w[s];
+    o.x = fmaf(w, a.x, o.x); o.y = fmaf(w, a.y, o.y); o.z = fmaf(w, a.z, o.z); o.w = fmaf(w, a.w, o.w);
+  }
+  if (sg == 1) s_o[cq] = o;
+  __syncthreads();
+  if (sg == 0) {
+    const float4 p = s_o[cq];
+    o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+  }
+  gm_out = gm; gl_out = gl; o_out = o;      // o is complete in threads 0..127
+}
+
+template <bool PTRS>
+__global__ __launch_bounds__(256) void lse_combine_kernel(
     const float* __restrict__ part_m, const float* __restrict__ part_l,
     const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
     const float* const* __restrict__ ptrs_l, const float* const* __restrict__ ptrs_acc,
     int n_split, int64_t rows, __half* __restrict__ out) {
   const int64_t r = blockIdx.x;
-  const int t = threadIdx.x;
-  float gm = -INFINITY;
-  for (int s = 0; s < n_split; s++) {
-    const float* pm = PTRS ? ptrs_m[s] : part_m + (size_t)s * rows;
-    gm = fmaxf(gm, pm[r]);
+  float gm, gl;
+  float4 o;
+  lse_reduce_row<PTRS>(part_m, part_l, part_acc, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, r, gm, gl, o);
+  if (threadIdx.x < 128) {
+    const float inv = gl > 0.f ? 1.f / gl : 0.f;
+    __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
+    __half2 h1 = __floats2half2_rn(o.z * inv, o.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + threadIdx.x * 4) = pk;
   }
-  float gl = 0.f;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (gm != -INFINITY) {
-    for (int s = 0; s < n_split; s++) {
-      const float* pm = PTRS ? ptrs_m[s] : part_m + (size_t)s * rows;
-      const float* pl = PTRS ? ptrs_l[s] : part_l + (size_t)s * rows;
-      const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
-      const float ms = pm[r];
-      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
-      gl += sc * pl[r];
-      const float4 a = *reinterpret_cast<const float4*>(pa + (size_t)r * LATENT + t * 4);
-      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
-    }
-  }
-  const float inv = gl > 0.f ? 1.f / gl : 0.f;
-  __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
-  __half2 h1 = __floats2half2_rn(o.z * inv, o.w * inv);
-  uint2 pk;
-  pk.x = *reinterpret_cast<uint32_t*>(&h0);
-  pk.y = *reinterpret_cast<uint32_t*>(&h1);
-  *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + t * 4) = pk;
 }
 
 // ---- merge of S partial sets into ONE partial set (still un-normalised): the per-GPU reduction before
 // the cross-GPU exchange, so that only 2,056 B per (row, head) cross NVLink ----
-__global__ __launch_bounds__(128) void lse_merge_partials_kernel(
+__global__ __launch_bounds__(256) void lse_merge_partials_kernel(
     const float* __restrict__ part_m, const float* __restrict__ part_l, const float* __restrict__ part_acc,
     int n_split, int64_t rows, float* __restrict__ out_m, float* __restrict__ out_l, float* __restrict__ out_acc) {
   const int64_t r = blockIdx.x;
-  const int t = threadIdx.x;
-  float gm = -INFINITY;
-  for (int s = 0; s < n_split; s++) gm = fmaxf(gm, part_m[(size_t)s * rows + r]);
-  float gl = 0.f;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (gm != -INFINITY) {
-    for (int s = 0; s < n_split; s++) {
-      const float ms = part_m[(size_t)s * rows + r];
-      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
-      gl += sc * part_l[(size_t)s * rows + r];
-      const float4 a = *reinterpret_cast<const float4*>(part_acc + ((size_t)s * rows + r) * LATENT + t * 4);
-      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
-    }
-  }
-  *reinterpret_cast<float4*>(out_acc + (size_t)r * LATENT + t * 4) = o;
-  if (t == 0) {
+  float gm, gl;
+  float4 o;
+  lse_reduce_row<false>(part_m, part_l, part_acc, nullptr, nullptr, nullptr, n_split, rows, r, gm, gl, o);
+  if (threadIdx.x < 128) *reinterpret_cast<float4*>(out_acc + (size_t)r * LATENT + threadIdx.x * 4) = o;
+  if (threadIdx.x == 0) {
     out_m[r] = gm;
     out_l[r] = gl;
   }
