@@ -47,6 +47,11 @@ SIGNATURES = {
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_lse_combine_ptrs": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
+    "hk_enable_peer_access": (_i, [_i]),
+    "hk_peer_region_alloc": (_i, [_sz, _vp, _vp]),
+    "hk_peer_region_open": (_i, [_vp, _vp]),
+    "hk_peer_region_close": (_i, [_vp]),
+    "hk_peer_region_free": (_i, [_vp]),
     "hk_lse_combine_peers": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _i, _vp]),
     "hk_q_latent": (_i, [_vp, _vp, _vp, _i, _vp]),
     "hk_o_absorb": (_i, [_vp, _vp, _vp, _i, _vp]),
@@ -283,6 +288,54 @@ def lse_combine_ptrs(ptrs_m, ptrs_l, ptrs_acc, n_split, rows, out, stream=None):
 def peer_signal(flag_ptrs, n_ranks, my_rank, epoch, stream=None):
     """Publish `epoch` into slot my_rank of every rank's flag array (flag_ptrs: device int64 tensor)."""
     _call("hk_peer_signal", _ptr(flag_ptrs), n_ranks, my_rank, epoch, _stream(stream))
+
+
+def enable_peer_access(peer_device):
+    """kernels of the current device may then dereference memory of `peer_device`"""
+    _call("hk_enable_peer_access", int(peer_device))
+
+
+class DeviceRegion:
+    """Raw device memory that is not owned by torch (an exchange region or a peer's mapping of one).
+    as_tensor(offset, nbytes, dtype) gives a torch view of a slice (through __cuda_array_interface__)."""
+
+    def __init__(self, ptr, nbytes):
+        self.ptr, self.nbytes = int(ptr), int(nbytes)
+
+    def data_ptr(self):
+        return self.ptr
+
+    def as_tensor(self, offset, nbytes, dtype):
+        torch = _require_cuda()
+
+        class _View:
+            pass
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (self.ptr + int(offset), False),
+                                      "version": 2, "strides": None}
+        return torch.as_tensor(v, device="cuda").view(dtype)
+
+
+def peer_region_alloc(nbytes):
+    """(DeviceRegion, 64-byte handle) of zeroed device memory that other processes can map"""
+    p, h = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    _call("hk_peer_region_alloc", int(nbytes), ctypes.byref(p), h)
+    return DeviceRegion(p.value, nbytes), h.raw
+
+
+def peer_region_open(handle, nbytes):
+    """map another process's region for kernels of the CURRENT device"""
+    p = ctypes.c_void_p()
+    _call("hk_peer_region_open", ctypes.create_string_buffer(handle, 64), ctypes.byref(p))
+    return DeviceRegion(p.value, nbytes)
+
+
+def peer_region_close(region):
+    _call("hk_peer_region_close", ctypes.c_void_p(region.ptr))
+
+
+def peer_region_free(region):
+    _call("hk_peer_region_free", ctypes.c_void_p(region.ptr))
 
 
 def lse_combine_peers(ptrs_m, ptrs_l, ptrs_acc, n_split, rows, out, local_flags, epoch, max_wait_ms=1000,

@@ -59,12 +59,24 @@ constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units: P stays below 2
 // hand-off points of its first 64 tiles; hk_debug_flash_trace copies the stamps to the host.
 #ifdef HK_FLASH_TRACE
 __device__ long long hk_flash_trace[64 * 16];
+__device__ unsigned long long hk_flash_cta[2 * 4096];   // per CTA: globaltimer at start and end
+__device__ __forceinline__ unsigned long long ft_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define FT_CTA_STAMP(which)                                                                       \
+  do {                                                                                             \
+    const unsigned cta = blockIdx.y * gridDim.x + blockIdx.x;                                      \
+    if (threadIdx.x == 0 && cta < 4096) hk_flash_cta[2 * cta + (which)] = ft_globaltimer();        \
+  } while (0)
 #define FT_TRACE(slot, tile)                                                         \
   do {                                                                               \
     if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) hk_flash_trace[(tile) * 16 + (slot)] = clock64(); \
   } while (0)
 #else
 #define FT_TRACE(slot, tile) do { } while (0)
+#define FT_CTA_STAMP(which) do { } while (0)
 #endif
 
 __device__ __forceinline__ void softmax_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -96,6 +108,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sp = blockIdx.x, r = blockIdx.y;
+  FT_CTA_STAMP(0);
   const bool sparse = a.raw_idx != nullptr;
   int n;
   int64_t base = 0;
@@ -461,12 +474,16 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
+  FT_CTA_STAMP(1);
 }
 
 #ifdef HK_FLASH_TRACE
 }  // namespace hk
 extern "C" __attribute__((visibility("default"))) int hk_debug_flash_trace(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, hk::hk_flash_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : 3;
+}
+extern "C" __attribute__((visibility("default"))) int hk_debug_flash_cta(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, hk::hk_flash_cta, sizeof(unsigned long long) * 2 * 4096) == cudaSuccess ? 0 : 3;
 }
 namespace hk {
 #endif

@@ -2,7 +2,7 @@
 
 Rank g owns a contiguous slice of the latent cache.  A decode step is, on every rank:
   1. ``hk_mla_dense_partial`` over the local slice -> un-normalised (m, l, acc) partial in a buffer that
-     every peer has mapped (CUDA IPC; NVLink peer access),
+     every peer has mapped (CUDA inter-process handle opened by each peer on its own device; NVLink),
   2. ``hk_peer_signal``: store the step's epoch into this rank's slot of every rank's flag array,
   3. ``hk_lse_combine_peers``: bounded wait until all slots of the local flag array show the epoch,
      then read the G partial sets through their peer pointers (plain loads over NVLink) and write the
@@ -40,21 +40,26 @@ class SplitKVDecoder:
     def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000):
         import torch
         import torch.distributed as dist
-        from torch.multiprocessing.reductions import reduce_tensor
-        self.torch, self.dist = torch, dist
+        import helios_glm53flash_b200 as hk
+        self.torch, self.dist, self.hk = torch, dist, hk
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.m, self.n_heads, self.rows = m, n_heads, m * n_heads
         self.max_wait_ms = max_wait_ms
         self.lay = region_layout(self.rows, self.world)
-        self.local = torch.zeros(self.lay["total"], dtype=torch.uint8, device="cuda")
-        # exchange CUDA IPC handles (set-up only); keep the rebuilt peer tensors alive
-        fn, args = reduce_tensor(self.local)
+        # The exchange region is library-owned device memory with an inter-process handle; every peer
+        # opens the handle with ITS OWN device current, which is what makes the mapping usable by that
+        # device's kernels (set-up only: torch.distributed carries the 64-byte handles).
+        self.local, handle = hk.peer_region_alloc(self.lay["total"])
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (fn, args), group=group)
+        dist.all_gather_object(gathered, (handle, torch.cuda.current_device()), group=group)
         self.peers = []
-        for r, (f, a) in enumerate(gathered):
-            self.peers.append(self.local if r == self.rank else f(*a))
+        for r, (h, dev_index) in enumerate(gathered):
+            if r == self.rank:
+                self.peers.append(self.local)
+            else:
+                hk.enable_peer_access(dev_index)
+                self.peers.append(hk.peer_region_open(h, self.lay["total"]))
         bases = [p.data_ptr() for p in self.peers]
 
         def table(key):
@@ -69,10 +74,22 @@ class SplitKVDecoder:
 
     def _views(self):
         t, lay, rows = self.torch, self.lay, self.rows
-        self.flags = self.local[lay["flags"]:lay["flags"] + 4 * self.world].view(t.int32)
-        self.part_m = self.local[lay["m"]:lay["m"] + rows * 4].view(t.float32)
-        self.part_l = self.local[lay["l"]:lay["l"] + rows * 4].view(t.float32)
-        self.part_acc = self.local[lay["acc"]:lay["acc"] + rows * 2048].view(t.float32)
+        self.flags = self.local.as_tensor(lay["flags"], 4 * self.world, t.int32)
+        self.part_m = self.local.as_tensor(lay["m"], rows * 4, t.float32)
+        self.part_l = self.local.as_tensor(lay["l"], rows * 4, t.float32)
+        self.part_acc = self.local.as_tensor(lay["acc"], rows * 2048, t.float32)
+
+    def close(self):
+        """unmap the peers' regions, then (after a barrier: nobody still has it open) free the own one"""
+        self.torch.cuda.synchronize()
+        for r, p in enumerate(self.peers):
+            if r != self.rank and p is not None:
+                self.hk.peer_region_close(p)
+        self.peers = []
+        self.dist.barrier(group=self.group)
+        if self.local is not None:
+            self.hk.peer_region_free(self.local)
+            self.local = None
 
     def step(self, q_lat, ckv_shard, n_local_keys, out, scale, signal=True):
         """one decode step; q_lat [m, 64, 512] f16 (same on every rank), ckv_shard = this rank's rows,

@@ -199,6 +199,20 @@ int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
  * with plain loads over NVLink.  Epochs must increase from call to call; flags are never reset.
  * No counterpart in the reference (it is single-GPU for this path).                              */
 int hk_peer_signal(int* const* flag_ptrs, int n_ranks, int my_rank, int epoch, void* stream);
+
+/* Enables access from kernels of the current device to memory of `peer_device` (needed once per peer
+ * before the two calls around this one touch buffers of another GPU that were mapped into this
+ * process).  Idempotent; HK_ERR_UNSUPPORTED when the two GPUs have no peer path.                  */
+int hk_enable_peer_access(int peer_device);
+
+/* Exchange regions of the split-KV decode.  hk_peer_region_alloc: zeroed device memory on the current
+ * device plus its 64-byte inter-process handle.  hk_peer_region_open (in another process, with ITS OWN
+ * device current): a pointer that kernels of that device may read and write over NVLink.  A region is
+ * closed by every process that opened it before its owner frees it.                               */
+int hk_peer_region_alloc(size_t bytes, void** dev_ptr, void* handle_out_64);
+int hk_peer_region_open(const void* handle_64, void** dev_ptr);
+int hk_peer_region_close(void* dev_ptr);
+int hk_peer_region_free(void* dev_ptr);
 int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* ptrs_l,
                          const float* const* ptrs_acc, int n_split, int64_t rows, void* out_f16,
                          const int* local_flags, int epoch, int max_wait_ms, void* stream);

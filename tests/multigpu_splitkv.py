@@ -96,6 +96,7 @@ def main():
                           "us_per_step": float(t) * 1e3, "single_gpu_us": t1 * 1e3,
                           "hbm_gbs_aggregate": L * 1024 / (float(t) * 1e-3) / 1e9,
                           "timeout_path_ok": timeout_seen, "all_ranks_ok": bool(ok.item())}), flush=True)
+    dec.close()
     dist.destroy_process_group()
     sys.exit(0 if ok.item() else 1)
 

@@ -206,3 +206,50 @@ def test_peer_combine_on_one_gpu_and_bounded_wait_times_out_cleanly():
     _, full32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=np.zeros(m, np.int64),
                                kv_len=np.full(m, L, np.int32))
     assert max_rel(synth.f16_bits_to_f32(bits(out)).reshape(m, 64, 512), full32) < TOL
+
+
+def test_enable_peer_access_is_idempotent_and_rejects_bad_devices():
+    """own device: nothing to enable; a device index that does not exist: HK_ERR_INVALID; every other
+    visible GPU: enabled (or already enabled), twice in a row"""
+    cur = torch.cuda.current_device()
+    hk.enable_peer_access(cur)
+    with pytest.raises(Exception):
+        hk.enable_peer_access(torch.cuda.device_count() + 3)
+    for d in range(torch.cuda.device_count()):
+        if d != cur and torch.cuda.can_device_access_peer(cur, d):
+            hk.enable_peer_access(d)
+            hk.enable_peer_access(d)
+
+
+@pytest.mark.parametrize("m,L,n_split", [(1, 3000, 7), (2, 1111, 0), (1, 40, 1)])
+def test_partial_with_local_splits_equals_one_split_partial(m, L, n_split):
+    """hk_mla_dense_partial_ws: the splits over this GPU's SMs, merged on the GPU, give one partial set
+    that normalises to the dense result (and to the oracle)"""
+    inp = synth.mla_inputs(L, m, seed=33, cache_std=0.5)
+    rows = m * 64
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    base, lens = dev(np.zeros(m, np.int64)), dev(np.full(m, L, np.int32))
+    pm = torch.empty(rows, dtype=torch.float32, device="cuda")
+    pl = torch.empty(rows, dtype=torch.float32, device="cuda")
+    pa = torch.empty(rows, 512, dtype=torch.float32, device="cuda")
+    hk.mla_dense_partial_ws(q, c, base, lens, 0, pm, pl, pa, m, L, n_split=n_split)
+    out = torch.empty(rows, 512, dtype=torch.float16, device="cuda")
+    hk.lse_combine(pm, pl, pa, 1, rows, out)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    full16, full32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=np.zeros(m, np.int64),
+                                    kv_len=np.full(m, L, np.int32))
+    g = synth.f16_bits_to_f32(bits(out)).reshape(m, 64, 512)
+    assert max_rel(g, full32) < TOL
+
+
+def test_exchange_region_alloc_view_and_free():
+    """library-owned exchange region: zeroed, viewable as torch tensors, writable by kernels, freed"""
+    region, handle = hk.peer_region_alloc(4096)
+    assert len(handle) == 64 and region.data_ptr() % 256 == 0
+    v = region.as_tensor(256, 1024, torch.float32)
+    assert v.shape == (256,) and float(v.abs().sum()) == 0.0
+    v.fill_(2.0)
+    torch.cuda.synchronize()
+    assert float(region.as_tensor(0, 4096, torch.uint8).float().sum()) > 0
+    hk.peer_region_free(region)
