@@ -318,31 +318,41 @@ def main():
         dist.destroy_process_group()
 
 
-def _time_loop(torch, fns, iters=10, warm=2, flush=None):
-    """median time of running every callable of `fns` back to back (one launch chain), in ms"""
+def _time_loop(torch, fns, iters=10, warm=2, flush=None, sustain_ms=2.0):
+    """median device time, in ms, of ONE pass over the callables of `fns` run back to back.  The chain is
+    captured in a CUDA graph after the warm-up and replays are timed, so host launch latency is not in the
+    figure; a timed region holds as many replays as fill about `sustain_ms` (a decode loop keeps the GPU
+    busy: a single short launch after an idle gap would be timed at idle clocks)."""
     for _ in range(warm):
         for f in fns:
             f()
     torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+
+    def once(reps):
         if flush is not None:
             flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for f in fns:
-            f()
+        for _ in range(reps):
+            graph.replay()
         b.record()
         torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
-    ts.sort()
+        return a.elapsed_time(b) / reps
+
+    reps = max(1, min(200, int(sustain_ms / max(once(1), 1e-3) + 0.999)))
+    ts = sorted(once(reps) for _ in range(iters))
     return ts[len(ts) // 2]
 
 
 def side_measurements(hk, synth, torch, np):
     """Decode-side figures.  Each is the median device time of a chain of launches over DISTINCT
     per-layer buffers (34 KDA layers, 11 MLA layers, as in the hybrid trunk), divided by the number of
-    layers; L2 is flushed (256 MB write) before every chain unless the buffers exceed L2 on their own."""
+    layers; L2 is flushed (256 MB write) before every timed region unless the buffers exceed L2 on their
+    own.  A timed region repeats the chain until it lasts about 2 ms (see _time_loop)."""
     from gpu_util import dev, dev_bf16, dev_f16
     res = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")

@@ -10,6 +10,8 @@
 // histogram sweeps and two compaction sweeps).  Sweep 1 histograms the top 11 key bits, sweep 2 the
 // low 5 bits inside the crossing bucket, sweep 3 is a single ordered compaction that places the
 // "above" entries and the tie entries at once (their final offsets are known after sweep 2).
+#include <cooperative_groups.h>
+
 #include "hk_common.cuh"
 
 namespace hk {
@@ -184,7 +186,174 @@ __global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
   for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Rows of at most 65,536 scores (the decode case is ONE such row): a thread-block cluster of 8 CTAs
+// works on a row, CTA c on elements [8192 c, 8192 (c+1)), every thread on 8 consecutive elements that
+// stay in registers, so the row is read from global memory once and no sweep is longer than 8 keys
+// per thread.  The CTAs meet through distributed shared memory: per-CTA histograms are reduced
+// slice-wise into CTA 0, which finds the crossing bucket and later the threshold and hands them back;
+// the per-CTA counts of selected entries give every CTA the offset of its ordered output.
+// ------------------------------------------------------------------------------------------------
+#ifdef HK_TOPK_TRACE
+__device__ long long hk_topk_trace[16];
+#define TK_TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x == 0) hk_topk_trace[slot] = clock64(); } while (0)
+#else
+#define TK_TRACE(slot) do { } while (0)
+#endif
+constexpr int TKC_CTAS = 8;
+constexpr int TKC_MAX_T = TKC_CTAS * TK_THREADS * 8;      // 65536
+
+template <bool VEC>
+__global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void dsa_topk_cluster_kernel(
+    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k, int k_pad) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int c = (int)cluster.block_rank();
+  const int row_id = blockIdx.x / TKC_CTAS;
+  const uint16_t* row = scores + (size_t)row_id * s_stride;
+  int* row_o = out + (size_t)row_id * k_pad;
+  const int t = threadIdx.x;
+
+  __shared__ int hist[2048];       // this CTA's bucket counts
+  __shared__ int ghist[2048];      // CTA 0: counts of the whole row
+  __shared__ int low[32], glow[32];
+  __shared__ int scan_ws[TK_WARPS + 1];
+  __shared__ int meta[4];          // b1, count above b1 (later: above the threshold), selectable total, low bits
+  __shared__ int cta_cnt[TKC_CTAS];
+
+  TK_TRACE(0);
+  uint32_t key[8];
+  const int i8 = c * TK_THREADS + t;
+  load8<VEC>(row, i8, T, key);     // beyond T: key 0, never selectable
+  for (int i = t; i < 2048; i += TK_THREADS) hist[i] = 0;
+  if (t < 32) { low[t] = 0; glow[t] = 0; }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+    if (key[j] > KEY_NEG_INF) atomicAdd(&hist[key[j] >> 5], 1);
+  cluster.sync();
+  TK_TRACE(1);
+  // slice c of the buckets, summed over the CTAs, into CTA 0
+  if (t < 2048 / TKC_CTAS) {
+    const int bin = c * (2048 / TKC_CTAS) + t;
+    int sum = 0;
+#pragma unroll
+    for (int rk = 0; rk < TKC_CTAS; rk++) sum += cluster.map_shared_rank(hist, rk)[bin];
+    cluster.map_shared_rank(ghist, 0)[bin] = sum;
+  }
+  cluster.sync();
+  TK_TRACE(2);
+  if (c == 0) {
+    // thread t owns buckets 2047-2t and 2046-2t (descending); find where the running count crosses k
+    const int h_hi = ghist[2047 - 2 * t], h_lo = ghist[2046 - 2 * t];
+    int total_sel;
+    const int excl = block_exscan(h_hi + h_lo, scan_ws, &total_sel);
+    if (t == 0) { meta[0] = -1; meta[1] = 0; meta[2] = total_sel; }
+    __syncthreads();
+    if (total_sel >= k && k > 0) {
+      if (excl < k && excl + h_hi >= k) { meta[0] = 2047 - 2 * t; meta[1] = excl; }
+      else if (excl + h_hi < k && excl + h_hi + h_lo >= k) { meta[0] = 2046 - 2 * t; meta[1] = excl + h_hi; }
+    }
+    __syncthreads();
+    if (t < 3 * TKC_CTAS && t >= 3) cluster.map_shared_rank(meta, t / 3)[t % 3] = meta[t % 3];
+  }
+  cluster.sync();
+  TK_TRACE(3);
+  const int b1 = meta[0];
+  uint32_t thresh;
+  int cnt_gt, n_eq_take;
+  if (b1 < 0) {
+    // fewer than k selectable entries (or k == 0): take them all, no ties
+    thresh = KEY_NEG_INF;
+    cnt_gt = k > 0 ? meta[2] : 0;
+    n_eq_take = 0;
+    if (k == 0) thresh = 0xffffu;
+    cluster.sync();                // keeps the barrier count equal on both paths
+    cluster.sync();
+  } else {
+    // low 5 bits inside bucket b1: local counts, then added into CTA 0
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      if ((int)(key[j] >> 5) == b1) atomicAdd(&low[key[j] & 31u], 1);
+    __syncthreads();
+    if (t < 32 && low[t] > 0) atomicAdd(&cluster.map_shared_rank(glow, 0)[t], low[t]);
+    cluster.sync();
+    if (c == 0 && t < 32) {
+      // lane l owns low value 31-l (descending)
+      const int hv = glow[31 - t];
+      int incl = hv;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (t >= o) incl += n;
+      }
+      const int need = k - meta[1];
+      int found = (incl - hv < need && incl >= need) ? 1 : 0;
+      const unsigned who = __ballot_sync(0xffffffffu, found);
+      const int src = __ffs((int)who) - 1;
+      const int lowbits = __shfl_sync(0xffffffffu, 31 - t, src);
+      const int above = __shfl_sync(0xffffffffu, meta[1] + incl - hv, src);
+      if (t < TKC_CTAS) {
+        int* m = cluster.map_shared_rank(meta, t);
+        m[3] = lowbits;
+        m[1] = above;
+      }
+    }
+    cluster.sync();
+    thresh = ((uint32_t)b1 << 5) | (uint32_t)meta[3];
+    cnt_gt = meta[1];
+    n_eq_take = k - cnt_gt;
+  }
+  TK_TRACE(4);
+  // ---- ordered compaction: thread masks, block scan, CTA offsets from the per-CTA totals ----
+  uint32_t m_gt = 0, m_eq = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if (key[j] > thresh && key[j] > KEY_NEG_INF) m_gt |= 1u << j;
+    if (key[j] == thresh && n_eq_take > 0) m_eq |= 1u << j;
+  }
+  int tot;
+  const int ex = block_exscan(__popc(m_gt) | (__popc(m_eq) << 16), scan_ws, &tot);
+  if (t < TKC_CTAS) cluster.map_shared_rank(cta_cnt, t)[c] = tot;
+  cluster.sync();
+  TK_TRACE(5);
+  int base_gt = 0, base_eq = 0, all_eq = 0;
+#pragma unroll
+  for (int rk = 0; rk < TKC_CTAS; rk++) {
+    const int v = cta_cnt[rk];
+    if (rk < c) { base_gt += v & 0xffff; base_eq += v >> 16; }
+    all_eq += v >> 16;
+  }
+  int o_gt = base_gt + (ex & 0xffff);
+  int o_eq = base_eq + (ex >> 16);
+  const int ibase = i8 * 8;
+  while (m_gt) {
+    const int j = __ffs((int)m_gt) - 1;
+    m_gt &= m_gt - 1;
+    row_o[o_gt++] = ibase + j;
+  }
+  while (m_eq) {
+    const int j = __ffs((int)m_eq) - 1;
+    m_eq &= m_eq - 1;
+    if (o_eq < n_eq_take) row_o[cnt_gt + o_eq] = ibase + j;
+    o_eq++;
+  }
+  if (c == 0) {
+    const int emitted = cnt_gt + min(all_eq, n_eq_take);
+    for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
+  }
+  TK_TRACE(6);
+  cluster.sync();                  // no CTA leaves while a peer may still read its shared memory
+}
+
 }  // namespace hk
+
+#ifdef HK_TOPK_TRACE
+extern "C" __attribute__((visibility("default"))) int hk_debug_topk_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, hk::hk_topk_trace, sizeof(long long) * 16) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, int T, int k,
                        int k_pad, const int* t_ptr, int t_seq, void* stream) {
@@ -194,6 +363,15 @@ HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, in
   if (R == 0) return HK_OK;
   const bool vec = (s_stride % 8 == 0) && aligned(scores, 16);
   cudaStream_t s = as_stream(stream);
+  if (T <= TKC_MAX_T && !t_ptr) {
+    // rows of up to 65,536 scores: one 8-CTA cluster per row
+    if (vec)
+      dsa_topk_cluster_kernel<true><<<R * TKC_CTAS, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad);
+    else
+      dsa_topk_cluster_kernel<false><<<R * TKC_CTAS, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad);
+    HK_LAUNCH_CHECK();
+    return HK_OK;
+  }
   if (vec)
     dsa_topk_kernel<true><<<R, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad, t_ptr, t_seq);
   else

@@ -316,3 +316,23 @@ HK_API int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* 
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
+
+// One split-KV decode step of one rank in ONE host call: local partial (with local splits), signal,
+// bounded-wait combine over all ranks' partial sets.
+HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
+                               float* part_m, float* part_l, float* part_acc, int m, int n_heads, float scale,
+                               int n_split, int n_keys_hint, void* workspace, size_t workspace_bytes,
+                               int* const* flag_ptrs, const float* const* ptrs_m, const float* const* ptrs_l,
+                               const float* const* ptrs_acc, int n_ranks, int my_rank, int epoch,
+                               const int* local_flags, void* out_f16, int max_wait_ms, int signal, void* stream) {
+  int st = hk_mla_dense_partial_ws(q_lat, ckv_shard, kv_base, kv_len, 0, part_m, part_l, part_acc, m, n_heads, scale,
+                                   n_split, n_keys_hint, workspace, workspace_bytes, stream);
+  if (st != HK_OK) return st;
+  if (signal) {
+    st = hk_peer_signal(flag_ptrs, n_ranks, my_rank, epoch, stream);
+    if (st != HK_OK) return st;
+  }
+  return hk_lse_combine_peers(ptrs_m, ptrs_l, ptrs_acc, n_ranks, (int64_t)m * n_heads, out_f16, local_flags, epoch,
+                              max_wait_ms, stream);
+}
+

@@ -202,30 +202,48 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     prefetch_tile(FT_NBUF - 1);
     prefetch_tile(FT_NBUF);
     prefetch_tile(FT_NBUF + 1);
+    // Gathered rows: the row numbers a warp needs for a tile are fetched one tile AHEAD, one per lane
+    // (lane j: the row of item j; warp 0 also the rows behind the validity mask), and handed out by
+    // shuffle, so the row loads of a tile are not each behind an index load of their own.
+    auto item_index = [&](int tile_i, int j) -> int {      // row number of item j of this warp, -1 = hole
+      const int it = lw + j * FT_LOAD_WARPS;
+      const int p = k0 + tile_i * FT_KEYS + (it >> 1);
+      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? a.raw_idx[(size_t)r * a.kidx + p] : -1;
+    };
+    auto mask_index = [&](int tile_i, int half) -> int {   // warp 0: row number of key half*32 + lane
+      const int p = k0 + tile_i * FT_KEYS + half * 32 + lane;
+      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? a.raw_idx[(size_t)r * a.kidx + p] : -1;
+    };
+    int idx_next = item_index(0, lane), mk0_next = mask_index(0, 0), mk1_next = mask_index(0, 1);
     for (int tile = 0; tile < n_tiles; tile++) {
       const int buf = tile % FT_NBUF;
       const int p0 = k0 + tile * FT_KEYS;
       const bool via_tma = tile_is_tma(tile);
       prefetch_tile(tile + FT_NBUF + 2);
+      const int idx_cur = idx_next, mk0 = mk0_next, mk1 = mk1_next;
+      idx_next = item_index(tile + 1, lane);
+      mk0_next = mask_index(tile + 1, 0);
+      mk1_next = mask_index(tile + 1, 1);
       // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
 #pragma unroll
       for (int j = 0; j < FT_ITEMS; j++) {
         const int it = lw + j * FT_LOAD_WARPS;
         stage[j] = make_uint4(0, 0, 0, 0);
+        const int row_j = __shfl_sync(0xffffffffu, idx_cur, j);
         if (!via_tma && it < 2 * FT_KEYS) {
           const int p = p0 + (it >> 1);
           int64_t tok = -1;
-          if (p < k1) tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + p] : base + p;
+          if (p < k1) tok = sparse ? (int64_t)row_j : base + p;
           if (tok >= 0) stage[j] = ld_stream16(a.ckv + (size_t)tok * LATENT + ((it & 1) * 32 + lane) * 8);
         }
       }
-      unsigned long long mk = 0;                       // validity of the 64 key slots of this tile
+      unsigned long long mk = 0;                       // validity of the key slots of this tile
       if (lw == 0) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int p = p0 + half * 32 + lane;
           bool v = half * 32 + lane < FT_KEYS && p < k1;
-          if (v && sparse) v = a.raw_idx[(size_t)r * a.kidx + p] >= 0;
+          if (v && sparse) v = (half ? mk1 : mk0) >= 0;
           mk |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
         }
       }
@@ -290,6 +308,15 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         ok = tc::mbar_wait<FT_POLL_NS>(&k_full[kb], (tile / FT_NBUF) & 1, &abort_flag, 1) && ok;
         if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&s_free[b], ((tile - 2) >> 1) & 1, &abort_flag, 2) && ok;
         tc::fence_after_sync();
+        // second chance after the wait for this tile's keys: retiring the previous tile first frees its key
+        // buffer one QK^T earlier, and the refill of that buffer is what the next tiles wait for
+        if (tile >= 1 && !g2_issued_early && tc::mbar_try_wait(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
+          tc::fence_after_sync();
+          FT_TRACE(5, tile - 1);
+          gemm2(tile - 1);
+          FT_TRACE(6, tile - 1);
+          g2_issued_early = true;
+        }
         FT_TRACE(3, tile);                             // operands ready, QK^T issue starts
         const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
         const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);

@@ -125,6 +125,8 @@ def main():
     ap.add_argument("--case", required=True, help="one of: " + ", ".join(CASES) + ", or 'all'")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the call in a CUDA graph and time its replay (no host launch latency in the figure)")
     args = ap.parse_args()
     import torch
     import helios_glm53flash_b200 as hk
@@ -134,19 +136,26 @@ def main():
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            call = graph.replay
+        else:
+            call = fn
         ts = []
         for _ in range(args.iters):
             if buf is not None:
                 buf.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            fn()
+            call()
             b.record()
             torch.cuda.synchronize()
             ts.append(a.elapsed_time(b))
         ts.sort()
         ms = ts[len(ts) // 2]
-        print(json.dumps({"case": name, "desc": desc, "us": ms * 1e3, "algorithmic_GBps": nbytes / (ms * 1e-3) / 1e9,
+        print(json.dumps({"case": name + ("+graph" if args.graph else ""), "desc": desc, "us": ms * 1e3, "algorithmic_GBps": nbytes / (ms * 1e-3) / 1e9,
                           "device_status": hk.read_device_status()}), flush=True)
         del fn, buf
         torch.cuda.empty_cache()

@@ -24,14 +24,20 @@ def shard_tokens(n_tokens, rank, world):
 
 
 def region_layout(rows, world):
-    """byte offsets inside one rank's exchange region: flags | m | l | acc"""
-    off_flags = 0
-    off_m = 256
-    off_l = off_m + ((rows * 4 + 255) // 256) * 256
-    off_acc = off_l + ((rows * 4 + 255) // 256) * 256
-    total = off_acc + rows * 512 * 4
+    """byte offsets inside one rank's exchange region: flags | (m | l | acc) x 2.  The partial sets are
+    double buffered by step parity: a rank may already write step s+1 while a slower peer still reads
+    step s; it cannot reach step s+2 before that peer has signalled s+1, i.e. has finished reading s."""
     assert world * 4 <= 256
-    return {"flags": off_flags, "m": off_m, "l": off_l, "acc": off_acc, "total": total}
+    pad = ((rows * 4 + 255) // 256) * 256
+    lay = {"flags": 0}
+    off = 256
+    for par in (0, 1):
+        lay["m%d" % par] = off
+        lay["l%d" % par] = off + pad
+        lay["acc%d" % par] = off + 2 * pad
+        off += 2 * pad + rows * 512 * 4
+    lay["total"] = off
+    return lay
 
 
 class SplitKVDecoder:
@@ -65,7 +71,8 @@ class SplitKVDecoder:
         def table(key):
             return torch.tensor([b + self.lay[key] for b in bases], dtype=torch.int64, device="cuda")
 
-        self.flag_ptrs, self.m_ptrs, self.l_ptrs, self.acc_ptrs = table("flags"), table("m"), table("l"), table("acc")
+        self.flag_ptrs = table("flags")
+        self.m_ptrs, self.l_ptrs, self.acc_ptrs = [[table(k + str(par)) for par in (0, 1)] for k in ("m", "l", "acc")]
         self.epoch = 0
         self.workspace = None
         self._views()
@@ -75,9 +82,9 @@ class SplitKVDecoder:
     def _views(self):
         t, lay, rows = self.torch, self.lay, self.rows
         self.flags = self.local.as_tensor(lay["flags"], 4 * self.world, t.int32)
-        self.part_m = self.local.as_tensor(lay["m"], rows * 4, t.float32)
-        self.part_l = self.local.as_tensor(lay["l"], rows * 4, t.float32)
-        self.part_acc = self.local.as_tensor(lay["acc"], rows * 2048, t.float32)
+        self.part_m = [self.local.as_tensor(lay["m%d" % par], rows * 4, t.float32) for par in (0, 1)]
+        self.part_l = [self.local.as_tensor(lay["l%d" % par], rows * 4, t.float32) for par in (0, 1)]
+        self.part_acc = [self.local.as_tensor(lay["acc%d" % par], rows * 2048, t.float32) for par in (0, 1)]
 
     def close(self):
         """unmap the peers' regions, then (after a barrier: nobody still has it open) free the own one"""
@@ -104,13 +111,12 @@ class SplitKVDecoder:
             self._n_split = hk.mla_auto_splits(self.m, max(1, self._n_keys))
             nbytes = hk.mla_partial_bytes(self._n_split, self.rows) if self._n_split > 1 else 256
             self.workspace = t.empty(max(256, nbytes), dtype=t.uint8, device="cuda")
-        hk.mla_dense_partial_ws(q_lat, ckv_shard, self._base, self._lens, 0, self.part_m, self.part_l, self.part_acc,
-                                self.m, self._n_keys, n_heads=self.n_heads, scale=scale, n_split=self._n_split,
-                                workspace=self.workspace)
-        if signal:
-            hk.peer_signal(self.flag_ptrs, self.world, self.rank, self.epoch)
-        hk.lse_combine_peers(self.m_ptrs, self.l_ptrs, self.acc_ptrs, self.world, self.rows, out, self.flags,
-                             self.epoch, max_wait_ms=self.max_wait_ms)
+        par = self.epoch & 1
+        hk.mla_splitkv_step(q_lat, ckv_shard, self._base, self._lens, self.part_m[par], self.part_l[par],
+                            self.part_acc[par], self.m, self.n_heads, scale, self._n_split, self._n_keys, self.workspace,
+                            self.flag_ptrs, self.m_ptrs[par], self.l_ptrs[par], self.acc_ptrs[par], self.world,
+                            self.rank, self.epoch, self.flags, out,
+                            max_wait_ms=self.max_wait_ms, signal=signal)
 
 
 def merge_partials_numpy(parts):

@@ -200,6 +200,16 @@ int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
  * No counterpart in the reference (it is single-GPU for this path).                              */
 int hk_peer_signal(int* const* flag_ptrs, int n_ranks, int my_rank, int epoch, void* stream);
 
+/* One split-KV decode step of one rank in one call: hk_mla_dense_partial_ws over this rank's shard
+ * into its exchange region, hk_peer_signal (skipped when signal == 0: failure injection in tests),
+ * hk_lse_combine_peers.  Arguments as in those three calls.                                          */
+int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
+                        float* part_m, float* part_l, float* part_acc, int m, int n_heads, float scale,
+                        int n_split, int n_keys_hint, void* workspace, size_t workspace_bytes,
+                        int* const* flag_ptrs, const float* const* ptrs_m, const float* const* ptrs_l,
+                        const float* const* ptrs_acc, int n_ranks, int my_rank, int epoch,
+                        const int* local_flags, void* out_f16, int max_wait_ms, int signal, void* stream);
+
 /* Enables access from kernels of the current device to memory of `peer_device` (needed once per peer
  * before the two calls around this one touch buffers of another GPU that were mapped into this
  * process).  Idempotent; HK_ERR_UNSUPPORTED when the two GPUs have no peer path.                  */

@@ -79,5 +79,7 @@ def test_shard_and_region_layout():
         spans = [splitkv.shard_tokens(n, r, w) for r in range(w)]
         assert spans[0][0] == 0 and spans[-1][1] == n and all(spans[i][1] == spans[i + 1][0] for i in range(w - 1))
     lay = splitkv.region_layout(64, 8)
-    assert lay["m"] % 256 == 0 and lay["l"] % 256 == 0 and lay["acc"] % 256 == 0
-    assert lay["total"] == lay["acc"] + 64 * 2048
+    for par in (0, 1):
+        assert all(lay[k + str(par)] % 256 == 0 for k in ("m", "l", "acc"))
+    assert lay["m0"] >= 256 and lay["m1"] == lay["acc0"] + 64 * 2048      # two partial sets, one per step parity
+    assert lay["total"] == lay["acc1"] + 64 * 2048
