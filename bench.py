@@ -148,7 +148,19 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL may print a version banner on stdout when the communicator comes up; stdout carries exactly
+        # one JSON line, so the banner goes to stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     T, H, D = args.tokens, HEADS, DIM
     dim = 3 * H * D
@@ -281,7 +293,7 @@ def main():
 
     extras = {}
     if rank == 0 and not args.no_extras:
-        extras = side_measurements(hk, synth, torch, np)
+        extras = side_measurements(hk, synth, torch, np, local_rank)
 
     if rank == 0:
         peaks, peak_kind = _peaks()
@@ -348,7 +360,7 @@ def _time_loop(torch, fns, iters=10, warm=2, flush=None, sustain_ms=2.0):
     return ts[len(ts) // 2]
 
 
-def side_measurements(hk, synth, torch, np):
+def side_measurements(hk, synth, torch, np, gpu_index=0):
     """Decode-side figures.  Each is the median device time of a chain of launches over DISTINCT
     per-layer buffers (34 KDA layers, 11 MLA layers, as in the hybrid trunk), divided by the number of
     layers; L2 is flushed (256 MB write) before every timed region unless the buffers exceed L2 on their
@@ -384,6 +396,22 @@ def side_measurements(hk, synth, torch, np):
         res["mla_dense_decode_32k_b%d_us_per_layer" % B] = ms * 1e3
         res["mla_dense_decode_32k_b%d_hbm_gbs" % B] = B * L * 1024 / (ms * 1e-3) / 1e9
         res["mla_dense_decode_32k_b%d_splits" % B] = ns
+        if B == 8:
+            # SM clock under this kernel: a 0.4 s loop of the same chain with the sampler running
+            sampler = ClockSampler(gpu_index)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for f in fns:
+                    f()
+            torch.cuda.synchronize()
+            t0 = time.time()
+            while time.time() - t0 < 0.4:
+                for _ in range(50):
+                    graph.replay()
+                torch.cuda.synchronize()
+            t1 = time.time()
+            sampler.stop()
+            res["mla_dense_decode_32k_b8_clocks"] = sampler.summary(t0 + 0.1, t1)
         del cks
     # ---- indexer -> top-512 -> expand -> sparse MLA at 262,144 tokens of context, 11 layers ----
     npools, L, n_mla = 65536, 262144, 11

@@ -47,8 +47,8 @@ SIGNATURES = {
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_lse_combine_ptrs": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
     "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
-    "hk_mla_splitkv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _vp, _vp, _vp, _i, _i, _i,
-                                 _vp, _vp, _i, _i, _vp]),
+    "hk_mla_splitkv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _vp, _vp,
+                                 _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "hk_enable_peer_access": (_i, [_i]),
     "hk_peer_region_alloc": (_i, [_sz, _vp, _vp]),
     "hk_peer_region_open": (_i, [_vp, _vp]),
@@ -292,14 +292,16 @@ def peer_signal(flag_ptrs, n_ranks, my_rank, epoch, stream=None):
     _call("hk_peer_signal", _ptr(flag_ptrs), n_ranks, my_rank, epoch, _stream(stream))
 
 
-def mla_splitkv_step(q_lat, ckv_shard, kv_base, kv_len, part_m, part_l, part_acc, m, n_heads, scale, n_split,
-                     n_keys_hint, workspace, flag_ptrs, ptrs_m, ptrs_l, ptrs_acc, n_ranks, my_rank, epoch, local_flags,
-                     out, max_wait_ms=1000, signal=True, stream=None):
-    """partial over the local shard + signal + bounded-wait combine over all ranks, one host call"""
-    _call("hk_mla_splitkv_step", _ptr(q_lat), _ptr(ckv_shard), _ptr(kv_base), _ptr(kv_len), _ptr(part_m), _ptr(part_l),
-          _ptr(part_acc), m, n_heads, float(scale), n_split, n_keys_hint, _ptr(workspace),
-          0 if workspace is None else workspace.numel(), _ptr(flag_ptrs), _ptr(ptrs_m), _ptr(ptrs_l), _ptr(ptrs_acc),
-          n_ranks, my_rank, epoch, _ptr(local_flags), _ptr(out), max_wait_ms, int(bool(signal)), _stream(stream))
+def mla_splitkv_step(q_lat, ckv_shard, kv_base, kv_len, parts0, parts1, m, n_heads, scale, n_split, n_keys_hint,
+                     workspace, flag_ptrs, ptrs_m, ptrs_l, ptrs_acc, n_ranks, my_rank, step_ctr, local_flags, out,
+                     max_wait_ms=1000, signal=True, stream=None):
+    """partial over the local shard + signal + bounded-wait combine over all ranks, one host call;
+    parts0 / parts1 = (m, l, acc) tensors of this rank's two exchange sets, step_ctr = device int32[1]"""
+    _call("hk_mla_splitkv_step", _ptr(q_lat), _ptr(ckv_shard), _ptr(kv_base), _ptr(kv_len), _ptr(parts0[0]),
+          _ptr(parts0[1]), _ptr(parts0[2]), _ptr(parts1[0]), _ptr(parts1[1]), _ptr(parts1[2]), m, n_heads, float(scale),
+          n_split, n_keys_hint, _ptr(workspace), workspace.numel(), _ptr(flag_ptrs), _ptr(ptrs_m), _ptr(ptrs_l),
+          _ptr(ptrs_acc), n_ranks, my_rank, _ptr(step_ctr), _ptr(local_flags), _ptr(out), max_wait_ms,
+          int(bool(signal)), _stream(stream))
 
 
 def enable_peer_access(peer_device):

@@ -191,9 +191,10 @@ __global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
 // Rows of at most 65,536 scores (the decode case is ONE such row): a thread-block cluster of 8 CTAs
 // works on a row, CTA c on elements [8192 c, 8192 (c+1)), every thread on 8 consecutive elements that
 // stay in registers, so the row is read from global memory once and no sweep is longer than 8 keys
-// per thread.  The CTAs meet through distributed shared memory: per-CTA histograms are reduced
-// slice-wise into CTA 0, which finds the crossing bucket and later the threshold and hands them back;
-// the per-CTA counts of selected entries give every CTA the offset of its ordered output.
+// per thread.  The CTAs meet through distributed shared memory: the bucket histograms are summed
+// slice-wise and the sums stored into every CTA, each CTA then finds the crossing bucket itself; the
+// low-bit count sets are read by every CTA, which finds the threshold and, from the per-CTA counts, the
+// offset of its own ordered output - four cluster barriers in all, no hand-back round trips.
 // ------------------------------------------------------------------------------------------------
 #ifdef HK_TOPK_TRACE
 __device__ long long hk_topk_trace[16];
@@ -213,100 +214,118 @@ __global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void d
   const int row_id = blockIdx.x / TKC_CTAS;
   const uint16_t* row = scores + (size_t)row_id * s_stride;
   int* row_o = out + (size_t)row_id * k_pad;
-  const int t = threadIdx.x;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 
   __shared__ int hist[2048];       // this CTA's bucket counts
-  __shared__ int ghist[2048];      // CTA 0: counts of the whole row
-  __shared__ int low[32], glow[32];
+  __shared__ int ghist[2048];      // bucket counts of the whole row (every CTA gets a copy)
+  __shared__ int low[33];          // this CTA: counts of the low 5 bits inside the crossing bucket; [32] = keys above it
   __shared__ int scan_ws[TK_WARPS + 1];
-  __shared__ int meta[4];          // b1, count above b1 (later: above the threshold), selectable total, low bits
-  __shared__ int cta_cnt[TKC_CTAS];
+  __shared__ int sh_sel[3];
+  __shared__ int sh_off[6];        // threshold low bits, count above threshold, this CTA's bases, total ties
 
   TK_TRACE(0);
   uint32_t key[8];
   const int i8 = c * TK_THREADS + t;
   load8<VEC>(row, i8, T, key);     // beyond T: key 0, never selectable
   for (int i = t; i < 2048; i += TK_THREADS) hist[i] = 0;
-  if (t < 32) { low[t] = 0; glow[t] = 0; }
+  if (t < 33) low[t] = 0;
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 8; j++)
     if (key[j] > KEY_NEG_INF) atomicAdd(&hist[key[j] >> 5], 1);
-  cluster.sync();
+  cluster.sync();                  // (1) all local histograms complete
   TK_TRACE(1);
-  // slice c of the buckets, summed over the CTAs, into CTA 0
+  // slice c of the buckets is summed over the eight CTAs by CTA c and stored into EVERY CTA's copy of
+  // the row histogram (reading all eight histograms in all eight CTAs costs far more distributed traffic)
   if (t < 2048 / TKC_CTAS) {
     const int bin = c * (2048 / TKC_CTAS) + t;
     int sum = 0;
 #pragma unroll
     for (int rk = 0; rk < TKC_CTAS; rk++) sum += cluster.map_shared_rank(hist, rk)[bin];
-    cluster.map_shared_rank(ghist, 0)[bin] = sum;
-  }
-  cluster.sync();
-  TK_TRACE(2);
-  if (c == 0) {
-    // thread t owns buckets 2047-2t and 2046-2t (descending); find where the running count crosses k
-    const int h_hi = ghist[2047 - 2 * t], h_lo = ghist[2046 - 2 * t];
-    int total_sel;
-    const int excl = block_exscan(h_hi + h_lo, scan_ws, &total_sel);
-    if (t == 0) { meta[0] = -1; meta[1] = 0; meta[2] = total_sel; }
-    __syncthreads();
-    if (total_sel >= k && k > 0) {
-      if (excl < k && excl + h_hi >= k) { meta[0] = 2047 - 2 * t; meta[1] = excl; }
-      else if (excl + h_hi < k && excl + h_hi + h_lo >= k) { meta[0] = 2046 - 2 * t; meta[1] = excl + h_hi; }
-    }
-    __syncthreads();
-    if (t < 3 * TKC_CTAS && t >= 3) cluster.map_shared_rank(meta, t / 3)[t % 3] = meta[t % 3];
-  }
-  cluster.sync();
-  TK_TRACE(3);
-  const int b1 = meta[0];
-  uint32_t thresh;
-  int cnt_gt, n_eq_take;
-  if (b1 < 0) {
-    // fewer than k selectable entries (or k == 0): take them all, no ties
-    thresh = KEY_NEG_INF;
-    cnt_gt = k > 0 ? meta[2] : 0;
-    n_eq_take = 0;
-    if (k == 0) thresh = 0xffffu;
-    cluster.sync();                // keeps the barrier count equal on both paths
-    cluster.sync();
-  } else {
-    // low 5 bits inside bucket b1: local counts, then added into CTA 0
 #pragma unroll
-    for (int j = 0; j < 8; j++)
-      if ((int)(key[j] >> 5) == b1) atomicAdd(&low[key[j] & 31u], 1);
-    __syncthreads();
-    if (t < 32 && low[t] > 0) atomicAdd(&cluster.map_shared_rank(glow, 0)[t], low[t]);
-    cluster.sync();
-    if (c == 0 && t < 32) {
-      // lane l owns low value 31-l (descending)
-      const int hv = glow[31 - t];
-      int incl = hv;
+    for (int rk = 0; rk < TKC_CTAS; rk++) cluster.map_shared_rank(ghist, rk)[bin] = sum;
+  }
+  cluster.sync();                  // (2) every CTA holds the row histogram
+  // thread t owns buckets 2047-2t and 2046-2t (descending) and finds where the running count crosses k
+  const int h_hi = ghist[2047 - 2 * t], h_lo = ghist[2046 - 2 * t];
+  int total_sel;
+  const int excl = block_exscan(h_hi + h_lo, scan_ws, &total_sel);
+  if (t == 0) { sh_sel[0] = -1; sh_sel[1] = 0; }
+  __syncthreads();
+  if (total_sel >= k && k > 0) {
+    if (excl < k && excl + h_hi >= k) { sh_sel[0] = 2047 - 2 * t; sh_sel[1] = excl; }
+    else if (excl + h_hi < k && excl + h_hi + h_lo >= k) { sh_sel[0] = 2046 - 2 * t; sh_sel[1] = excl + h_hi; }
+  }
+  __syncthreads();
+  const int b1 = sh_sel[0], above1 = sh_sel[1];
+  TK_TRACE(2);
+  // local counts: low 5 bits inside bucket b1, and the keys in buckets above it.  Without a crossing bucket
+  // (fewer than k selectable entries, or k == 0) every selectable key counts as "above".
+  const int b_eff = b1 < 0 ? 31 : b1;
+  int n_above = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const int bk = (int)(key[j] >> 5);
+    if (bk == b1) atomicAdd(&low[key[j] & 31u], 1);
+    n_above += bk > b_eff;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) n_above += __shfl_xor_sync(0xffffffffu, n_above, o);
+  if (lane == 0 && n_above) atomicAdd(&low[32], n_above);
+  cluster.sync();                  // (3) all local low-bit counts complete
+  TK_TRACE(3);
+  if (warp == 0) {
+    // lane l owns low value 31-l (descending); per CTA counts first, then the row's
+    int mine[TKC_CTAS], above_c[TKC_CTAS], g = 0;
+#pragma unroll
+    for (int rk = 0; rk < TKC_CTAS; rk++) {
+      const int* rl = cluster.map_shared_rank(low, rk);
+      mine[rk] = rl[31 - lane];
+      above_c[rk] = rl[32];
+      g += mine[rk];
+    }
+    int lowbits = 0, cnt_gt_row = k > 0 ? total_sel : 0, need_eq = 0;
+    if (b1 >= 0) {
+      int incl = g;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         int n = __shfl_up_sync(0xffffffffu, incl, o);
-        if (t >= o) incl += n;
+        if (lane >= o) incl += n;
       }
-      const int need = k - meta[1];
-      int found = (incl - hv < need && incl >= need) ? 1 : 0;
-      const unsigned who = __ballot_sync(0xffffffffu, found);
-      const int src = __ffs((int)who) - 1;
-      const int lowbits = __shfl_sync(0xffffffffu, 31 - t, src);
-      const int above = __shfl_sync(0xffffffffu, meta[1] + incl - hv, src);
-      if (t < TKC_CTAS) {
-        int* m = cluster.map_shared_rank(meta, t);
-        m[3] = lowbits;
-        m[1] = above;
+      const int need = k - above1;
+      const unsigned who = __ballot_sync(0xffffffffu, incl - g < need && incl >= need);
+      const int src = __ffs((int)who) - 1;                  // lane of the crossing low value
+      lowbits = 31 - src;
+      cnt_gt_row = above1 + __shfl_sync(0xffffffffu, incl - g, src);
+      need_eq = k - cnt_gt_row;
+      // per CTA: keys above the threshold = above the bucket + low values above lowbits (lanes < src); ties = lane src
+      int base_gt = 0, base_eq = 0, all_eq = 0;
+#pragma unroll
+      for (int rk = 0; rk < TKC_CTAS; rk++) {
+        int hi = lane < src ? mine[rk] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) hi += __shfl_xor_sync(0xffffffffu, hi, o);
+        const int eq = __shfl_sync(0xffffffffu, mine[rk], src);
+        if (rk < c) { base_gt += above_c[rk] + hi; base_eq += eq; }
+        all_eq += eq;
       }
+      if (lane == 0) { sh_off[2] = base_gt; sh_off[3] = base_eq; sh_off[4] = all_eq; }
+    } else {
+      int base_gt = 0;
+#pragma unroll
+      for (int rk = 0; rk < TKC_CTAS; rk++)
+        if (rk < c) base_gt += above_c[rk];
+      if (lane == 0) { sh_off[2] = k > 0 ? base_gt : 0; sh_off[3] = 0; sh_off[4] = 0; }
     }
-    cluster.sync();
-    thresh = ((uint32_t)b1 << 5) | (uint32_t)meta[3];
-    cnt_gt = meta[1];
-    n_eq_take = k - cnt_gt;
+    if (lane == 0) { sh_off[0] = lowbits; sh_off[1] = cnt_gt_row; sh_off[5] = need_eq; }
   }
+  __syncthreads();
+  uint32_t thresh;
+  const int cnt_gt = sh_off[1], n_eq_take = sh_off[5];
+  if (b1 < 0) thresh = k == 0 ? 0xffffu : KEY_NEG_INF;
+  else thresh = ((uint32_t)b1 << 5) | (uint32_t)sh_off[0];
   TK_TRACE(4);
-  // ---- ordered compaction: thread masks, block scan, CTA offsets from the per-CTA totals ----
+  // ---- ordered compaction inside the CTA, offset by the counts of the CTAs before it ----
   uint32_t m_gt = 0, m_eq = 0;
 #pragma unroll
   for (int j = 0; j < 8; j++) {
@@ -315,18 +334,9 @@ __global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void d
   }
   int tot;
   const int ex = block_exscan(__popc(m_gt) | (__popc(m_eq) << 16), scan_ws, &tot);
-  if (t < TKC_CTAS) cluster.map_shared_rank(cta_cnt, t)[c] = tot;
-  cluster.sync();
   TK_TRACE(5);
-  int base_gt = 0, base_eq = 0, all_eq = 0;
-#pragma unroll
-  for (int rk = 0; rk < TKC_CTAS; rk++) {
-    const int v = cta_cnt[rk];
-    if (rk < c) { base_gt += v & 0xffff; base_eq += v >> 16; }
-    all_eq += v >> 16;
-  }
-  int o_gt = base_gt + (ex & 0xffff);
-  int o_eq = base_eq + (ex >> 16);
+  int o_gt = sh_off[2] + (ex & 0xffff);
+  int o_eq = sh_off[3] + (ex >> 16);
   const int ibase = i8 * 8;
   while (m_gt) {
     const int j = __ffs((int)m_gt) - 1;
@@ -340,11 +350,11 @@ __global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void d
     o_eq++;
   }
   if (c == 0) {
-    const int emitted = cnt_gt + min(all_eq, n_eq_take);
+    const int emitted = cnt_gt + min(sh_off[4], n_eq_take);
     for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
   }
   TK_TRACE(6);
-  cluster.sync();                  // no CTA leaves while a peer may still read its shared memory
+  cluster.sync();                  // (4) no CTA leaves while a peer may still read its shared memory
 }
 
 }  // namespace hk

@@ -133,49 +133,60 @@ __device__ __forceinline__ void block16_store(float* __restrict__ D, const float
   }
 }
 
-// Stage 4 of the preparation kernel for one warp: rows 16 IB .. 16 IB + 15 of A (k warps) or B (q warps)
-// against the column blocks jb <= IB.  v = this thread's left-operand fragment values (rows g8, g8 + 8;
+// Stage 4 of the preparation kernel for one warp: rows 16 ib .. 16 ib + 15 of A (k warps) or B (q warps)
+// against the column blocks jb <= ib.  v = this thread's left-operand fragment values (rows g8, g8 + 8;
 // channel 32 m + 8 tig + j at index 8 m + j).  k-step ks of the m16n8k8 product contracts the channel
 // pairs (32 m + 8 tig + j, + 1), j = 2 (ks % 4), m = ks / 4, in MMA k slots tig and tig + 4.
-template <int IB>
-__device__ __forceinline__ void prep_ab_block(const float (&v)[2][32], bool is_q, const float* __restrict__ sR,
+__device__ __forceinline__ void prep_ab_block(const int ib, const float (&v)[2][32], bool is_q, const float* __restrict__ sR,
                                               const float* __restrict__ sDD, const float* __restrict__ sBeta,
                                               float* __restrict__ sA, uint8_t* __restrict__ unit, int g8, int tig) {
-  float acc[IB + 1][2][4];
+  // one code path for all row blocks (column blocks jb > ib are skipped by warp-uniform branches): four
+  // specialised copies of this fully unrolled body would not fit the instruction cache
+  float acc[4][2][4];
 #pragma unroll
-  for (int jb = 0; jb <= IB; jb++)
+  for (int jb = 0; jb < 4; jb++)
 #pragma unroll
     for (int nt = 0; nt < 2; nt++)
 #pragma unroll
       for (int e = 0; e < 4; e++) acc[jb][nt][e] = 0.f;
+  const float* dd_base = sDD + (ib * (ib - 1) / 2) * KD;
+  // two k-steps per pass: the R rows are read 16 bytes at a time (4 channels = both channel pairs of the
+  // two k-steps), which with the 132-float row pitch is free of bank conflicts (a quarter-warp covers
+  // rows g8, g8 + 1 and the four tig: 4 g8 + 8 tig are eight different 4-bank groups)
 #pragma unroll
-  for (int ks = 0; ks < 16; ks++) {
-    const int m = ks >> 2, j = (ks & 3) * 2;
+  for (int kp = 0; kp < 8; kp++) {
+    const int m = kp >> 1, j = (kp & 1) * 4;
     const int c0 = 32 * m + 8 * tig + j;
-    uint32_t a[4];
-    a[0] = f2tf32(v[0][8 * m + j]); a[1] = f2tf32(v[1][8 * m + j]);
-    a[2] = f2tf32(v[0][8 * m + j + 1]); a[3] = f2tf32(v[1][8 * m + j + 1]);
+    uint32_t a0[4], a1[4];
+    a0[0] = f2tf32(v[0][8 * m + j]); a0[1] = f2tf32(v[1][8 * m + j]);
+    a0[2] = f2tf32(v[0][8 * m + j + 1]); a0[3] = f2tf32(v[1][8 * m + j + 1]);
+    a1[0] = f2tf32(v[0][8 * m + j + 2]); a1[1] = f2tf32(v[1][8 * m + j + 2]);
+    a1[2] = f2tf32(v[0][8 * m + j + 3]); a1[3] = f2tf32(v[1][8 * m + j + 3]);
 #pragma unroll
-    for (int jb = 0; jb <= IB; jb++) {
-      float2 dd = make_float2(1.f, 1.f);
-      if (jb < IB) dd = *reinterpret_cast<const float2*>(sDD + (IB * (IB - 1) / 2 + jb) * KD + c0);
+    for (int jb = 0; jb < 4; jb++) {
+      if (jb <= ib) {
+        float4 dd = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (jb < ib) dd = *reinterpret_cast<const float4*>(dd_base + jb * KD + c0);
 #pragma unroll
-      for (int nt = 0; nt < 2; nt++) {
-        const float2 r2 = *reinterpret_cast<const float2*>(sR + (jb * 16 + nt * 8 + g8) * P1_LD + c0);
-        mma_tf32(acc[jb][nt], a, f2tf32(r2.x * dd.x), f2tf32(r2.y * dd.y));
+        for (int nt = 0; nt < 2; nt++) {
+          const float4 r4 = *reinterpret_cast<const float4*>(sR + (jb * 16 + nt * 8 + g8) * P1_LD + c0);
+          mma_tf32(acc[jb][nt], a0, f2tf32(r4.x * dd.x), f2tf32(r4.y * dd.y));
+          mma_tf32(acc[jb][nt], a1, f2tf32(r4.z * dd.z), f2tf32(r4.w * dd.w));
+        }
       }
     }
   }
-  // accumulator fragment: rows t = 16 IB + g8 (+8), columns s = 16 jb + 8 nt + 2 tig (+1)
+  // accumulator fragment: rows t = 16 ib + g8 (+8), columns s = 16 jb + 8 nt + 2 tig (+1)
 #pragma unroll
-  for (int jb = 0; jb <= IB; jb++)
+  for (int jb = 0; jb < 4; jb++) {
+    if (jb > ib) continue;
 #pragma unroll
     for (int nt = 0; nt < 2; nt++) {
       const int s0 = jb * 16 + nt * 8 + tig * 2;
       const float b0 = sBeta[s0], b1 = sBeta[s0 + 1];
 #pragma unroll
       for (int hrow = 0; hrow < 2; hrow++) {
-        const int t = IB * 16 + g8 + hrow * 8;
+        const int t = ib * 16 + g8 + hrow * 8;
         if (!is_q) {            // N = A beta, strictly lower
           if (s0 < t) sA[t * P1_LDA + s0] = acc[jb][nt][2 * hrow] * b0;
           if (s0 + 1 < t) sA[t * P1_LDA + s0 + 1] = acc[jb][nt][2 * hrow + 1] * b1;
@@ -187,6 +198,7 @@ __device__ __forceinline__ void prep_ab_block(const float (&v)[2][32], bool is_q
         }
       }
     }
+  }
 }
 
 __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
@@ -219,7 +231,9 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   const size_t row = (size_t)3 * H * KD;
   const __nv_bfloat16* tok0 = qkv + ((size_t)b * seqlen + t0) * row;
   const float* g0 = g + (((size_t)b * seqlen + t0) * H + head) * KD;
-  uint8_t* unit = ws + (((size_t)b * H + head) * n_chunks + chunk) * U_BYTES;
+  // units are chunk-major: the CTAs that run together (same chunks, all heads) touch adjacent units, in
+  // this kernel and in the scan, so their traffic spreads over all memory channels
+  uint8_t* unit = ws + (((size_t)b * n_chunks + chunk) * H + head) * U_BYTES;
 
   if (tid == 0) {
     tc::mbar_init(&bar, 1);
@@ -246,11 +260,12 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   // ---- stage 1: loads.  Ownership for stages 1-4 is the TF32 MMA fragment layout, so that the left
   //      operands of the A/B products never pass through shared memory: warp -> (16-token row block ib,
   //      k or q), lane = 4*g8 + tig owns rows 16 ib + g8 and + 8 and, of every 32 channels, the 8
-  //      starting at 8 tig (one 16-byte piece).  The row blocks are paired over the four scheduler
-  //      partitions as (0,3) and (1,2): block ib has ib+1 column blocks of work.
+  //      starting at 8 tig (one 16-byte piece).  Block ib has ib+1 column blocks of work and the k warps
+  //      carry the exponentials of stage 3: every scheduler partition gets one k warp and one q warp
+  //      whose row blocks add up to the same work.
   const int g8 = lane >> 2, tig = lane & 3;
-  const int ib = (0x22331100u >> (4 * warp)) & 3;
-  const bool is_q = warp & 1;
+  const bool is_q = warp >> 2;                              // warps 0-3: k rows, warps 4-7: q rows
+  const int ib = is_q ? 3 - (warp & 3) : (warp & 3);        // partition s hosts k block s and q block 3 - s
   float v[2][32];                                           // [row half][4 pieces x 8 channels]
   {
     uint4 raw[2][4];
@@ -355,7 +370,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   // phase A: k warps write the Kt^T tile (rows = channels, K = tokens) straight to the workspace;
   //          q warps scale their rows by e^{x}
   if (!is_q) {
-    for (int i = (warp >> 1) * 32 + lane; i < KD * (KC / 8); i += 128) {
+    for (int i = warp * 32 + lane; i < KD * (KC / 8); i += 128) {
       const int c = i & 127, tg = i >> 7;
       const float glp = sGLP[(tg >> 1) * KD + c];
       float kt[8];
@@ -420,12 +435,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   //      rows (fragments from registers) with the R rows of the column blocks jb <= ib; R of an earlier
   //      block is moved from its own reference P_jb to P_ib by the pair decay while it is loaded.  The
   //      contraction runs over the channels in the order the registers hold them. ----
-  switch (ib) {
-    case 0: prep_ab_block<0>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
-    case 1: prep_ab_block<1>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
-    case 2: prep_ab_block<2>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
-    default: prep_ab_block<3>(v, is_q, sG, sDD, sBeta, sA, unit, g8, tig); break;
-  }
+  prep_ab_block(ib, v, is_q, sG, sDD, sBeta, sA, unit, g8, tig);
   if (!is_q) {
     // K+ = k^ e^{G_t}: first half of the [K+ | V] operand
 #pragma unroll
@@ -601,7 +611,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vs = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
   const int v0 = vs * KNV;
-  const uint8_t* unit0 = ws + (((size_t)b * H + head) * n_chunks) * U_BYTES;
+  const uint8_t* unit0 = ws + ((size_t)b * n_chunks * H + head) * U_BYTES;   // unit of chunk c: + c * H * U_BYTES
   const int slot = slots ? slots[b] : b;
   float* st = state + ((size_t)slot * H + head) * KD * KD + (size_t)tid * KD + v0;  // row k = tid
 
@@ -641,7 +651,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
 
   auto issue_loads = [&](int chunk) {
     uint8_t* stg = smem + (chunk % S_NSTAGE) * S_STAGE;
-    const uint8_t* u = unit0 + (size_t)chunk * U_BYTES;
+    const uint8_t* u = unit0 + (size_t)chunk * H * U_BYTES;
     uint64_t* bar = &full_bar[chunk % S_NSTAGE];
     tc::mbar_arrive_expect_tx(bar, S_TX);
     tc::bulk_g2s(stg + S_WQ, u + U_WQ, 32768, bar);

@@ -66,7 +66,7 @@ static int launch_simt(const MlaArgs& a, cudaStream_t s) {
 static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
                    __half* out, cudaStream_t s) {
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
-  lse_combine_kernel<false><<<(unsigned)rows, 256, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
+  lse_combine_kernel<false><<<(unsigned)rows, LSE_THREADS, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
                                                             n_split, rows, out);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
@@ -267,8 +267,8 @@ HK_API int hk_mla_dense_partial_ws(const void* q_lat, const void* ckv, const int
   if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
   if (st != HK_OK) return st;
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
-  lse_merge_partials_kernel<<<(unsigned)rows, 256, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows,
-                                                           part_m, part_l, part_acc);
+  lse_merge_partials_kernel<<<(unsigned)rows, LSE_THREADS, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows,
+                                                           part_m, part_l, part_acc, nullptr, nullptr, nullptr, nullptr);
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
@@ -288,7 +288,7 @@ HK_API int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* p
   using namespace hk;
   HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && n_split >= 1 && n_split <= LSE_MAX_SPLITS && rows >= 0);
   if (rows == 0) return HK_OK;
-  lse_combine_kernel<true><<<(unsigned)rows, 256, 0, as_stream(stream)>>>(
+  lse_combine_kernel<true><<<(unsigned)rows, LSE_THREADS, 0, as_stream(stream)>>>(
       nullptr, nullptr, nullptr, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16);
   HK_LAUNCH_CHECK();
   return HK_OK;
@@ -312,27 +312,56 @@ HK_API int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* 
   const long long cycles = (long long)max_wait_ms * 2000000LL;   // ~2 GHz
   lse_combine_peers_kernel<<<(unsigned)rows, 128, 0, as_stream(stream)>>>(
       ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16, local_flags, epoch, cycles,
-      device_status_ptr());
+      device_status_ptr(), nullptr);
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
 
-// One split-KV decode step of one rank in ONE host call: local partial (with local splits), signal,
-// bounded-wait combine over all ranks' partial sets.
+// One split-KV decode step of one rank in ONE host call: local partial (local splits, merged), signal,
+// bounded-wait combine over all ranks' partial sets.  The step number lives on the device (step_ctr,
+// advanced by the signal kernel), so a captured graph of this call can be replayed: the exchange set
+// written and read in step e is set e & 1, the flags carry e.
 HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
-                               float* part_m, float* part_l, float* part_acc, int m, int n_heads, float scale,
-                               int n_split, int n_keys_hint, void* workspace, size_t workspace_bytes,
-                               int* const* flag_ptrs, const float* const* ptrs_m, const float* const* ptrs_l,
-                               const float* const* ptrs_acc, int n_ranks, int my_rank, int epoch,
-                               const int* local_flags, void* out_f16, int max_wait_ms, int signal, void* stream) {
-  int st = hk_mla_dense_partial_ws(q_lat, ckv_shard, kv_base, kv_len, 0, part_m, part_l, part_acc, m, n_heads, scale,
-                                   n_split, n_keys_hint, workspace, workspace_bytes, stream);
+                               float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
+                               float* part_acc1, int m, int n_heads, float scale, int n_split, int n_keys_hint,
+                               void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
+                               const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
+                               int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
+                               int max_wait_ms, int signal, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv_shard && part_m0 && part_l0 && part_acc0 && part_m1 && part_l1 && part_acc1);
+  HK_REQUIRE(flag_ptrs && ptrs_m && ptrs_l && ptrs_acc && step_ctr && local_flags && out_f16 && workspace);
+  HK_REQUIRE(m > 0 && n_heads > 0 && n_heads % SIMT_HG == 0 && n_ranks >= 1 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv_shard, 16) && aligned(part_acc0, 16) && aligned(part_acc1, 16) && aligned(workspace, 256));
+  HK_REQUIRE(max_wait_ms > 0 && max_wait_ms <= 10000);
+  const bool tc = (n_heads == 64) && !force_simt();
+  if (n_split <= 0)
+    n_split = tc ? mla_flash_tc_auto_splits(m, n_keys_hint > 0 ? n_keys_hint : 4096)
+                 : simt_auto_splits(m, n_heads, n_keys_hint > 0 ? n_keys_hint : 4096);
+  if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
+  const int64_t rows = (int64_t)m * n_heads;
+  PartialLayout pl = partial_layout(n_split, rows);
+  if (workspace_bytes < pl.total) return HK_ERR_WORKSPACE;
+  char* ws = (char*)workspace;
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv_shard;
+  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = 0;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  a.n_split = n_split;
+  a.part_m = (float*)ws; a.part_l = (float*)(ws + pl.off_l); a.part_acc = (float*)(ws + pl.off_acc);
+  cudaStream_t s = as_stream(stream);
+  int st = HK_ERR_UNSUPPORTED;
+  if (tc) st = mla_flash_tc_launch(a, s);
+  if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
   if (st != HK_OK) return st;
-  if (signal) {
-    st = hk_peer_signal(flag_ptrs, n_ranks, my_rank, epoch, stream);
-    if (st != HK_OK) return st;
-  }
-  return hk_lse_combine_peers(ptrs_m, ptrs_l, ptrs_acc, n_ranks, (int64_t)m * n_heads, out_f16, local_flags, epoch,
-                              max_wait_ms, stream);
+  lse_merge_partials_kernel<<<(unsigned)rows, LSE_THREADS, 0, s>>>(a.part_m, a.part_l, a.part_acc, n_split, rows, part_m0, part_l0,
+                                                           part_acc0, part_m1, part_l1, part_acc1, step_ctr);
+  HK_LAUNCH_CHECK();
+  peer_signal_ctr_kernel<<<1, 32, 0, s>>>(flag_ptrs, n_ranks, my_rank, step_ctr, signal);
+  HK_LAUNCH_CHECK();
+  lse_combine_peers_kernel<<<(unsigned)rows, 128, 0, s>>>(ptrs_m, ptrs_l, ptrs_acc, n_ranks, rows, (__half*)out_f16, local_flags,
+                                                          0, (long long)max_wait_ms * 2000000LL, device_status_ptr(), step_ctr);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
 }
 

@@ -131,10 +131,12 @@ constexpr size_t MLA_SIMT_SMEM = (size_t)(8 * SIMT_HG * LATENT + 2 * 8 * SIMT_HG
 // ---- split-KV log-sum-exp combine: one CTA (128 threads x 4 channels) per (row, head) ----
 // gm = max m_s; gl = sum e^{m_s-gm} l_s; o = sum e^{m_s-gm} acc_s / gl; m_s = -inf weighs 0; all
 // -inf (or gl = 0) gives zeros (reference in-kernel merge: src/cuda/attn/attn.cu:462-481).
-// One CTA of 256 threads per (row, head).  The split weights e^{m_s-gm} are computed once into shared
-// memory (splits strided over the threads); the accumulators are then summed by two thread groups (even
-// and odd splits), thread = one float4 of the 512 channels, several independent loads in flight each.
+// One CTA of 1024 threads per (row, head).  The split weights e^{m_s-gm} are computed once into shared
+// memory (splits strided over the threads); the accumulators are then summed by eight thread groups
+// (splits strided over the groups), thread = one float4 of the 512 channels, independent loads in flight.
 constexpr int LSE_MAX_SPLITS = 1024;
+constexpr int LSE_GROUPS = 8;
+constexpr int LSE_THREADS = 128 * LSE_GROUPS;
 
 template <bool PTRS>
 __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m, const float* __restrict__ part_l,
@@ -143,11 +145,11 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
                                                const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows,
                                                int64_t r, float& gm_out, float& gl_out, float4& o_out) {
   __shared__ float s_w[LSE_MAX_SPLITS];
-  __shared__ float s_red[8];
-  __shared__ float4 s_o[128];
+  __shared__ float s_red[LSE_THREADS / 32];
+  __shared__ float4 s_o[LSE_GROUPS - 1][128];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   float mloc = -INFINITY;
-  for (int s = t; s < n_split; s += 256) {
+  for (int s = t; s < n_split; s += LSE_THREADS) {
     const float m = (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
     s_w[s] = m;
     mloc = fmaxf(mloc, m);
@@ -158,10 +160,10 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __syncthreads();
   float gm = s_red[0];
 #pragma unroll
-  for (int w = 1; w < 8; w++) gm = fmaxf(gm, s_red[w]);
+  for (int w = 1; w < LSE_THREADS / 32; w++) gm = fmaxf(gm, s_red[w]);
   __syncthreads();
   float lloc = 0.f;
-  for (int s = t; s < n_split; s += 256) {
+  for (int s = t; s < n_split; s += LSE_THREADS) {
     const float m = s_w[s];
     const float w = (m == -INFINITY) ? 0.f : __expf(m - gm);
     s_w[s] = w;
@@ -173,28 +175,31 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __syncthreads();
   float gl = 0.f;
 #pragma unroll
-  for (int w = 0; w < 8; w++) gl += s_red[w];
+  for (int w = 0; w < LSE_THREADS / 32; w++) gl += s_red[w];
   const int cq = t & 127, sg = t >> 7;
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-  for (int s = sg; s < n_split; s += 2) {
+  for (int s = sg; s < n_split; s += LSE_GROUPS) {
     const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
     const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
     const float4 a = PTRS ? __ldcv(ap) : __ldg(ap);   // peer memory: never through the read-only cache
     const float w = s_w[s];
     o.x = fmaf(w, a.x, o.x); o.y = fmaf(w, a.y, o.y); o.z = fmaf(w, a.z, o.z); o.w = fmaf(w, a.w, o.w);
   }
-  if (sg == 1) s_o[cq] = o;
+  if (sg > 0) s_o[sg - 1][cq] = o;
   __syncthreads();
   if (sg == 0) {
-    const float4 p = s_o[cq];
-    o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+#pragma unroll
+    for (int gi = 0; gi < LSE_GROUPS - 1; gi++) {
+      const float4 p = s_o[gi][cq];
+      o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+    }
   }
   gm_out = gm; gl_out = gl; o_out = o;      // o is complete in threads 0..127
 }
 
 template <bool PTRS>
-__global__ __launch_bounds__(256) void lse_combine_kernel(
+__global__ __launch_bounds__(LSE_THREADS) void lse_combine_kernel(
     const float* __restrict__ part_m, const float* __restrict__ part_l,
     const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
     const float* const* __restrict__ ptrs_l, const float* const* __restrict__ ptrs_acc,
@@ -216,13 +221,20 @@ __global__ __launch_bounds__(256) void lse_combine_kernel(
 
 // ---- merge of S partial sets into ONE partial set (still un-normalised): the per-GPU reduction before
 // the cross-GPU exchange, so that only 2,056 B per (row, head) cross NVLink ----
-__global__ __launch_bounds__(256) void lse_merge_partials_kernel(
+// With a step counter (split-KV across GPUs, double-buffered exchange sets) the set of the step that is
+// being computed, (*step_ctr + 1) & 1, is the one written.
+__global__ __launch_bounds__(LSE_THREADS) void lse_merge_partials_kernel(
     const float* __restrict__ part_m, const float* __restrict__ part_l, const float* __restrict__ part_acc,
-    int n_split, int64_t rows, float* __restrict__ out_m, float* __restrict__ out_l, float* __restrict__ out_acc) {
+    int n_split, int64_t rows, float* __restrict__ out_m, float* __restrict__ out_l, float* __restrict__ out_acc,
+    float* __restrict__ out_m1, float* __restrict__ out_l1, float* __restrict__ out_acc1,
+    const int* __restrict__ step_ctr) {
   const int64_t r = blockIdx.x;
   float gm, gl;
   float4 o;
   lse_reduce_row<false>(part_m, part_l, part_acc, nullptr, nullptr, nullptr, n_split, rows, r, gm, gl, o);
+  if (step_ctr && ((*step_ctr + 1) & 1)) {
+    out_m = out_m1; out_l = out_l1; out_acc = out_acc1;
+  }
   if (threadIdx.x < 128) *reinterpret_cast<float4*>(out_acc + (size_t)r * LATENT + threadIdx.x * 4) = o;
   if (threadIdx.x == 0) {
     out_m[r] = gm;
@@ -242,14 +254,36 @@ __global__ void peer_signal_kernel(int* const* __restrict__ flag_ptrs, int n_ran
   }
 }
 
+// The same with the step number kept on the device (so that a captured graph can be replayed): the
+// step is *step_ctr + 1; the counter is advanced here, after the stores (or instead of them when
+// do_store == 0: a rank that stays silent for one step, used by failure-injection tests).
+__global__ void peer_signal_ctr_kernel(int* const* __restrict__ flag_ptrs, int n_ranks, int my_rank,
+                                       int* __restrict__ step_ctr, int do_store) {
+  const int s = threadIdx.x;
+  const int epoch = *step_ctr + 1;
+  __syncthreads();
+  if (s < n_ranks && do_store) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag_ptrs[s] + my_rank), "r"(epoch) : "memory");
+  }
+  if (s == 0) *step_ctr = epoch;
+}
+
 // Combine that first waits (bounded) until every rank's flag in THIS GPU's flag array has reached
 // `epoch`, then reads the S partial sets through their pointers (peer memory: plain cache-volatile
 // loads over NVLink, nothing else).  On expiry the CTA writes nothing and reports a timeout.
 __global__ __launch_bounds__(128) void lse_combine_peers_kernel(
     const float* const* __restrict__ ptrs_m, const float* const* __restrict__ ptrs_l,
     const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows, __half* __restrict__ out,
-    const int* __restrict__ flags, int epoch, long long max_wait_cycles, int* __restrict__ status) {
+    const int* __restrict__ flags, int epoch, long long max_wait_cycles, int* __restrict__ status,
+    const int* __restrict__ step_ctr) {
   __shared__ int ready;
+  if (step_ctr) {
+    // device-side step number; the pointer tables hold both exchange sets, [parity][rank]
+    epoch = *step_ctr;
+    const int par = epoch & 1;
+    ptrs_m += par * n_split; ptrs_l += par * n_split; ptrs_acc += par * n_split;
+  }
   if (threadIdx.x == 0) {
     int ok = 1;
     const long long t0 = clock64();

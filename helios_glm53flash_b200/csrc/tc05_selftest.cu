@@ -16,8 +16,10 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  const bool b_mn = flags & 1, a_mn = flags & 2, swap_a = flags & 0x100, swap_b = flags & 0x200;
   const bool a_sw = flags & 4, b_sw = flags & 8;   // 128-byte swizzle: rows of 128 B, 16-byte chunk c of row r at c ^ (r % 8)
+  // the offset-swap diagnostics exist for the no-swizzle layouts only: a swapped stride offset of a
+  // swizzled tile would point past the operand region
+  const bool b_mn = flags & 1, a_mn = flags & 2, swap_a = (flags & 0x100) && !a_sw, swap_b = (flags & 0x200) && !b_sw;
   const int tid = threadIdx.x, warp = tid >> 5;
   uint8_t* sA = smem;
   uint8_t* sB = smem + 128 * 128 * 2;

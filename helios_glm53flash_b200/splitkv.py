@@ -72,7 +72,9 @@ class SplitKVDecoder:
             return torch.tensor([b + self.lay[key] for b in bases], dtype=torch.int64, device="cuda")
 
         self.flag_ptrs = table("flags")
-        self.m_ptrs, self.l_ptrs, self.acc_ptrs = [[table(k + str(par)) for par in (0, 1)] for k in ("m", "l", "acc")]
+        # pointer tables of both exchange sets, [set][rank]
+        self.m_ptrs, self.l_ptrs, self.acc_ptrs = [torch.cat([table(k + str(par)) for par in (0, 1)]) for k in ("m", "l", "acc")]
+        self.step_ctr = torch.zeros(1, dtype=torch.int32, device="cuda")   # step number, advanced on the device
         self.epoch = 0
         self.workspace = None
         self._views()
@@ -98,24 +100,26 @@ class SplitKVDecoder:
             self.hk.peer_region_free(self.local)
             self.local = None
 
-    def step(self, q_lat, ckv_shard, n_local_keys, out, scale, signal=True):
+    def step(self, q_lat, ckv_shard, n_local_keys, out, scale, signal=True, kv_base=None):
         """one decode step; q_lat [m, 64, 512] f16 (same on every rank), ckv_shard = this rank's rows,
-        out [m, 64, 512] f16.  signal=False withholds this rank's flag (failure-injection in tests)."""
+        out [m, 64, 512] f16.  Every query row attends n_local_keys rows of ckv_shard starting at row
+        kv_base[row] (device int64 [m]; default 0: one sequence).  signal=False withholds this rank's flag
+        (failure-injection in tests)."""
         import helios_glm53flash_b200 as hk
         t = self.torch
         self.epoch += 1
         if getattr(self, "_n_keys", None) != int(n_local_keys):
             self._n_keys = int(n_local_keys)
-            self._base = t.zeros(self.m, dtype=t.int64, device="cuda")
+            self._zero_base = t.zeros(self.m, dtype=t.int64, device="cuda")
             self._lens = t.full((self.m,), self._n_keys, dtype=t.int32, device="cuda")
             self._n_split = hk.mla_auto_splits(self.m, max(1, self._n_keys))
-            nbytes = hk.mla_partial_bytes(self._n_split, self.rows) if self._n_split > 1 else 256
+            nbytes = hk.mla_partial_bytes(self._n_split, self.rows)
             self.workspace = t.empty(max(256, nbytes), dtype=t.uint8, device="cuda")
-        par = self.epoch & 1
-        hk.mla_splitkv_step(q_lat, ckv_shard, self._base, self._lens, self.part_m[par], self.part_l[par],
-                            self.part_acc[par], self.m, self.n_heads, scale, self._n_split, self._n_keys, self.workspace,
-                            self.flag_ptrs, self.m_ptrs[par], self.l_ptrs[par], self.acc_ptrs[par], self.world,
-                            self.rank, self.epoch, self.flags, out,
+        hk.mla_splitkv_step(q_lat, ckv_shard, self._zero_base if kv_base is None else kv_base, self._lens,
+                            (self.part_m[0], self.part_l[0], self.part_acc[0]),
+                            (self.part_m[1], self.part_l[1], self.part_acc[1]), self.m, self.n_heads, scale,
+                            self._n_split, self._n_keys, self.workspace, self.flag_ptrs, self.m_ptrs, self.l_ptrs,
+                            self.acc_ptrs, self.world, self.rank, self.step_ctr, self.flags, out,
                             max_wait_ms=self.max_wait_ms, signal=signal)
 
 

@@ -200,15 +200,20 @@ int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* ptrs_l,
  * No counterpart in the reference (it is single-GPU for this path).                              */
 int hk_peer_signal(int* const* flag_ptrs, int n_ranks, int my_rank, int epoch, void* stream);
 
-/* One split-KV decode step of one rank in one call: hk_mla_dense_partial_ws over this rank's shard
- * into its exchange region, hk_peer_signal (skipped when signal == 0: failure injection in tests),
- * hk_lse_combine_peers.  Arguments as in those three calls.                                          */
+/* One split-KV decode step of one rank in one call: the partial over this rank's shard (n_split local
+ * splits in `workspace`, merged on the GPU) into exchange set (step & 1) of its region, the signal
+ * (withheld when signal == 0: failure injection in tests), the bounded-wait combine.  The step number
+ * lives in device memory (step_ctr, one int of this rank, zero at set-up, advanced by the call), so a
+ * CUDA graph that captured this call can be replayed.  part_*0 / part_*1: the two exchange sets of THIS
+ * rank; ptrs_*: DEVICE arrays of 2 * n_ranks pointers, [set][rank]; other arguments as in
+ * hk_mla_dense_partial_ws, hk_peer_signal and hk_lse_combine_peers.                               */
 int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
-                        float* part_m, float* part_l, float* part_acc, int m, int n_heads, float scale,
-                        int n_split, int n_keys_hint, void* workspace, size_t workspace_bytes,
-                        int* const* flag_ptrs, const float* const* ptrs_m, const float* const* ptrs_l,
-                        const float* const* ptrs_acc, int n_ranks, int my_rank, int epoch,
-                        const int* local_flags, void* out_f16, int max_wait_ms, int signal, void* stream);
+                        float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
+                        float* part_acc1, int m, int n_heads, float scale, int n_split, int n_keys_hint,
+                        void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
+                        const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
+                        int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
+                        int max_wait_ms, int signal, void* stream);
 
 /* Enables access from kernels of the current device to memory of `peer_device` (needed once per peer
  * before the two calls around this one touch buffers of another GPU that were mapped into this
