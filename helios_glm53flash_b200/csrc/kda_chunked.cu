@@ -544,7 +544,11 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     }
     tc::mma_commit(&bar);
   }
-  const bool ok = tc::mbar_wait(&bar, 0, &abort_flag, 1);
+  // one warp polls the barrier (with a back-off); the others park at the block barrier instead of spending
+  // issue slots that the other CTA of this SM can use
+  if (warp == 0) tc::mbar_wait<64>(&bar, 0, &abort_flag, 1);
+  __syncthreads();
+  const bool ok = abort_flag == 0;
   tc::fence_after_sync();
   KT_TRACE(11);
   // ---- stage 7: epilogue. Lanes 0-63 are the tokens; warps 0,1 take W, warps 4,5 take Uloc ----

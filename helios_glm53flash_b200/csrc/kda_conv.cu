@@ -3,8 +3,11 @@
 // (reference: src/cuda/aux/gdn.cu:880-1023): fp32 fma chain k ascending, SiLU as a * 1/(1+exp(-a)),
 // bf16 round-to-nearest output, state = last K inputs.
 //
-// Two kernels:
-//   conv4_tile_kernel  prefill: K = 4, no history.  A CTA transposes a [64 channel][128 token] tile
+// Three kernels:
+//   conv4_row_kernel   prefill with whole 16-token groups: K = 4, no history, seqlen % 16 == 0.  No
+//                      shared memory: a lane keeps 2 channels x 16 tokens in registers (32-byte reads
+//                      per channel row, 128-byte warp stores per output row).
+//   conv4_tile_kernel  other prefill lengths: a CTA transposes a [64 channel][128 token] tile
 //                      through shared memory: 16-byte coalesced reads along tokens (the input is
 //                      channel-major), 128-byte coalesced writes along channels (the output is
 //                      token-major).  HBM-bound: 2 B read + 2 B written per channel-token.
@@ -111,6 +114,80 @@ __global__ __launch_bounds__(256) void conv4_tile_kernel(
   }
 }
 
+// Prefill with whole 16-token groups (seqlen % 16 == 0): no shared memory at all.  A lane owns 2 adjacent
+// channels and 16 consecutive tokens: it reads 32 contiguous bytes per channel row (full sectors), keeps
+// the 19 inputs per channel in registers and writes 4 bytes per token, so that a warp's store covers 128
+// contiguous bytes of one output row.  Same arithmetic as above, about half the instructions per output.
+template <bool ACT>
+__global__ __launch_bounds__(256) void conv4_row_kernel(
+    const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ state,
+    const int* __restrict__ slots, const __nv_bfloat16* __restrict__ weight,
+    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int dim, int seqlen,
+    int state_size) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CT_CH + lane * 2;
+  const int t0 = blockIdx.y * CT_TOK + wid * 16;
+  const int b = blockIdx.z;
+  if (t0 >= seqlen) return;                                  // warp-uniform
+  const __nv_bfloat16* r0 = x + ((size_t)b * dim + c0) * seqlen;
+  const __nv_bfloat16* r1 = r0 + seqlen;
+  const uint4 a_lo = ld_stream16(r0 + t0), a_hi = ld_stream16(r0 + t0 + 8);
+  const uint4 e_lo = ld_stream16(r1 + t0), e_hi = ld_stream16(r1 + t0 + 8);
+  float xa[19], xe[19];                                      // inputs t0-3 .. t0+15 of the two channels
+  if (t0 == 0) {
+    // the first group takes its 3 predecessors from the window state and rolls the state forward
+    const int slot = slots ? slots[b] : b;
+    __nv_bfloat16* st0 = state + ((size_t)slot * dim + c0) * state_size;
+    __nv_bfloat16* st1 = st0 + state_size;
+#pragma unroll
+    for (int h = 0; h < 3; h++) {
+      xa[h] = __bfloat162float(st0[h + 1]);
+      xe[h] = __bfloat162float(st1[h + 1]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) {                            // seqlen >= 16: the new window is the last 4 inputs
+      st0[k] = r0[seqlen - 4 + k];
+      st1[k] = r1[seqlen - 4 + k];
+    }
+  } else {
+    const uint2 pa = *reinterpret_cast<const uint2*>(r0 + t0 - 4);   // tokens t0-4 .. t0-1
+    const uint2 pe = *reinterpret_cast<const uint2*>(r1 + t0 - 4);
+    xa[0] = bf16hi(pa.x); xa[1] = bf16lo(pa.y); xa[2] = bf16hi(pa.y);
+    xe[0] = bf16hi(pe.x); xe[1] = bf16lo(pe.y); xe[2] = bf16hi(pe.y);
+  }
+  {
+    const uint32_t wa[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+    const uint32_t we[8] = {e_lo.x, e_lo.y, e_lo.z, e_lo.w, e_hi.x, e_hi.y, e_hi.z, e_hi.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      xa[3 + 2 * i] = bf16lo(wa[i]); xa[4 + 2 * i] = bf16hi(wa[i]);
+      xe[3 + 2 * i] = bf16lo(we[i]); xe[4 + 2 * i] = bf16hi(we[i]);
+    }
+  }
+  const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)c0 * 4);
+  const float w00 = bf16lo(wv.x), w01 = bf16hi(wv.x), w02 = bf16lo(wv.y), w03 = bf16hi(wv.y);
+  const float w10 = bf16lo(wv.z), w11 = bf16hi(wv.z), w12 = bf16lo(wv.w), w13 = bf16hi(wv.w);
+  float b0 = 0.f, b1 = 0.f;
+  if (bias) {
+    b0 = __bfloat162float(bias[c0]);
+    b1 = __bfloat162float(bias[c0 + 1]);
+  }
+  __nv_bfloat16* ob = out + ((size_t)b * seqlen + t0) * dim + c0;
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    float y0 = fmaf(w03, xa[i + 3], fmaf(w02, xa[i + 2], fmaf(w01, xa[i + 1], fmaf(w00, xa[i], b0))));
+    float y1 = fmaf(w13, xe[i + 3], fmaf(w12, xe[i + 2], fmaf(w11, xe[i + 1], fmaf(w10, xe[i], b1))));
+    if (ACT) {
+      y0 = silu_fast(y0);
+      y1 = silu_fast(y1);
+    }
+    __nv_bfloat162 pk;
+    pk.x = __float2bfloat16_rn(y0);
+    pk.y = __float2bfloat16_rn(y1);
+    *reinterpret_cast<__nv_bfloat162*>(ob + (size_t)i * dim) = pk;
+  }
+}
+
 template <bool ACT, bool HISTORY>
 __global__ __launch_bounds__(256) void conv_generic_kernel(
     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ state,
@@ -184,7 +261,11 @@ HK_API int hk_conv1d_update(const void* x, void* conv_state, const int* slots, c
 
   const bool tile_ok = (K == 4) && !history && (dim % CT_CH == 0) && seqlen >= 16 &&
                        aligned(weight, 16) && aligned(out, 4);
-  if (tile_ok) {
+  if (tile_ok && seqlen % 16 == 0 && aligned(x, 16)) {
+    dim3 grid(dim / CT_CH, (seqlen + CT_TOK - 1) / CT_TOK, bsz);
+    if (activation) conv4_row_kernel<true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+    else            conv4_row_kernel<false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+  } else if (tile_ok) {
     dim3 grid(dim / CT_CH, (seqlen + CT_TOK - 1) / CT_TOK, bsz);
     const bool vec = (seqlen % 8 == 0) && aligned(x, 16);
     if (activation) {

@@ -89,12 +89,6 @@ __device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
 }
 
-// One cache line into L2 through the load/store path (its own request queue: usable next to bulk copies
-// whose engine already has all of its requests in flight).
-__device__ __forceinline__ void prefetch_l2_line(const void* gmem) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(gmem) : "memory");
-}
-
 // 16-byte asynchronous copy global -> shared that bypasses L1 (cp.async.cg).  The .ca form allocates
 // an L1 line per request; in kernels that give almost all of the SM's 256 KB to shared memory the few
 // KB left for L1 cap the bytes in flight and with them the copy rate.
