@@ -312,7 +312,10 @@ def main():
             "kernel_ms": {"conv1d": conv_ms, "kda_chunked_prefill(prep+scan)": kda_ms},
             "roofline": {"bound": "hbm", "kernel": "kda_chunk_prep_kernel + kda_chunk_scan_kernel",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": None, "peak_kind": peak_kind,
+                         # dram__bytes_read + dram__bytes_write of prep + scan from the ncu capture of the T = 8,192
+                         # case (985 MB), scaled by the chunk count: traffic is linear in T
+                         "traffic": 985.0e6 * (T / 8192.0), "traffic_source": "profiles/kda_chunked_prefill_8k_ncu_full.md",
+                         "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "tensor_tflops_dense_chunk_math": (T // 64) * H * 11.71e6 / (kda_ms * 1e-3) / 1e12},
             "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,

@@ -1,11 +1,22 @@
 // Absorbed MLA projections either side of the attention: q_lat = q_nope * W_uk (256 -> 512) and
 // o = lat_out * W_uv^T (512 -> 256), per head, plus the one-off W_uv transpose.  Interfaces of
 // helios::attn::q_latent / q_latent_t / o_absorb / o_absorb_t / wuv_transpose
-// (reference: src/cuda/attn/attn.cu:12-130).  They are adjacent to the hot path, not part of it:
-// kept as plain CUDA-core kernels with fp32 accumulation so the engine's layer loop links.
+// (reference: src/cuda/attn/attn.cu:12-130).  The entry points run the tensor-core GEMM of absorb_tc.cu;
+// the plain CUDA-core kernels below (fp32 accumulation, one block per (row, head)) are the cross-check
+// (HK_ABSORB_FORCE_SIMT=1) and the path for buffers the tensor copies cannot address (not 16-byte aligned).
+#include <cstdlib>
+
 #include "hk_common.cuh"
 
 namespace hk {
+
+int absorb_gemm_tc(const void* a, const void* b, void* out, int n_rows, int K, int n_out, bool b_mn,
+                   uint64_t b_rows, uint64_t b_cols, int b_rows_per_head, int b_row_off, cudaStream_t s);
+
+static bool absorb_force_simt() {
+  static const bool v = getenv("HK_ABSORB_FORCE_SIMT") != nullptr;
+  return v;
+}
 
 // kv_b is the raw [64*512][512] fp16 tensor: rows h*512 .. +255 = W_uk[h], +256 .. +511 = W_uv[h].
 // grid (m, 64), 256 threads: thread t owns output columns 2t, 2t+1; q row staged in shared memory.
@@ -82,6 +93,10 @@ HK_API int hk_q_latent(const void* q_nope, const void* kv_b, void* q_lat, int m,
   using namespace hk;
   HK_REQUIRE(q_nope && kv_b && q_lat && m >= 0);
   if (m == 0) return HK_OK;
+  if (!absorb_force_simt()) {   // q_nope [m][64*256] x W_uk[h] = kv_b rows h*512 .. +255, [k][n] with n contiguous
+    const int st = absorb_gemm_tc(q_nope, kv_b, q_lat, m, 256, 512, true, 64 * 512, 512, 512, 0, as_stream(stream));
+    if (st != HK_ERR_UNSUPPORTED) return st;
+  }
   q_latent_kernel<<<dim3(m, 64), 256, 0, as_stream(stream)>>>((const __half*)q_nope, (const __half*)kv_b, (__half*)q_lat);
   HK_LAUNCH_CHECK();
   return HK_OK;
@@ -91,6 +106,10 @@ HK_API int hk_o_absorb(const void* lat_out, const void* kv_b, void* o, int m, vo
   using namespace hk;
   HK_REQUIRE(lat_out && kv_b && o && m >= 0);
   if (m == 0) return HK_OK;
+  if (!absorb_force_simt()) {   // lat_out [m][64*512] x W_uv[h]^T: kv_b rows h*512+256 .. +511 are [n][k], k contiguous
+    const int st = absorb_gemm_tc(lat_out, kv_b, o, m, 512, 256, false, 64 * 512, 512, 512, 256, as_stream(stream));
+    if (st != HK_ERR_UNSUPPORTED) return st;
+  }
   o_absorb_kernel<<<dim3(m, 64), 256, 0, as_stream(stream)>>>((const __half*)lat_out, (const __half*)kv_b, (__half*)o);
   HK_LAUNCH_CHECK();
   return HK_OK;
@@ -108,6 +127,10 @@ HK_API int hk_o_absorb_t(const void* lat_out, const void* wuv_t, void* o, int nr
   using namespace hk;
   HK_REQUIRE(lat_out && wuv_t && o && nrows >= 0);
   if (nrows == 0) return HK_OK;
+  if (!absorb_force_simt()) {   // lat_out [n][64*512] x wuv_t[h] = [512 k][256 n], n contiguous
+    const int st = absorb_gemm_tc(lat_out, wuv_t, o, nrows, 512, 256, true, 64 * 512, 256, 512, 0, as_stream(stream));
+    if (st != HK_ERR_UNSUPPORTED) return st;
+  }
   o_absorb_t_kernel<<<dim3(nrows, 64), 128, 0, as_stream(stream)>>>((const __half*)lat_out, (const __half*)wuv_t, (__half*)o);
   HK_LAUNCH_CHECK();
   return HK_OK;

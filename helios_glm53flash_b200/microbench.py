@@ -93,6 +93,22 @@ def build_case(name):
         def fn():
             hk.indexer_score(qi, pk, w, q_pos, sc, m, npools)
         return fn, npools * 256 + m * npools * 2, True, "indexer scores, %d rows x 65536 pools" % m
+    if name in ("q_latent_4096", "o_absorb_4096"):
+        n = 4096
+        kb = (0.05 * torch.randn(32768, 512, device="cuda")).half()
+        if name == "q_latent_4096":
+            qn = torch.randn(n, 64, 256, device="cuda").half()
+            ql = torch.empty(n, 64, 512, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.q_latent(qn, kb, ql, n)
+        else:
+            lo = torch.randn(n, 64, 512, device="cuda").half()
+            o = torch.empty(n, 64, 256, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.o_absorb(lo, kb, o, n)
+        return fn, n * 64 * (256 + 512) * 2 + 64 * 256 * 512 * 2, True, "absorbed projection, 4096 rows x 64 heads (68.7 GFLOP)"
     if name == "topk_262k":
         npools = 65536
         sc = torch.randn(1, npools, device="cuda").half()
@@ -117,7 +133,7 @@ def build_case(name):
 
 
 CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
-         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k"]
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "q_latent_4096", "o_absorb_4096"]
 
 
 def main():

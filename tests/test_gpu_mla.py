@@ -152,8 +152,10 @@ def test_combine_edge_cases_and_pointer_variant():
     assert np.array_equal(bits(out), bits(out2))
 
 
-def test_absorbed_projections_vs_oracle():
-    m = 2
+@pytest.mark.parametrize("m", [2, 131])
+def test_absorbed_projections_vs_oracle(m):
+    """tensor-core batched GEMMs (row tiles of 128: m = 131 leaves a ragged second tile) against the oracle;
+    both weight layouts of the output projection"""
     r = synth.rng(9)
     qn = synth.f32_to_f16_bits(r.uniform(-1, 1, (m, 64, 256)).astype(np.float32))
     kb = synth.f32_to_f16_bits((0.3 * r.uniform(-1, 1, (32768, 512))).astype(np.float32))

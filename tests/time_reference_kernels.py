@@ -101,6 +101,18 @@ def cases(torch, hk, ref, synth):
         theirs = lambda: ref.mla_dense_prefill(q, ck, lo, qlen, pos)
         return ours, theirs
 
+    def absorb(n, which):
+        kb = (0.05 * torch.randn(32768, 512, device="cuda")).half()
+        if which == "q":
+            qn = torch.randn(n, 64, 256, device="cuda").half()
+            ql = torch.empty(n, 64, 512, dtype=torch.float16, device="cuda")
+            return (lambda: hk.q_latent(qn, kb, ql, n)), (lambda: ref.q_latent_t(qn, kb, ql, n))
+        lo = torch.randn(n, 64, 512, device="cuda").half()
+        o = torch.empty(n, 64, 256, dtype=torch.float16, device="cuda")
+        wt = torch.empty(64, 512, 256, dtype=torch.float16, device="cuda")
+        ref.wuv_transpose(kb, wt)
+        return (lambda: hk.o_absorb(lo, kb, o, n)), (lambda: ref.o_absorb_t(lo, wt, o, n))
+
     return {
         "kda_prefill_32k": (lambda: kda(32768), "KDA layer prefill, T=32768, H=32, d=128 (reference: per-token recurrence)", 3),
         "kda_prefill_4k": (lambda: kda(4096), "KDA layer prefill, T=4096, H=32", 5),
@@ -113,6 +125,8 @@ def cases(torch, hk, ref, synth):
         "sparse_m256": (lambda: sparse(256), "sparse MLA, 256 rows x 2052 gathered latents", 5),
         "dense_decode_32k": (lambda: dense(1, 32767), "dense MLA decode, 1 row over 32768 latents", 10),
         "dense_prefill_256": (lambda: dense(256, 32768), "dense causal MLA prefill, 256 rows after 32768", 3),
+        "q_latent_4096": (lambda: absorb(4096, "q"), "absorbed query projection, 4096 rows x 64 heads (reference: q_latent_t)", 5),
+        "o_absorb_4096": (lambda: absorb(4096, "o"), "absorbed output projection, 4096 rows x 64 heads (reference: o_absorb_t on transposed weights)", 5),
     }
 
 
