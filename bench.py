@@ -9,7 +9,7 @@ between steps.  With N > 1 every rank runs the same workload on its own sequence
 collective on the data path); timing is device-side, max over ranks.
 
 One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the reference's
-algorithm (the reference has no CPU implementation of this path and is CUDA-only; see DESIGN.md) on
+algorithm (the reference has no CPU implementation of this path and is CUDA-only) on
 the host cores instead.
 """
 import argparse
@@ -314,7 +314,7 @@ def main():
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          # dram__bytes_read + dram__bytes_write of prep + scan from the ncu capture of the T = 8,192
                          # case (985 MB), scaled by the chunk count: traffic is linear in T
-                         "traffic": 985.0e6 * (T / 8192.0), "traffic_source": "profiles/kda_chunked_prefill_8k_ncu_full.md",
+                         "traffic": 985.0e6 * (T / 8192.0), "traffic_source": "ncu dram bytes of prep + scan at T = 8192, scaled by T / 8192",
                          "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "tensor_tflops_dense_chunk_math": (T // 64) * H * 11.71e6 / (kda_ms * 1e-3) / 1e12},
