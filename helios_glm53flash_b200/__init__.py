@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("HELIOS_B200_LIB") or os.path.join(_HERE, "libhelios_b200.so")
 
 HK_OK, HK_ERR_INVALID, HK_ERR_UNSUPPORTED, HK_ERR_CUDA, HK_ERR_WORKSPACE, HK_ERR_TIMEOUT = range(6)
-HK_F16, HK_BF16 = 0, 1
+HK_F16, HK_BF16, HK_F32 = 0, 1, 2
 
 _c = ctypes
 _vp, _i, _f, _sz, _i64 = _c.c_void_p, _c.c_int, _c.c_float, _c.c_size_t, _c.c_int64
@@ -31,6 +31,12 @@ SIGNATURES = {
     "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
     "hk_kda_chunked_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "hk_kda_chunked_prefill_gated": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "hk_kda_transpose_cast": (_i, [_vp, _vp, _i, _i, _vp]),
+    "hk_kda_gate": (_i, [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp]),
+    "hk_kda_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "hk_kda_cast_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "hk_gated_rms_norm": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _c.c_longlong, _i, _f, _f, _i, _i, _i, _vp]),
     "hk_kpool_write": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "hk_indexer_score": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hk_indexer_score_legacy": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
@@ -167,6 +173,58 @@ def cuda_recurrent_gated_delta_rule(mixed_qkv, g, beta, recurrent_state, core_at
 
 def kda_chunked_workspace_bytes(bsz, seqlen, num_heads):
     return load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)
+
+
+def kda_chunked_prefill_gated(mixed_qkv, f, b, dt_bias, a_log, lower_bound, recurrent_state, core_attn_out,
+                              bsz, seqlen, num_heads, slots=None, stream=None, out_f32=None, workspace=None):
+    """Chunked KDA prefill that forms g and beta itself from the raw gate projection ``f``, the raw beta
+    logit ``b`` and the layer's ``dt_bias`` / ``a_log`` (the arithmetic of helios::glue::kda_gate,
+    src/engine/glue2.cu:347-360), head dim 128."""
+    nbytes = load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)
+    ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device)
+    _call("hk_kda_chunked_prefill_gated", _ptr(mixed_qkv), _ptr(f), _ptr(b), _ptr(dt_bias), _ptr(a_log),
+          float(lower_bound), _ptr(recurrent_state), _ptr(core_attn_out), _ptr(out_f32), bsz, seqlen,
+          num_heads, _ptr(slots), _ptr(ws), ws.numel(), _stream(stream))
+
+
+# ---------------------------------------------------------------------------------------------
+# helios::glue (KDA producers) and helios::aux::gated_rms_norm (KDA consumer)
+# ---------------------------------------------------------------------------------------------
+def kda_transpose_cast(dst_bf16, src, S, F, stream=None):
+    """helios::glue::kda_transpose_cast (src/engine/glue2.cuh:61): [S][F] f32 -> [F][S] bf16."""
+    _call("hk_kda_transpose_cast", _ptr(dst_bf16), _ptr(src), S, F, _stream(stream))
+
+
+def kda_gate(b, f, dt_bias, a_log, lower_bound, beta_bf16, g, S, H, Dk, stream=None):
+    """helios::glue::kda_gate (src/engine/glue2.cuh:62-63)."""
+    _call("hk_kda_gate", _ptr(b), _ptr(f), _ptr(dt_bias), _ptr(a_log), float(lower_bound), _ptr(beta_bf16),
+          _ptr(g), S, H, Dk, _stream(stream))
+
+
+def kda_prepare(qkv, b, f, dt_bias, a_log, lower_bound, mixed_qkv_bf16, beta_bf16, g, S, F, H, Dk,
+                stream=None):
+    """helios::glue::kda_prepare (src/engine/glue2.cuh:64-67)."""
+    _call("hk_kda_prepare", _ptr(qkv), _ptr(b), _ptr(f), _ptr(dt_bias), _ptr(a_log), float(lower_bound),
+          _ptr(mixed_qkv_bf16), _ptr(beta_bf16), _ptr(g), S, F, H, Dk, _stream(stream))
+
+
+def kda_cast_conv(x_f32, conv_state, slots, weight, bias, out, bsz, dim, seqlen, activation, stream=None):
+    """kda_transpose_cast + cuda_causal_conv1d_update(K = 4) in one pass over token-major fp32 input."""
+    _call("hk_kda_cast_conv", _ptr(x_f32), _ptr(conv_state), _ptr(slots), _ptr(weight), _ptr(bias), _ptr(out),
+          bsz, dim, seqlen, int(bool(activation)), _stream(stream))
+
+
+def _dtype_code(t):
+    torch = _require_cuda()
+    return {torch.float16: HK_F16, torch.bfloat16: HK_BF16, torch.float32: HK_F32}[t.dtype]
+
+
+def gated_rms_norm(x, w, y, g, rows, dim, epsilon, constant_bias=0.0, w_groups=1, gate_first=False,
+                   gate_act=0, stream=None):
+    """helios::aux::gated_rms_norm (src/cuda/aux/norm.cuh:71-87); dtypes taken from the tensors."""
+    _call("hk_gated_rms_norm", _ptr(x), _ptr(w), _dtype_code(w), _ptr(y), _dtype_code(y), _ptr(g),
+          _dtype_code(g), rows, dim, float(epsilon), float(constant_bias), w_groups, int(bool(gate_first)),
+          int(gate_act), _stream(stream))
 
 
 def dsa_topk(scores, s_stride, indices, R, T, k, k_pad, t_ptr=None, t_seq=0, stream=None):

@@ -201,10 +201,16 @@ __device__ __forceinline__ void prep_ab_block(const int ib, const float (&v)[2][
   }
 }
 
+// GATED: `g` holds the raw gate projection f and `beta_in` the raw fp32 b; the kernel applies
+//   g = lower_bound * sigmoid(exp(a_log[head]) * (f + dt_bias[head][channel])),  beta = bf16(sigmoid(b))
+// itself (the arithmetic of the reference's separate gate kernel, src/engine/glue2.cu:347-360), so the
+// fp32 gate tensor is never written to or read back from memory.
+template <bool GATED>
 __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
-    const __nv_bfloat16* __restrict__ beta, uint8_t* __restrict__ ws, int seqlen, int H,
-    int n_chunks, int prefetch_dist, int* __restrict__ status) {
+    const void* __restrict__ beta_in, uint8_t* __restrict__ ws, int seqlen, int H,
+    int n_chunks, int prefetch_dist, int* __restrict__ status, const float* __restrict__ dt_bias,
+    const float* __restrict__ a_log, float lower_bound) {
   extern __shared__ __align__(128) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + P1_G);
   uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
@@ -296,7 +302,15 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       else *reinterpret_cast<uint4*>(vdst) = make_uint4(0, 0, 0, 0);
     }
     __pipeline_commit();
-    if (tid < KC) sBeta[tid] = tid < n_valid ? __bfloat162float(beta[((size_t)b * seqlen + t0 + tid) * H + head]) : 0.f;
+    if (tid < KC) {
+      float bv = 0.f;
+      if (tid < n_valid) {
+        const size_t bi = ((size_t)b * seqlen + t0 + tid) * H + head;
+        if (GATED) bv = __bfloat162float(__float2bfloat16(1.0f / (1.0f + __expf(-static_cast<const float*>(beta_in)[bi]))));
+        else bv = __bfloat162float(static_cast<const __nv_bfloat16*>(beta_in)[bi]);
+      }
+      sBeta[tid] = bv;
+    }
     for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
     // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
     if (tid < 192) {
@@ -332,6 +346,24 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   KT_TRACE(1);
   __pipeline_wait_prior(1);                                 // g has landed; the v rows may still be in flight
+  if (GATED) {
+    // every thread turns the pieces it copied itself (tokens warp, warp + 8, ...; 4 channels) into gates
+    const float decay = __expf(__ldg(a_log + head));
+    const float4 bias = __ldg(reinterpret_cast<const float4*>(dt_bias + (size_t)head * KD) + lane);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int t = warp + 8 * i;
+      if (t < n_valid) {
+        float4* gp = reinterpret_cast<float4*>(sG + t * P1_LD + lane * 4);
+        float4 fv = *gp;
+        fv.x = lower_bound * (1.0f / (1.0f + __expf(-(decay * (fv.x + bias.x)))));
+        fv.y = lower_bound * (1.0f / (1.0f + __expf(-(decay * (fv.y + bias.y)))));
+        fv.z = lower_bound * (1.0f / (1.0f + __expf(-(decay * (fv.z + bias.z)))));
+        fv.w = lower_bound * (1.0f / (1.0f + __expf(-(decay * (fv.w + bias.w)))));
+        *gp = fv;
+      }
+    }
+  }
   __syncthreads();
 
   KT_TRACE(2);
@@ -822,15 +854,17 @@ HK_API size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads)
   return (size_t)bsz * num_heads * n_chunks * hk::U_BYTES;
 }
 
-HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* beta,
-                                  float* state, void* out, float* out_f32, int bsz, int seqlen,
-                                  int num_heads, const int* slots, void* workspace,
-                                  size_t workspace_bytes, void* stream) {
-  using namespace hk;
-  HK_REQUIRE(mixed_qkv && g && beta && state && out && workspace);
+namespace hk {
+namespace {
+int chunked_prefill_launch(const void* mixed_qkv, const float* g_or_f, const void* beta_or_b, const float* dt_bias,
+                           const float* a_log, float lower_bound, bool gated, float* state, void* out,
+                           float* out_f32, int bsz, int seqlen, int num_heads, const int* slots,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  HK_REQUIRE(mixed_qkv && g_or_f && beta_or_b && state && out && workspace);
+  HK_REQUIRE(!gated || (dt_bias && a_log && aligned(dt_bias, 16) && aligned(beta_or_b, 4)));
   HK_REQUIRE(bsz > 0 && seqlen > 0 && num_heads > 0);
   HK_REQUIRE(bsz <= 65535 && (seqlen + KC - 1) / KC <= 65535);   // grid limits
-  HK_REQUIRE(aligned(mixed_qkv, 16) && aligned(g, 16) && aligned(state, 16) && aligned(out, 16) &&
+  HK_REQUIRE(aligned(mixed_qkv, 16) && aligned(g_or_f, 16) && aligned(state, 16) && aligned(out, 16) &&
              aligned(workspace, 256) && (!out_f32 || aligned(out_f32, 16)));
   if (workspace_bytes < hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)) return HK_ERR_WORKSPACE;
   const int n_chunks = (seqlen + KC - 1) / KC;
@@ -838,20 +872,46 @@ HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const v
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(kda_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P1_SMEM) != cudaSuccess ||
+    if (cudaFuncSetAttribute(kda_chunk_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P1_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(kda_chunk_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P1_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM) != cudaSuccess)
       return HK_ERR_CUDA;
     attr_set[dev] = true;
   }
   cudaStream_t s = as_stream(stream);
   int* st = device_status_ptr();
-  kda_chunk_prep_kernel<<<dim3(num_heads, n_chunks, bsz), 256, P1_SMEM, s>>>(
-      (const __nv_bfloat16*)mixed_qkv, g, (const __nv_bfloat16*)beta, (uint8_t*)workspace, seqlen,
-      num_heads, n_chunks, 2 * sm_count(), st);
+  const dim3 grid(num_heads, n_chunks, bsz);
+  if (gated)
+    kda_chunk_prep_kernel<true><<<grid, 256, P1_SMEM, s>>>((const __nv_bfloat16*)mixed_qkv, g_or_f, beta_or_b,
+                                                         (uint8_t*)workspace, seqlen, num_heads, n_chunks,
+                                                         2 * sm_count(), st, dt_bias, a_log, lower_bound);
+  else
+    kda_chunk_prep_kernel<false><<<grid, 256, P1_SMEM, s>>>((const __nv_bfloat16*)mixed_qkv, g_or_f, beta_or_b,
+                                                          (uint8_t*)workspace, seqlen, num_heads, n_chunks,
+                                                          2 * sm_count(), st, nullptr, nullptr, 0.f);
   HK_LAUNCH_CHECK();
   kda_chunk_scan_kernel<<<dim3(KVS, num_heads, bsz), 128, P2_SMEM, s>>>(
       (const uint8_t*)workspace, state, (__nv_bfloat16*)out, out_f32, seqlen, num_heads, n_chunks,
       slots, 1.0f / sqrtf((float)KD), st);
   HK_LAUNCH_CHECK();
   return HK_OK;
+}
+}  // namespace
+}  // namespace hk
+
+HK_API int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* beta,
+                                  float* state, void* out, float* out_f32, int bsz, int seqlen,
+                                  int num_heads, const int* slots, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  return hk::chunked_prefill_launch(mixed_qkv, g, beta, nullptr, nullptr, 0.f, false, state, out, out_f32, bsz,
+                                    seqlen, num_heads, slots, workspace, workspace_bytes, stream);
+}
+
+HK_API int hk_kda_chunked_prefill_gated(const void* mixed_qkv, const float* f, const float* b,
+                                        const float* dt_bias, const float* a_log, float lower_bound,
+                                        float* state, void* out, float* out_f32, int bsz, int seqlen,
+                                        int num_heads, const int* slots, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  return hk::chunked_prefill_launch(mixed_qkv, f, b, dt_bias, a_log, lower_bound, true, state, out, out_f32, bsz,
+                                    seqlen, num_heads, slots, workspace, workspace_bytes, stream);
 }

@@ -3,7 +3,7 @@
 // (reference: src/cuda/aux/gdn.cu:880-1023): fp32 fma chain k ascending, SiLU as a * 1/(1+exp(-a)),
 // bf16 round-to-nearest output, state = last K inputs.
 //
-// Three kernels:
+// Four kernels (the last one is the fused cast + convolution over token-major fp32 input, further below):
 //   conv4_row_kernel   prefill with whole 16-token groups: K = 4, no history, seqlen % 16 == 0.  No
 //                      shared memory: a lane keeps 2 channels x 16 tokens in registers (32-byte reads
 //                      per channel row, 128-byte warp stores per output row).
@@ -243,7 +243,121 @@ __global__ __launch_bounds__(256) void conv_generic_kernel(
   }
 }
 
+
+// Cast + convolution in one pass over TOKEN-major fp32 input (the projection's own output layout): the
+// transposed bf16 copy that the channel-major kernels read is never made.  A thread owns 4 adjacent
+// channels (one 16-byte load per token; a warp reads 512 contiguous bytes of a token row and writes 256)
+// and walks CR_TOK consecutive tokens with the three previous inputs in registers.  Inputs are rounded
+// to bf16 first, so the result equals transpose-cast followed by the channel-major convolution, bit for
+// bit.  x [bsz][seqlen][dim] f32, out [bsz][seqlen][dim] bf16, state [slots][dim][4] bf16.
+constexpr int CR_TOK = 64;
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <bool ACT>
+__global__ __launch_bounds__(128) void conv4_cast_rows_kernel(
+    const float* __restrict__ x, __nv_bfloat16* __restrict__ state, const int* __restrict__ slots,
+    const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
+    __nv_bfloat16* __restrict__ out, int dim, int seqlen) {
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 4;
+  if (c >= dim) return;
+  const int s0 = blockIdx.y * CR_TOK, b = blockIdx.z;
+  const int s1 = min(s0 + CR_TOK, seqlen);
+  const float* xb = x + (size_t)b * seqlen * dim + c;
+  float w[4][4], bs[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const uint4 w01 = *reinterpret_cast<const uint4*>(weight + (size_t)c * 4);
+    const uint4 w23 = *reinterpret_cast<const uint4*>(weight + (size_t)c * 4 + 8);
+    const uint32_t ww[8] = {w01.x, w01.y, w01.z, w01.w, w23.x, w23.y, w23.z, w23.w};
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+      w[ch][0] = bf16lo(ww[2 * ch]); w[ch][1] = bf16hi(ww[2 * ch]);
+      w[ch][2] = bf16lo(ww[2 * ch + 1]); w[ch][3] = bf16hi(ww[2 * ch + 1]);
+    }
+    if (bias) {
+#pragma unroll
+      for (int ch = 0; ch < 4; ch++) bs[ch] = __bfloat162float(bias[c + ch]);
+    }
+  }
+  float h0[4], h1[4], h2[4];                                // inputs s-3, s-2, s-1 of the four channels
+  if (s0 == 0) {
+    // the first segment takes its predecessors from the window state and rolls the state forward
+    const int slot = slots ? slots[b] : b;
+    __nv_bfloat16* st = state + ((size_t)slot * dim + c) * 4;
+    const uint4 o01 = *reinterpret_cast<const uint4*>(st), o23 = *reinterpret_cast<const uint4*>(st + 8);
+    const uint32_t ow[8] = {o01.x, o01.y, o01.z, o01.w, o23.x, o23.y, o23.z, o23.w};
+    uint32_t nw[8];
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+      const float old[4] = {bf16lo(ow[2 * ch]), bf16hi(ow[2 * ch]), bf16lo(ow[2 * ch + 1]), bf16hi(ow[2 * ch + 1])};
+      h0[ch] = old[1]; h1[ch] = old[2]; h2[ch] = old[3];
+      float nv[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {                          // new window = last 4 of [old | x]
+        const int src_t = seqlen + k;
+        nv[k] = src_t < 4 ? old[src_t] : xb[(size_t)(src_t - 4) * dim + ch];
+      }
+      nw[2 * ch] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(nv[0])) |
+                   ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(nv[1])) << 16);
+      nw[2 * ch + 1] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(nv[2])) |
+                       ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(nv[3])) << 16);
+    }
+    *reinterpret_cast<uint4*>(st) = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+    *reinterpret_cast<uint4*>(st + 8) = make_uint4(nw[4], nw[5], nw[6], nw[7]);
+  } else {
+    const float4 p0 = *reinterpret_cast<const float4*>(xb + (size_t)(s0 - 3) * dim);
+    const float4 p1 = *reinterpret_cast<const float4*>(xb + (size_t)(s0 - 2) * dim);
+    const float4 p2 = *reinterpret_cast<const float4*>(xb + (size_t)(s0 - 1) * dim);
+    h0[0] = round_bf16(p0.x); h0[1] = round_bf16(p0.y); h0[2] = round_bf16(p0.z); h0[3] = round_bf16(p0.w);
+    h1[0] = round_bf16(p1.x); h1[1] = round_bf16(p1.y); h1[2] = round_bf16(p1.z); h1[3] = round_bf16(p1.w);
+    h2[0] = round_bf16(p2.x); h2[1] = round_bf16(p2.y); h2[2] = round_bf16(p2.z); h2[3] = round_bf16(p2.w);
+  }
+  __nv_bfloat16* ob = out + (size_t)b * seqlen * dim + c;
+  for (int t0 = s0; t0 < s1; t0 += 8) {
+    uint4 raw[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      raw[j] = t0 + j < s1 ? ld_stream16(xb + (size_t)(t0 + j) * dim) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      if (t0 + j >= s1) break;
+      const float cur[4] = {round_bf16(__uint_as_float(raw[j].x)), round_bf16(__uint_as_float(raw[j].y)),
+                            round_bf16(__uint_as_float(raw[j].z)), round_bf16(__uint_as_float(raw[j].w))};
+      float y[4];
+#pragma unroll
+      for (int ch = 0; ch < 4; ch++) {
+        y[ch] = fmaf(w[ch][3], cur[ch], fmaf(w[ch][2], h2[ch], fmaf(w[ch][1], h1[ch], fmaf(w[ch][0], h0[ch], bs[ch]))));
+        if (ACT) y[ch] = silu_fast(y[ch]);
+        h0[ch] = h1[ch]; h1[ch] = h2[ch]; h2[ch] = cur[ch];
+      }
+      uint2 pk;
+      pk.x = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y[0])) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y[1])) << 16);
+      pk.y = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y[2])) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y[3])) << 16);
+      *reinterpret_cast<uint2*>(ob + (size_t)(t0 + j) * dim) = pk;
+    }
+  }
+}
+
 }  // namespace hk
+
+HK_API int hk_kda_cast_conv(const float* x, void* conv_state, const int* slots, const void* weight,
+                            const void* bias, void* out, int bsz, int dim, int seqlen, int activation,
+                            void* stream) {
+  using namespace hk;
+  HK_REQUIRE(x && conv_state && weight && out);
+  HK_REQUIRE(bsz > 0 && bsz <= 65535 && dim > 0 && dim % 4 == 0 && seqlen > 0);
+  HK_REQUIRE((seqlen + CR_TOK - 1) / CR_TOK <= 65535);
+  HK_REQUIRE(aligned(x, 16) && aligned(conv_state, 16) && aligned(weight, 16) && aligned(out, 8));
+  dim3 grid((dim / 4 + 127) / 128, (seqlen + CR_TOK - 1) / CR_TOK, bsz);
+  auto st = (__nv_bfloat16*)conv_state;
+  auto w = (const __nv_bfloat16*)weight;
+  auto bs = (const __nv_bfloat16*)bias;
+  auto o = (__nv_bfloat16*)out;
+  if (activation) conv4_cast_rows_kernel<true><<<grid, 128, 0, as_stream(stream)>>>(x, st, slots, w, bs, o, dim, seqlen);
+  else            conv4_cast_rows_kernel<false><<<grid, 128, 0, as_stream(stream)>>>(x, st, slots, w, bs, o, dim, seqlen);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}
 
 HK_API int hk_conv1d_update(const void* x, void* conv_state, const int* slots, const void* weight,
                             const void* bias, void* out, int bsz, int dim, int seqlen,

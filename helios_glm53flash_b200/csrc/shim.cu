@@ -175,5 +175,32 @@ void dsa_topk(const half* scores, int s_stride, int* indices, int R, int T, int 
 
 void dsa_topk_free_workspace(void) {}  // this implementation keeps no top-k workspace
 
+void gated_rms_norm(const void* x, const void* w, DType tw, void* y, DType ty, const void* g, DType tg,
+                    int rows, int dim, float epsilon, float constant_bias, int w_groups, bool gate_first,
+                    int gate_act, Stream s) {
+  auto code = [](DType t) { return t == kFloat ? HK_F32 : (t == kHalf ? HK_F16 : HK_BF16); };
+  check(hk_gated_rms_norm(x, w, code(tw), y, code(ty), g, code(tg), rows, dim, epsilon, constant_bias,
+                          w_groups, gate_first, gate_act, s),
+        "gated_rms_norm");
+}
+
 }  // namespace aux
+
+namespace glue {
+
+void kda_transpose_cast(void* dst_bf16, const float* src, int S, int F, Stream s) {
+  check(hk_kda_transpose_cast(dst_bf16, src, S, F, s), "kda_transpose_cast");
+}
+void kda_gate(const float* b, const float* f, const float* dt_bias, const float* a_log,
+              float lower_bound, void* beta_bf16, float* g, int S, int H, int Dk, Stream s) {
+  check(hk_kda_gate(b, f, dt_bias, a_log, lower_bound, beta_bf16, g, S, H, Dk, s), "kda_gate");
+}
+void kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
+                 const float* a_log, float lower_bound, void* mixed_qkv_bf16, void* beta_bf16, float* g,
+                 int S, int F, int H, int Dk, Stream s) {
+  check(hk_kda_prepare(qkv, b, f, dt_bias, a_log, lower_bound, mixed_qkv_bf16, beta_bf16, g, S, F, H, Dk, s),
+        "kda_prepare");
+}
+
+}  // namespace glue
 }  // namespace helios

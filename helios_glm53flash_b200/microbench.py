@@ -49,6 +49,53 @@ def build_case(name):
         def fn():
             hk.cuda_causal_conv1d_update(x, st, None, w, None, out, 1, dim, T, 4, 4, True, False)
         return fn, 4 * dim * T, False, "short conv + SiLU, 12288 channels x %d tokens" % T
+    if name in ("transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k",
+                "transpose_cast_4k", "gate_4k", "gated_norm_4k", "cast_conv_4k"):
+        T = 4096 if name.endswith("_4k") else 32768
+        F = 3 * H * D
+        kind = name.rsplit("_", 1)[0]
+        if kind == "transpose_cast":
+            x = torch.randn(T, F, device="cuda")
+            dst = torch.empty(F, T, dtype=torch.bfloat16, device="cuda")
+
+            def fn():
+                hk.kda_transpose_cast(dst, x, T, F)
+            return fn, 6 * T * F, False, "transpose + cast, %d tokens x 12288 channels (fp32 in, bf16 out)" % T
+        if kind == "cast_conv":
+            x = torch.randn(1, T, F, device="cuda")
+            w = (0.1 * torch.randn(F, 4, device="cuda")).to(torch.bfloat16)
+            st = torch.zeros(1, F, 4, dtype=torch.bfloat16, device="cuda")
+            out = torch.empty(1, T, F, dtype=torch.bfloat16, device="cuda")
+
+            def fn():
+                hk.kda_cast_conv(x, st, None, w, None, out, 1, F, T, True)
+            return fn, 6 * T * F, False, "cast + short conv + SiLU from token-major fp32, %d tokens x 12288 channels" % T
+        raw = synth.kda_raw_gates(T, H, D, seed=2)
+        f, b = torch.from_numpy(raw["f"]).cuda(), torch.from_numpy(raw["b"]).cuda()
+        dtb, al = torch.from_numpy(raw["dt_bias"]).cuda(), torch.from_numpy(raw["a_log"]).cuda()
+        if kind == "gate":
+            beta = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+            g = torch.empty(T, H, D, dtype=torch.float32, device="cuda")
+
+            def fn():
+                hk.kda_gate(b, f, dtb, al, raw["lower_bound"], beta, g, T, H, D)
+            return fn, T * H * (8 * D + 6), False, "gate preparation, %d tokens x 32 heads x 128" % T
+        if kind == "gated_norm":
+            x = torch.randn(T * H, D, device="cuda").to(torch.bfloat16)
+            w = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+            y = torch.empty(T * H, D, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)
+            return fn, T * H * D * 8, False, "gated RMS norm (sigmoid), %d rows of 128 (bf16 in, fp32 gate, fp16 out)" % (T * H)
+        qkv = torch.randn(1, T, F, device="cuda").to(torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(hk.kda_chunked_workspace_bytes(1, T, H), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.kda_chunked_prefill_gated(qkv, f, b, dtb, al, raw["lower_bound"], st, out, 1, T, H, workspace=ws)
+        return fn, T * H * 1538 + 2 * H * D * D * 4, False, "KDA prefill with the gates formed in the kernel, T=%d H=32" % T
     if name == "kda_decode":
         kd = synth.kda_inputs(1, H, D, seed=5)
         q, g, b = _bits16(kd["mixed_qkv"], torch.bfloat16), torch.from_numpy(kd["g"]).cuda(), _bits16(kd["beta"], torch.bfloat16)
@@ -133,7 +180,9 @@ def build_case(name):
 
 
 CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
-         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "q_latent_4096", "o_absorb_4096"]
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "q_latent_4096", "o_absorb_4096",
+         "transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k", "transpose_cast_4k",
+         "gate_4k", "gated_norm_4k", "cast_conv_4k"]
 
 
 def main():

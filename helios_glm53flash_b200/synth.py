@@ -60,6 +60,17 @@ def kda_gates(seqlen, heads=32, dim=128, bsz=1, seed=0):
     return {"g": g.astype(np.float32), "beta": f32_to_bf16_bits(beta)}
 
 
+def kda_raw_gates(seqlen, heads=32, dim=128, seed=0):
+    """Inputs of the gate preparation: raw gate projection f [T][H][D] ~ N(0,1), raw beta logit b [T][H] ~ N(0,1),
+    dt_bias [H][D] ~ N(0,0.5), a_log [H] ~ U(log 0.5, log 4); the model's lower bound is -5."""
+    r = rng(seed + 606)
+    return {"f": r.standard_normal((seqlen, heads, dim), dtype=np.float32),
+            "b": r.standard_normal((seqlen, heads), dtype=np.float32),
+            "dt_bias": (0.5 * r.standard_normal((heads, dim), dtype=np.float32)).astype(np.float32),
+            "a_log": r.uniform(np.log(0.5), np.log(4.0), heads).astype(np.float32),
+            "lower_bound": -5.0}
+
+
 def conv_inputs(seqlen, dim, bsz=1, K=4, seed=0):
     """Short-conv inputs: x ~ N(0,1) channel-major [bsz][dim][T], weights ~ N(0,0.1) [dim][K],
     previous window state ~ N(0,1) [bsz][dim][K]."""

@@ -37,7 +37,7 @@ typedef enum hk_status {
 } hk_status;
 
 /* dtype tags for the entry points that accept either 16-bit float format */
-enum { HK_F16 = 0, HK_BF16 = 1 };
+enum { HK_F16 = 0, HK_BF16 = 1, HK_F32 = 2 };
 
 const char* hk_status_string(int status);
 int hk_abi_version(void);
@@ -79,6 +79,54 @@ int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* be
                            void* out, float* out_f32, int bsz, int seqlen, int num_heads,
                            const int* slots, void* workspace, size_t workspace_bytes,
                            void* stream);
+
+/* The same prefill with the gate preparation inside the first kernel: `f` [bsz][seqlen][H][128] f32 is the
+ * raw gate projection and `b` [bsz][seqlen][H] f32 the raw beta logit;
+ *   g = lower_bound * sigmoid(exp(a_log[h]) * (f + dt_bias[h][d])),  beta = bf16(sigmoid(b))
+ * are formed on the fly, so the fp32 gate tensor of helios::glue::kda_gate (src/engine/glue2.cuh:62-63,
+ * glue2.cu:347-368) is neither written nor read back.  Results equal hk_kda_gate followed by
+ * hk_kda_chunked_prefill, bit for bit.  dt_bias [H][128] f32 (16-byte aligned), a_log [H] f32.      */
+int hk_kda_chunked_prefill_gated(const void* mixed_qkv, const float* f, const float* b,
+                                 const float* dt_bias, const float* a_log, float lower_bound,
+                                 float* state, void* out, float* out_f32, int bsz, int seqlen,
+                                 int num_heads, const int* slots, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * (a') producers and consumer either side of the KDA recurrence
+ * ------------------------------------------------------------------------------------------- */
+
+/* dst[f][s] = bf16(src[s][f]): token-major fp32 projection output -> channel-major conv input.
+ * Replaces helios::glue::kda_transpose_cast (src/engine/glue2.cuh:61, glue2.cu:318-344).          */
+int hk_kda_transpose_cast(void* dst_bf16, const float* src, int S, int F, void* stream);
+
+/* beta[s][h] = bf16(sigmoid(b[s][h]));  g[s][h][d] = lower_bound * sigmoid(exp(a_log[h]) * (f[s][h][d] +
+ * dt_bias[h][d])).  Replaces helios::glue::kda_gate (src/engine/glue2.cuh:62-63, glue2.cu:347-368). */
+int hk_kda_gate(const float* b, const float* f, const float* dt_bias, const float* a_log,
+                float lower_bound, void* beta_bf16, float* g, int S, int H, int Dk, void* stream);
+
+/* Both of the above in one call.  Replaces helios::glue::kda_prepare (src/engine/glue2.cuh:64-67,
+ * glue2.cu:370-404).                                                                              */
+int hk_kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
+                   const float* a_log, float lower_bound, void* mixed_qkv_bf16, void* beta_bf16,
+                   float* g, int S, int F, int H, int Dk, void* stream);
+
+/* Cast + short convolution (window 4) in one pass over the TOKEN-major fp32 projection output, i.e.
+ * hk_kda_transpose_cast followed by hk_conv1d_update(K = 4, state_size = 4, history = 0) without the
+ * transposed intermediate; same bits.   x [bsz][seqlen][dim] f32 (16-byte aligned, dim % 4 == 0)
+ * state [slots][dim][4] bf16 (in place)   w [dim][4] bf16   bias [dim] bf16 or NULL
+ * out [bsz][seqlen][dim] bf16.                                                                    */
+int hk_kda_cast_conv(const float* x, void* conv_state, const int* slots, const void* weight,
+                     const void* bias, void* out, int bsz, int dim, int seqlen, int activation,
+                     void* stream);
+
+/* y = x * w * rsqrt(mean(x^2) + epsilon) * act(g) per row of `dim` channels (gate_first: the gate is
+ * applied to x before the norm).  Replaces helios::aux::gated_rms_norm (src/cuda/aux/norm.cuh:71-87,
+ * norm.cu:294-468).  x bf16; w_type HK_F32 / HK_BF16 ([w_groups][dim], row r uses w[r % w_groups]);
+ * y_type HK_F16 / HK_F32; g_type HK_BF16 / HK_F32; gate_act 0 = SiLU, 1 = sigmoid; dim % 4 == 0.     */
+int hk_gated_rms_norm(const void* x, const void* w, int w_type, void* y, int y_type, const void* g,
+                      int g_type, long long rows, int dim, float epsilon, float constant_bias,
+                      int w_groups, int gate_first, int gate_act, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * (c) DSA indexer

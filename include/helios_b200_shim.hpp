@@ -6,7 +6,7 @@
 // test_deterministic_reductions.cu).  Names, namespaces, argument order, argument meaning and the
 // error behaviour (precondition failure -> message on stderr + abort()) are the reference's
 // (declared there in src/cuda/attn/attn.cuh:24-108, src/cuda/aux/gdn.cuh:47-83,
-// src/cuda/aux/dsa_topk.cuh:15-43); the bodies forward to the hk_* C ABI (helios_b200.h).
+// src/cuda/aux/dsa_topk.cuh:15-43, src/cuda/aux/norm.cuh:71-87, src/engine/glue2.cuh:57-67); the bodies forward to the hk_* C ABI (helios_b200.h).
 //
 // Differences a maintainer should know:
 //   * the reference signatures carry no scratch pointers, so this layer keeps one grow-only device
@@ -70,7 +70,24 @@ void cuda_causal_conv1d_update(const bfloat16* x, bfloat16* conv_state, const in
 void dsa_topk(const half* scores, int s_stride, int* indices, int R, int T, int k, int k_pad,
               const int* t_ptr = nullptr, int t_seq = 0, Stream stream = 0);
 void dsa_topk_free_workspace(void);
+
+// dtype tags of the raw-pointer launchers (src/cuda/aux/dtypes.hpp:10-15; same values)
+enum DType : int { kFloat = 0, kHalf = 1, kBFloat16 = 2 };
+// y = norm(x) * w * act(g) (src/cuda/aux/norm.cuh:71-87): x bf16; w float/bf16; y half/float; g bf16/float
+void gated_rms_norm(const void* x, const void* w, DType tw, void* y, DType ty, const void* g, DType tg,
+                    int rows, int dim, float epsilon, float constant_bias = 0.0f, int w_groups = 1,
+                    bool gate_first = false, int gate_act = 0, Stream s = 0);
 }  // namespace aux
+
+namespace glue {
+// KDA producers (src/engine/glue2.cuh:57-67)
+void kda_transpose_cast(void* dst_bf16, const float* src, int S, int F, Stream s = 0);
+void kda_gate(const float* b, const float* f, const float* dt_bias, const float* a_log,
+              float lower_bound, void* beta_bf16, float* g, int S, int H, int Dk, Stream s = 0);
+void kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
+                 const float* a_log, float lower_bound, void* mixed_qkv_bf16, void* beta_bf16, float* g,
+                 int S, int F, int H, int Dk, Stream s = 0);
+}  // namespace glue
 
 namespace b200 {
 // frees this layer's per-GPU scratch buffer on the current device (it regrows on demand)

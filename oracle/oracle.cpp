@@ -577,4 +577,79 @@ int orc_o_absorb(const uint16_t* lat_out, const uint16_t* kv_b, uint16_t* o, int
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// N2  KDA producers: transpose + cast and gate preparation
+// follows src/engine/glue2.cu:318-344 (kda_transpose_cast_k) and :347-368 (kda_gate_k; the same
+// arithmetic is in kda_prepare_k :370-396)
+//   mixed[f][s] = bf16_rn(qkv[s][f]);  beta[s][h] = bf16_rn(sigmoid(b[s][h]))
+//   g[s][h][d]  = lower_bound * sigmoid(exp(a_log[h]) * (f[s][h][d] + dt_bias[h][d]))
+// exp here is the host's (the device uses its fast exponential): compare within a few ulp.
+// ---------------------------------------------------------------------------------------------
+int orc_kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
+                    const float* a_log, float lower_bound, uint16_t* mixed, uint16_t* beta, float* g,
+                    int S, int F, int H, int Dk) {
+  if (qkv && mixed) {
+    parallel_for(F, [&](int64_t ff) {
+      for (int s = 0; s < S; s++) mixed[(size_t)ff * S + s] = f_to_bf16_rn(qkv[(size_t)s * F + ff]);
+    });
+  }
+  if (b && beta) {
+    for (int64_t j = 0; j < (int64_t)S * H; j++) beta[j] = f_to_bf16_rn(1.0f / (1.0f + std::exp(-b[j])));
+  }
+  if (f && g) {
+    parallel_for(S, [&](int64_t s) {
+      for (int h = 0; h < H; h++) {
+        const float decay = std::exp(a_log[h]);
+        for (int d = 0; d < Dk; d++) {
+          const size_t i = ((size_t)s * H + h) * Dk + d;
+          g[i] = lower_bound * (1.0f / (1.0f + std::exp(-(decay * (f[i] + dt_bias[h * Dk + d])))));
+        }
+      }
+    });
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// N3  gated RMS norm (the KDA output gate)
+// follows src/cuda/aux/norm.cu:294-392 (gated_rms_norm_kernel) and the launcher :402-468
+//   y = x * w * rsqrt(mean(x^2) + eps) * act(g)        (gate_first: act(g) multiplies x before the norm)
+//   x bf16; w f32 or bf16, row r uses w[r % w_groups]; g f32 or bf16; y f16 (rn) or f32
+//   act = SiLU (gate_act 0) or sigmoid (gate_act 1).  The sum of squares runs in fp64 here (the device
+//   sums fp32 partials in lane order); products follow the device order x * w * rmf, then * act(g).
+// ---------------------------------------------------------------------------------------------
+int orc_gated_rms_norm(const uint16_t* x, const void* w, int w_bf16, void* y, int y_f32, const void* g,
+                       int g_bf16, int64_t rows, int dim, float eps, float constant_bias, int w_groups,
+                       int gate_first, int gate_act) {
+  if (dim % 4 != 0 || w_groups < 1) return 1;
+  parallel_for(rows, [&](int64_t r) {
+    auto wv = [&](int c) {
+      const size_t i = (size_t)(r % w_groups) * dim + c;
+      return (w_bf16 ? bf16_to_f(((const uint16_t*)w)[i]) : ((const float*)w)[i]) + (constant_bias != 0.0f ? constant_bias : 0.0f);
+    };
+    auto gv = [&](int c) {
+      const size_t i = (size_t)r * dim + c;
+      const float v = g_bf16 ? bf16_to_f(((const uint16_t*)g)[i]) : ((const float*)g)[i];
+      const float sg = 1.0f / (1.0f + std::exp(-v));
+      return gate_act == 1 ? sg : v * sg;
+    };
+    double ss = 0.0;
+    for (int c = 0; c < dim; c++) {
+      float xv = bf16_to_f(x[(size_t)r * dim + c]);
+      if (gate_first) xv *= gv(c);
+      ss += (double)xv * xv;
+    }
+    const float rmf = 1.0f / std::sqrt((float)(ss / dim) + eps);
+    for (int c = 0; c < dim; c++) {
+      float xv = bf16_to_f(x[(size_t)r * dim + c]);
+      if (gate_first) xv *= gv(c);
+      float o = xv * wv(c) * rmf;
+      if (!gate_first) o *= gv(c);
+      if (y_f32) ((float*)y)[(size_t)r * dim + c] = o;
+      else ((uint16_t*)y)[(size_t)r * dim + c] = f_to_h_rn(o);
+    }
+  });
+  return 0;
+}
+
 }  // extern "C"

@@ -2,11 +2,13 @@
 // the reference's kernels (its sm_86-era sources recompiled for sm_100a) beside the new library on
 // identical device buffers.  TEST INFRASTRUCTURE ONLY: this file contains no kernel code; it
 // includes the reference's headers from the reference tree at build time (see oracle/Makefile) and
-// is linked with objects compiled from the reference's attn.cu, gdn.cu and dsa_topk.cu where they
-// lie.  Nothing from the reference is copied into this repository.
+// is linked with objects compiled from the reference's attn.cu, gdn.cu, dsa_topk.cu, norm.cu and
+// glue2.cu where they lie.  Nothing from the reference is copied into this repository.
 #include "cuda/attn/attn.cuh"
 #include "cuda/aux/gdn.cuh"
 #include "cuda/aux/dsa_topk.cuh"
+#include "cuda/aux/norm.cuh"
+#include "engine/glue2.cuh"
 
 #define REF_API extern "C" __attribute__((visibility("default")))
 using bf16 = __nv_bfloat16;
@@ -100,4 +102,33 @@ REF_API void ref_wuv_transpose(const void* kv_b, void* wuv_t, void* stream) {
 
 REF_API void ref_o_absorb_t(const void* lat_out, const void* wuv_t, void* o, int n, void* stream) {
   helios::attn::o_absorb_t((const half*)lat_out, (const half*)wuv_t, (half*)o, n, (Stream)stream);
+}
+
+REF_API void ref_kda_transpose_cast(void* dst_bf16, const float* src, int S, int F, void* stream) {
+  helios::glue::kda_transpose_cast(dst_bf16, src, S, F, (Stream)stream);
+}
+
+REF_API void ref_kda_gate(const float* b, const float* f, const float* dt_bias, const float* a_log,
+                          float lower_bound, void* beta_bf16, float* g, int S, int H, int Dk,
+                          void* stream) {
+  helios::glue::kda_gate(b, f, dt_bias, a_log, lower_bound, beta_bf16, g, S, H, Dk, (Stream)stream);
+}
+
+REF_API void ref_kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
+                             const float* a_log, float lower_bound, void* mixed_qkv_bf16,
+                             void* beta_bf16, float* g, int S, int F, int H, int Dk, void* stream) {
+  helios::glue::kda_prepare(qkv, b, f, dt_bias, a_log, lower_bound, mixed_qkv_bf16, beta_bf16, g, S, F,
+                            H, Dk, (Stream)stream);
+}
+
+// dtype codes of this wrapper: 0 = half, 1 = bfloat16, 2 = float
+static helios::aux::DType ref_dtype(int code) {
+  return code == 0 ? helios::aux::kHalf : (code == 1 ? helios::aux::kBFloat16 : helios::aux::kFloat);
+}
+
+REF_API void ref_gated_rms_norm(const void* x, const void* w, int tw, void* y, int ty, const void* g,
+                                int tg, int rows, int dim, float epsilon, float constant_bias,
+                                int w_groups, int gate_first, int gate_act, void* stream) {
+  helios::aux::gated_rms_norm(x, w, ref_dtype(tw), y, ref_dtype(ty), g, ref_dtype(tg), rows, dim, epsilon,
+                              constant_bias, w_groups, gate_first != 0, gate_act, (Stream)stream);
 }

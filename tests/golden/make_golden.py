@@ -52,6 +52,14 @@ def cases():
     c["mla"] = ml
     pidx = np.where(np.arange(2 * 512) % 5 == 0, -1, rs.randint(0, 40, 2 * 512)).astype(np.int32).reshape(2, 512)
     c["expand"] = {"pool_idx": pidx, "q_pos": np.array([150, 3], dtype=np.int32)}
+    # KDA producers / consumer: gate preparation, transpose + cast, gated RMS norm (sigmoid gate, dim 128)
+    gt = synth.kda_raw_gates(10, 3, 128, seed=51)
+    gt["qkv"] = synth.rng(52).standard_normal((10, 72), dtype=np.float32)
+    c["kda_prepare"] = gt
+    r = synth.rng(53)
+    c["gated_norm"] = {"x": synth.f32_to_bf16_bits(r.standard_normal((12, 128), dtype=np.float32)),
+                       "w": synth.f32_to_bf16_bits((1 + 0.1 * r.standard_normal(128, dtype=np.float32)).astype(np.float32)),
+                       "g": (2 * r.standard_normal((12, 128), dtype=np.float32)).astype(np.float32)}
     return c
 
 
@@ -109,6 +117,19 @@ def main(out_path):
     ref.pool_expand_row(dev(k["pool_idx"]), dev(k["q_pos"]), raw, 2)
     torch.cuda.synchronize()
     g["expand_raw"] = raw.cpu().numpy()
+    k = c["kda_prepare"]
+    mixed = torch.empty(72, 10, dtype=torch.bfloat16, device="cuda")
+    beta = torch.empty(10, 3, dtype=torch.bfloat16, device="cuda")
+    gg = torch.empty(10, 3, 128, dtype=torch.float32, device="cuda")
+    ref.kda_transpose_cast(mixed, dev(k["qkv"]), 10, 72)
+    ref.kda_gate(dev(k["b"]), dev(k["f"]), dev(k["dt_bias"]), dev(k["a_log"]), k["lower_bound"], beta, gg, 10, 3, 128)
+    torch.cuda.synchronize()
+    g["prepare_mixed"], g["prepare_beta"], g["prepare_g"] = bits(mixed), bits(beta), gg.cpu().numpy()
+    k = c["gated_norm"]
+    y = torch.empty(12, 128, dtype=torch.float16, device="cuda")
+    ref.gated_rms_norm(dev_bf16(k["x"]), dev_bf16(k["w"]), y, dev(k["g"]), 12, 128, 1e-6, gate_act=1)
+    torch.cuda.synchronize()
+    g["gated_norm_y"] = bits(y)
     np.savez_compressed(out_path, **g)
     print("wrote", out_path, {n: v.shape for n, v in g.items()})
 

@@ -127,3 +127,25 @@ def o_absorb(lat_out, kv_b, m, n_heads=64):
     out = np.empty((m, n_heads, 256), dtype=np.uint16)
     assert lib().orc_o_absorb(_p(lat_out), _p(kv_b), _p(out), m, n_heads) == 0
     return out
+
+
+def kda_prepare(qkv, b, f, dt_bias, a_log, lower_bound, S, F, H, Dk):
+    """returns (mixed bf16 bits [F][S], beta bf16 bits [S][H], g f32 [S][H][Dk]); any of qkv / b / f may be None"""
+    mixed = np.empty((F, S), dtype=np.uint16) if qkv is not None else None
+    beta = np.empty((S, H), dtype=np.uint16) if b is not None else None
+    g = np.empty((S, H, Dk), dtype=np.float32) if f is not None else None
+    rc = lib().orc_kda_prepare(_p(qkv), _p(b), _p(f), _p(dt_bias), _p(a_log), _f(lower_bound), _p(mixed), _p(beta),
+                               _p(g), S, F, H, Dk)
+    assert rc == 0
+    return mixed, beta, g
+
+
+def gated_rms_norm(x, w, g, rows, dim, eps, y_f32=False, constant_bias=0.0, w_groups=1, gate_first=False,
+                   gate_act=0):
+    """x bf16 bits; w / g float32 arrays or uint16 (bf16 bits); returns y as f16 bits or float32"""
+    y = np.empty((rows, dim), dtype=np.float32 if y_f32 else np.uint16)
+    rc = lib().orc_gated_rms_norm(_p(x), _p(w), int(w.dtype == np.uint16), _p(y), int(y_f32), _p(g),
+                                  int(g.dtype == np.uint16), ctypes.c_int64(rows), dim, _f(eps), _f(constant_bias),
+                                  w_groups, int(gate_first), int(gate_act))
+    assert rc == 0
+    return y

@@ -91,3 +91,25 @@ def wuv_transpose(kv_b, wuv_t):
 
 def o_absorb_t(lat_out, wuv_t, o, n):
     lib().ref_o_absorb_t(_p(lat_out), _p(wuv_t), _p(o), n, _s())
+
+
+def kda_transpose_cast(dst_bf16, src, S, F):
+    lib().ref_kda_transpose_cast(_p(dst_bf16), _p(src), S, F, _s())
+
+
+def kda_gate(b, f, dt_bias, a_log, lower_bound, beta_bf16, g, S, H, Dk):
+    lib().ref_kda_gate(_p(b), _p(f), _p(dt_bias), _p(a_log), ctypes.c_float(lower_bound), _p(beta_bf16), _p(g),
+                       S, H, Dk, _s())
+
+
+def kda_prepare(qkv, b, f, dt_bias, a_log, lower_bound, mixed_qkv_bf16, beta_bf16, g, S, F, H, Dk):
+    lib().ref_kda_prepare(_p(qkv), _p(b), _p(f), _p(dt_bias), _p(a_log), ctypes.c_float(lower_bound),
+                          _p(mixed_qkv_bf16), _p(beta_bf16), _p(g), S, F, H, Dk, _s())
+
+
+def gated_rms_norm(x, w, y, g, rows, dim, epsilon, constant_bias=0.0, w_groups=1, gate_first=False, gate_act=0):
+    import torch
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+    lib().ref_gated_rms_norm(_p(x), _p(w), code[w.dtype], _p(y), code[y.dtype], _p(g), code[g.dtype], rows, dim,
+                             ctypes.c_float(epsilon), ctypes.c_float(constant_bias), w_groups, int(gate_first),
+                             int(gate_act), _s())

@@ -46,7 +46,8 @@ def test_reference_named_launchers_are_exported(built):
                  "helios::aux::dsa_topk(", "helios::attn::kpool_write(", "helios::attn::indexer_score(",
                  "helios::attn::pool_expand_row(", "helios::attn::mla_sparse_decode(",
                  "helios::attn::mla_dense_prefill(", "helios::attn::q_latent_t(", "helios::attn::o_absorb_t(",
-                 "helios::attn::o_absorb(", "helios::attn::wuv_transpose("]:
+                 "helios::attn::o_absorb(", "helios::attn::wuv_transpose(", "helios::aux::gated_rms_norm(",
+                 "helios::glue::kda_transpose_cast(", "helios::glue::kda_gate(", "helios::glue::kda_prepare("]:
         assert name in out, name
 
 
