@@ -449,6 +449,46 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
         hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
     f_chain = [(lambda pk=pk, ck=ck: chain(pk, ck)) for pk, ck in zip(pks, ckvs)]
     res["dsa_sparse_mla_decode_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_chain, flush=flush) / n_mla
+    del pks, ckvs, f_sparse, f_chain
+    torch.cuda.empty_cache()
+    # ---- one KDA layer of the 32K prefill from the projections' fp32 outputs to the gated, normalised fp16
+    #      activations: the reference's call sequence (transpose+cast, gate, conv, recurrence, gated norm) and the
+    #      fused form (cast+conv, prefill that forms its own gates, gated norm).  Buffers exceed L2. ----
+    T, F = T_FULL, 3 * H * D
+    raw_g = synth.kda_raw_gates(T, H, D, seed=2)
+    f_raw, b_raw = dev(raw_g["f"]), dev(raw_g["b"])
+    dtb, alog, lb = dev(raw_g["dt_bias"]), dev(raw_g["a_log"]), raw_g["lower_bound"]
+    x32 = torch.randn(1, T, F, device="cuda")
+    g_out = torch.randn(T * H, D, device="cuda")
+    w_conv = (0.1 * torch.randn(F, 4, device="cuda")).to(torch.bfloat16)
+    w_norm = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    mixed = torch.empty(F, T, dtype=torch.bfloat16, device="cuda")
+    conv_out = torch.empty(1, T, F, dtype=torch.bfloat16, device="cuda")
+    beta = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    gate = torch.empty(T, H, D, dtype=torch.float32, device="cuda")
+    cst = torch.zeros(1, F, 4, dtype=torch.bfloat16, device="cuda")
+    rst = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+    rec = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+    y16 = torch.empty(T * H, D, dtype=torch.float16, device="cuda")
+    ws = torch.empty(hk.kda_chunked_workspace_bytes(1, T, H), dtype=torch.uint8, device="cuda")
+
+    def layer_two_step():
+        hk.kda_transpose_cast(mixed, x32, T, F)
+        hk.kda_gate(b_raw, f_raw, dtb, alog, lb, beta, gate, T, H, D)
+        hk.cuda_causal_conv1d_update(mixed, cst, None, w_conv, None, conv_out, 1, F, T, 4, 4, True, False)
+        hk.cuda_recurrent_gated_delta_rule(conv_out, gate, beta, rst, rec, 1, T, H, H, D, D, 1, None, True, False, workspace=ws)
+        hk.gated_rms_norm(rec, w_norm, y16, g_out, T * H, D, 1e-6, gate_act=1)
+
+    def layer_fused():
+        hk.kda_cast_conv(x32, cst, None, w_conv, None, conv_out, 1, F, T, True)
+        hk.kda_chunked_prefill_gated(conv_out, f_raw, b_raw, dtb, alog, lb, rst, rec, 1, T, H, workspace=ws)
+        hk.gated_rms_norm(rec, w_norm, y16, g_out, T * H, D, 1e-6, gate_act=1)
+
+    ms2 = _time_loop(torch, [layer_two_step], iters=5, sustain_ms=0.0)
+    ms1 = _time_loop(torch, [layer_fused], iters=5, sustain_ms=0.0)
+    res["kda_layer_prefill_32k_reference_call_sequence_ms"] = ms2
+    res["kda_layer_prefill_32k_fused_ms"] = ms1
+    res["kda_layer_prefill_32k_fused_tokens_per_s"] = T / (ms1 * 1e-3)
     return res
 
 

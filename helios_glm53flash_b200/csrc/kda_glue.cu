@@ -188,42 +188,55 @@ __device__ __forceinline__ float sum_squares(float s, float4 v) {
 }
 
 // dim <= 256: one warp per row, one group of four channels per lane (two when dim > 128: TWO), rows in a
-// grid-stride loop, ROWS rows in flight per warp.
+// grid-stride loop.  A warp works on sets of ROWS rows and keeps two sets in registers: the loads of the
+// next set are in flight while the current one is normalised, so that memory and arithmetic overlap
+// inside every warp.
+template <typename G, int ROWS, bool TWO>
+struct NormRows {
+  uint2 x0[ROWS], x1[ROWS];
+  decltype(raw4(static_cast<const G*>(nullptr))) g0[ROWS], g1[ROWS];
+
+  __device__ __forceinline__ void load(const __nv_bfloat16* __restrict__ x, const G* __restrict__ g, long long r0,
+                                       long long rows, int dim, int lane, bool c0, bool c1) {
+#pragma unroll
+    for (int i = 0; i < ROWS; i++) {
+      const long long r = r0 + i;
+      const bool ok = r < rows;
+      zero_raw(x0[i]); zero_raw(g0[i]);
+      if (TWO) { zero_raw(x1[i]); zero_raw(g1[i]); }
+      if (ok && c0) {
+        x0[i] = raw4(x + r * dim + 4 * lane);
+        g0[i] = raw4(g + r * dim + 4 * lane);
+      }
+      if (TWO && ok && c1) {
+        x1[i] = raw4(x + r * dim + 4 * (lane + 32));
+        g1[i] = raw4(g + r * dim + 4 * (lane + 32));
+      }
+    }
+  }
+};
+
 template <typename W, typename Y, typename G, int ROWS, bool TWO>
-__global__ void __launch_bounds__(256, 2) gated_rms_norm_warp_kernel(
+__global__ void __launch_bounds__(256, 3) gated_rms_norm_warp_kernel(
     const __nv_bfloat16* __restrict__ x, const W* __restrict__ w, Y* __restrict__ y, const G* __restrict__ g,
     float eps, long long rows, int dim, float cbias, int w_groups, int gate_first, int gate_act) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long step = (((long long)gridDim.x * blockDim.x) >> 5) * ROWS;
   const int columns = dim >> 2;
   const bool c0 = lane < columns, c1 = TWO && lane + 32 < columns;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   // one weight row for all rows (the usual case): kept in registers
   const float4 wf0 = (w_groups == 1 && c0) ? load4(w + 4 * lane) : zero4;
   const float4 wf1 = (w_groups == 1 && c1) ? load4(w + 4 * (lane + 32)) : zero4;
-  for (long long r0 = warp0 * ROWS; r0 < rows; r0 += n_warps * ROWS) {
-    uint2 x0[ROWS], x1[ROWS];
-    decltype(raw4(g)) g0[ROWS], g1[ROWS];
-#pragma unroll
-    for (int i = 0; i < ROWS; i++) {
-      const long long r = r0 + i;
-      const bool ok = r < rows;
-      zero_raw(x0[i]); zero_raw(x1[i]); zero_raw(g0[i]); zero_raw(g1[i]);
-      if (ok && c0) {
-        x0[i] = raw4(x + r * dim + 4 * lane);
-        g0[i] = raw4(g + r * dim + 4 * lane);
-      }
-      if (ok && c1) {
-        x1[i] = raw4(x + r * dim + 4 * (lane + 32));
-        g1[i] = raw4(g + r * dim + 4 * (lane + 32));
-      }
-    }
+
+  auto compute = [&](const NormRows<G, ROWS, TWO>& set, long long r0) {
 #pragma unroll
     for (int i = 0; i < ROWS; i++) {
       const long long r = r0 + i;
       if (r >= rows) break;                                // uniform over the warp
-      const float4 xa = cvt4(x0[i]), xb = cvt4(x1[i]), ga = cvt4(g0[i]), gb = cvt4(g1[i]);
+      const float4 xa = cvt4(set.x0[i]), ga = cvt4(set.g0[i]);
+      const float4 xb = TWO ? cvt4(set.x1[i]) : zero4, gb = TWO ? cvt4(set.g1[i]) : zero4;
       float4 a0 = xa, a1 = xb;
       if (gate_first) {
         a0.x *= act_gate(ga.x, gate_act);
@@ -240,7 +253,8 @@ __global__ void __launch_bounds__(256, 2) gated_rms_norm_warp_kernel(
       if (c1) s = sum_squares(s, a1);
       s = warp_sum(s);
       const float rmf = rsqrtf(s / (float)dim + eps);
-      const W* wr = w + (size_t)(r % w_groups) * dim;
+      const W* wr = w;
+      if (w_groups != 1) wr += (size_t)(r % w_groups) * dim;
       if (c0) {
         const float4 w4 = w_groups == 1 ? wf0 : load4(wr + 4 * lane);
         store4(y + r * dim + 4 * lane, finish4(xa, w4, ga, rmf, cbias, gate_first, gate_act));
@@ -250,6 +264,19 @@ __global__ void __launch_bounds__(256, 2) gated_rms_norm_warp_kernel(
         store4(y + r * dim + 4 * (lane + 32), finish4(xb, w4, gb, rmf, cbias, gate_first, gate_act));
       }
     }
+  };
+
+  NormRows<G, ROWS, TWO> even, odd;
+  long long r0 = warp0 * ROWS;
+  if (r0 < rows) even.load(x, g, r0, rows, dim, lane, c0, c1);
+  while (r0 < rows) {
+    if (r0 + step < rows) odd.load(x, g, r0 + step, rows, dim, lane, c0, c1);
+    compute(even, r0);
+    r0 += step;
+    if (r0 >= rows) break;
+    if (r0 + step < rows) even.load(x, g, r0 + step, rows, dim, lane, c0, c1);
+    compute(odd, r0);
+    r0 += step;
   }
 }
 
@@ -297,16 +324,16 @@ int launch_gated_rms_norm(const void* x, const void* w, void* y, const void* g, 
   auto yp = static_cast<Y*>(y);
   auto gp = static_cast<const G*>(g);
   if (dim <= 256) {
-    const int rows_per_warp = dim <= 128 ? 8 : 4;
+    const int rows_per_warp = dim <= 128 ? 4 : 2;
     const long long warps_needed = (rows + rows_per_warp - 1) / rows_per_warp;
     const long long ctas_needed = (warps_needed + 7) / 8;
-    const long long cap = (long long)sm_count() * 8 * 4;  // a few grid-stride passes per warp at most
+    const long long cap = (long long)sm_count() * 3;       // resident CTAs only: every warp streams many row sets
     const int grid = (int)(ctas_needed < cap ? ctas_needed : cap);
     if (dim <= 128)
-      gated_rms_norm_warp_kernel<W, Y, G, 8, false><<<grid, 256, 0, st>>>(xp, wp, yp, gp, eps, rows, dim, cbias,
+      gated_rms_norm_warp_kernel<W, Y, G, 4, false><<<grid, 256, 0, st>>>(xp, wp, yp, gp, eps, rows, dim, cbias,
                                                                          w_groups, gate_first, gate_act);
     else
-      gated_rms_norm_warp_kernel<W, Y, G, 4, true><<<grid, 256, 0, st>>>(xp, wp, yp, gp, eps, rows, dim, cbias,
+      gated_rms_norm_warp_kernel<W, Y, G, 2, true><<<grid, 256, 0, st>>>(xp, wp, yp, gp, eps, rows, dim, cbias,
                                                                         w_groups, gate_first, gate_act);
   } else {
     gated_rms_norm_block_kernel<W, Y, G><<<(unsigned)rows, 1024, 0, st>>>(xp, wp, yp, gp, eps, dim, cbias, w_groups,

@@ -113,7 +113,29 @@ def cases(torch, hk, ref, synth):
         ref.wuv_transpose(kb, wt)
         return (lambda: hk.o_absorb(lo, kb, o, n)), (lambda: ref.o_absorb_t(lo, wt, o, n))
 
+    def glue(kind, T):
+        F = 3 * H * D
+        if kind == "transpose":
+            x = torch.randn(T, F, device="cuda")
+            dst = torch.empty(F, T, dtype=bf, device="cuda")
+            return (lambda: hk.kda_transpose_cast(dst, x, T, F)), (lambda: ref.kda_transpose_cast(dst, x, T, F))
+        raw = synth.kda_raw_gates(T, H, D, seed=2)
+        f, b = torch.from_numpy(raw["f"]).cuda(), torch.from_numpy(raw["b"]).cuda()
+        dtb, al, lb = torch.from_numpy(raw["dt_bias"]).cuda(), torch.from_numpy(raw["a_log"]).cuda(), raw["lower_bound"]
+        if kind == "gate":
+            beta = torch.empty(T, H, dtype=bf, device="cuda")
+            g = torch.empty(T, H, D, dtype=torch.float32, device="cuda")
+            return (lambda: hk.kda_gate(b, f, dtb, al, lb, beta, g, T, H, D)), (lambda: ref.kda_gate(b, f, dtb, al, lb, beta, g, T, H, D))
+        x = torch.randn(T * H, D, device="cuda").to(bf)
+        w = torch.ones(D, dtype=bf, device="cuda")
+        y = torch.empty(T * H, D, dtype=torch.float16, device="cuda")
+        return ((lambda: hk.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)),
+                (lambda: ref.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)))
+
     return {
+        "transpose_cast_32k": (lambda: glue("transpose", 32768), "transpose + cast, 32768 tokens x 12288 channels", 10),
+        "gate_32k": (lambda: glue("gate", 32768), "gate preparation, 32768 tokens x 32 heads x 128", 10),
+        "gated_norm_32k": (lambda: glue("norm", 32768), "gated RMS norm, 1048576 rows of 128", 10),
         "kda_prefill_32k": (lambda: kda(32768), "KDA layer prefill, T=32768, H=32, d=128 (reference: per-token recurrence)", 3),
         "kda_prefill_4k": (lambda: kda(4096), "KDA layer prefill, T=4096, H=32", 5),
         "kda_decode": (lambda: kda(1), "KDA decode step, H=32", 20),
