@@ -65,6 +65,8 @@ SIGNATURES = {
     "hk_o_absorb": (_i, [_vp, _vp, _vp, _i, _vp]),
     "hk_wuv_transpose": (_i, [_vp, _vp, _vp]),
     "hk_o_absorb_t": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "hk_mla_cache_append": (_i, [_vp, _vp, _vp, _vp, _c.c_longlong, _i, _f, _vp]),
+    "hk_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "hk_read_device_status": (_i, [_vp, _i]),
     "hk_tc05_selftest": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
@@ -225,6 +227,18 @@ def gated_rms_norm(x, w, y, g, rows, dim, epsilon, constant_bias=0.0, w_groups=1
     _call("hk_gated_rms_norm", _ptr(x), _ptr(w), _dtype_code(w), _ptr(y), _dtype_code(y), _ptr(g),
           _dtype_code(g), rows, dim, float(epsilon), float(constant_bias), w_groups, int(bool(gate_first)),
           int(gate_act), _stream(stream))
+
+
+def layernorm_f16(x, w, b, y, rows, dim, eps, stream=None):
+    """helios::glue::layernorm_f16 (src/engine/glue2.cuh:73-75)."""
+    _call("hk_layernorm_f16", _ptr(x), _ptr(w), _ptr(b), _ptr(y), rows, dim, float(eps), _stream(stream))
+
+
+def mla_cache_append(kv_pre, ln_w, ckv, pos, n, eps, ckv_new=None, stream=None):
+    """aux::rms_norm (fp32 in, fp16 weight, fp16 out, dim 512) + the copy into the latent cache
+    (src/engine/runner.cpp:569-572) as one kernel."""
+    _call("hk_mla_cache_append", _ptr(kv_pre), _ptr(ln_w), _ptr(ckv), _ptr(ckv_new), pos, n, float(eps),
+          _stream(stream))
 
 
 def dsa_topk(scores, s_stride, indices, R, T, k, k_pad, t_ptr=None, t_seq=0, stream=None):

@@ -10,7 +10,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libhelios_b200.so")
 SOURCES = [
     "status.cu", "kda_conv.cu", "kda_glue.cu", "kda_recurrent.cu", "kda_chunked.cu", "indexer_aux.cu",
-    "indexer_score.cu", "dsa_topk.cu", "mla_attend.cu", "mla_flash_tc.cu", "absorb.cu", "absorb_tc.cu",
+    "indexer_score.cu", "dsa_topk.cu", "mla_attend.cu", "mla_flash_tc.cu", "mla_append.cu", "absorb.cu", "absorb_tc.cu",
     "tc05_selftest.cu", "shim.cu",
 ]
 NVCC_FLAGS = [

@@ -202,5 +202,10 @@ void kda_prepare(const float* qkv, const float* b, const float* f, const float* 
         "kda_prepare");
 }
 
+void layernorm_f16(const half* x, const half* w, const half* b, half* y, int rows, int dim, float eps,
+                   Stream s) {
+  check(hk_layernorm_f16(x, w, b, y, rows, dim, eps, s), "layernorm_f16");
+}
+
 }  // namespace glue
 }  // namespace helios

@@ -291,6 +291,24 @@ int hk_wuv_transpose(const void* kv_b, void* wuv_t, void* stream);
 int hk_o_absorb_t(const void* lat_out, const void* wuv_t, void* o, int nrows, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * (b') producers of the latent cache and of the indexer keys
+ * ------------------------------------------------------------------------------------------- */
+
+/* RMS norm of the n new compressed-KV rows, written into the latent cache at rows pos .. pos+n-1:
+ *   ckv[pos + r][c] = f16(kv_pre[r][c] * ln_w[c] * rsqrt(mean_c(kv_pre[r]^2) + epsilon))
+ * Replaces aux::rms_norm(float in, half weight, half out, dim 512) followed by the device copy into the
+ * cache (src/engine/runner.cpp:569-572; kernel src/cuda/aux/norm.cu:16-164).  kv_pre [n][512] f32,
+ * ln_w [512] f16, ckv [.][512] f16; ckv_new (optional, may be NULL) [n][512] f16 receives the same rows
+ * (the reference's staging buffer).                                                              */
+int hk_mla_cache_append(const float* kv_pre, const void* ln_w_f16, void* ckv, void* ckv_new,
+                        long long pos, int n, float epsilon, void* stream);
+
+/* y = (x - mean) * rsqrt(var + epsilon) * w + b per row of `dim` fp16 values (in place allowed).
+ * Replaces helios::glue::layernorm_f16 (src/engine/glue2.cuh:73-75, glue2.cu:420-455).            */
+int hk_layernorm_f16(const void* x, const void* w, const void* b, void* y, int rows, int dim,
+                     float epsilon, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * diagnostics
  * ------------------------------------------------------------------------------------------- */
 

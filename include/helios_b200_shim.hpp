@@ -87,6 +87,9 @@ void kda_gate(const float* b, const float* f, const float* dt_bias, const float*
 void kda_prepare(const float* qkv, const float* b, const float* f, const float* dt_bias,
                  const float* a_log, float lower_bound, void* mixed_qkv_bf16, void* beta_bf16, float* g,
                  int S, int F, int H, int Dk, Stream s = 0);
+// layer norm with weight + bias over fp16 rows (src/engine/glue2.cuh:73-75)
+void layernorm_f16(const half* x, const half* w, const half* b, half* y, int rows, int dim, float eps,
+                   Stream s = 0);
 }  // namespace glue
 
 namespace b200 {

@@ -652,4 +652,42 @@ int orc_gated_rms_norm(const uint16_t* x, const void* w, int w_bf16, void* y, in
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// N4  producers of the latent cache and of the indexer keys
+// orc_mla_cache_append follows src/cuda/aux/norm.cu:16-164 (rms_norm_kernel, float in / half weight /
+// half out) and the copy into the cache at src/engine/runner.cpp:571-572:
+//   ckv[pos + r][c] = f16_rn(kv_pre[r][c] * ln_w[c] * rsqrt(mean(kv_pre[r]^2) + eps)),  dim 512
+// orc_layernorm_f16 follows src/engine/glue2.cu:420-447:
+//   y = f16_rn((x - mean) * rsqrt(E[x^2] - mean^2 + eps) * w + b)
+// Sums run in fp64 here (the device adds fp32 partials in lane order).
+// ---------------------------------------------------------------------------------------------
+int orc_mla_cache_append(const float* kv_pre, const uint16_t* ln_w, uint16_t* ckv, int64_t pos, int n, float eps) {
+  parallel_for(n, [&](int64_t r) {
+    const float* x = kv_pre + (size_t)r * 512;
+    double ss = 0.0;
+    for (int c = 0; c < 512; c++) ss += (double)x[c] * x[c];
+    const float rmf = 1.0f / std::sqrt((float)(ss / 512.0) + eps);
+    for (int c = 0; c < 512; c++) ckv[(size_t)(pos + r) * 512 + c] = f_to_h_rn(x[c] * h_to_f(ln_w[c]) * rmf);
+  });
+  return 0;
+}
+
+int orc_layernorm_f16(const uint16_t* x, const uint16_t* w, const uint16_t* b, uint16_t* y, int rows, int dim,
+                      float eps) {
+  parallel_for(rows, [&](int64_t r) {
+    const uint16_t* xr = x + (size_t)r * dim;
+    double sum = 0.0, sq = 0.0;
+    for (int i = 0; i < dim; i++) {
+      const double v = h_to_f(xr[i]);
+      sum += v;
+      sq += v * v;
+    }
+    const float mean = (float)(sum / dim), var = (float)(sq / dim) - mean * mean;
+    const float inv = 1.0f / std::sqrt(var + eps);
+    for (int i = 0; i < dim; i++)
+      y[(size_t)r * dim + i] = f_to_h_rn((h_to_f(xr[i]) - mean) * inv * h_to_f(w[i]) + h_to_f(b[i]));
+  });
+  return 0;
+}
+
 }  // extern "C"

@@ -132,3 +132,15 @@ REF_API void ref_gated_rms_norm(const void* x, const void* w, int tw, void* y, i
   helios::aux::gated_rms_norm(x, w, ref_dtype(tw), y, ref_dtype(ty), g, ref_dtype(tg), rows, dim, epsilon,
                               constant_bias, w_groups, gate_first != 0, gate_act, (Stream)stream);
 }
+
+REF_API void ref_rms_norm(const void* x, int tx, const void* w, int tw, void* y, int ty, int rows, int dim,
+                          float epsilon, void* stream) {
+  helios::aux::rms_norm(x, ref_dtype(tx), w, ref_dtype(tw), y, ref_dtype(ty), rows, dim, epsilon, 0.0f, 1.0f,
+                        false, 1, (Stream)stream);
+}
+
+REF_API void ref_layernorm_f16(const void* x, const void* w, const void* b, void* y, int rows, int dim,
+                               float eps, void* stream) {
+  helios::glue::layernorm_f16((const half*)x, (const half*)w, (const half*)b, (half*)y, rows, dim, eps,
+                              (Stream)stream);
+}

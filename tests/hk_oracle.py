@@ -149,3 +149,17 @@ def gated_rms_norm(x, w, g, rows, dim, eps, y_f32=False, constant_bias=0.0, w_gr
                                   w_groups, int(gate_first), int(gate_act))
     assert rc == 0
     return y
+
+
+def mla_cache_append(kv_pre, ln_w, ckv, pos, n, eps):
+    """normalises the n rows of kv_pre into ckv (f16 bits, modified in place) at rows pos.."""
+    rc = lib().orc_mla_cache_append(_p(kv_pre), _p(ln_w), _p(ckv), ctypes.c_int64(pos), n, _f(eps))
+    assert rc == 0
+    return ckv
+
+
+def layernorm_f16(x, w, b, rows, dim, eps):
+    y = np.empty((rows, dim), dtype=np.uint16)
+    rc = lib().orc_layernorm_f16(_p(x), _p(w), _p(b), _p(y), rows, dim, _f(eps))
+    assert rc == 0
+    return y

@@ -113,3 +113,14 @@ def gated_rms_norm(x, w, y, g, rows, dim, epsilon, constant_bias=0.0, w_groups=1
     lib().ref_gated_rms_norm(_p(x), _p(w), code[w.dtype], _p(y), code[y.dtype], _p(g), code[g.dtype], rows, dim,
                              ctypes.c_float(epsilon), ctypes.c_float(constant_bias), w_groups, int(gate_first),
                              int(gate_act), _s())
+
+
+def rms_norm(x, w, y, rows, dim, epsilon):
+    import torch
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+    lib().ref_rms_norm(_p(x), code[x.dtype], _p(w), code[w.dtype], _p(y), code[y.dtype], rows, dim,
+                       ctypes.c_float(epsilon), _s())
+
+
+def layernorm_f16(x, w, b, y, rows, dim, eps):
+    lib().ref_layernorm_f16(_p(x), _p(w), _p(b), _p(y), rows, dim, ctypes.c_float(eps), _s())

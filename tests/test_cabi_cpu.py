@@ -47,7 +47,7 @@ def test_reference_named_launchers_are_exported(built):
                  "helios::attn::pool_expand_row(", "helios::attn::mla_sparse_decode(",
                  "helios::attn::mla_dense_prefill(", "helios::attn::q_latent_t(", "helios::attn::o_absorb_t(",
                  "helios::attn::o_absorb(", "helios::attn::wuv_transpose(", "helios::aux::gated_rms_norm(",
-                 "helios::glue::kda_transpose_cast(", "helios::glue::kda_gate(", "helios::glue::kda_prepare("]:
+                 "helios::glue::kda_transpose_cast(", "helios::glue::kda_gate(", "helios::glue::kda_prepare(", "helios::glue::layernorm_f16("]:
         assert name in out, name
 
 

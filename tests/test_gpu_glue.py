@@ -8,7 +8,7 @@ import torch
 
 import hk_oracle as orc
 import hk_ref as ref
-from gpu_util import bf16_ulp_diff, bits, dev, dev_bf16, max_rel
+from gpu_util import bf16_ulp_diff, bits, dev, dev_bf16, dev_f16, max_rel
 import helios_glm53flash_b200 as hk
 from helios_glm53flash_b200 import synth
 
@@ -181,3 +181,49 @@ def test_chunked_prefill_gated_equals_gate_then_prefill(T, H):
         torch.cuda.synchronize()
         assert max_rel(got.cpu().numpy(), o32) < 2e-3          # the path's stated tolerance
         assert max_rel(st_c.cpu().numpy(), o_st) < 2e-3
+
+
+@pytest.mark.parametrize("n,pos", [(1, 0), (1, 777), (37, 100), (4096, 32768)])
+def test_mla_cache_append(n, pos):
+    r = synth.rng(n + pos)
+    kv = (3 * r.standard_normal((n, 512), dtype=np.float32)).astype(np.float32)
+    lw = synth.f32_to_f16_bits((1 + 0.1 * r.standard_normal(512, dtype=np.float32)).astype(np.float32))
+    rows = pos + n + 3
+    cache0 = synth.f32_to_f16_bits(r.standard_normal((rows, 512), dtype=np.float32))
+    ck, stage = dev_f16(cache0), torch.zeros(n, 512, dtype=torch.float16, device="cuda")
+    hk.mla_cache_append(dev(kv), dev_f16(lw), ck, pos, n, 1e-6, ckv_new=stage)
+    torch.cuda.synchronize()
+    got = bits(ck)
+    want = orc.mla_cache_append(kv, lw, cache0.copy(), pos, n, 1e-6)
+    assert np.array_equal(got[:pos], cache0[:pos]) and np.array_equal(got[pos + n:], cache0[pos + n:]), "other rows untouched"
+    assert _f16_ulp(got[pos:pos + n], want[pos:pos + n]).max() <= 1
+    assert np.array_equal(bits(stage), got[pos:pos + n])
+    if ref.available():
+        y = torch.zeros(n, 512, dtype=torch.float16, device="cuda")
+        ref.rms_norm(dev(kv), dev_f16(lw), y, n, 512, 1e-6)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(y), got[pos:pos + n]), "same summation order as the reference kernel: bit-exact"
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 128), (300, 128), (17, 96), (5, 1000)])
+def test_layernorm_f16(rows, dim):
+    r = synth.rng(rows + dim)
+    x = synth.f32_to_f16_bits((2 * r.standard_normal((rows, dim), dtype=np.float32) + 0.5).astype(np.float32))
+    w = synth.f32_to_f16_bits((1 + 0.1 * r.standard_normal(dim, dtype=np.float32)).astype(np.float32))
+    b = synth.f32_to_f16_bits((0.1 * r.standard_normal(dim, dtype=np.float32)).astype(np.float32))
+    dx, dw, db = dev_f16(x), dev_f16(w), dev_f16(b)
+    y = torch.zeros(rows, dim, dtype=torch.float16, device="cuda")
+    hk.layernorm_f16(dx, dw, db, y, rows, dim, 1e-5)
+    torch.cuda.synchronize()
+    want = orc.layernorm_f16(x, w, b, rows, dim, 1e-5)
+    assert max_rel(synth.f16_bits_to_f32(bits(y)), synth.f16_bits_to_f32(want)) < 2e-3
+    assert (_f16_ulp(bits(y), want) > 1).mean() < 1e-3
+    if ref.available():
+        yr = torch.zeros(rows, dim, dtype=torch.float16, device="cuda")
+        ref.layernorm_f16(dx, dw, db, yr, rows, dim, 1e-5)
+        torch.cuda.synchronize()
+        assert torch.equal(y, yr)
+    # in place, as the engine calls it (src/engine/runner.cpp:577)
+    hk.layernorm_f16(dx, dw, db, dx, rows, dim, 1e-5)
+    torch.cuda.synchronize()
+    assert torch.equal(dx, y)
