@@ -5,7 +5,7 @@
 //
 // Four kernels (the last one is the fused cast + convolution over token-major fp32 input, further below):
 //   conv4_row_kernel   prefill with whole 16-token groups: K = 4, no history, seqlen % 16 == 0.  No
-//                      shared memory: a lane keeps 2 channels x 16 tokens in registers (32-byte reads
+//                      shared memory: a lane keeps 2 channels x 16 (or 32) tokens in registers (32-byte reads
 //                      per channel row, 128-byte warp stores per output row).
 //   conv4_tile_kernel  other prefill lengths: a CTA transposes a [64 channel][128 token] tile
 //                      through shared memory: 16-byte coalesced reads along tokens (the input is
@@ -118,22 +118,27 @@ __global__ __launch_bounds__(256) void conv4_tile_kernel(
 // channels and 16 consecutive tokens: it reads 32 contiguous bytes per channel row (full sectors), keeps
 // the 19 inputs per channel in registers and writes 4 bytes per token, so that a warp's store covers 128
 // contiguous bytes of one output row.  Same arithmetic as above, about half the instructions per output.
-template <bool ACT>
+template <bool ACT, int NG>   // NG groups of 16 consecutive tokens per lane
 __global__ __launch_bounds__(256) void conv4_row_kernel(
     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ state,
     const int* __restrict__ slots, const __nv_bfloat16* __restrict__ weight,
     const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int dim, int seqlen,
     int state_size) {
+  constexpr int NT = 16 * NG;                                // tokens per lane
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int c0 = blockIdx.x * CT_CH + lane * 2;
-  const int t0 = blockIdx.y * CT_TOK + wid * 16;
+  const int t0 = (blockIdx.y * 8 + wid) * NT;
   const int b = blockIdx.z;
   if (t0 >= seqlen) return;                                  // warp-uniform
   const __nv_bfloat16* r0 = x + ((size_t)b * dim + c0) * seqlen;
   const __nv_bfloat16* r1 = r0 + seqlen;
-  const uint4 a_lo = ld_stream16(r0 + t0), a_hi = ld_stream16(r0 + t0 + 8);
-  const uint4 e_lo = ld_stream16(r1 + t0), e_hi = ld_stream16(r1 + t0 + 8);
-  float xa[19], xe[19];                                      // inputs t0-3 .. t0+15 of the two channels
+  uint4 ra[2 * NG], re[2 * NG];                              // all loads of the lane are issued before any use
+#pragma unroll
+  for (int j = 0; j < 2 * NG; j++) {
+    ra[j] = ld_stream16(r0 + t0 + 8 * j);
+    re[j] = ld_stream16(r1 + t0 + 8 * j);
+  }
+  float xa[NT + 3], xe[NT + 3];                              // inputs t0-3 .. t0+NT-1 of the two channels
   if (t0 == 0) {
     // the first group takes its 3 predecessors from the window state and rolls the state forward
     const int slot = slots ? slots[b] : b;
@@ -155,13 +160,14 @@ __global__ __launch_bounds__(256) void conv4_row_kernel(
     xa[0] = bf16hi(pa.x); xa[1] = bf16lo(pa.y); xa[2] = bf16hi(pa.y);
     xe[0] = bf16hi(pe.x); xe[1] = bf16lo(pe.y); xe[2] = bf16hi(pe.y);
   }
-  {
-    const uint32_t wa[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-    const uint32_t we[8] = {e_lo.x, e_lo.y, e_lo.z, e_lo.w, e_hi.x, e_hi.y, e_hi.z, e_hi.w};
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      xa[3 + 2 * i] = bf16lo(wa[i]); xa[4 + 2 * i] = bf16hi(wa[i]);
-      xe[3 + 2 * i] = bf16lo(we[i]); xe[4 + 2 * i] = bf16hi(we[i]);
+  for (int j = 0; j < 2 * NG; j++) {
+    const uint32_t wa[4] = {ra[j].x, ra[j].y, ra[j].z, ra[j].w};
+    const uint32_t we[4] = {re[j].x, re[j].y, re[j].z, re[j].w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      xa[3 + 8 * j + 2 * i] = bf16lo(wa[i]); xa[4 + 8 * j + 2 * i] = bf16hi(wa[i]);
+      xe[3 + 8 * j + 2 * i] = bf16lo(we[i]); xe[4 + 8 * j + 2 * i] = bf16hi(we[i]);
     }
   }
   const uint4 wv = *reinterpret_cast<const uint4*>(weight + (size_t)c0 * 4);
@@ -174,7 +180,7 @@ __global__ __launch_bounds__(256) void conv4_row_kernel(
   }
   __nv_bfloat16* ob = out + ((size_t)b * seqlen + t0) * dim + c0;
 #pragma unroll
-  for (int i = 0; i < 16; i++) {
+  for (int i = 0; i < NT; i++) {
     float y0 = fmaf(w03, xa[i + 3], fmaf(w02, xa[i + 2], fmaf(w01, xa[i + 1], fmaf(w00, xa[i], b0))));
     float y1 = fmaf(w13, xe[i + 3], fmaf(w12, xe[i + 2], fmaf(w11, xe[i + 1], fmaf(w10, xe[i], b1))));
     if (ACT) {
@@ -376,9 +382,11 @@ HK_API int hk_conv1d_update(const void* x, void* conv_state, const int* slots, c
   const bool tile_ok = (K == 4) && !history && (dim % CT_CH == 0) && seqlen >= 16 &&
                        aligned(weight, 16) && aligned(out, 4);
   if (tile_ok && seqlen % 16 == 0 && aligned(x, 16)) {
+    // one 16-token group per lane: two groups (NG = 2) measured slower (419 vs 367 us at 32K tokens), fewer warps per SM
+
     dim3 grid(dim / CT_CH, (seqlen + CT_TOK - 1) / CT_TOK, bsz);
-    if (activation) conv4_row_kernel<true><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
-    else            conv4_row_kernel<false><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+    if (activation) conv4_row_kernel<true, 1><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
+    else            conv4_row_kernel<false, 1><<<grid, 256, 0, s>>>(xs, st, slots, w, bs, o, dim, seqlen, state_size);
   } else if (tile_ok) {
     dim3 grid(dim / CT_CH, (seqlen + CT_TOK - 1) / CT_TOK, bsz);
     const bool vec = (seqlen % 8 == 0) && aligned(x, 16);
