@@ -827,7 +827,10 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     __syncthreads();
     tc::fence_after_sync();
     KS_TRACE(6, chunk);
-    if (tid == 0 && chunk + S_NSTAGE < n_chunks) issue_loads(chunk + S_NSTAGE);
+    // The refill is issued by a thread of warp 3, not by thread 0: the five copy instructions take about 400 cycles
+    // to issue, which the MMA-issuing thread would add to the per-chunk chain (measured: 1.95 -> 1.87 ms at 32K
+    // tokens).  Issuing them while the next contraction runs instead was slower (the barrier polls queue behind them).
+    if (tid == 96 && chunk + S_NSTAGE < n_chunks) issue_loads(chunk + S_NSTAGE);
   }
   if (!abort_flag) {
 #pragma unroll
