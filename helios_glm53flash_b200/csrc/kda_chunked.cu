@@ -641,6 +641,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[S_NSTAGE];
   __shared__ uint64_t mma_bar;
+  __shared__ uint64_t out_bar;    // completion of the output contraction (B beta) U, waited on by warps 2, 3 only
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -654,10 +655,11 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   if (tid == 0) {
     for (int i = 0; i < S_NSTAGE; i++) tc::mbar_init(&full_bar[i], 1);
     tc::mbar_init(&mma_bar, 1);
+    tc::mbar_init(&out_bar, 1);
     tc::mbar_fence_init();
     abort_flag = 0;
   }
-  if (warp == 0) tc::tmem_alloc(&tmem_slot, 64);
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 128);
   // zero halves of the [0 ; B beta] operands
   for (int i = tid; i < 8192 / 16; i += 128) {
     for (int st_i = 0; st_i < S_NSTAGE; st_i++) reinterpret_cast<uint4*>(smem + st_i * S_STAGE + S_BB)[i] = make_uint4(0, 0, 0, 0);
@@ -683,7 +685,9 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t d1 = tmem, d2 = tmem + 32;
+  // D1 alternates between two column ranges by chunk parity: the output rows of chunk c are read while the first
+  // contraction of chunk c + 1 fills the other range
+  const uint32_t d2 = tmem + 32;
 
   auto issue_loads = [&](int chunk) {
     uint8_t* stg = smem + (chunk % S_NSTAGE) * S_STAGE;
@@ -702,12 +706,45 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
 
   const uint32_t idesc = tc::make_idesc(128, KNV, tc::FMT_F16, tc::FMT_F16, false, true);
   const uint32_t s_addr = tc::smem_u32(smem + P2_S), u_addr = tc::smem_u32(smem + P2_U);
-  uint32_t mma_parity = 0;
+  uint32_t mma_parity = 0, out_parity = 0;
+
+  // output rows of chunk c (TMEM lanes 64-127 of that chunk's D1 range = tokens), warps 2 and 3
+  auto emit_outputs = [&](int c, bool valid) {
+    const int tok = c * KC + (tid - 64);
+    uint32_t r[32];
+    tc::tmem_ld32(tmem + ((c & 1) ? 64u : 0u) + ((uint32_t)(warp * 32) << 16), r);
+    tc::tmem_ld_wait();
+    if (tok < seqlen && valid) {
+      const size_t oi = (((size_t)b * seqlen + tok) * H + head) * KD + v0;
+      uint4* o = reinterpret_cast<uint4*>(out + oi);
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float a = __uint_as_float(r[8 * u + 2 * e]) * scale, c2 = __uint_as_float(r[8 * u + 2 * e + 1]) * scale;
+          const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rz(a));
+          const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c2));
+          w[e] = lo | (hi << 16);
+        }
+        o[u] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (out_f32) {
+        float4* of = reinterpret_cast<float4*>(out_f32 + oi);
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+          of[u] = make_float4(__uint_as_float(r[4 * u]) * scale, __uint_as_float(r[4 * u + 1]) * scale,
+                              __uint_as_float(r[4 * u + 2]) * scale, __uint_as_float(r[4 * u + 3]) * scale);
+      }
+    }
+  };
+  bool prev_ok = true;                                      // warps 2, 3: the previous chunk's waits all succeeded
 
   for (int chunk = 0; chunk < n_chunks; chunk++) {
     const int sidx = chunk % S_NSTAGE;
     uint8_t* stg = smem + sidx * S_STAGE;
     const uint32_t stg_addr = tc::smem_u32(stg);
+    const uint32_t d1 = tmem + ((chunk & 1) ? 64u : 0u);
     KS_TRACE(0, chunk);
     bool ok = tc::mbar_wait(&full_bar[sidx], (chunk / S_NSTAGE) & 1, &abort_flag, 2);
     KS_TRACE(1, chunk);
@@ -721,6 +758,8 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
       }
       tc::mma_commit(&mma_bar);
     }
+    // the previous chunk's output rows leave while this chunk's first contraction runs (off the chain)
+    if (warp >= 2 && chunk > 0) emit_outputs(chunk - 1, prev_ok);
     ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 3) && ok;
     mma_parity ^= 1;
     tc::fence_after_sync();
@@ -754,14 +793,8 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     __syncthreads();
     tc::fence_after_sync();
     KS_TRACE(3, chunk);
-    // ---- D1 rows 64-127 += (B beta) U ;  D2 = Kt^T U ----
+    // ---- D2 = Kt^T U (state path, committed first) ;  D1 rows 64-127 += (B beta) U (outputs, own barrier) ----
     if (tid == 0) {
-#pragma unroll
-      for (int kk = 0; kk < KC / 16; kk++) {
-        const uint64_t ad = tc::make_sdesc(stg_addr + S_BB + kk * 2 * LBO, LBO, SBO_K64);
-        const uint64_t bd = tc::make_sdesc(u_addr + kk * 2 * 128, 128, 1024);
-        tc::mma_f16(d1, ad, bd, idesc, true);
-      }
 #pragma unroll
       for (int kk = 0; kk < KC / 16; kk++) {
         const uint64_t ad = tc::make_sdesc(stg_addr + S_KT + kk * 2 * LBO, LBO, SBO_K64);
@@ -769,44 +802,20 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
         tc::mma_f16(d2, ad, bd, idesc, kk > 0);
       }
       tc::mma_commit(&mma_bar);
+#pragma unroll
+      for (int kk = 0; kk < KC / 16; kk++) {
+        const uint64_t ad = tc::make_sdesc(stg_addr + S_BB + kk * 2 * LBO, LBO, SBO_K64);
+        const uint64_t bd = tc::make_sdesc(u_addr + kk * 2 * 128, 128, 1024);
+        tc::mma_f16(d1, ad, bd, idesc, true);
+      }
+      tc::mma_commit(&out_bar);
     }
     ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 4) && ok;
     mma_parity ^= 1;
     tc::fence_after_sync();
     KS_TRACE(4, chunk);
-    // ---- outputs (TMEM lanes 64-127 = tokens) ----
-    if (warp >= 2) {
-      const int t = tid - 64;
-      const int tok = chunk * KC + t;
-      uint32_t r[32];
-      tc::tmem_ld32(d1 + ((uint32_t)(warp * 32) << 16), r);
-      tc::tmem_ld_wait();
-      if (tok < seqlen && ok) {
-        const size_t oi = (((size_t)b * seqlen + tok) * H + head) * KD + v0;
-        uint4* o = reinterpret_cast<uint4*>(out + oi);
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float a = __uint_as_float(r[8 * u + 2 * e]) * scale, c = __uint_as_float(r[8 * u + 2 * e + 1]) * scale;
-            const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rz(a));
-            const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c));
-            w[e] = lo | (hi << 16);
-          }
-          o[u] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        if (out_f32) {
-          float4* of = reinterpret_cast<float4*>(out_f32 + oi);
-#pragma unroll
-          for (int u = 0; u < 8; u++)
-            of[u] = make_float4(__uint_as_float(r[4 * u]) * scale, __uint_as_float(r[4 * u + 1]) * scale,
-                                __uint_as_float(r[4 * u + 2]) * scale, __uint_as_float(r[4 * u + 3]) * scale);
-        }
-      }
-    }
-    KS_TRACE(5, chunk);
-    // ---- state: S <- S e^{G_last} + Kt^T U (lane = k row), refresh the fp16 operand copy ----
+    // ---- state: S <- S e^{G_last} + Kt^T U (lane = k row), refresh the fp16 operand copy.  The output
+    //      contraction is still running: only the state is on the chunk-to-chunk chain. ----
     {
       uint32_t r[32];
       tc::tmem_ld32(d2 + ((uint32_t)(warp * 32) << 16), r);
@@ -822,6 +831,14 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
         *reinterpret_cast<uint4*>(sS_row + u * 2048) = p;
       }
     }
+    KS_TRACE(5, chunk);
+    // ---- warps 2, 3 make sure the output contraction is complete before the block barrier (the stage and the U
+    //      tile it reads are rewritten after it); the rows themselves are read in the next iteration ----
+    if (warp >= 2) {
+      ok = tc::mbar_wait(&out_bar, out_parity, &abort_flag, 5) && ok;
+      prev_ok = ok;
+    }
+    out_parity ^= 1;
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
@@ -832,6 +849,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
     // tokens).  Issuing them while the next contraction runs instead was slower (the barrier polls queue behind them).
     if (tid == 96 && chunk + S_NSTAGE < n_chunks) issue_loads(chunk + S_NSTAGE);
   }
+  if (warp >= 2 && n_chunks > 0) emit_outputs(n_chunks - 1, prev_ok);
   if (!abort_flag) {
 #pragma unroll
     for (int u = 0; u < KNV / 4; u++)
@@ -839,7 +857,7 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, 64);
+  if (warp == 0) tc::tmem_dealloc(tmem, 128);
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
 
