@@ -107,6 +107,8 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // provably warp-uniform flag: the branch into the tensor-core issue role stays converged for the compiler
+  const bool mma_warp = tc::warp_index_uniform() == 4;
   const int sp = blockIdx.x, r = blockIdx.y;
   FT_CTA_STAMP(0);
   const bool sparse = a.raw_idx != nullptr;
@@ -149,7 +151,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const uint32_t tS = tmem, tO = tmem + 128;   // S: 2 x 64 columns; O^T: 4 x 64 columns
   bool ok = true;
 
-  if (warp >= 5) {
+  if (!mma_warp && warp >= 5) {
     // =========================== loaders: Q once, then the key tiles ===========================
     // Register-staged copies: every loader warp first issues all of its 16-byte loads of the NEXT
     // tile (they fly while the tensor pipe still owns the buffer), then waits for the buffer, then
@@ -272,9 +274,24 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       }
       if (tid == 160) FT_TRACE(1, tile);               // tile published
     }
-  } else if (warp == 4) {
-    // =========================== tensor-core issue (one thread) ===========================
-    if (lane == 0) {
+  } else if (mma_warp) {
+    // =========================== tensor-core issue (whole warp, one elected lane) ===========================
+    // Every lane runs the loop, polls the barriers and computes the (warp-uniform) descriptors; the elected
+    // lane alone issues.  See tc05.cuh: issued from a single diverged thread each MMA costs ~47 cycles of
+    // operand moves, from a converged warp the M64 N48 products go out every ~29 cycles.
+    {
+      const uint32_t leader = tc::elect_one();
+      // EVERY lane polls (one shared-memory request per warp either way).  A leader-only wait would split the
+      // warp into two groups that run this loop at different times while the compiler, which sees only
+      // warp-uniform branch conditions here, keeps loop state in per-warp uniform registers.
+      auto wait_u = [&](uint64_t* bar, uint32_t parity, int code) {
+        const bool done = tc::mbar_wait<FT_POLL_NS>(bar, parity, &abort_flag, code);
+        return __all_sync(0xffffffffu, done) != 0;
+      };
+      auto try_u = [&](uint64_t* bar, uint32_t parity) {
+        const bool hit = tc::mbar_test_wait(bar, parity);   // must not block: QK^T of this tile goes first if P is not ready
+        return __all_sync(0xffffffffu, hit) != 0;
+      };
       const uint32_t q_addr = tc::smem_u32(sQ);
       const uint32_t idesc_s = tc::make_idesc(64, FT_KEYS, tc::FMT_F16, tc::FMT_F16, false, false);
       const uint32_t idesc_o = tc::make_idesc(128, FT_HEADS, tc::FMT_F16, tc::FMT_F16, true, false);
@@ -289,55 +306,57 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         for (int mt = 0; mt < 4; mt++)
 #pragma unroll
           for (int kk = 0; kk < FT_KEYS / 16; kk++)
-            tc::mma_f16(tO + mt * 64, tc::sdesc_advance(ad0, mt * 2 * FT_BLK + kk * 2048),
-                        tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
-        tc::mma_commit(&t_done[kb]);
+            tc::mma_f16_if(leader, tO + mt * 64, tc::sdesc_advance(ad0, mt * 2 * FT_BLK + kk * 2048),
+                           tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
+        tc::mma_commit_if(leader, &t_done[kb]);
       };
       for (int tile = 0; tile < n_tiles; tile++) {
         const int b = tile & 1, kb = tile % FT_NBUF;
         // If the previous tile's P is already published, retire that tile first: its key buffer is
         // then refilled while this tile's QK^T runs.  Otherwise QK^T goes first and hides the softmax.
         bool g2_issued_early = false;
-        if (tile >= 1 && tc::mbar_try_wait(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
+        if (tile >= 1 && try_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
           tc::fence_after_sync();
-          FT_TRACE(5, tile - 1);
+          if (leader) FT_TRACE(5, tile - 1);
           gemm2(tile - 1);
-          FT_TRACE(6, tile - 1);
+          if (leader) FT_TRACE(6, tile - 1);
           g2_issued_early = true;
         }
-        ok = tc::mbar_wait<FT_POLL_NS>(&k_full[kb], (tile / FT_NBUF) & 1, &abort_flag, 1) && ok;
-        if (tile >= 2) ok = tc::mbar_wait<FT_POLL_NS>(&s_free[b], ((tile - 2) >> 1) & 1, &abort_flag, 2) && ok;
+        if (leader) FT_TRACE(12, tile);                // waits for this tile's keys start
+        ok = wait_u(&k_full[kb], (tile / FT_NBUF) & 1, 1) && ok;
+        if (leader) FT_TRACE(2, tile);                 // keys seen landed by the issuing warp
+        if (tile >= 2) ok = wait_u(&s_free[b], ((tile - 2) >> 1) & 1, 2) && ok;
         tc::fence_after_sync();
         // second chance after the wait for this tile's keys: retiring the previous tile first frees its key
         // buffer one QK^T earlier, and the refill of that buffer is what the next tiles wait for
-        if (tile >= 1 && !g2_issued_early && tc::mbar_try_wait(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
+        if (tile >= 1 && !g2_issued_early && try_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
           tc::fence_after_sync();
-          FT_TRACE(5, tile - 1);
+          if (leader) FT_TRACE(5, tile - 1);
           gemm2(tile - 1);
-          FT_TRACE(6, tile - 1);
+          if (leader) FT_TRACE(6, tile - 1);
           g2_issued_early = true;
         }
-        FT_TRACE(3, tile);                             // operands ready, QK^T issue starts
+        if (leader) FT_TRACE(3, tile);                 // operands ready, QK^T issue starts
         const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
         const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
         // keys as N in 1 KB atoms; 16 channels = 32 B inside the 128-byte row, 64 channels per block
         const uint64_t bd0 = tc::make_sdesc_sw128(k_addr, 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < LATENT / 16; kk++)       // S = Q K^T
-          tc::mma_f16(tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO), tc::sdesc_advance(bd0, (kk >> 2) * FT_BLK + (kk & 3) * 32),
-                      idesc_s, kk > 0);
-        tc::mma_commit(&s_full[b]);
-        FT_TRACE(4, tile);                             // QK^T issued
+          tc::mma_f16_if(leader, tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO),
+                         tc::sdesc_advance(bd0, (kk >> 2) * FT_BLK + (kk & 3) * 32), idesc_s, kk > 0);
+        tc::mma_commit_if(leader, &s_full[b]);
+        if (leader) FT_TRACE(4, tile);                 // QK^T issued
         if (tile >= 1 && !g2_issued_early) {
-          ok = tc::mbar_wait<FT_POLL_NS>(&p_full[b ^ 1], ((tile - 1) >> 1) & 1, &abort_flag, 3) && ok;
+          ok = wait_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1, 3) && ok;
           tc::fence_after_sync();
-          FT_TRACE(5, tile - 1);                       // P ready
+          if (leader) FT_TRACE(5, tile - 1);           // P ready
           gemm2(tile - 1);
-          FT_TRACE(6, tile - 1);                       // V^T P^T issued
+          if (leader) FT_TRACE(6, tile - 1);           // V^T P^T issued
         }
       }
       if (n_tiles > 0) {
-        ok = tc::mbar_wait<FT_POLL_NS>(&p_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, &abort_flag, 3) && ok;
+        ok = wait_u(&p_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 3) && ok;
         tc::fence_after_sync();
         gemm2(n_tiles - 1);
       }

@@ -47,6 +47,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking phase test.  mbarrier.try_wait may SUSPEND the thread for a system-dependent time (measured
+// here: well over a thousand cycles) before it reports "not yet", so it is the wrong instruction for
+// "is it ready? otherwise do something else first"; test_wait returns at once.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Cycle budget of one wait (~1 s at 2 GHz).  A wait that expires records `code` in *abort_flag
 // (shared memory, CTA-wide); once the flag is set every later wait returns at once, so a kernel
 // with a broken dependency still terminates within about one budget and reports where it gave up.
@@ -261,6 +276,47 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
+// ---- issue from a CONVERGED warp ----
+// A tcgen05.mma takes its descriptors from uniform registers.  Inside `if (threadIdx.x == 0)` the compiler
+// cannot treat them as warp-uniform and moves every operand across for every instruction: the issuing
+// thread then spends about 47 cycles per MMA whatever its shape (measured: M64 N16 ... M128 N64 all 47
+// cycles per instruction, the tensor pipe idle in between).  Issued by a whole warp whose index is provably
+// uniform (warp_index_uniform) with one elected lane as the predicate, the same instructions go out every
+// 24 (M64 N16), 29 (M64 N48), 41 (M128 N32), 49 (M128 N64, M64 N96) cycles; shapes with N >= 128 are bound
+// by the tensor pipe either way (N / 2 cycles for M = 64 and M = 128 alike).
+__device__ __forceinline__ int warp_index_uniform() {
+  return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+}
+// nonzero in exactly one lane of a fully active warp
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred;
+}
+// executed by every lane of the warp; only the lane with leader != 0 issues
+__device__ __forceinline__ void mma_f16_if(uint32_t leader, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                           uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_if(uint32_t leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
+      "r"(leader)
       : "memory");
 }
 

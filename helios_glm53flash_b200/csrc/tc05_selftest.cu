@@ -20,7 +20,8 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   // the offset-swap diagnostics exist for the no-swizzle layouts only: a swapped stride offset of a
   // swizzled tile would point past the operand region
   const bool b_mn = flags & 1, a_mn = flags & 2, swap_a = (flags & 0x100) && !a_sw, swap_b = (flags & 0x200) && !b_sw;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool converged_issue = flags & 0x400;   // issue from the whole of warp 0 with one elected lane (tc::mma_f16_if)
+  const int tid = threadIdx.x, warp = tc::warp_index_uniform();
   uint8_t* sA = smem;
   uint8_t* sB = smem + 128 * 128 * 2;
   const uint32_t kchunks = K / 8;
@@ -88,7 +89,10 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  if (tid == 0) {
+  if (warp == 0) {
+    // both issue forms run the same loop: every lane of warp 0 computes the (warp-uniform) descriptors; either
+    // lane 0 alone issues from a diverged branch, or an elected lane issues from the converged warp
+    const uint32_t leader = converged_issue ? tc::elect_one() : (uint32_t)(tid == 0);
     const uint32_t idesc = tc::make_idesc(M, N, tc::FMT_F16, tc::FMT_F16, a_mn, b_mn);
     for (int kk = 0; kk < K / 16; kk++) {
       uint64_t ad = swap_a ? tc::make_sdesc(tc::smem_u32(sA) + kk * 2 * lbo_a, sbo_a, lbo_a)
@@ -105,9 +109,12 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
         const uint32_t st = tc::smem_u32(sB) + (b_mn ? kk * 2048 : (kk >> 2) * blk_b + (kk & 3) * 32);
         bd = swap_b ? tc::make_sdesc_sw128(st, 1024, blk_b) : tc::make_sdesc_sw128(st, blk_b, 1024);
       }
-      tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
+      if (converged_issue) tc::mma_f16_if(leader, tmem, ad, bd, idesc, kk > 0);
+      else if (leader) tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
     }
-    tc::mma_commit(&bar);
+    if (converged_issue) tc::mma_commit_if(leader, &bar);
+    else if (leader) tc::mma_commit(&bar);
+    __syncwarp();
   }
   const bool ok = tc::mbar_wait(&bar, 0, &abort_flag, 1);
   tc::fence_after_sync();

@@ -17,7 +17,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
                                             (128, 16, 128, 0), (128, 128, 16, 1), (128, 256, 64, 1), (128, 64, 64, 2), (128, 64, 128, 3),
                                             # 128-byte-swizzle operands (bit 2: A, bit 3: B), K-major and MN-major
                                             (64, 64, 64, 0x8), (64, 48, 128, 0x8), (128, 32, 128, 0x4), (128, 32, 128, 0xc),
-                                            (128, 64, 64, 0x6), (128, 64, 48, 0x6), (128, 64, 64, 0x9), (128, 128, 64, 0xf)])
+                                            (128, 64, 64, 0x6), (128, 64, 48, 0x6), (128, 64, 64, 0x9), (128, 128, 64, 0xf),
+                                            # bit 10: issued by a converged warp with an elected lane (tc::mma_f16_if)
+                                            (128, 32, 128, 0x400), (128, 256, 128, 0x400), (64, 48, 128, 0x408), (64, 64, 64, 0x408),
+                                            (128, 64, 48, 0x406), (128, 128, 64, 0x40f)])
 def test_tc05_gemm_matches_fp32_matmul(M, N, K, b_layout):
     g = torch.Generator(device="cpu").manual_seed(M + N + K + b_layout)
     a = torch.randn(M, K, generator=g).half()
