@@ -37,7 +37,7 @@ namespace hk {
 constexpr int FT_KEYS = 48;                       // keys per tile
 constexpr int FT_NBUF = 3;                        // key tiles in flight
 constexpr int FT_HEADS = 64;
-constexpr int FT_THREADS = 384;
+constexpr int FT_THREADS = 416;                   // 4 softmax warps, QK^T issue warp, 7 loader warps, V^T P^T issue warp
 constexpr int FT_LOAD_WARPS = 7;                  // warps 5-11
 constexpr int FT_LOADERS = FT_LOAD_WARPS * 32;
 constexpr int FT_ITEMS = (2 * FT_KEYS + FT_LOAD_WARPS - 1) / FT_LOAD_WARPS;   // half-rows per loader warp and tile
@@ -51,6 +51,10 @@ constexpr uint32_t FS_K = 65536;                  // FT_NBUF tiles, 1 KB aligned
 constexpr uint32_t FS_P = FS_K + FT_NBUF * FT_TILE; // 2 x FP_BYTES
 constexpr uint32_t FS_MISC = FS_P + 2 * FP_BYTES;  // alpha[2][64], m[64], l[64], masks, flags
 constexpr uint32_t FS_SMEM = FS_MISC + 1536 + 1024;   // + slack to align the base to 1 KB (swizzle atoms)
+#ifndef HK_FT_PF_AHEAD
+#define HK_FT_PF_AHEAD 5
+#endif
+constexpr int FT_PF_AHEAD = HK_FT_PF_AHEAD;         // tiles between the L2 look-ahead prefetch and the tile being staged
 constexpr int FT_POLL_NS = 40;                    // poll back-off of the waiting warps
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units: P stays below 2^8, fine for fp16
@@ -108,7 +112,8 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // provably warp-uniform flag: the branch into the tensor-core issue role stays converged for the compiler
-  const bool mma_warp = tc::warp_index_uniform() == 4;
+  const int warp_u = tc::warp_index_uniform();
+  const bool mma_warp = warp_u == 4 || warp_u == 12;   // 4 issues S = Q K^T, 12 issues O^T += V^T P^T
   const int sp = blockIdx.x, r = blockIdx.y;
   FT_CTA_STAMP(0);
   const bool sparse = a.raw_idx != nullptr;
@@ -151,7 +156,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const uint32_t tS = tmem, tO = tmem + 128;   // S: 2 x 64 columns; O^T: 4 x 64 columns
   bool ok = true;
 
-  if (!mma_warp && warp >= 5) {
+  if (!mma_warp && warp >= 5) {   // warps 5-11
     // =========================== loaders: Q once, then the key tiles ===========================
     // Register-staged copies: every loader warp first issues all of its 16-byte loads of the NEXT
     // tile (they fly while the tensor pipe still owns the buffer), then waits for the buffer, then
@@ -201,9 +206,8 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         }
       }
     };
-    prefetch_tile(FT_NBUF - 1);
-    prefetch_tile(FT_NBUF);
-    prefetch_tile(FT_NBUF + 1);
+#pragma unroll 1
+    for (int t = FT_NBUF - 1; t < FT_PF_AHEAD; t++) prefetch_tile(t);
     // Gathered rows: the row numbers a warp needs for a tile are fetched one tile AHEAD, one per lane
     // (lane j: the row of item j; warp 0 also the rows behind the validity mask), and handed out by
     // shuffle, so the row loads of a tile are not each behind an index load of their own.
@@ -221,7 +225,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       const int buf = tile % FT_NBUF;
       const int p0 = k0 + tile * FT_KEYS;
       const bool via_tma = tile_is_tma(tile);
-      prefetch_tile(tile + FT_NBUF + 2);
+      prefetch_tile(tile + FT_PF_AHEAD);
       const int idx_cur = idx_next, mk0 = mk0_next, mk1 = mk1_next;
       idx_next = item_index(tile + 1, lane);
       mk0_next = mask_index(tile + 1, 0);
@@ -288,10 +292,6 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         const bool done = tc::mbar_wait<FT_POLL_NS>(bar, parity, &abort_flag, code);
         return __all_sync(0xffffffffu, done) != 0;
       };
-      auto try_u = [&](uint64_t* bar, uint32_t parity) {
-        const bool hit = tc::mbar_test_wait(bar, parity);   // must not block: QK^T of this tile goes first if P is not ready
-        return __all_sync(0xffffffffu, hit) != 0;
-      };
       const uint32_t q_addr = tc::smem_u32(sQ);
       const uint32_t idesc_s = tc::make_idesc(64, FT_KEYS, tc::FMT_F16, tc::FMT_F16, false, false);
       const uint32_t idesc_o = tc::make_idesc(128, FT_HEADS, tc::FMT_F16, tc::FMT_F16, true, false);
@@ -310,55 +310,37 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
                            tc::sdesc_advance(bd0, kk * 2 * FP_LBO), idesc_o, t > 0 || kk > 0);
         tc::mma_commit_if(leader, &t_done[kb]);
       };
-      for (int tile = 0; tile < n_tiles; tile++) {
-        const int b = tile & 1, kb = tile % FT_NBUF;
-        // If the previous tile's P is already published, retire that tile first: its key buffer is
-        // then refilled while this tile's QK^T runs.  Otherwise QK^T goes first and hides the softmax.
-        bool g2_issued_early = false;
-        if (tile >= 1 && try_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
+      // The two products have issuing warps of their own: S = Q K^T of tile t + 1 goes out as soon as its keys
+      // have landed and the S buffer is free, whatever the state of tile t's softmax; O^T += V^T P^T of tile t
+      // follows its P.  (One warp issuing both spent ~700 cycles per tile between its two waits.)
+      if (warp_u == 4) {
+        for (int tile = 0; tile < n_tiles; tile++) {
+          const int b = tile & 1, kb = tile % FT_NBUF;
+          if (leader) FT_TRACE(12, tile);              // waits for this tile's keys start
+          ok = wait_u(&k_full[kb], (tile / FT_NBUF) & 1, 1) && ok;
+          if (leader) FT_TRACE(2, tile);               // keys seen landed by the issuing warp
+          if (tile >= 2) ok = wait_u(&s_free[b], ((tile - 2) >> 1) & 1, 2) && ok;
           tc::fence_after_sync();
-          if (leader) FT_TRACE(5, tile - 1);
-          gemm2(tile - 1);
-          if (leader) FT_TRACE(6, tile - 1);
-          g2_issued_early = true;
-        }
-        if (leader) FT_TRACE(12, tile);                // waits for this tile's keys start
-        ok = wait_u(&k_full[kb], (tile / FT_NBUF) & 1, 1) && ok;
-        if (leader) FT_TRACE(2, tile);                 // keys seen landed by the issuing warp
-        if (tile >= 2) ok = wait_u(&s_free[b], ((tile - 2) >> 1) & 1, 2) && ok;
-        tc::fence_after_sync();
-        // second chance after the wait for this tile's keys: retiring the previous tile first frees its key
-        // buffer one QK^T earlier, and the refill of that buffer is what the next tiles wait for
-        if (tile >= 1 && !g2_issued_early && try_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1)) {
-          tc::fence_after_sync();
-          if (leader) FT_TRACE(5, tile - 1);
-          gemm2(tile - 1);
-          if (leader) FT_TRACE(6, tile - 1);
-          g2_issued_early = true;
-        }
-        if (leader) FT_TRACE(3, tile);                 // operands ready, QK^T issue starts
-        const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
-        const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
-        // keys as N in 1 KB atoms; 16 channels = 32 B inside the 128-byte row, 64 channels per block
-        const uint64_t bd0 = tc::make_sdesc_sw128(k_addr, 16, 1024);
+          if (leader) FT_TRACE(3, tile);               // operands ready, QK^T issue starts
+          const uint32_t k_addr = tc::smem_u32(smem + FS_K + kb * FT_TILE);
+          const uint64_t ad0 = tc::make_sdesc(q_addr, FQ_LBO, FQ_SBO);
+          // keys as N in 1 KB atoms; 16 channels = 32 B inside the 128-byte row, 64 channels per block
+          const uint64_t bd0 = tc::make_sdesc_sw128(k_addr, 16, 1024);
 #pragma unroll
-        for (int kk = 0; kk < LATENT / 16; kk++)       // S = Q K^T
-          tc::mma_f16_if(leader, tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO),
-                         tc::sdesc_advance(bd0, (kk >> 2) * FT_BLK + (kk & 3) * 32), idesc_s, kk > 0);
-        tc::mma_commit_if(leader, &s_full[b]);
-        if (leader) FT_TRACE(4, tile);                 // QK^T issued
-        if (tile >= 1 && !g2_issued_early) {
-          ok = wait_u(&p_full[b ^ 1], ((tile - 1) >> 1) & 1, 3) && ok;
-          tc::fence_after_sync();
-          if (leader) FT_TRACE(5, tile - 1);           // P ready
-          gemm2(tile - 1);
-          if (leader) FT_TRACE(6, tile - 1);           // V^T P^T issued
+          for (int kk = 0; kk < LATENT / 16; kk++)     // S = Q K^T
+            tc::mma_f16_if(leader, tS + b * 64, tc::sdesc_advance(ad0, kk * 2 * FQ_LBO),
+                           tc::sdesc_advance(bd0, (kk >> 2) * FT_BLK + (kk & 3) * 32), idesc_s, kk > 0);
+          tc::mma_commit_if(leader, &s_full[b]);
+          if (leader) FT_TRACE(4, tile);               // QK^T issued
         }
-      }
-      if (n_tiles > 0) {
-        ok = wait_u(&p_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 3) && ok;
-        tc::fence_after_sync();
-        gemm2(n_tiles - 1);
+      } else {
+        for (int tile = 0; tile < n_tiles; tile++) {
+          ok = wait_u(&p_full[tile & 1], (tile >> 1) & 1, 3) && ok;
+          tc::fence_after_sync();
+          if (leader) FT_TRACE(5, tile);               // P ready
+          gemm2(tile);
+          if (leader) FT_TRACE(6, tile);               // V^T P^T issued
+        }
       }
     }
   } else {

@@ -137,6 +137,7 @@ constexpr size_t MLA_SIMT_SMEM = (size_t)(8 * SIMT_HG * LATENT + 2 * 8 * SIMT_HG
 constexpr int LSE_MAX_SPLITS = 1024;
 constexpr int LSE_GROUPS = 8;
 constexpr int LSE_THREADS = 128 * LSE_GROUPS;
+constexpr int LSE_PRE = 3;                        // accumulator pieces per thread loaded ahead of the weights (24 splits)
 
 template <bool PTRS>
 __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m, const float* __restrict__ part_l,
@@ -148,9 +149,29 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __shared__ float s_red[LSE_THREADS / 32];
   __shared__ float4 s_o[LSE_GROUPS - 1][128];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int cq = t & 127, sg = t >> 7;
+  auto load_acc = [&](int s) -> float4 {
+    const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
+    const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
+    return PTRS ? __ldcv(ap) : __ldg(ap);             // peer memory: never through the read-only cache
+  };
+  // All loads that do not depend on the weights go out first: this thread's first LSE_PRE accumulator pieces
+  // and the (m, l) pair of split t.  The weight phases below then run while they are in flight (one memory
+  // round trip on the critical path instead of three).
+  float4 pre[LSE_PRE];
+#pragma unroll
+  for (int u = 0; u < LSE_PRE; u++) {
+    const int s = sg + u * LSE_GROUPS;
+    pre[u] = s < n_split ? load_acc(s) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float m_first = -INFINITY, l_first = 0.f;
+  if (t < n_split) {
+    m_first = (PTRS ? ptrs_m[t] : part_m + (size_t)t * rows)[r];
+    l_first = (PTRS ? ptrs_l[t] : part_l + (size_t)t * rows)[r];
+  }
   float mloc = -INFINITY;
   for (int s = t; s < n_split; s += LSE_THREADS) {
-    const float m = (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
+    const float m = s == t ? m_first : (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
     s_w[s] = m;
     mloc = fmaxf(mloc, m);
   }
@@ -167,7 +188,7 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
     const float m = s_w[s];
     const float w = (m == -INFINITY) ? 0.f : __expf(m - gm);
     s_w[s] = w;
-    lloc += w * (PTRS ? ptrs_l[s] : part_l + (size_t)s * rows)[r];
+    lloc += w * (s == t ? l_first : (PTRS ? ptrs_l[s] : part_l + (size_t)s * rows)[r]);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
@@ -176,13 +197,19 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   float gl = 0.f;
 #pragma unroll
   for (int w = 0; w < LSE_THREADS / 32; w++) gl += s_red[w];
-  const int cq = t & 127, sg = t >> 7;
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  // same summation order as a plain loop over s = sg, sg + LSE_GROUPS, ...
+#pragma unroll
+  for (int u = 0; u < LSE_PRE; u++) {
+    const int s = sg + u * LSE_GROUPS;
+    if (s < n_split) {
+      const float w = s_w[s];
+      o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+    }
+  }
 #pragma unroll 4
-  for (int s = sg; s < n_split; s += LSE_GROUPS) {
-    const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
-    const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
-    const float4 a = PTRS ? __ldcv(ap) : __ldg(ap);   // peer memory: never through the read-only cache
+  for (int s = sg + LSE_PRE * LSE_GROUPS; s < n_split; s += LSE_GROUPS) {
+    const float4 a = load_acc(s);
     const float w = s_w[s];
     o.x = fmaf(w, a.x, o.x); o.y = fmaf(w, a.y, o.y); o.z = fmaf(w, a.z, o.z); o.w = fmaf(w, a.w, o.w);
   }
