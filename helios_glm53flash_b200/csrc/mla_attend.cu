@@ -66,8 +66,12 @@ static int launch_simt(const MlaArgs& a, cudaStream_t s) {
 static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
                    __half* out, cudaStream_t s) {
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
-  lse_combine_kernel<false><<<(unsigned)rows, LSE_THREADS, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
-                                                            n_split, rows, out);
+  if (n_split <= LSE_FEW_SPLITS && rows >= 256)
+    lse_combine_kernel<false, LSE_GROUPS_FEW><<<(unsigned)rows, 128 * LSE_GROUPS_FEW, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
+                                                                                         n_split, rows, out);
+  else
+    lse_combine_kernel<false, LSE_GROUPS><<<(unsigned)rows, LSE_THREADS, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
+                                                                            n_split, rows, out);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 
@@ -288,7 +292,7 @@ HK_API int hk_lse_combine_ptrs(const float* const* ptrs_m, const float* const* p
   using namespace hk;
   HK_REQUIRE(ptrs_m && ptrs_l && ptrs_acc && out_f16 && n_split >= 1 && n_split <= LSE_MAX_SPLITS && rows >= 0);
   if (rows == 0) return HK_OK;
-  lse_combine_kernel<true><<<(unsigned)rows, LSE_THREADS, 0, as_stream(stream)>>>(
+  lse_combine_kernel<true, LSE_GROUPS><<<(unsigned)rows, LSE_THREADS, 0, as_stream(stream)>>>(
       nullptr, nullptr, nullptr, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, (__half*)out_f16);
   HK_LAUNCH_CHECK();
   return HK_OK;

@@ -137,17 +137,22 @@ constexpr size_t MLA_SIMT_SMEM = (size_t)(8 * SIMT_HG * LATENT + 2 * 8 * SIMT_HG
 constexpr int LSE_MAX_SPLITS = 1024;
 constexpr int LSE_GROUPS = 8;
 constexpr int LSE_THREADS = 128 * LSE_GROUPS;
-constexpr int LSE_PRE = 3;                        // accumulator pieces per thread loaded ahead of the weights (24 splits)
+// Few splits over many rows (batched decode): two thread groups per row instead of eight, so that every row's CTA
+// is resident at once (256 threads: 8 CTAs per SM) and a thread keeps up to 12 independent loads in flight.
+constexpr int LSE_GROUPS_FEW = 2;
+constexpr int LSE_FEW_SPLITS = 24;
 
-template <bool PTRS>
+template <bool PTRS, int GROUPS>
 __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                                const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
                                                const float* const* __restrict__ ptrs_l,
                                                const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows,
                                                int64_t r, float& gm_out, float& gl_out, float4& o_out) {
+  constexpr int THREADS = 128 * GROUPS;
+  constexpr int PRE = 24 / GROUPS;                  // accumulator pieces per thread loaded ahead of the weights (24 splits)
   __shared__ float s_w[LSE_MAX_SPLITS];
-  __shared__ float s_red[LSE_THREADS / 32];
-  __shared__ float4 s_o[LSE_GROUPS - 1][128];
+  __shared__ float s_red[THREADS / 32];
+  __shared__ float4 s_o[GROUPS - 1][128];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int cq = t & 127, sg = t >> 7;
   auto load_acc = [&](int s) -> float4 {
@@ -155,13 +160,13 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
     const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
     return PTRS ? __ldcv(ap) : __ldg(ap);             // peer memory: never through the read-only cache
   };
-  // All loads that do not depend on the weights go out first: this thread's first LSE_PRE accumulator pieces
+  // All loads that do not depend on the weights go out first: this thread's first PRE accumulator pieces
   // and the (m, l) pair of split t.  The weight phases below then run while they are in flight (one memory
   // round trip on the critical path instead of three).
-  float4 pre[LSE_PRE];
+  float4 pre[PRE];
 #pragma unroll
-  for (int u = 0; u < LSE_PRE; u++) {
-    const int s = sg + u * LSE_GROUPS;
+  for (int u = 0; u < PRE; u++) {
+    const int s = sg + u * GROUPS;
     pre[u] = s < n_split ? load_acc(s) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float m_first = -INFINITY, l_first = 0.f;
@@ -170,7 +175,7 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
     l_first = (PTRS ? ptrs_l[t] : part_l + (size_t)t * rows)[r];
   }
   float mloc = -INFINITY;
-  for (int s = t; s < n_split; s += LSE_THREADS) {
+  for (int s = t; s < n_split; s += THREADS) {
     const float m = s == t ? m_first : (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
     s_w[s] = m;
     mloc = fmaxf(mloc, m);
@@ -181,10 +186,10 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __syncthreads();
   float gm = s_red[0];
 #pragma unroll
-  for (int w = 1; w < LSE_THREADS / 32; w++) gm = fmaxf(gm, s_red[w]);
+  for (int w = 1; w < THREADS / 32; w++) gm = fmaxf(gm, s_red[w]);
   __syncthreads();
   float lloc = 0.f;
-  for (int s = t; s < n_split; s += LSE_THREADS) {
+  for (int s = t; s < n_split; s += THREADS) {
     const float m = s_w[s];
     const float w = (m == -INFINITY) ? 0.f : __expf(m - gm);
     s_w[s] = w;
@@ -196,19 +201,19 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __syncthreads();
   float gl = 0.f;
 #pragma unroll
-  for (int w = 0; w < LSE_THREADS / 32; w++) gl += s_red[w];
+  for (int w = 0; w < THREADS / 32; w++) gl += s_red[w];
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  // same summation order as a plain loop over s = sg, sg + LSE_GROUPS, ...
+  // same summation order as a plain loop over s = sg, sg + GROUPS, ...
 #pragma unroll
-  for (int u = 0; u < LSE_PRE; u++) {
-    const int s = sg + u * LSE_GROUPS;
+  for (int u = 0; u < PRE; u++) {
+    const int s = sg + u * GROUPS;
     if (s < n_split) {
       const float w = s_w[s];
       o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
     }
   }
 #pragma unroll 4
-  for (int s = sg + LSE_PRE * LSE_GROUPS; s < n_split; s += LSE_GROUPS) {
+  for (int s = sg + PRE * GROUPS; s < n_split; s += GROUPS) {
     const float4 a = load_acc(s);
     const float w = s_w[s];
     o.x = fmaf(w, a.x, o.x); o.y = fmaf(w, a.y, o.y); o.z = fmaf(w, a.z, o.z); o.w = fmaf(w, a.w, o.w);
@@ -217,7 +222,7 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   __syncthreads();
   if (sg == 0) {
 #pragma unroll
-    for (int gi = 0; gi < LSE_GROUPS - 1; gi++) {
+    for (int gi = 0; gi < GROUPS - 1; gi++) {
       const float4 p = s_o[gi][cq];
       o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
     }
@@ -225,8 +230,8 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   gm_out = gm; gl_out = gl; o_out = o;      // o is complete in threads 0..127
 }
 
-template <bool PTRS>
-__global__ __launch_bounds__(LSE_THREADS) void lse_combine_kernel(
+template <bool PTRS, int GROUPS>
+__global__ __launch_bounds__(128 * GROUPS) void lse_combine_kernel(
     const float* __restrict__ part_m, const float* __restrict__ part_l,
     const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
     const float* const* __restrict__ ptrs_l, const float* const* __restrict__ ptrs_acc,
@@ -234,7 +239,7 @@ __global__ __launch_bounds__(LSE_THREADS) void lse_combine_kernel(
   const int64_t r = blockIdx.x;
   float gm, gl;
   float4 o;
-  lse_reduce_row<PTRS>(part_m, part_l, part_acc, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, r, gm, gl, o);
+  lse_reduce_row<PTRS, GROUPS>(part_m, part_l, part_acc, ptrs_m, ptrs_l, ptrs_acc, n_split, rows, r, gm, gl, o);
   if (threadIdx.x < 128) {
     const float inv = gl > 0.f ? 1.f / gl : 0.f;
     __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
@@ -258,7 +263,7 @@ __global__ __launch_bounds__(LSE_THREADS) void lse_merge_partials_kernel(
   const int64_t r = blockIdx.x;
   float gm, gl;
   float4 o;
-  lse_reduce_row<false>(part_m, part_l, part_acc, nullptr, nullptr, nullptr, n_split, rows, r, gm, gl, o);
+  lse_reduce_row<false, LSE_GROUPS>(part_m, part_l, part_acc, nullptr, nullptr, nullptr, n_split, rows, r, gm, gl, o);
   if (step_ctr && ((*step_ctr + 1) & 1)) {
     out_m = out_m1; out_l = out_l1; out_acc = out_acc1;
   }
