@@ -133,6 +133,71 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
   if (tid == 0) status[0] = abort_flag;
 }
 
+
+// Issue-rate probe: `count` products (K = 16 each, operands cycling through a zeroed K = 128 tile, all
+// accumulated into one TMEM tile) are issued back to back, then committed and waited for.  cycles[0] = clock64
+// ticks until the last product was issued, cycles[1] = until all had completed.  converged = 0: issued by one
+// thread inside a diverged branch; 1: by the whole of warp 0 with an elected lane (tc::mma_f16_if).
+__global__ __launch_bounds__(128) void tc05_issue_probe_kernel(int M, int N, int converged, int count,
+                                                               long long* __restrict__ cycles, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tc::warp_index_uniform();
+  for (int i = tid; i < (128 * 128 * 2 + 256 * 128 * 2) / 16; i += 128) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (warp == 0) {
+    const uint32_t idesc = tc::make_idesc(M, N, tc::FMT_F16, tc::FMT_F16, false, false);
+    const uint64_t ad0 = tc::make_sdesc(tc::smem_u32(smem), 128, 2048);
+    const uint64_t bd0 = tc::make_sdesc(tc::smem_u32(smem + 128 * 128 * 2), 128, 2048);
+    long long t0 = 0, t1 = 0;
+    if (converged) {
+      const uint32_t leader = tc::elect_one();
+      t0 = clock64();
+#pragma unroll 1
+      for (int it = 0; it < count / 8; it++) {
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++)
+          tc::mma_f16_if(leader, tmem, tc::sdesc_advance(ad0, kk * 256), tc::sdesc_advance(bd0, kk * 256), idesc, true);
+      }
+      t1 = clock64();
+      tc::mma_commit_if(leader, &bar);
+    } else if (tid == 0) {
+      t0 = clock64();
+#pragma unroll 1
+      for (int it = 0; it < count / 8; it++) {
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++)
+          tc::mma_f16(tmem, tc::sdesc_advance(ad0, kk * 256), tc::sdesc_advance(bd0, kk * 256), idesc, true);
+      }
+      t1 = clock64();
+      tc::mma_commit(&bar);
+    }
+    __syncwarp();
+    const bool ok = tc::mbar_wait(&bar, 0, &abort_flag, 1);       // every lane waits
+    const long long t2 = clock64();
+    if (tid == 0) {
+      cycles[0] = t1 - t0;
+      cycles[1] = t2 - t0;
+      status[0] = ok ? 0 : abort_flag;
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 256);
+}
+
 }  // namespace hk
 
 HK_API int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,
@@ -154,6 +219,24 @@ HK_API int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int 
   tc05_selftest_kernel<<<1, 128, smem, as_stream(stream)>>>((const __half*)a_f16,
                                                             (const __half*)b_f16, d, M, N, K,
                                                             b_layout, status);
+  HK_LAUNCH_CHECK();
+  return HK_OK;
+}
+
+HK_API int hk_tc05_issue_probe(int M, int N, int converged, int count, long long* cycles, int* status, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(cycles && status);
+  HK_REQUIRE((M == 64 || M == 128) && N >= 16 && N <= 256 && N % 16 == 0 && count >= 8 && count <= 65536 && count % 8 == 0);
+  const size_t smem = 128 * 128 * 2 + 256 * 128 * 2;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(tc05_issue_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return HK_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  tc05_issue_probe_kernel<<<1, 128, smem, as_stream(stream)>>>(M, N, converged, count, cycles, status);
   HK_LAUNCH_CHECK();
   return HK_OK;
 }

@@ -187,7 +187,7 @@ CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "c
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, help="one of: " + ", ".join(CASES) + ", or 'all'")
+    ap.add_argument("--case", required=True, help="one of: " + ", ".join(CASES) + ", 'all', or 'tc05_issue' (cycles per tensor-core product by shape and issue form)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--graph", action="store_true",
@@ -195,6 +195,17 @@ def main():
     args = ap.parse_args()
     import torch
     import helios_glm53flash_b200 as hk
+    if args.case == "tc05_issue":
+        # not a timing of a library call: SM clock ticks per tcgen05 product by shape and issue form
+        for M, N in [(64, 16), (64, 48), (64, 96), (64, 128), (64, 256), (128, 32), (128, 64), (128, 128), (128, 256)]:
+            row = {"case": "tc05_issue", "M": M, "N": N, "K": 16}
+            for conv in (0, 1):
+                for count in (32, 512):
+                    hk.tc05_issue_probe(M, N, conv, count)
+                    issue, done = hk.tc05_issue_probe(M, N, conv, count)
+                    row["%s_burst%d_cycles_per_mma" % ("converged_warp" if conv else "single_thread", count)] = round(done / count, 1)
+            print(json.dumps(row), flush=True)
+        return
     for name in (CASES if args.case == "all" else [args.case]):
         fn, nbytes, flush, desc = build_case(name)
         buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
