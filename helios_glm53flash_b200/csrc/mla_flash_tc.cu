@@ -116,6 +116,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const bool mma_warp = warp_u == 4 || warp_u == 12;   // 4 issues S = Q K^T, 12 issues O^T += V^T P^T
   const int sp = blockIdx.x, r = blockIdx.y;
   FT_CTA_STAMP(0);
+  if (tid == 0) FT_TRACE(13, 0);                      // kernel entry
   const bool sparse = a.raw_idx != nullptr;
   int n;
   int64_t base = 0;
@@ -147,8 +148,42 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     }
     tc::mbar_fence_init();
     abort_flag = 0;
+    // The copies of the first FT_NBUF dense tiles leave at once, from the thread that has just initialised their
+    // barriers: they fly while the queries are staged below (measured before: 6 us from kernel entry to the first
+    // tile copy at batch 8, the queries being loaded first in five dependent batches by the loader warps alone).
+    // The byte count is raised without an arrival; the loader thread that owns the copies arrives like the others.
+    for (int t = 0; t < FT_NBUF && t < n_tiles; t++) {
+      if (tile_is_tma(t)) {
+        tc::mbar_expect_tx(&k_full[t], FT_KEYS * LATENT * 2);
+        tma_load_tile(smem + FS_K + t * FT_TILE, &tmap, (int)(base + k0 + t * FT_KEYS), &k_full[t]);
+      }
+    }
   }
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 512);
+  if (n_tiles > 0) {
+    // Q [64 heads][512] -> K-major operand tile, staged by ALL warps with every load of a thread in flight at
+    // once.  item = (head group, chunk quad); lanes = 8 heads x 4 chunks -> one 128-byte core matrix per octet
+    constexpr int NW = FT_THREADS / 32, QI = (128 + NW - 1) / NW;
+    const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
+    uint4 qs[QI];
+#pragma unroll
+    for (int u = 0; u < QI; u++) {
+      const int it = warp + u * NW;
+      if (it < 128) {
+        const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
+        qs[u] = *reinterpret_cast<const uint4*>(q + (size_t)h * LATENT + ch * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < QI; u++) {
+      const int it = warp + u * NW;
+      if (it < 128) {
+        const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3);
+        *reinterpret_cast<uint4*>(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16) = qs[u];
+      }
+    }
+    tc::fence_async_smem();
+  }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -157,36 +192,12 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   bool ok = true;
 
   if (!mma_warp && warp >= 5) {   // warps 5-11
-    // =========================== loaders: Q once, then the key tiles ===========================
+    // =========================== loaders: the key tiles ===========================
     // Register-staged copies: every loader warp first issues all of its 16-byte loads of the NEXT
     // tile (they fly while the tensor pipe still owns the buffer), then waits for the buffer, then
     // stores.  Plain vector loads: the per-thread cp.async path sustains far fewer bytes in flight.
     const int lw = warp - 5;
     uint4 stage[FT_ITEMS];
-    if (n_tiles > 0) {
-      // Q: item = (head group, chunk quad); lanes = 8 heads x 4 chunks -> one 128-byte core matrix per octet
-      const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
-#pragma unroll 1
-      for (int it0 = lw; it0 < 128; it0 += 4 * FT_LOAD_WARPS) {      // 128 items, four in flight per warp
-        uint4 qs[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          const int it = it0 + u * FT_LOAD_WARPS;
-          if (it < 128) {
-            const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
-            qs[u] = *reinterpret_cast<const uint4*>(q + (size_t)h * LATENT + ch * 8);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          const int it = it0 + u * FT_LOAD_WARPS;
-          if (it < 128) {
-            const int hg = it >> 4, ch = (it & 15) * 4 + (lane >> 3);
-            *reinterpret_cast<uint4*>(sQ + hg * FQ_SBO + ch * FQ_LBO + (lane & 7) * 16) = qs[u];
-          }
-        }
-      }
-    }
     // L2 prefetch of the tiles ahead keeps HBM busy while this CTA computes: the register-staged
     // loads below then hit L2.  Dense: one contiguous range per tile; sparse: one 1 KB row per lane.
     auto prefetch_tile = [&](int t) {
@@ -270,8 +281,12 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       if (via_tma && lw == 0 && lane == 0) {
         // one thread arms the barrier with the byte count and fires the tensor copy; the other loader
         // threads just arrive, the phase completes when the 64 KB have landed
-        tc::mbar_arrive_expect_tx(&k_full[buf], FT_KEYS * LATENT * 2);
-        tma_load_tile(dst0, &tmap, (int)(base + p0), &k_full[buf]);
+        if (tile >= FT_NBUF) {
+          tc::mbar_arrive_expect_tx(&k_full[buf], FT_KEYS * LATENT * 2);
+          tma_load_tile(dst0, &tmap, (int)(base + p0), &k_full[buf]);
+        } else {
+          tc::mbar_arrive(&k_full[buf]);               // this tile's copy left at kernel entry
+        }
       } else {
         tc::fence_async_smem();
         tc::mbar_arrive(&k_full[buf]);
@@ -458,9 +473,11 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       s_m[hB] = mB; s_l[hB] = lB;
     }
     // ---- epilogue (softmax warps): wait for the last V^T P^T, then write the result ----
+    if (tid == 0) FT_TRACE(14, 0);                    // softmax loop done
     if (n_tiles > 0) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[(n_tiles - 1) % FT_NBUF], ((n_tiles - 1) / FT_NBUF) & 1, &abort_flag, 10) && ok;
     tc::fence_after_sync();
     softmax_group_sync();
+    if (tid == 0) FT_TRACE(15, 0);                    // last V^T P^T complete, write-out starts
     const size_t rows = (size_t)a.m * FT_HEADS;
     const size_t rh0 = (size_t)r * FT_HEADS;
     if (ok && !abort_flag) {
@@ -500,6 +517,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   }
   tc::fence_before_sync();
   __syncthreads();
+  if (tid == 0) FT_TRACE(13, 1);                      // all roles done
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
   FT_CTA_STAMP(1);
