@@ -63,16 +63,36 @@ static int launch_simt(const MlaArgs& a, cudaStream_t s) {
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 
+// Launched with programmatic stream serialisation: the flash kernel releases its dependents at entry, so the
+// combine's CTAs are placed while the partial kernel still runs and block in griddepcontrol.wait (first statement
+// of lse_combine_kernel) until that grid has completed and its writes are visible; the launch latency of the
+// second kernel disappears from every decode step.  Behind any other kernel the attribute only delays the start
+// until that kernel has finished, as a plain launch would.
+template <int GROUPS>
+static int combine_launch(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows, __half* out,
+                          cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows);
+  cfg.blockDim = dim3(128 * GROUPS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* const* none = nullptr;
+  return cudaLaunchKernelEx(&cfg, lse_combine_kernel<false, GROUPS>, pm, pl, pa, none, none, none, n_split, rows, out) ==
+                 cudaSuccess
+             ? HK_OK
+             : HK_ERR_CUDA;
+}
+
 static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
                    __half* out, cudaStream_t s) {
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
-  if (n_split <= LSE_FEW_SPLITS && rows >= 256)
-    lse_combine_kernel<false, LSE_GROUPS_FEW><<<(unsigned)rows, 128 * LSE_GROUPS_FEW, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
-                                                                                         n_split, rows, out);
-  else
-    lse_combine_kernel<false, LSE_GROUPS><<<(unsigned)rows, LSE_THREADS, 0, s>>>(pm, pl, pa, nullptr, nullptr, nullptr,
-                                                                            n_split, rows, out);
-  return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+  if (n_split <= LSE_FEW_SPLITS && rows >= 256) return combine_launch<LSE_GROUPS_FEW>(pm, pl, pa, n_split, rows, out, s);
+  return combine_launch<LSE_GROUPS>(pm, pl, pa, n_split, rows, out, s);
 }
 
 // common driver: final output, optionally through split partials in the workspace

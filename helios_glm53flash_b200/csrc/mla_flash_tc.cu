@@ -115,6 +115,9 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const int warp_u = tc::warp_index_uniform();
   const bool mma_warp = warp_u == 4 || warp_u == 12;   // 4 issues S = Q K^T, 12 issues O^T += V^T P^T
   const int sp = blockIdx.x, r = blockIdx.y;
+  // a kernel launched as this grid's programmatic dependent (the LSE combine) may be placed from now on; it waits
+  // for this grid's completion itself before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   FT_CTA_STAMP(0);
   if (tid == 0) FT_TRACE(13, 0);                      // kernel entry
   const bool sparse = a.raw_idx != nullptr;

@@ -236,6 +236,9 @@ __global__ __launch_bounds__(128 * GROUPS) void lse_combine_kernel(
     const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
     const float* const* __restrict__ ptrs_l, const float* const* __restrict__ ptrs_acc,
     int n_split, int64_t rows, __half* __restrict__ out) {
+  // when launched as a programmatic dependent of the kernel that writes the partials: wait until that grid has
+  // completed and its writes are visible (a no-op after a plain launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t r = blockIdx.x;
   float gm, gl;
   float4 o;
