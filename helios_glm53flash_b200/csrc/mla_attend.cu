@@ -88,9 +88,30 @@ static int combine_launch(const float* pm, const float* pl, const float* pa, int
              : HK_ERR_CUDA;
 }
 
+template <int GROUPS>
+static int combine_cs_launch(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows, __half* out,
+                             cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows, LSE_CSPLIT);
+  cfg.blockDim = dim3(32 * GROUPS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, lse_combine_cs_kernel<GROUPS>, pm, pl, pa, n_split, rows, out) == cudaSuccess ? HK_OK
+                                                                                                                 : HK_ERR_CUDA;
+}
+
 static int combine(const float* pm, const float* pl, const float* pa, int n_split, int64_t rows,
                    __half* out, cudaStream_t s) {
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
+  // few rows and few splits (sparse decode of one sequence: 64 rows x 22 splits): channel-split form, four CTAs per
+  // row (15.1 vs 16.1 us per layer for the sparse step).  With many splits (dense decode of one sequence, 137) the
+  // same form with 32 thread groups measured slower than eight groups of 128 lanes (24.5 vs 23.5 us): not used.
+  if (rows < 256 && n_split <= LSE_FEW_SPLITS) return combine_cs_launch<8>(pm, pl, pa, n_split, rows, out, s);
   if (n_split <= LSE_FEW_SPLITS && rows >= 256) return combine_launch<LSE_GROUPS_FEW>(pm, pl, pa, n_split, rows, out, s);
   return combine_launch<LSE_GROUPS>(pm, pl, pa, n_split, rows, out, s);
 }

@@ -142,22 +142,23 @@ constexpr int LSE_THREADS = 128 * LSE_GROUPS;
 constexpr int LSE_GROUPS_FEW = 2;
 constexpr int LSE_FEW_SPLITS = 24;
 
-template <bool PTRS, int GROUPS>
+// LANES float4 lanes per thread group = the channels [cpart * 4 LANES, (cpart + 1) * 4 LANES) of the row; PRE =
+// accumulator pieces per thread requested ahead of the weights.
+template <bool PTRS, int GROUPS, int LANES = 128, int PRE = 24 / GROUPS>
 __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                                const float* __restrict__ part_acc, const float* const* __restrict__ ptrs_m,
                                                const float* const* __restrict__ ptrs_l,
                                                const float* const* __restrict__ ptrs_acc, int n_split, int64_t rows,
-                                               int64_t r, float& gm_out, float& gl_out, float4& o_out) {
-  constexpr int THREADS = 128 * GROUPS;
-  constexpr int PRE = 24 / GROUPS;                  // accumulator pieces per thread loaded ahead of the weights (24 splits)
+                                               int64_t r, float& gm_out, float& gl_out, float4& o_out, int cpart = 0) {
+  constexpr int THREADS = LANES * GROUPS;
   __shared__ float s_w[LSE_MAX_SPLITS];
   __shared__ float s_red[THREADS / 32];
-  __shared__ float4 s_o[GROUPS - 1][128];
+  __shared__ float4 s_o[GROUPS - 1][LANES];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-  const int cq = t & 127, sg = t >> 7;
+  const int cq = t % LANES, sg = t / LANES;
   auto load_acc = [&](int s) -> float4 {
     const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
-    const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cq;
+    const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cpart * LANES + cq;
     return PTRS ? __ldcv(ap) : __ldg(ap);             // peer memory: never through the read-only cache
   };
   // All loads that do not depend on the weights go out first: this thread's first PRE accumulator pieces
@@ -227,7 +228,7 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
       o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
     }
   }
-  gm_out = gm; gl_out = gl; o_out = o;      // o is complete in threads 0..127
+  gm_out = gm; gl_out = gl; o_out = o;      // o is complete in threads 0..LANES-1
 }
 
 template <bool PTRS, int GROUPS>
@@ -251,6 +252,33 @@ __global__ __launch_bounds__(128 * GROUPS) void lse_combine_kernel(
     pk.x = *reinterpret_cast<uint32_t*>(&h0);
     pk.y = *reinterpret_cast<uint32_t*>(&h1);
     *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + threadIdx.x * 4) = pk;
+  }
+}
+
+// The same for few rows (single-sequence decode: 64 (row, head) pairs): every row is shared by CSPLIT CTAs, each
+// owning 512 / CSPLIT channels, with GROUPS groups of 32 float4 lanes over the splits, so that 64 rows still cover
+// the machine and a thread has all of its loads in flight at once.  grid = (rows, CSPLIT).
+constexpr int LSE_CSPLIT = 4;
+template <int GROUPS>
+__global__ __launch_bounds__(32 * GROUPS) void lse_combine_cs_kernel(
+    const float* __restrict__ part_m, const float* __restrict__ part_l, const float* __restrict__ part_acc,
+    int n_split, int64_t rows, __half* __restrict__ out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // see lse_combine_kernel
+  constexpr int LANES = 128 / LSE_CSPLIT;
+  const int64_t r = blockIdx.x;
+  const int cpart = blockIdx.y;
+  float gm, gl;
+  float4 o;
+  lse_reduce_row<false, GROUPS, LANES, 3>(part_m, part_l, part_acc, nullptr, nullptr, nullptr, n_split, rows, r,
+                                                                gm, gl, o, cpart);
+  if (threadIdx.x < LANES) {
+    const float inv = gl > 0.f ? 1.f / gl : 0.f;
+    __half2 h0 = __floats2half2_rn(o.x * inv, o.y * inv);
+    __half2 h1 = __floats2half2_rn(o.z * inv, o.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(out + (size_t)r * LATENT + (cpart * LANES + threadIdx.x) * 4) = pk;
   }
 }
 
