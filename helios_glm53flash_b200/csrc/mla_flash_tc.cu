@@ -6,23 +6,25 @@
 //
 // Work item = (query row, key split) -> one CTA; all 64 heads of the row share every latent row that
 // is staged, so the cache is read once per row (the reference re-reads it per head pair).
-// Per tile of 64 keys (64 KB, double buffered, invalid slots zero-filled):
-//   S  [64 heads x 64 keys]  = Q  K^T   tcgen05 M64  N64 K512: Q and the tile both K-major
+// Per tile of 48 keys (48 KB, three tiles in flight, invalid slots zero-filled):
+//   S  [64 heads x 48 keys]  = Q  K^T   tcgen05 M64  N48 K512: Q and the tile both K-major
 //   softmax: heads are TMEM lanes, keys are columns -> max / exp2 / sum run inside one thread; the
 //            running reference max only moves when a tile exceeds it by 2^8 (lazy rescale of O)
-//   O^T[512 ch x 64 heads] += V^T P^T   4 x tcgen05 M128 N64 K64: the SAME tile read MN-major as A
+//   O^T[512 ch x 64 heads] += V^T P^T   4 x tcgen05 M128 N64 K48: the SAME tile read MN-major as A
 //            (the latent row is both key and value), P written K-major by the head threads
-// The key tile sits in the 128-byte-swizzle layout: 8 blocks of 64 channels, each block = 64 key rows
+// The key tile sits in the 128-byte-swizzle layout: 8 blocks of 64 channels, each block = 48 key rows
 // of 128 bytes with 16-byte chunk c of row r stored at c ^ (r % 8).  Read K-major (rows = keys) it is
 // the B operand of Q K^T; the same bytes read MN-major (64 contiguous channels per key) are the A
-// operand V^T.  Whole 64-key tiles of a dense range arrive with ONE TMA tensor copy each (3-D box
-// {64 channels, 64 keys, 8 blocks} over the cache viewed as [row][block][64], 128-byte swizzle);
+// operand V^T.  Whole tiles of a dense range arrive with ONE TMA tensor copy each (3-D box
+// {64 channels, 48 keys, 8 blocks} over the cache viewed as [row][block][64], 128-byte swizzle);
 // gathered rows and ragged tails go through register-staged vector loads into the same layout.
 //
-// Warp roles (384 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
-// every tcgen05.mma, warps 5-11 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1
-// runs on the tensor pipe while tile i is in the softmax, and the copy of tile i+1 is in flight during
-// both.  All hand-offs are mbarriers with bounded waits.
+// Warp roles (416 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
+// S = Q K^T, warp 12 issues O^T += V^T P^T (each as a converged warp with an elected lane, tc05.cuh),
+// warps 5-11 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1 runs on the tensor
+// pipe while tile i is in the softmax, and the copies of the next tiles are in flight during both.  The
+// copies of the first three dense tiles leave at kernel entry; all warps stage the queries.  All
+// hand-offs are mbarriers with bounded waits, executed by every lane of the waiting warp.
 // HBM-bound by design: 1 KB per key for 128 K flops (128 flop/B), accumulators never leave TMEM.
 #include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime at first use)
 #include <cuda_pipeline_primitives.h>
