@@ -255,3 +255,81 @@ def test_exchange_region_alloc_view_and_free():
     torch.cuda.synchronize()
     assert float(region.as_tensor(0, 4096, torch.uint8).float().sum()) > 0
     hk.peer_region_free(region)
+
+
+def _planted_cache(L, m, seed, plant):
+    """cache ~ N(0, 0.5) with keys planted as scaled copies of one head's query: (position, row, head, gain).
+    A planted key's logit for its head is scale * gain * |q|^2 (about scale * gain * 512), far above
+    the others' (about 0.7 sigma at scale 1/16), so the running maximum of that head jumps when the tile
+    holding the planted key arrives."""
+    inp = synth.mla_inputs(L, m, seed=seed, cache_std=0.5)
+    ckv = synth.f16_bits_to_f32(inp["ckv"]).copy()
+    q = synth.f16_bits_to_f32(inp["q_lat"])
+    for pos, row, head, gain in plant:
+        ckv[pos] = gain * q[row, head]
+    inp["ckv"] = synth.f32_to_f16_bits(ckv)
+    return inp
+
+
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_dense_running_max_jumps_late_in_the_key_range(n_split):
+    """peaked logits: several heads meet their (much larger) maximum many key tiles into the range, one of
+    them twice with growing gains, so the accumulated output is rescaled in flight (jumps of 20+ log2 units)"""
+    L, m = 1500, 2
+    plant = [(700, 0, 3, 0.5), (1203, 0, 3, 1.0), (333, 0, 40, 0.6), (1450, 1, 63, 0.75), (97, 1, 0, 0.4),
+             (610, 1, 17, 0.5)]
+    inp = _planted_cache(L, m, 51, plant)
+    base, lens = np.zeros(m, np.int64), np.full(m, L, np.int32)
+    _, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=base, kv_len=lens)
+    out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_dense_prefill(dev_f16(inp["q_lat"]), dev_f16(inp["ckv"]), out, m, 0, kv_base=dev(base), kv_len=dev(lens),
+                         n_split=n_split, n_keys_hint=L)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    g = synth.f16_bits_to_f32(bits(out))
+    assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
+    # the planted heads are dominated by their planted key: a wrong rescale would show there first
+    for _, row, head, _ in plant:
+        assert max_rel(g[row, head], o32[row, head]) < TOL
+
+
+@pytest.mark.parametrize("n_split", [1, 2])
+def test_sparse_leading_tiles_fully_masked_and_late_maximum(n_split):
+    """a gathered row whose first 100 indices are holes (two whole key tiles contribute nothing, the first live
+    key arrives at tile 2) plus a planted maximum near the end; a second row that is live from the start"""
+    T, m, kidx = 4096, 2, 400
+    plant = [(3000, 0, 7, 0.6), (3001, 0, 50, 0.9), (123, 1, 9, 0.5)]
+    inp = _planted_cache(T, m, 52, plant)
+    r = np.random.RandomState(5)
+    ridx = r.randint(0, T, (m, kidx)).astype(np.int32)
+    ridx[0, :100] = -1
+    ridx[0, 350] = 3000
+    ridx[0, 390] = 3001
+    ridx[1, 200] = 123
+    ridx[1, 5::9] = -1
+    _, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, raw_idx=ridx, kidx=kidx)
+    out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_sparse_decode(dev_f16(inp["q_lat"]), dev_f16(inp["ckv"]), dev(ridx), kidx, out, m, n_split=n_split)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    g = synth.f16_bits_to_f32(bits(out))
+    assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
+    for _, row, head, _ in plant:
+        assert max_rel(g[row, head], o32[row, head]) < TOL
+
+
+def test_dense_large_logit_scale():
+    """cache ~ N(0, 4): logits of 10+ log2 units per sigma, maxima move by more than the lazy-rescale
+    threshold in most tiles"""
+    L, m = 2000, 1
+    inp = synth.mla_inputs(L, m, seed=53, cache_std=4.0)
+    base, lens = np.zeros(m, np.int64), np.full(m, L, np.int32)
+    _, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=base, kv_len=lens)
+    for n_split in (1, 4):
+        out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+        hk.mla_dense_prefill(dev_f16(inp["q_lat"]), dev_f16(inp["ckv"]), out, m, 0, kv_base=dev(base), kv_len=dev(lens),
+                             n_split=n_split, n_keys_hint=L)
+        torch.cuda.synchronize()
+        assert hk.read_device_status() == 0
+        g = synth.f16_bits_to_f32(bits(out))
+        assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
