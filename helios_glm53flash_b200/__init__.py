@@ -29,6 +29,7 @@ SIGNATURES = {
     "hk_abi_version": (_i, []),
     "hk_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
+    "hk_kda_chunked_set_form": (_i, [_i]),
     "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
     "hk_kda_chunked_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "hk_kda_chunked_prefill_gated": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
@@ -172,6 +173,11 @@ def cuda_recurrent_gated_delta_rule(mixed_qkv, g, beta, recurrent_state, core_at
           v_head_dim, history_stride, _ptr(slots), int(bool(channelwise)), int(bool(history)),
           _stream(stream))
     return "recurrent"
+
+
+def kda_chunked_set_form(form):
+    """0: automatic choice between the fused persistent launch and the two-kernel form; 1: always two kernels"""
+    _call("hk_kda_chunked_set_form", int(form))
 
 
 def kda_chunked_workspace_bytes(bsz, seqlen, num_heads):

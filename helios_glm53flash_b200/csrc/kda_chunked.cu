@@ -84,12 +84,12 @@ constexpr uint32_t P1_TOT = P1_DD + 3072;                // f32 [4][128] log-dec
 constexpr uint32_t P1_SMEM = P1_TOT + 2048;
 static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_LDH * 2 == KC * P1_LDA * 4, "aliases");
 
-// Optional stage timeline (compile with -DHK_KDA_TRACE): one CTA in the middle of the grid stamps clock64
-// at its stage boundaries; hk_debug_kda_trace copies the stamps to the host.
-#ifdef HK_KDA_TRACE
+// Optional stage timeline (diagnostic build, -DHK_DIAG): one preparation worker and one scan CTA stamp clock64 at
+// their stage boundaries; hk_debug_kda_trace copies the stamps to the host.
+#ifdef HK_DIAG
 __device__ long long hk_kda_trace[64];
-#define KT_TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.y == 200 && blockIdx.x == 3) hk_kda_trace[slot] = clock64(); } while (0)
-#define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 3 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
+#define KT_TRACE(slot) do { if (ctx.trace && ctx.tid == 0) hk_kda_trace[slot] = clock64(); } while (0)
+#define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #else
 #define KT_TRACE(slot) do { } while (0)
 #define KS_TRACE(slot, ch) do { } while (0)
@@ -201,17 +201,38 @@ __device__ __forceinline__ void prep_ab_block(const int ib, const float (&v)[2][
   }
 }
 
+// What one preparation worker (256 threads) needs besides the tensors: its shared memory, its completion barrier
+// for the tensor-core product, its 256 TMEM columns and how it synchronises.  SUB = false: the worker is a whole
+// CTA (__syncthreads); SUB = true: it is one half of a 512-thread CTA and uses the named barrier `bar_id`.
+struct PrepCtx {
+  uint8_t* smem;
+  uint64_t* bar;
+  uint32_t bar_parity;
+  volatile int* abort_flag;
+  uint32_t tmem;
+  int tid;
+  int bar_id;
+  bool trace;
+};
+template <bool SUB>
+__device__ __forceinline__ void prep_sync(const PrepCtx& ctx) {
+  if (SUB) asm volatile("bar.sync %0, 256;" ::"r"(ctx.bar_id) : "memory");
+  else __syncthreads();
+}
+
+// One (batch, head, chunk) unit of the preparation.
 // GATED: `g` holds the raw gate projection f and `beta_in` the raw fp32 b; the kernel applies
 //   g = lower_bound * sigmoid(exp(a_log[head]) * (f + dt_bias[head][channel])),  beta = bf16(sigmoid(b))
 // itself (the arithmetic of the reference's separate gate kernel, src/engine/glue2.cu:347-360), so the
 // fp32 gate tensor is never written to or read back from memory.
-template <bool GATED>
-__global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
-    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
-    const void* __restrict__ beta_in, uint8_t* __restrict__ ws, int seqlen, int H,
-    int n_chunks, int prefetch_dist, int* __restrict__ status, const float* __restrict__ dt_bias,
-    const float* __restrict__ a_log, float lower_bound) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// (pf_head, pf_chunk): a unit whose input rows this worker asks the copy engine to pull into L2 (pf_chunk < 0: none).
+template <bool GATED, bool SUB>
+__device__ __forceinline__ void prep_unit(
+    const PrepCtx& ctx, const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
+    const void* __restrict__ beta_in, uint8_t* __restrict__ unit, int seqlen, int H, int head, int chunk, int b,
+    int pf_head, int pf_chunk, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+    float lower_bound) {
+  uint8_t* smem = ctx.smem;
   float* sG = reinterpret_cast<float*>(smem + P1_G);
   uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
   float* sA = reinterpret_cast<float*>(smem + P1_A);
@@ -224,43 +245,24 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   uint8_t* sKV = smem + P1_KP;                             // [K+ | V]; the V half aliases sG, valid after the A/B stage
   float* sX = reinterpret_cast<float*>(smem + P1_KR);      // alias, valid after the A/B stage
   uint8_t* sT = smem + P1_L;                               // alias, valid after the A/B stage
-  __shared__ uint64_t bar;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // heads are the fastest grid dimension: CTAs that run together read the same tokens, i.e. whole
-  // contiguous rows of the activations
-  const int head = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
+  const int tid = ctx.tid, lane = tid & 31, warp = tid >> 5;
   const int t0 = chunk * KC;
   const int n_valid = min(KC, seqlen - t0);
   const size_t row = (size_t)3 * H * KD;
   const __nv_bfloat16* tok0 = qkv + ((size_t)b * seqlen + t0) * row;
   const float* g0 = g + (((size_t)b * seqlen + t0) * H + head) * KD;
-  // units are chunk-major: the CTAs that run together (same chunks, all heads) touch adjacent units, in
-  // this kernel and in the scan, so their traffic spreads over all memory channels
-  uint8_t* unit = ws + (((size_t)b * n_chunks + chunk) * H + head) * U_BYTES;
-
-  if (tid == 0) {
-    tc::mbar_init(&bar, 1);
-    tc::mbar_fence_init();
-    abort_flag = 0;
-  }
-  if (warp == 0) tc::tmem_alloc(&tmem_slot, 256);
 
   KT_TRACE(0);
-  // L2 prefetch for the CTA that will run `prefetch_dist` blocks later (about one wave ahead: blocks are
-  // scheduled in linear order, heads fastest): its q, k, v rows (256 B each) and g rows (512 B), one
-  // request per thread.  This CTA's own loads below then mostly hit L2.
+  // L2 prefetch of the input rows of a later unit (about one wave of workers ahead): its q, k, v rows (256 B each)
+  // and g rows (512 B), one request per thread.  That unit's own loads then mostly hit L2.
   {
-    const long long lin = (long long)blockIdx.y * H + blockIdx.x + prefetch_dist;
-    const int phead = (int)(lin % H), pchunk = (int)(lin / H);
-    const int pt = pchunk * KC + (tid & 63);
-    if (prefetch_dist > 0 && pchunk < n_chunks && pt < seqlen) {
+    const int pt = pf_chunk * KC + (tid & 63);
+    if (pf_chunk >= 0 && pt < seqlen) {
       const __nv_bfloat16* ptok = qkv + ((size_t)b * seqlen + pt) * row;
       const int part = tid >> 6;                          // 0: q, 1: k, 2: v, 3: g
-      if (part < 3) tc::prefetch_l2(ptok + (size_t)(part * H + phead) * KD, KD * 2);
-      else tc::prefetch_l2(g + (((size_t)b * seqlen + pt) * H + phead) * KD, KD * 4);
+      if (part < 3) tc::prefetch_l2(ptok + (size_t)(part * H + pf_head) * KD, KD * 2);
+      else tc::prefetch_l2(g + (((size_t)b * seqlen + pt) * H + pf_head) * KD, KD * 4);
     }
   }
   // ---- stage 1: loads.  Ownership for stages 1-4 is the TF32 MMA fragment layout, so that the left
@@ -364,7 +366,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       }
     }
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
 
   KT_TRACE(2);
   // ---- stage 2: log-decay sums per channel.  x_t = inclusive sum INSIDE the 16-token block (in place
@@ -383,7 +385,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     sTot[b0 * KD + c] = a0;
     sTot[(b0 + 1) * KD + c] = a1;
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   if (tid < KD) {
     const float t0s = sTot[tid], t1s = sTot[KD + tid], t2s = sTot[2 * KD + tid], t3s = sTot[3 * KD + tid];
     const float P1v = t0s, P2v = P1v + t1s, P3v = P2v + t2s, GL = P3v + t3s;
@@ -395,7 +397,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     sDD[3 * KD + tid] = __expf(t0s + t1s + t2s); sDD[4 * KD + tid] = __expf(t1s + t2s); sDD[5 * KD + tid] = __expf(t2s);
     reinterpret_cast<float*>(unit + U_DEC)[tid] = __expf(GL);
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
 
   KT_TRACE(3);
   // ---- stage 3 (two phases; k and q warps swap jobs so that x is read before it is overwritten) ----
@@ -429,7 +431,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       }
     }
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   KT_TRACE(4);
   // phase B: k warps turn x into the RIGHT operand R[s][c] = k^_s e^{-x_s} (in place, fp32: up to e^85)
   //          and scale their own rows by e^{x}; q warps emit Q+ = q^ e^{G_t} (fp16 tile rows 64..127)
@@ -460,7 +462,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       }
     }
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
 
   KT_TRACE(5);
   // ---- stage 4: A and B on the warp-level tensor cores (TF32).  Every warp multiplies its own 16
@@ -485,7 +487,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     }
   }
   __pipeline_wait_prior(0);                                 // v rows
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   KT_TRACE(6);
   // from here on sG, sKr and sL are dead: the V half of sKV, sX and sT take their place
 
@@ -502,7 +504,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     *reinterpret_cast<uint4*>(sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
   }
   for (int i = tid; i < KC * P1_LDA; i += 256) sX[i] = 0.f;
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   KT_TRACE(7);
   // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
   if (warp < 4 && lane < 16) {
@@ -522,7 +524,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
 #pragma unroll
     for (int r = 0; r < 16; r++) sX[(ib * 16 + r) * P1_LDA + ib * 16 + lane] = x[r];
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   KT_TRACE(8);
   // 5b: off-diagonal blocks.  M_im = X_ii N_im for the six pairs i > m (kept in the unused mirror block
   //     (m, i) of sA), then by distance d = i - j: X_ij = - sum_{m=j}^{i-1} M_im X_mj.  One warp per
@@ -533,7 +535,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     block16_mma(sX + (i * 16) * P1_LDA + i * 16, sA + (i * 16) * P1_LDA + m * 16, acc, lane);
     block16_store(sA + (m * 16) * P1_LDA + i * 16, acc, 1.f, lane);
   }
-  __syncthreads();
+  prep_sync<SUB>(ctx);
 #pragma unroll 1
   for (int d = 1; d < 4; d++) {
     if (warp < 4 - d) {
@@ -543,7 +545,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
         block16_mma(sA + (m * 16) * P1_LDA + i * 16, sX + (m * 16) * P1_LDA + j * 16, acc, lane);
       block16_store(sX + (i * 16) * P1_LDA + j * 16, acc, -1.f, lane);
     }
-    __syncthreads();
+    prep_sync<SUB>(ctx);
   }
   KT_TRACE(9);
   // 5c: T = fp16(X) as the K-major A operand (K = 64): lanes = 8 rows x 4 chunks.  Rows 64..127 of the
@@ -559,12 +561,12 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   tc::fence_after_sync();
 
   KT_TRACE(10);
   // ---- stage 6: [W | Uloc] = T [K+ | V] : tcgen05 M128 N256 K64, fp16 in, fp32 TMEM accumulators ----
-  const uint32_t tmem = tmem_slot;
+  const uint32_t tmem = ctx.tmem;
   if (tid == 0) {
     const uint32_t idesc = tc::make_idesc(128, 256, tc::FMT_F16, tc::FMT_F16, false, true);
     const uint32_t a_addr = tc::smem_u32(sT), b_addr = tc::smem_u32(sKV);
@@ -574,13 +576,13 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
       const uint64_t bd = tc::make_sdesc(b_addr + kk * 2 * 128, 128, 1024);
       tc::mma_f16(tmem, ad, bd, idesc, kk > 0);
     }
-    tc::mma_commit(&bar);
+    tc::mma_commit(ctx.bar);
   }
   // one warp polls the barrier (with a back-off); the others park at the block barrier instead of spending
   // issue slots that the other CTA of this SM can use
-  if (warp == 0) tc::mbar_wait<64>(&bar, 0, &abort_flag, 1);
-  __syncthreads();
-  const bool ok = abort_flag == 0;
+  if (warp == 0) tc::mbar_wait<64>(ctx.bar, ctx.bar_parity, ctx.abort_flag, 1);
+  prep_sync<SUB>(ctx);
+  const bool ok = *ctx.abort_flag == 0;
   tc::fence_after_sync();
   KT_TRACE(11);
   // ---- stage 7: epilogue. Lanes 0-63 are the tokens; warps 0,1 take W, warps 4,5 take Uloc ----
@@ -613,9 +615,43 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
     }
   }
   tc::fence_before_sync();
-  __syncthreads();
+  prep_sync<SUB>(ctx);
   KT_TRACE(12);
-  if (warp == 0) tc::tmem_dealloc(tmem, 256);
+}
+
+template <bool GATED>
+__global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g,
+    const void* __restrict__ beta_in, uint8_t* __restrict__ ws, int seqlen, int H,
+    int n_chunks, int prefetch_dist, int* __restrict__ status, const float* __restrict__ dt_bias,
+    const float* __restrict__ a_log, float lower_bound) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x;
+  // heads are the fastest grid dimension: CTAs that run together read the same tokens, i.e. whole
+  // contiguous rows of the activations
+  const int head = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
+  // units are chunk-major: the CTAs that run together (same chunks, all heads) touch adjacent units, in
+  // this kernel and in the scan, so their traffic spreads over all memory channels
+  uint8_t* unit = ws + (((size_t)b * n_chunks + chunk) * H + head) * U_BYTES;
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (tid < 32) tc::tmem_alloc(&tmem_slot, 256);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // the CTA that runs `prefetch_dist` blocks later (blocks are scheduled in linear order, heads fastest)
+  const long long lin = (long long)blockIdx.y * H + blockIdx.x + prefetch_dist;
+  const int pchunk = (int)(lin / H);
+  PrepCtx ctx{smem, &bar, 0u, &abort_flag, tmem_slot, tid, 0, false};
+  prep_unit<GATED, false>(ctx, qkv, g, beta_in, unit, seqlen, H, head, chunk, b, (int)(lin % H),
+                          (prefetch_dist > 0 && pchunk < n_chunks) ? pchunk : -1, dt_bias, a_log, lower_bound);
+  if (tid < 32) tc::tmem_dealloc(tmem_slot, 256);
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
 
@@ -866,16 +902,398 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
   if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
 }
 
+
+// =================================================================================================
+// fused form: preparation and scan in ONE persistent launch, for calls with few (batch, head) chains
+//
+// One CTA of 512 threads per SM.  The first n_jobs CTAs each walk the chunks of one (batch, head) chain: the whole
+// 128-column state of the head, sixteen warps = four TMEM lane quarters x four 32-column blocks.  Every other CTA
+// hosts two preparation workers of 256 threads (its two halves, each with its own shared memory, TMEM columns and
+// named barrier), which take the units (chunk-major) round robin.  A unit travels through a ring of KR chunk slots
+// per chain in global memory - a few tens of MB that stay in L2 - instead of a per-chunk workspace in HBM:
+//   ready[job][slot]  = chunk + 1 once the unit of that chunk is complete (release store after the worker's writes),
+//   consumed[job]     = number of chunks whose unit has landed in the chain CTA's shared memory (the slot of chunk c
+//                       may be rewritten once consumed > c).
+// A worker that finds its slot still occupied, and a chain CTA that finds its unit not yet written, poll with a
+// bound (about a second); on expiry they record HK_ERR_TIMEOUT, raise the launch-wide abort word and finish without
+// waiting again.  All CTAs must be resident at once: the launch is cooperative and sized to the SM count.
+// =================================================================================================
+constexpr int KR = 16;                                    // ring slots (chunks) per chain
+constexpr int F_NSTAGE = 2;                               // the ring protocol of the chain CTA is written for two stages
+constexpr uint32_t F_WQ = 0;                              // 32768
+constexpr uint32_t F_BB = 32768;                          // 16384: rows 0-63 zero (never overwritten), rows 64-127 = B beta
+constexpr uint32_t F_KT = 49152;                          // 16384
+constexpr uint32_t F_UL = 65536;                          // 16384: Uloc as [4 column blocks][64 tokens][32]
+constexpr uint32_t F_DEC = 81920;                         // 512
+constexpr uint32_t F_STAGE = 82432;
+constexpr uint32_t F_S = F_NSTAGE * F_STAGE;              // fp16 B operand: state [128 k][128 v], MN-major, 32 KB
+constexpr uint32_t F_U = F_S + 32768;                     // fp16 B operand: U [64 tokens][128 v], MN-major, 16 KB
+constexpr uint32_t F_SMEM_SCAN = F_U + 16384;
+constexpr uint32_t F_SMEM = F_SMEM_SCAN > 2 * P1_SMEM ? F_SMEM_SCAN : 2 * P1_SMEM;
+static_assert(U_KT + 16384 == U_UL && U_UL + 16384 == U_DEC && F_KT + 16384 == F_UL && F_UL + 16384 == F_DEC,
+              "Kt^T, Uloc and the decay row travel as one copy");
+constexpr int F_FLAG_INTS = 16;                           // [0] launch-wide abort word; the flag arrays follow
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// orders this thread's generic-proxy accesses with its async-proxy accesses (bulk copies) in every state space
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded poll of a flag in global memory until it is at least `want`.  Returns false once the CTA has given up
+// (this wait or an earlier one) or another CTA has raised the launch-wide abort word.
+__device__ __forceinline__ bool poll_flag_ge(const int* flag, int want, volatile int* abort_flag, int* g_abort, int code) {
+  if (ld_acquire_gpu(flag) >= want) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (*abort_flag) return false;
+    if (ld_acquire_gpu(flag) >= want) return true;
+    __nanosleep(64);
+    if (ld_relaxed_gpu(g_abort) != 0 || clock64() - t0 > tc::MBAR_WAIT_CYCLES) {
+      *abort_flag = code;
+      atomicExch(g_abort, code);
+      return false;
+    }
+  }
+}
+
+template <bool GATED>
+__global__ __launch_bounds__(512, 1) void kda_fused_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g, const void* __restrict__ beta_in,
+    uint8_t* __restrict__ ring, int* __restrict__ flags, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ out_f32, int seqlen, int H, int n_chunks, int n_jobs, const int* __restrict__ slots, float scale,
+    int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t full_bar[F_NSTAGE];
+  __shared__ uint64_t mma_bar;       // scan: state-path contractions; preparation worker 0: its product
+  __shared__ uint64_t out_bar;       // scan: output contraction;      preparation worker 1: its product
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  int* g_abort = flags;
+  int* ready = flags + F_FLAG_INTS;                        // [n_jobs][KR]
+  int* consumed = ready + (size_t)n_jobs * KR;             // [n_jobs]
+
+  if (tid == 0) {
+    for (int i = 0; i < F_NSTAGE; i++) tc::mbar_init(&full_bar[i], 1);
+    tc::mbar_init(&mma_bar, 1);
+    tc::mbar_init(&out_bar, 1);
+    tc::mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 512);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if ((int)blockIdx.x >= n_jobs) {
+    // =========================== two preparation workers ===========================
+    const int sub = warp >> 3;
+    const int worker = ((int)blockIdx.x - n_jobs) * 2 + sub, n_workers = ((int)gridDim.x - n_jobs) * 2;
+    const long long n_units = (long long)n_chunks * n_jobs;
+    PrepCtx ctx{smem + sub * P1_SMEM, sub ? &out_bar : &mma_bar, 0u, &abort_flag, tmem + sub * 256, tid & 255, 1 + sub, false};
+#ifdef HK_DIAG
+    ctx.trace = false;
+#endif
+    int it = 0;
+    for (long long u = worker; u < n_units; u += n_workers, it++) {
+      const int chunk = (int)(u / n_jobs), job = (int)(u % n_jobs);
+      const int b = job / H, head = job % H;
+      // the slot of this chunk must have been drained by the chain CTA (it held chunk - KR)
+      if (chunk >= KR) {
+        if (ctx.tid == 0) poll_flag_ge(consumed + job, chunk - KR + 1, &abort_flag, g_abort, 20);
+        prep_sync<true>(ctx);
+      }
+      uint8_t* unit = ring + ((size_t)(chunk % KR) * n_jobs + job) * U_BYTES;
+      const long long pu = u + n_workers;
+      int pf_head = 0, pf_chunk = -1;
+      if (pu < n_units && (int)(pu % n_jobs) / H == b) { pf_chunk = (int)(pu / n_jobs); pf_head = (int)(pu % n_jobs) % H; }
+      ctx.bar_parity = it & 1;
+#ifdef HK_DIAG
+      ctx.trace = (worker == 7 && it == 20);
+#endif
+      prep_unit<GATED, true>(ctx, qkv, g, beta_in, unit, seqlen, H, head, chunk, b, pf_head, pf_chunk, dt_bias, a_log, lower_bound);
+      // publish: every thread's writes of this unit, then the flag
+      __threadfence();
+      fence_proxy_async_all();
+      prep_sync<true>(ctx);
+      if (ctx.tid == 0) st_release_gpu(ready + (size_t)job * KR + (chunk % KR), chunk + 1);
+    }
+  } else {
+    // =========================== one (batch, head) chain ===========================
+    const int job = blockIdx.x, b = job / H, head = job % H;
+    const int lq = warp & 3, cb = warp >> 2;               // TMEM lane quarter, 32-column block
+    const int rowi = lq * 32 + (tid & 31);                       // k row of the state / token row of W S0 / output row - 64
+    const int v0 = cb * KNV;
+    const int slot = slots ? slots[b] : b;
+    float* st = state + ((size_t)slot * H + head) * KD * KD + (size_t)rowi * KD + v0;
+    const int* my_ready = ready + (size_t)job * KR;
+
+    for (int i = tid; i < 8192 / 16; i += 512)
+      for (int s_i = 0; s_i < F_NSTAGE; s_i++) reinterpret_cast<uint4*>(smem + s_i * F_STAGE + F_BB)[i] = make_uint4(0, 0, 0, 0);
+    float S[KNV];
+#pragma unroll
+    for (int u = 0; u < KNV / 4; u++) {
+      const float4 v = *reinterpret_cast<const float4*>(st + u * 4);
+      S[4 * u] = v.x; S[4 * u + 1] = v.y; S[4 * u + 2] = v.z; S[4 * u + 3] = v.w;
+    }
+    // B operand, MN-major, N = 128: off(k, n) = (n/8)*2048 + (k/8)*128 + (k%8)*16 + (n%8)*2
+    uint8_t* sS_row = smem + F_S + (4 * cb) * 2048 + (rowi >> 3) * 128 + (rowi & 7) * 16;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      uint4 p;
+      p.x = pack_h2(S[8 * u], S[8 * u + 1]); p.y = pack_h2(S[8 * u + 2], S[8 * u + 3]);
+      p.z = pack_h2(S[8 * u + 4], S[8 * u + 5]); p.w = pack_h2(S[8 * u + 6], S[8 * u + 7]);
+      *reinterpret_cast<uint4*>(sS_row + u * 2048) = p;
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t d2 = tmem + 256;                        // D1 alternates between columns 0-127 and 128-255
+
+    // the producer thread (a lane of the last warp, which is never on the token-row path) owns the ring protocol
+    const bool producer = tid == 480;
+    int issued = 0;                                        // producer only: chunks whose copies have been issued
+    auto issue_loads = [&](int chunk) {
+      uint8_t* stg = smem + (chunk % F_NSTAGE) * F_STAGE;
+      const uint8_t* u = ring + ((size_t)(chunk % KR) * n_jobs + job) * U_BYTES;
+      uint64_t* bar = &full_bar[chunk % F_NSTAGE];
+      fence_proxy_async_all();
+      tc::mbar_arrive_expect_tx(bar, U_BYTES);
+      tc::bulk_g2s(stg + F_WQ, u + U_WQ, 32768, bar);
+      tc::bulk_g2s(stg + F_BB + 8192, u + U_BB, 8192, bar);
+      tc::bulk_g2s(stg + F_KT, u + U_KT, 16384 + 16384 + 512, bar);
+    };
+    if (producer) {
+      for (; issued < F_NSTAGE && issued < n_chunks; issued++) {
+        poll_flag_ge(my_ready + (issued % KR), issued + 1, &abort_flag, g_abort, 21);
+        issue_loads(issued);
+      }
+    }
+
+    const uint32_t idesc = tc::make_idesc(128, KD, tc::FMT_F16, tc::FMT_F16, false, true);
+    const uint32_t s_addr = tc::smem_u32(smem + F_S), u_addr = tc::smem_u32(smem + F_U);
+    const bool issue_warp = tc::warp_index_uniform() == 0;
+    const uint32_t leader = issue_warp ? tc::elect_one() : 0u;
+    uint32_t mma_parity = 0, out_parity = 0;
+
+    // output rows of chunk c: TMEM lanes 64-127 of that chunk's D1 range = tokens, lane quarters 2 and 3
+    auto emit_outputs = [&](int c, bool valid) {
+      const int tok = c * KC + (rowi - 64);
+      uint32_t r[32];
+      tc::tmem_ld32(tmem + ((c & 1) ? 128u : 0u) + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
+      tc::tmem_ld_wait();
+      if (tok < seqlen && valid) {
+        const size_t oi = (((size_t)b * seqlen + tok) * H + head) * KD + v0;
+        uint4* o = reinterpret_cast<uint4*>(out + oi);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float a = __uint_as_float(r[8 * u + 2 * e]) * scale, c2 = __uint_as_float(r[8 * u + 2 * e + 1]) * scale;
+            const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rz(a));
+            const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c2));
+            w[e] = lo | (hi << 16);
+          }
+          o[u] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (out_f32) {
+          float4* of = reinterpret_cast<float4*>(out_f32 + oi);
+#pragma unroll
+          for (int u = 0; u < 8; u++)
+            of[u] = make_float4(__uint_as_float(r[4 * u]) * scale, __uint_as_float(r[4 * u + 1]) * scale,
+                                __uint_as_float(r[4 * u + 2]) * scale, __uint_as_float(r[4 * u + 3]) * scale);
+        }
+      }
+    };
+    bool prev_ok = true;
+
+    for (int chunk = 0; chunk < n_chunks; chunk++) {
+      const int sidx = chunk % F_NSTAGE;
+      uint8_t* stg = smem + sidx * F_STAGE;
+      const uint32_t stg_addr = tc::smem_u32(stg);
+      const uint32_t d1 = tmem + ((chunk & 1) ? 128u : 0u);
+      int next_flag = 0;
+      if (producer && issued <= chunk) {                   // the earlier attempts found the unit not written yet
+        poll_flag_ge(my_ready + (chunk % KR), chunk + 1, &abort_flag, g_abort, 22);
+        issue_loads(chunk);
+        issued = chunk + 1;
+      }
+      KS_TRACE(0, chunk);
+      bool ok = tc::mbar_wait(&full_bar[sidx], (chunk / F_NSTAGE) & 1, &abort_flag, 2);
+      KS_TRACE(1, chunk);
+      if (producer) {
+        st_release_gpu(consumed + job, chunk + 1);         // this chunk's slot may be rewritten
+        // catch-up: the other stage is free while the next chunk's copies have not been issued
+        if (issued == chunk + 1 && chunk + 1 < n_chunks && ld_acquire_gpu(my_ready + ((chunk + 1) % KR)) >= chunk + 2) {
+          issue_loads(chunk + 1);
+          issued = chunk + 2;
+        }
+        // sampled now, used when this chunk's stage is released at the end of the iteration
+        if (issued == chunk + 2 && chunk + 2 < n_chunks) next_flag = ld_relaxed_gpu(my_ready + ((chunk + 2) % KR));
+      }
+      // ---- [W ; Q+] S0 -> D1 (128 x 128) ----
+      if (issue_warp) {
+#pragma unroll
+        for (int kk = 0; kk < KD / 16; kk++) {
+          const uint64_t ad = tc::make_sdesc(stg_addr + F_WQ + kk * 2 * LBO, LBO, SBO_K128);
+          const uint64_t bd = tc::make_sdesc(s_addr + kk * 2 * 128, 128, 2048);
+          tc::mma_f16_if(leader, d1, ad, bd, idesc, kk > 0);
+        }
+        tc::mma_commit_if(leader, &mma_bar);
+      }
+      // the previous chunk's output rows leave while this chunk's first contraction runs (off the chain)
+      if (lq >= 2 && chunk > 0) emit_outputs(chunk - 1, prev_ok);
+      ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 3) && ok;
+      mma_parity ^= 1;
+      tc::fence_after_sync();
+      KS_TRACE(2, chunk);
+      // ---- U = Uloc - W S0 (token rows = TMEM lanes 0-63) ----
+      if (lq < 2) {
+        const int t = rowi;
+        uint32_t r[32];
+        tc::tmem_ld32(d1 + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
+        tc::tmem_ld_wait();
+        const uint4* ul = reinterpret_cast<const uint4*>(stg + F_UL + cb * (KC * KNV * 2) + t * (KNV * 2));
+        uint8_t* urow = smem + F_U + (4 * cb) * 1024 + (t >> 3) * 128 + (t & 7) * 16;   // off(k=t, n) = (n/8)*1024 + ...
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const uint4 lv = ul[u];
+          const __half2* lh = reinterpret_cast<const __half2*>(&lv);
+          float uu[8];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float2 f = __half22float2(lh[e]);
+            uu[2 * e] = f.x - __uint_as_float(r[8 * u + 2 * e]);
+            uu[2 * e + 1] = f.y - __uint_as_float(r[8 * u + 2 * e + 1]);
+          }
+          uint4 p;
+          p.x = pack_h2(uu[0], uu[1]); p.y = pack_h2(uu[2], uu[3]); p.z = pack_h2(uu[4], uu[5]); p.w = pack_h2(uu[6], uu[7]);
+          *reinterpret_cast<uint4*>(urow + u * 1024) = p;
+        }
+      }
+      tc::fence_async_smem();
+      tc::fence_before_sync();
+      __syncthreads();
+      tc::fence_after_sync();
+      KS_TRACE(3, chunk);
+      // ---- D2 = Kt^T U (state path, committed first) ;  D1 rows 64-127 += (B beta) U (outputs, own barrier) ----
+      if (issue_warp) {
+#pragma unroll
+        for (int kk = 0; kk < KC / 16; kk++) {
+          const uint64_t ad = tc::make_sdesc(stg_addr + F_KT + kk * 2 * LBO, LBO, SBO_K64);
+          const uint64_t bd = tc::make_sdesc(u_addr + kk * 2 * 128, 128, 1024);
+          tc::mma_f16_if(leader, d2, ad, bd, idesc, kk > 0);
+        }
+        tc::mma_commit_if(leader, &mma_bar);
+#pragma unroll
+        for (int kk = 0; kk < KC / 16; kk++) {
+          const uint64_t ad = tc::make_sdesc(stg_addr + F_BB + kk * 2 * LBO, LBO, SBO_K64);
+          const uint64_t bd = tc::make_sdesc(u_addr + kk * 2 * 128, 128, 1024);
+          tc::mma_f16_if(leader, d1, ad, bd, idesc, true);
+        }
+        tc::mma_commit_if(leader, &out_bar);
+      }
+      ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 4) && ok;
+      mma_parity ^= 1;
+      tc::fence_after_sync();
+      KS_TRACE(4, chunk);
+      // ---- state: S <- S e^{G_last} + Kt^T U (lane = k row), refresh the fp16 operand copy ----
+      {
+        uint32_t r[32];
+        tc::tmem_ld32(d2 + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
+        tc::tmem_ld_wait();
+        const float dec = reinterpret_cast<const float*>(stg + F_DEC)[rowi];
+#pragma unroll
+        for (int j = 0; j < KNV; j++) S[j] = fmaf(S[j], dec, __uint_as_float(r[j]));
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          uint4 p;
+          p.x = pack_h2(S[8 * u], S[8 * u + 1]); p.y = pack_h2(S[8 * u + 2], S[8 * u + 3]);
+          p.z = pack_h2(S[8 * u + 4], S[8 * u + 5]); p.w = pack_h2(S[8 * u + 6], S[8 * u + 7]);
+          *reinterpret_cast<uint4*>(sS_row + u * 2048) = p;
+        }
+      }
+      KS_TRACE(5, chunk);
+      // the output contraction must be complete before the block barrier: the stage and the U tile it reads are
+      // rewritten after it; the rows themselves are read in the next iteration
+      if (lq >= 2) {
+        ok = tc::mbar_wait(&out_bar, out_parity, &abort_flag, 5) && ok;
+        prev_ok = ok;
+      }
+      out_parity ^= 1;
+      tc::fence_async_smem();
+      tc::fence_before_sync();
+      __syncthreads();
+      tc::fence_after_sync();
+      KS_TRACE(6, chunk);
+      // refill of this stage, if the unit two chunks ahead was already complete when its flag was sampled
+      if (producer && issued == chunk + 2 && chunk + 2 < n_chunks && next_flag >= chunk + 3) {
+        __threadfence();                                   // acquire side of the flag that was read relaxed
+        issue_loads(chunk + 2);
+        issued = chunk + 3;
+      }
+    }
+    if (lq >= 2 && n_chunks > 0) emit_outputs(n_chunks - 1, prev_ok);
+    if (!abort_flag) {
+#pragma unroll
+      for (int u = 0; u < KNV / 4; u++)
+        *reinterpret_cast<float4*>(st + u * 4) = make_float4(S[4 * u], S[4 * u + 1], S[4 * u + 2], S[4 * u + 3]);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 512);
+  if (tid == 0 && abort_flag && status) atomicExch(status, HK_ERR_TIMEOUT);
+}
+
 }  // namespace hk
 
-#ifdef HK_KDA_TRACE
+#ifdef HK_DIAG
 extern "C" __attribute__((visibility("default"))) int hk_debug_kda_trace(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, hk::hk_kda_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
 }
 #endif
 
+namespace hk {
+namespace {
+// The fused launch serves calls with few (batch, head) chains: every chain occupies one SM, the rest prepare.
+// hk_kda_chunked_set_form(1) keeps the two-kernel form for every call (cross-check of the two forms in the tests).
+int g_chunked_form = 0;
+bool fused_eligible(int n_jobs) {
+  return g_chunked_form == 0 && n_jobs <= 48 && sm_count() - n_jobs >= 64;
+}
+size_t fused_flag_bytes(int n_jobs) {
+  return (((size_t)F_FLAG_INTS + (size_t)n_jobs * (KR + 1)) * sizeof(int) + 255) / 256 * 256;
+}
+}  // namespace
+}  // namespace hk
+
+HK_API int hk_kda_chunked_set_form(int form) {
+  if (form != 0 && form != 1) return HK_ERR_INVALID;
+  hk::g_chunked_form = form;
+  return HK_OK;
+}
+
 HK_API size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads) {
   if (bsz <= 0 || seqlen <= 0 || num_heads <= 0) return 0;
+  const long long n_jobs = (long long)bsz * num_heads;
+  if (n_jobs <= 48 && hk::fused_eligible((int)n_jobs))
+    return hk::fused_flag_bytes((int)n_jobs) + (size_t)hk::KR * n_jobs * hk::U_BYTES;
   const size_t n_chunks = ((size_t)seqlen + hk::KC - 1) / hk::KC;
   return (size_t)bsz * num_heads * n_chunks * hk::U_BYTES;
 }
@@ -900,12 +1318,44 @@ int chunked_prefill_launch(const void* mixed_qkv, const float* g_or_f, const voi
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(kda_chunk_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P1_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(kda_chunk_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P1_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM) != cudaSuccess)
+        cudaFuncSetAttribute(kda_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(kda_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(kda_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM) != cudaSuccess)
       return HK_ERR_CUDA;
     attr_set[dev] = true;
   }
   cudaStream_t s = as_stream(stream);
   int* st = device_status_ptr();
+  if ((long long)bsz * num_heads <= 48 && fused_eligible(bsz * num_heads)) {
+    // one cooperative launch: chains on the first n_jobs CTAs, preparation workers on all others
+    const int n_jobs = bsz * num_heads;
+    const size_t flag_bytes = fused_flag_bytes(n_jobs);
+    if (cudaMemsetAsync(workspace, 0, flag_bytes, s) != cudaSuccess) return HK_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count());
+    cfg.blockDim = dim3(512);
+    cfg.dynamicSmemBytes = F_SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const __nv_bfloat16* a_qkv = (const __nv_bfloat16*)mixed_qkv;
+    uint8_t* a_ring = (uint8_t*)workspace + flag_bytes;
+    int* a_flags = (int*)workspace;
+    __nv_bfloat16* a_out = (__nv_bfloat16*)out;
+    const float a_scale = 1.0f / sqrtf((float)KD);
+    const float* a_dt = gated ? dt_bias : nullptr;
+    const float* a_al = gated ? a_log : nullptr;
+    const float a_lb = gated ? lower_bound : 0.f;
+    cudaError_t e = gated
+        ? cudaLaunchKernelEx(&cfg, kda_fused_kernel<true>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
+                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb)
+        : cudaLaunchKernelEx(&cfg, kda_fused_kernel<false>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
+                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb);
+    return e == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+  }
   const dim3 grid(num_heads, n_chunks, bsz);
   if (gated)
     kda_chunk_prep_kernel<true><<<grid, 256, P1_SMEM, s>>>((const __nv_bfloat16*)mixed_qkv, g_or_f, beta_or_b,

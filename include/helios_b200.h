@@ -73,7 +73,14 @@ int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* beta, fl
  * kernel: prefill calls the recurrence with seqlen = n, src/engine/runner.cpp:468-471).
  * Requires dk = dv = 128, Hk == Hv.  seqlen may be any positive length (a ragged tail shorter
  * than a chunk is processed by the same kernels).  `workspace` must hold at least
- * hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads) bytes, 256-byte aligned.             */
+ * hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads) bytes, 256-byte aligned.
+ * Two forms.  Calls with at most 48 (batch, head) chains run as ONE persistent cooperative launch: a chain
+ * per SM, the other SMs prepare the chunks and hand them over through a ring of 16 chunk slots per chain
+ * (workspace = bsz * num_heads * 16 * 74,240 B + flags, independent of seqlen; it stays in L2).  Larger
+ * calls run as two kernels with one 74,240-byte workspace unit per (batch, head, chunk).
+ * hk_kda_chunked_set_form(1) selects the two-kernel form for every later call and workspace query of this
+ * process, hk_kda_chunked_set_form(0) the automatic choice (default).                              */
+int hk_kda_chunked_set_form(int form);
 size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads);
 int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* beta, float* state,
                            void* out, float* out_f32, int bsz, int seqlen, int num_heads,

@@ -218,3 +218,43 @@ def test_chunked_batch_and_slots():
                                               out_f32=o32) == "chunked"
     torch.cuda.synchronize()
     assert max_rel(o32.cpu().numpy(), o_32) < 2e-3 and frob_rel(st.cpu().numpy(), o_st) < 1e-2
+
+
+@pytest.mark.parametrize("T,H,bsz", [(2100, 3, 1), (1500, 2, 2), (4096, 32, 1)])
+def test_chunked_fused_launch_equals_two_kernel_form(T, H, bsz):
+    """the persistent fused launch (chains + preparation workers through the L2 ring; T spans more chunks than the
+    ring has slots, so slots are reused) against the two-kernel form on the same inputs: same bits; the short
+    cases also against the oracle"""
+    D = 128
+    inp = synth.kda_inputs(T, H, D, bsz=bsz, seed=200 + T)
+    s0 = (0.1 * synth.rng(8).standard_normal((bsz, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    q, g, b = dev_bf16(inp["mixed_qkv"]), dev(inp["g"]), dev_bf16(inp["beta"])
+    res = []
+    try:
+        for form in (1, 0):
+            hk.kda_chunked_set_form(form)
+            st = dev(s0)
+            out = torch.empty(bsz, T, H, D, dtype=torch.bfloat16, device="cuda")
+            o32 = torch.empty(bsz, T, H, D, dtype=torch.float32, device="cuda")
+            ws_bytes = hk.kda_chunked_workspace_bytes(bsz, T, H)
+            assert hk.cuda_recurrent_gated_delta_rule(q, g, b, st, out, bsz, T, H, H, D, D, 1, None, True, False,
+                                                      out_f32=o32) == "chunked"
+            # a second call on the same workspace-sized buffer: the ring flags are reset by every call
+            st2 = dev(s0)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+            for _ in range(2):
+                st2.copy_(dev(s0))
+                hk.cuda_recurrent_gated_delta_rule(q, g, b, st2, out, bsz, T, H, H, D, D, 1, None, True, False,
+                                                   out_f32=o32, workspace=ws)
+            torch.cuda.synchronize()
+            assert hk.read_device_status() == 0
+            assert np.array_equal(st.cpu().numpy(), st2.cpu().numpy())
+            res.append((ws_bytes, o32.cpu().numpy(), st.cpu().numpy(), bits(out)))
+    finally:
+        hk.kda_chunked_set_form(0)
+    assert res[1][0] < res[0][0], "the fused form needs the ring only"
+    assert np.array_equal(res[0][1], res[1][1]) and np.array_equal(res[0][2], res[1][2])
+    assert np.array_equal(res[0][3], res[1][3])
+    if T * H * bsz <= 8192:
+        _, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, bsz, T, H, H, D, D)
+        assert max_rel(res[1][1], o_32) < 2e-3 and frob_rel(res[1][2], o_st) < 1e-2
