@@ -63,6 +63,43 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// ---- flags in global memory (fused form): release / acquire at GPU scope, bounded polls ----
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu(int* p, int v) {
+  asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// orders this thread's generic-proxy accesses with its async-proxy accesses (bulk copies) in every state space
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded poll of a flag in global memory until it is at least `want`.  Returns false once the CTA has given up
+// (this wait or an earlier one) or another CTA has raised the launch-wide abort word.
+__device__ __forceinline__ bool poll_flag_ge(const int* flag, int want, volatile int* abort_flag, int* g_abort, int code) {
+  if (ld_acquire_gpu(flag) >= want) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (*abort_flag) return false;
+    if (ld_acquire_gpu(flag) >= want) return true;
+    __nanosleep(64);
+    if (ld_relaxed_gpu(g_abort) != 0 || clock64() - t0 > tc::MBAR_WAIT_CYCLES) {
+      *abort_flag = code;
+      atomicExch(g_abort, code);
+      return false;
+    }
+  }
+}
+
 // =================================================================================================
 // kernel 1: per-chunk preparation.  256 threads, 104 KB of shared memory: two CTAs per SM, so the
 // serial stages of one chunk overlap with another chunk's.
@@ -90,7 +127,9 @@ static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_
 __device__ long long hk_kda_trace[64];
 #define KT_TRACE(slot) do { if (ctx.trace && ctx.tid == 0) hk_kda_trace[slot] = clock64(); } while (0)
 #define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
+#define KS_TRACE_AT(slot, ch, want) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == (want)) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #else
+#define KS_TRACE_AT(slot, ch, want) do { } while (0)
 #define KT_TRACE(slot) do { } while (0)
 #define KS_TRACE(slot, ch) do { } while (0)
 #endif
@@ -213,6 +252,11 @@ struct PrepCtx {
   int tid;
   int bar_id;
   bool trace;
+  // fused form only: the ring slot this unit is written to must have been drained (flag >= want); thread 0 sampled
+  // the flag at the start of the unit (slot_seen) and polls, with a bound, only if that was too early
+  const int* slot_flag;
+  int slot_want, slot_seen;
+  int* g_abort;
 };
 template <bool SUB>
 __device__ __forceinline__ void prep_sync(const PrepCtx& ctx) {
@@ -314,14 +358,6 @@ __device__ __forceinline__ void prep_unit(
       sBeta[tid] = bv;
     }
     for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
-    // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
-    if (tid < 192) {
-      const int blk = tid >> 5, e = tid & 31;             // 6 blocks x (16 rows x 2 chunks)
-      const int zi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
-      const int zj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
-      const int t = zi * 16 + (e >> 1), sc = zj * 2 + (e & 1);
-      *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
-    }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const int t = 16 * ib + g8 + 8 * h;
@@ -366,9 +402,22 @@ __device__ __forceinline__ void prep_unit(
       }
     }
   }
+  // fused form: the ring slot must have been drained before the first write to the unit (all of them follow)
+  if (SUB && tid == 0 && ctx.slot_seen < ctx.slot_want)
+    poll_flag_ge(ctx.slot_flag, ctx.slot_want, ctx.abort_flag, ctx.g_abort, 20);
   prep_sync<SUB>(ctx);
 
   KT_TRACE(2);
+  {
+  // blocks of B beta above the diagonal are never computed: they are zeros in the workspace tile
+  if (tid < 192) {
+    const int blk = tid >> 5, e = tid & 31;             // 6 blocks x (16 rows x 2 chunks)
+    const int zi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+    const int zj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+    const int t = zi * 16 + (e >> 1), sc = zj * 2 + (e & 1);
+    *reinterpret_cast<uint4*>(unit + U_BB + (t >> 3) * SBO_K64 + sc * LBO + (t & 7) * 16) = make_uint4(0, 0, 0, 0);
+  }
+  }
   // ---- stage 2: log-decay sums per channel.  x_t = inclusive sum INSIDE the 16-token block (in place
   //      over g), block totals, then the per-block tables: e^{P_blk} (P = sum before the block),
   //      G_last - P_blk, the decay between two block starts, and the chunk decay e^{G_last}. ----
@@ -648,7 +697,7 @@ __global__ __launch_bounds__(256, 2) void kda_chunk_prep_kernel(
   // the CTA that runs `prefetch_dist` blocks later (blocks are scheduled in linear order, heads fastest)
   const long long lin = (long long)blockIdx.y * H + blockIdx.x + prefetch_dist;
   const int pchunk = (int)(lin / H);
-  PrepCtx ctx{smem, &bar, 0u, &abort_flag, tmem_slot, tid, 0, false};
+  PrepCtx ctx{smem, &bar, 0u, &abort_flag, tmem_slot, tid, 0, false, nullptr, 0, 0, nullptr};
   prep_unit<GATED, false>(ctx, qkv, g, beta_in, unit, seqlen, H, head, chunk, b, (int)(lin % H),
                           (prefetch_dist > 0 && pchunk < n_chunks) ? pchunk : -1, dt_bias, a_log, lower_bound);
   if (tid < 32) tc::tmem_dealloc(tmem_slot, 256);
@@ -928,44 +977,13 @@ constexpr uint32_t F_DEC = 81920;                         // 512
 constexpr uint32_t F_STAGE = 82432;
 constexpr uint32_t F_S = F_NSTAGE * F_STAGE;              // fp16 B operand: state [128 k][128 v], MN-major, 32 KB
 constexpr uint32_t F_U = F_S + 32768;                     // fp16 B operand: U [64 tokens][128 v], MN-major, 16 KB
-constexpr uint32_t F_SMEM_SCAN = F_U + 16384;
+constexpr uint32_t F_O = F_U + 16384;                     // bf16 output rows of one chunk, [64 tokens][272 B] (256 + 16 pad)
+constexpr uint32_t F_OPITCH = 272;
+constexpr uint32_t F_SMEM_SCAN = F_O + KC * F_OPITCH;
 constexpr uint32_t F_SMEM = F_SMEM_SCAN > 2 * P1_SMEM ? F_SMEM_SCAN : 2 * P1_SMEM;
 static_assert(U_KT + 16384 == U_UL && U_UL + 16384 == U_DEC && F_KT + 16384 == F_UL && F_UL + 16384 == F_DEC,
               "Kt^T, Uloc and the decay row travel as one copy");
 constexpr int F_FLAG_INTS = 16;                           // [0] launch-wide abort word; the flag arrays follow
-
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
-  int v;
-  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// orders this thread's generic-proxy accesses with its async-proxy accesses (bulk copies) in every state space
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// Bounded poll of a flag in global memory until it is at least `want`.  Returns false once the CTA has given up
-// (this wait or an earlier one) or another CTA has raised the launch-wide abort word.
-__device__ __forceinline__ bool poll_flag_ge(const int* flag, int want, volatile int* abort_flag, int* g_abort, int code) {
-  if (ld_acquire_gpu(flag) >= want) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    if (*abort_flag) return false;
-    if (ld_acquire_gpu(flag) >= want) return true;
-    __nanosleep(64);
-    if (ld_relaxed_gpu(g_abort) != 0 || clock64() - t0 > tc::MBAR_WAIT_CYCLES) {
-      *abort_flag = code;
-      atomicExch(g_abort, code);
-      return false;
-    }
-  }
-}
 
 template <bool GATED>
 __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
@@ -975,12 +993,18 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[F_NSTAGE];
-  __shared__ uint64_t mma_bar;       // scan: state-path contractions; preparation worker 0: its product
-  __shared__ uint64_t out_bar;       // scan: output contraction;      preparation worker 1: its product
+  // chain: one barrier per contraction group, each completing once per chunk (parity = chunk & 1); the output warps
+  // never wait for the first one, which a barrier shared by both groups would not allow (a skipped phase aliases)
+  __shared__ uint64_t mma_bar;       // chain: [W;Q+] S0;       preparation worker 0: its product
+  __shared__ uint64_t mma2_bar;      // chain: Kt^T U (state path)
+  __shared__ uint64_t out_bar;       // chain: (B beta) U;      preparation worker 1: its product
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5;
+#ifdef HK_DIAG
+  if (tid == 0 && blockIdx.x == 1) hk_kda_trace[32 + 11] = clock64();
+#endif
   int* g_abort = flags;
   int* ready = flags + F_FLAG_INTS;                        // [n_jobs][KR]
   int* consumed = ready + (size_t)n_jobs * KR;             // [n_jobs]
@@ -988,6 +1012,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
   if (tid == 0) {
     for (int i = 0; i < F_NSTAGE; i++) tc::mbar_init(&full_bar[i], 1);
     tc::mbar_init(&mma_bar, 1);
+    tc::mbar_init(&mma2_bar, 1);
     tc::mbar_init(&out_bar, 1);
     tc::mbar_fence_init();
     abort_flag = 0;
@@ -1003,7 +1028,8 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     const int sub = warp >> 3;
     const int worker = ((int)blockIdx.x - n_jobs) * 2 + sub, n_workers = ((int)gridDim.x - n_jobs) * 2;
     const long long n_units = (long long)n_chunks * n_jobs;
-    PrepCtx ctx{smem + sub * P1_SMEM, sub ? &out_bar : &mma_bar, 0u, &abort_flag, tmem + sub * 256, tid & 255, 1 + sub, false};
+    PrepCtx ctx{smem + sub * P1_SMEM, sub ? &out_bar : &mma_bar, 0u, &abort_flag, tmem + sub * 256, tid & 255, 1 + sub, false,
+                nullptr, 0, 0, g_abort};
 #ifdef HK_DIAG
     ctx.trace = false;
 #endif
@@ -1011,25 +1037,26 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     for (long long u = worker; u < n_units; u += n_workers, it++) {
       const int chunk = (int)(u / n_jobs), job = (int)(u % n_jobs);
       const int b = job / H, head = job % H;
-      // the slot of this chunk must have been drained by the chain CTA (it held chunk - KR)
-      if (chunk >= KR) {
-        if (ctx.tid == 0) poll_flag_ge(consumed + job, chunk - KR + 1, &abort_flag, g_abort, 20);
-        prep_sync<true>(ctx);
-      }
+#ifdef HK_DIAG
+      ctx.trace = (worker == 7 && it == 20);
+#endif
+      KT_TRACE(13);
+      // the slot of this chunk must have been drained by the chain CTA (it held chunk - KR): thread 0 asks now and
+      // looks at the answer just before the worker's first write to the unit (prep_unit calls slot_wait there)
+      ctx.slot_flag = consumed + job;
+      ctx.slot_want = chunk >= KR ? chunk - KR + 1 : 0;
+      ctx.slot_seen = (ctx.tid == 0 && ctx.slot_want > 0) ? ld_relaxed_gpu(ctx.slot_flag) : 0;
       uint8_t* unit = ring + ((size_t)(chunk % KR) * n_jobs + job) * U_BYTES;
       const long long pu = u + n_workers;
       int pf_head = 0, pf_chunk = -1;
       if (pu < n_units && (int)(pu % n_jobs) / H == b) { pf_chunk = (int)(pu / n_jobs); pf_head = (int)(pu % n_jobs) % H; }
       ctx.bar_parity = it & 1;
-#ifdef HK_DIAG
-      ctx.trace = (worker == 7 && it == 20);
-#endif
+      KT_TRACE(14);
       prep_unit<GATED, true>(ctx, qkv, g, beta_in, unit, seqlen, H, head, chunk, b, pf_head, pf_chunk, dt_bias, a_log, lower_bound);
-      // publish: every thread's writes of this unit, then the flag
-      __threadfence();
-      fence_proxy_async_all();
-      prep_sync<true>(ctx);
+      // publish: prep_unit ends with the worker's barrier, so every thread's writes of this unit precede this
+      // release store (which is cumulative over them)
       if (ctx.tid == 0) st_release_gpu(ready + (size_t)job * KR + (chunk % KR), chunk + 1);
+      KT_TRACE(15);
     }
   } else {
     // =========================== one (batch, head) chain ===========================
@@ -1088,36 +1115,49 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     const uint32_t s_addr = tc::smem_u32(smem + F_S), u_addr = tc::smem_u32(smem + F_U);
     const bool issue_warp = tc::warp_index_uniform() == 0;
     const uint32_t leader = issue_warp ? tc::elect_one() : 0u;
-    uint32_t mma_parity = 0, out_parity = 0;
 
-    // output rows of chunk c: TMEM lanes 64-127 of that chunk's D1 range = tokens, lane quarters 2 and 3
+    // Output rows of chunk c: TMEM lanes 64-127 of that chunk's D1 range = tokens, lane quarters 2 and 3 (eight warps =
+    // two token halves x four column blocks).  A thread holds 32 columns of one token; stored directly, a warp-wide
+    // 16-byte store would touch 32 different rows (32 L1 requests per instruction, over a thousand per chunk on this
+    // one SM).  The bf16 rows are therefore assembled in shared memory (272-byte pitch: conflict-free both ways) and
+    // written out with every warp instruction covering two whole 256-byte rows.  The eight warps meet at a named
+    // barrier of their own; the block barriers of the chain separate one chunk's reads from the next chunk's writes.
     auto emit_outputs = [&](int c, bool valid) {
-      const int tok = c * KC + (rowi - 64);
+      const int trow = rowi - 64;
       uint32_t r[32];
       tc::tmem_ld32(tmem + ((c & 1) ? 128u : 0u) + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
       tc::tmem_ld_wait();
-      if (tok < seqlen && valid) {
-        const size_t oi = (((size_t)b * seqlen + tok) * H + head) * KD + v0;
-        uint4* o = reinterpret_cast<uint4*>(out + oi);
+      uint8_t* orow = smem + F_O + trow * F_OPITCH + cb * (KNV * 2);
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-          uint32_t w[4];
+      for (int u = 0; u < 4; u++) {
+        uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float a = __uint_as_float(r[8 * u + 2 * e]) * scale, c2 = __uint_as_float(r[8 * u + 2 * e + 1]) * scale;
-            const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rz(a));
-            const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c2));
-            w[e] = lo | (hi << 16);
-          }
-          o[u] = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int e = 0; e < 4; e++) {
+          const float a = __uint_as_float(r[8 * u + 2 * e]) * scale, c2 = __uint_as_float(r[8 * u + 2 * e + 1]) * scale;
+          const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rz(a));
+          const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c2));
+          w[e] = lo | (hi << 16);
         }
-        if (out_f32) {
-          float4* of = reinterpret_cast<float4*>(out_f32 + oi);
+        *reinterpret_cast<uint4*>(orow + u * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const int ot = (lq - 2) * 128 + cb * 32 + (tid & 31);   // 0..255 over the eight output warps
 #pragma unroll
-          for (int u = 0; u < 8; u++)
-            of[u] = make_float4(__uint_as_float(r[4 * u]) * scale, __uint_as_float(r[4 * u + 1]) * scale,
-                                __uint_as_float(r[4 * u + 2]) * scale, __uint_as_float(r[4 * u + 3]) * scale);
+      for (int i = 0; i < 4; i++) {
+        const int piece = ot + 256 * i, prow = piece >> 4, pc = piece & 15;
+        const int ptok = c * KC + prow;
+        if (ptok < seqlen && valid) {
+          const uint4 v = *reinterpret_cast<const uint4*>(smem + F_O + prow * F_OPITCH + pc * 16);
+          *reinterpret_cast<uint4*>(out + (((size_t)b * seqlen + ptok) * H + head) * KD + pc * 8) = v;
         }
+      }
+      const int tok = c * KC + trow;
+      if (out_f32 && tok < seqlen && valid) {
+        float4* of = reinterpret_cast<float4*>(out_f32 + (((size_t)b * seqlen + tok) * H + head) * KD + v0);
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+          of[u] = make_float4(__uint_as_float(r[4 * u]) * scale, __uint_as_float(r[4 * u + 1]) * scale,
+                              __uint_as_float(r[4 * u + 2]) * scale, __uint_as_float(r[4 * u + 3]) * scale);
       }
     };
     bool prev_ok = true;
@@ -1134,18 +1174,11 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
         issued = chunk + 1;
       }
       KS_TRACE(0, chunk);
+      KS_TRACE_AT(8, chunk, 0);
+      KS_TRACE_AT(9, chunk, 50);
+      KS_TRACE_AT(10, chunk, 450);
       bool ok = tc::mbar_wait(&full_bar[sidx], (chunk / F_NSTAGE) & 1, &abort_flag, 2);
       KS_TRACE(1, chunk);
-      if (producer) {
-        st_release_gpu(consumed + job, chunk + 1);         // this chunk's slot may be rewritten
-        // catch-up: the other stage is free while the next chunk's copies have not been issued
-        if (issued == chunk + 1 && chunk + 1 < n_chunks && ld_acquire_gpu(my_ready + ((chunk + 1) % KR)) >= chunk + 2) {
-          issue_loads(chunk + 1);
-          issued = chunk + 2;
-        }
-        // sampled now, used when this chunk's stage is released at the end of the iteration
-        if (issued == chunk + 2 && chunk + 2 < n_chunks) next_flag = ld_relaxed_gpu(my_ready + ((chunk + 2) % KR));
-      }
       // ---- [W ; Q+] S0 -> D1 (128 x 128) ----
       if (issue_warp) {
 #pragma unroll
@@ -1157,10 +1190,12 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
         tc::mma_commit_if(leader, &mma_bar);
       }
       // the previous chunk's output rows leave while this chunk's first contraction runs (off the chain)
+      const uint32_t cpar = chunk & 1;
       if (lq >= 2 && chunk > 0) emit_outputs(chunk - 1, prev_ok);
-      ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 3) && ok;
-      mma_parity ^= 1;
-      tc::fence_after_sync();
+      if (lq < 2) {
+        ok = tc::mbar_wait(&mma_bar, cpar, &abort_flag, 3) && ok;
+        tc::fence_after_sync();
+      }
       KS_TRACE(2, chunk);
       // ---- U = Uloc - W S0 (token rows = TMEM lanes 0-63) ----
       if (lq < 2) {
@@ -1186,11 +1221,30 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           *reinterpret_cast<uint4*>(urow + u * 1024) = p;
         }
       }
-      tc::fence_async_smem();
-      tc::fence_before_sync();
-      __syncthreads();
-      tc::fence_after_sync();
+      // only the token-row warps (lane quarters 0 and 1, the issuing warp among them) meet here: the output warps
+      // are still writing the previous chunk's rows and join again at the state update
+      if (lq < 2) {
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        tc::fence_after_sync();
+      }
       KS_TRACE(3, chunk);
+      // The ring protocol runs here, while the producer's warp has nothing to do until the state contraction is
+      // complete.  None of it waits for this thread's earlier global stores (a release store or a fence would, and
+      // the block barriers of the chain would then wait for the output rows to reach memory).
+      if (producer) {
+        // the unit of this chunk has landed in shared memory: its slot may be rewritten.  A relaxed store is enough:
+        // the copy engine's reads are complete, nothing this thread wrote is handed over with the flag.
+        st_relaxed_gpu(consumed + job, chunk + 1);
+        // catch-up: the other stage is free while the next chunk's copies have not been issued
+        if (issued == chunk + 1 && chunk + 1 < n_chunks && ld_acquire_gpu(my_ready + ((chunk + 1) % KR)) >= chunk + 2) {
+          issue_loads(chunk + 1);
+          issued = chunk + 2;
+        }
+        // sampled now, used when this chunk's stage is released at the end of the iteration
+        if (issued == chunk + 2 && chunk + 2 < n_chunks) next_flag = ld_acquire_gpu(my_ready + ((chunk + 2) % KR));
+      }
       // ---- D2 = Kt^T U (state path, committed first) ;  D1 rows 64-127 += (B beta) U (outputs, own barrier) ----
       if (issue_warp) {
 #pragma unroll
@@ -1199,7 +1253,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           const uint64_t bd = tc::make_sdesc(u_addr + kk * 2 * 128, 128, 1024);
           tc::mma_f16_if(leader, d2, ad, bd, idesc, kk > 0);
         }
-        tc::mma_commit_if(leader, &mma_bar);
+        tc::mma_commit_if(leader, &mma2_bar);
 #pragma unroll
         for (int kk = 0; kk < KC / 16; kk++) {
           const uint64_t ad = tc::make_sdesc(stg_addr + F_BB + kk * 2 * LBO, LBO, SBO_K64);
@@ -1208,8 +1262,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
         }
         tc::mma_commit_if(leader, &out_bar);
       }
-      ok = tc::mbar_wait(&mma_bar, mma_parity, &abort_flag, 4) && ok;
-      mma_parity ^= 1;
+      ok = tc::mbar_wait(&mma2_bar, cpar, &abort_flag, 4) && ok;
       tc::fence_after_sync();
       KS_TRACE(4, chunk);
       // ---- state: S <- S e^{G_last} + Kt^T U (lane = k row), refresh the fp16 operand copy ----
@@ -1232,10 +1285,9 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       // the output contraction must be complete before the block barrier: the stage and the U tile it reads are
       // rewritten after it; the rows themselves are read in the next iteration
       if (lq >= 2) {
-        ok = tc::mbar_wait(&out_bar, out_parity, &abort_flag, 5) && ok;
+        ok = tc::mbar_wait(&out_bar, cpar, &abort_flag, 5) && ok;
         prev_ok = ok;
       }
-      out_parity ^= 1;
       tc::fence_async_smem();
       tc::fence_before_sync();
       __syncthreads();
@@ -1243,7 +1295,6 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       KS_TRACE(6, chunk);
       // refill of this stage, if the unit two chunks ahead was already complete when its flag was sampled
       if (producer && issued == chunk + 2 && chunk + 2 < n_chunks && next_flag >= chunk + 3) {
-        __threadfence();                                   // acquire side of the flag that was read relaxed
         issue_loads(chunk + 2);
         issued = chunk + 3;
       }

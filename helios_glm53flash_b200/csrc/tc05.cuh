@@ -102,6 +102,24 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
       : "memory");
 }
 
+// bulk copy shared -> global through the TMA engine (both addresses 16-byte aligned, size a multiple of 16), tracked
+// by the issuing thread's bulk groups: commit, then wait until the engine has finished READING shared memory (the
+// source may be rewritten) - the global writes complete asynchronously and are flushed at kernel end
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Ask the TMA engine to pull a contiguous global range into L2 (no destination, no completion to wait
 // for): address 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {

@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+import hk_oracle as orc
 import helios_glm53flash_b200 as hk
 from helios_glm53flash_b200 import synth
 
@@ -34,7 +35,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     lib = hk.load_library()
     assert lib.hk_mla_sparse_static_max_slots() == 64
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for call, (m, kidx, T, n_split, seed) in enumerate([(1, 2052, 16384, 0, 3), (2, 700, 4096, 7, 4)]):
+    # third call: m = 2 rows x 32 splits = all 64 slots of the built-in array (the sizing is an exact fit)
+    for call, (m, kidx, T, n_split, seed) in enumerate([(1, 2052, 16384, 0, 3), (2, 700, 4096, 7, 4), (2, 1900, 8192, 32, 5)]):
         inp = synth.mla_inputs(T, m, seed=seed, cache_std=0.5)
         rs = np.random.RandomState(seed)
         ridx = rs.randint(0, T, (m, kidx)).astype(np.int32)
@@ -53,6 +55,11 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         assert hk.read_device_status() == 0
         err = _max_rel(got, want)
         assert err < TOL, "call %d: %.3e" % (call, err)
+        # and against the CPU oracle, so that the two CUDA entry points are not only compared with each other
+        _, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, raw_idx=ridx, kidx=kidx)
+        g32 = got.float().cpu().numpy().astype(np.float64)
+        err_o = float(np.max(np.abs(g32 - o32)) / np.max(np.abs(o32)))
+        assert err_o < TOL, "call %d vs oracle: %.3e" % (call, err_o)
 
 
 def test_static_scratch_entry_rejects_oversized_requests():
