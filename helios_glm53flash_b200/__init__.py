@@ -56,6 +56,9 @@ SIGNATURES = {
     "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
     "hk_mla_splitkv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _vp, _vp,
                                  _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "hk_splitkv_region_bytes": (_sz, [_i, _i]),
+    "hk_splitkv_region_reset": (_i, [_vp, _i, _i, _vp]),
+    "hk_mla_splitkv_heads_step": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _i, _i, _vp, _vp, _i, _i, _vp]),
     "hk_enable_peer_access": (_i, [_i]),
     "hk_peer_region_alloc": (_i, [_sz, _vp, _vp]),
     "hk_peer_region_open": (_i, [_vp, _vp]),

@@ -410,3 +410,5 @@ HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const i
   return HK_OK;
 }
 
+
+#include "mla_splitkv_heads.cuh"

@@ -1,6 +1,12 @@
 """Long-context MLA decode split over the GPUs of one node (split-KV), one process per GPU.
 
-Rank g owns a contiguous slice of the latent cache.  A decode step is, on every rank:
+Rank g owns a contiguous slice of the latent cache.  Two forms of the exchange exist.  The default
+("heads", needs 64 % world == 0) is ``hk_mla_splitkv_heads_step``: every rank merges its local splits
+into one partial set in its exchange region and signals; rank g then combines ONLY heads
+[g * 64 / world, (g + 1) * 64 / world) from all ranks' partial sets and stores the fp16 rows into every
+rank's region; a last kernel waits for all slices and copies them to the caller's tensor.  Bytes over
+NVLink per rank and step are independent of the number of ranks.  The older form ("all") lets every rank
+read every rank's whole partial set.  A decode step of the "all" form is, on every rank:
   1. ``hk_mla_dense_partial`` over the local slice -> un-normalised (m, l, acc) partial in a buffer that
      every peer has mapped (CUDA inter-process handle opened by each peer on its own device; NVLink),
   2. ``hk_peer_signal``: store the step's epoch into this rank's slot of every rank's flag array,
@@ -43,7 +49,7 @@ def region_layout(rows, world):
 class SplitKVDecoder:
     """Owns the peer-mapped exchange region of this rank and the pointer tables of all ranks."""
 
-    def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000):
+    def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000, form=None):
         import torch
         import torch.distributed as dist
         import helios_glm53flash_b200 as hk
@@ -52,7 +58,10 @@ class SplitKVDecoder:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.m, self.n_heads, self.rows = m, n_heads, m * n_heads
         self.max_wait_ms = max_wait_ms
+        self.form = form or ("heads" if n_heads == 64 and 64 % self.world == 0 else "all")
         self.lay = region_layout(self.rows, self.world)
+        if self.form == "heads":
+            self.lay = {"total": hk.load_library().hk_splitkv_region_bytes(m, n_heads)}
         # The exchange region is library-owned device memory with an inter-process handle; every peer
         # opens the handle with ITS OWN device current, which is what makes the mapping usable by that
         # device's kernels (set-up only: torch.distributed carries the 64-byte handles).
@@ -67,6 +76,14 @@ class SplitKVDecoder:
                 hk.enable_peer_access(dev_index)
                 self.peers.append(hk.peer_region_open(h, self.lay["total"]))
         bases = [p.data_ptr() for p in self.peers]
+        self.step_ctr = torch.zeros(1, dtype=torch.int32, device="cuda")   # "all" form: step number, advanced on the device
+        self.epoch = 0
+        self.workspace = None
+        if self.form == "heads":
+            self.region_ptrs = torch.tensor(bases, dtype=torch.int64, device="cuda")
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            return
 
         def table(key):
             return torch.tensor([b + self.lay[key] for b in bases], dtype=torch.int64, device="cuda")
@@ -74,9 +91,6 @@ class SplitKVDecoder:
         self.flag_ptrs = table("flags")
         # pointer tables of both exchange sets, [set][rank]
         self.m_ptrs, self.l_ptrs, self.acc_ptrs = [torch.cat([table(k + str(par)) for par in (0, 1)]) for k in ("m", "l", "acc")]
-        self.step_ctr = torch.zeros(1, dtype=torch.int32, device="cuda")   # step number, advanced on the device
-        self.epoch = 0
-        self.workspace = None
         self._views()
         torch.cuda.synchronize()
         dist.barrier(group=group)
@@ -115,12 +129,38 @@ class SplitKVDecoder:
             self._n_split = hk.mla_auto_splits(self.m, max(1, self._n_keys))
             nbytes = hk.mla_partial_bytes(self._n_split, self.rows)
             self.workspace = t.empty(max(256, nbytes), dtype=t.uint8, device="cuda")
+        if self.form == "heads":
+            base = self._zero_base if kv_base is None else kv_base
+            hk._call("hk_mla_splitkv_heads_step", hk._ptr(q_lat), hk._ptr(ckv_shard), hk._ptr(base), hk._ptr(self._lens),
+                     self.m, self.n_heads, float(scale), self._n_split, self._n_keys, hk._ptr(self.workspace),
+                     self.workspace.numel(), hk._ptr(self.region_ptrs), self.world, self.rank,
+                     hk._c.c_void_p(self.local.data_ptr()), hk._ptr(out), int(self.max_wait_ms), int(bool(signal)),
+                     hk._stream(None))
+            return
         hk.mla_splitkv_step(q_lat, ckv_shard, self._zero_base if kv_base is None else kv_base, self._lens,
                             (self.part_m[0], self.part_l[0], self.part_acc[0]),
                             (self.part_m[1], self.part_l[1], self.part_acc[1]), self.m, self.n_heads, scale,
                             self._n_split, self._n_keys, self.workspace, self.flag_ptrs, self.m_ptrs, self.l_ptrs,
                             self.acc_ptrs, self.world, self.rank, self.step_ctr, self.flags, out,
                             max_wait_ms=self.max_wait_ms, signal=signal)
+
+
+    def resync(self):
+        """After a step timed out (device status HK_ERR_TIMEOUT) the ranks are no longer in lock step and a slow peer
+        may still read an exchange set: every rank calls this before stepping again.  Host barrier, flags and step
+        counters back to zero, host barrier."""
+        self.torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
+        if self.form == "heads":
+            self.hk._call("hk_splitkv_region_reset", self.hk._c.c_void_p(self.local.data_ptr()), self.m, self.n_heads,
+                          self.hk._stream(None))
+        else:
+            self.flags.zero_()
+            self.step_ctr.zero_()
+        self.epoch = 0
+        self.hk.read_device_status(reset=True)
+        self.torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
 
 
 def merge_partials_numpy(parts):

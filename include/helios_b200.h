@@ -270,6 +270,24 @@ int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t*
                         int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
                         int max_wait_ms, int signal, void* stream);
 
+/* Split-KV across GPUs with the combine sharded by heads (n_heads = 64, 64 % n_ranks == 0): one decode step of one rank
+ * in one call.  Every rank owns an exchange region of hk_splitkv_region_bytes(m, n_heads) bytes (zeroed; allocate it
+ * with hk_peer_region_alloc) that every peer has mapped; region_ptrs is a DEVICE array of the n_ranks region addresses
+ * as mapped in THIS process, my_region == region_ptrs[my_rank].  The step: partial over this rank's shard (n_split
+ * local splits in `workspace`, sized by hk_mla_partial_bytes), merged into the region and signalled; rank g combines
+ * heads [g*64/n_ranks, (g+1)*64/n_ranks) from all ranks' partials and stores the fp16 rows into every rank's region;
+ * once all slices have arrived they are copied to out_f16 [m][64][512].  The step number lives in the region, so a
+ * CUDA graph that captured the call can be replayed.  Every wait is bounded by max_wait_ms (1..10000): on expiry the
+ * grid writes nothing, the device status word reports HK_ERR_TIMEOUT, and the ranks must stop stepping until every
+ * rank has called hk_splitkv_region_reset between two host-side barriers.  signal == 0 withholds this rank's first
+ * signal (failure injection in tests).  No counterpart in the reference (it is single-GPU for this path).           */
+size_t hk_splitkv_region_bytes(int m, int n_heads);
+int hk_splitkv_region_reset(void* region, int m, int n_heads, void* stream);
+int hk_mla_splitkv_heads_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
+                              int m, int n_heads, float scale, int n_split, int n_keys_hint, void* workspace,
+                              size_t workspace_bytes, void* const* region_ptrs, int n_ranks, int my_rank,
+                              void* my_region, void* out_f16, int max_wait_ms, int signal, void* stream);
+
 /* Enables access from kernels of the current device to memory of `peer_device` (needed once per peer
  * before the two calls around this one touch buffers of another GPU that were mapped into this
  * process).  Idempotent; HK_ERR_UNSUPPORTED when the two GPUs have no peer path.                  */

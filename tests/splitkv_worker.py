@@ -1,7 +1,7 @@
-"""Split-KV MLA decode over N GPUs (run with torchrun, one rank per GPU):
+"""Worker of tests/test_gpu_multigpu.py: split-KV MLA decode over N GPUs, one rank per GPU, started by
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29600 tests/multigpu_splitkv.py [--ctx 262144] [--iters 20]
+        --master-port 29600 tests/splitkv_worker.py [--ctx 262144] [--iters 20] [--form heads|all]
 
 Checks the N-GPU result against the single-GPU dense kernel on the whole cache (every rank builds the
 same seeded cache) and times the step (device events, max over ranks).  Also exercises the bounded wait:
@@ -20,6 +20,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=262144)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded per step, each with its own cache of --ctx rows")
+    ap.add_argument("--form", default=None, choices=[None, "heads", "all"], help="exchange form (default: heads when 64 % ranks == 0)")
     args = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -39,7 +40,7 @@ def main():
     shard_base = (torch.arange(m, device="cuda", dtype=torch.int64) * (e - b))
     full_base = (torch.arange(m, device="cuda", dtype=torch.int64) * L)
     full_len = torch.full((m,), L, dtype=torch.int32, device="cuda")
-    dec = splitkv.SplitKVDecoder(m, max_wait_ms=2000)
+    dec = splitkv.SplitKVDecoder(m, max_wait_ms=2000, form=args.form)
     out = torch.zeros(m, 64, 512, dtype=torch.float16, device="cuda")
     ref = torch.zeros_like(out)
     hk.mla_dense_prefill(q, ckv, ref, m, 0, scale=scale, kv_base=full_base, kv_len=full_len, n_keys_hint=L)   # single-GPU answer
@@ -106,11 +107,8 @@ def main():
         torch.cuda.synchronize()
         timeout_seen = hk.read_device_status() == hk.HK_ERR_TIMEOUT and bool((out2 == 3.0).all())
         dist.barrier()
-        # recovery: the withheld epoch is published late, the next step works again
-        if rank == 1:
-            hk.peer_signal(dec.flag_ptrs, world, rank, dec.epoch)
-        torch.cuda.synchronize()
-        dist.barrier()
+        # recovery: after a timeout the group re-synchronises on the host, then steps again
+        dec.resync()
         dec.max_wait_ms = 2000
         dec.step(q, shard, e - b, out, scale, kv_base=shard_base)
         torch.cuda.synchronize()
@@ -122,7 +120,7 @@ def main():
     ok = torch.tensor([int(all(flags))], device="cuda")
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(json.dumps({"test": "splitkv_decode", "n_gpus": world, "ctx": L, "batch": m, "max_rel_err": err,
+        print(json.dumps({"test": "splitkv_decode", "form": dec.form, "n_gpus": world, "ctx": L, "batch": m, "max_rel_err": err,
                           "us_per_step": float(t) * 1e3, "us_per_step_host_launched": float(t_host) * 1e3,
                           "single_gpu_us": t1 * 1e3,
                           "hbm_gbs_aggregate": m * L * 1024 / (float(t) * 1e-3) / 1e9,
