@@ -47,7 +47,7 @@ class ClockSampler:
         self.rows, self.proc, self.thread = [], None, None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "10"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -361,6 +361,9 @@ def main():
     ms_total, e2e_ms, conv_ms, kda_ms = [float(v) for v in t.cpu()]
     ms_step = ms_total / steps
 
+    multi = None
+    if world > 1:
+        multi = multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, kda_ms)
     extras = {}
     if rank == 0 and not args.no_extras:
         extras = side_measurements(hk, synth, torch, np, local_rank)
@@ -396,6 +399,8 @@ def main():
             "clocks": sampler.summary(t_begin, t_end),
             "extras": extras,
         }
+        if multi is not None:
+            line["multi_gpu"] = multi
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(steps=1)
         print(json.dumps(line), flush=True)
@@ -403,7 +408,179 @@ def main():
         dist.destroy_process_group()
 
 
-def _time_loop(torch, fns, iters=10, warm=2, flush=None, sustain_ms=2.0):
+def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, kda_ms_32_heads):
+    """The partitions of the path across the GPUs of one node, device-timed, max over ranks:
+      * split-KV decode over a 262,144-token latent cache (batch 1 and batch 8): every rank attends its slice, the
+        partials are combined by peer loads over NVLink; against the same decode on one GPU (rank 0's own time);
+      * KDA prefill sharded by heads (32 / N heads per GPU, same 32,768 tokens): strong scaling of the headline step;
+      * MLA dense decode of 8 sequences x 32,768 tokens sharded by sequences (8 / N per GPU); the tensor-core kernel
+        keeps all 64 heads of a sequence on one GPU (heads are its accumulator lanes);
+      * SM clocks of every rank, sampled on its own GPU while its split-KV loop runs."""
+    from helios_glm53flash_b200 import splitkv
+    res = {"n_gpus": world}
+    H, D, T = HEADS, DIM, T_FULL
+
+    def max_over_ranks(v):
+        t = torch.tensor([float(v)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def graph_time(fn, iters=30, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return g, a.elapsed_time(b) / iters
+
+    # ---- split-KV decode at 262,144 tokens of context ----
+    L, scale = 262144, 512 ** -0.5
+    sampler = ClockSampler(local_rank)
+    t_clk0 = time.time()
+    for m in (1, 8):
+        gen = torch.Generator(device="cuda").manual_seed(4321 + m)            # same cache and queries on every rank
+        q = torch.randn(m, 64, 512, generator=gen, device="cuda", dtype=torch.float32).half()
+        b0, e0 = splitkv.shard_tokens(L, rank, world)
+        # this rank's slice of every sequence, concatenated (a rank never holds the other ranks' rows)
+        shard = torch.randn(m * (e0 - b0), 512, device="cuda", dtype=torch.float16)
+        shard_base = torch.arange(m, device="cuda", dtype=torch.int64) * (e0 - b0)
+        out = torch.zeros(m, 64, 512, dtype=torch.float16, device="cuda")
+        dec = splitkv.SplitKVDecoder(m, max_wait_ms=2000)
+        g, ms = graph_time(lambda: dec.step(q, shard, e0 - b0, out, scale, kv_base=shard_base))
+        ms = max_over_ranks(ms)
+        status = hk.read_device_status()
+        # the same decode on one GPU (the whole cache of every sequence on this rank), rank 0's own time
+        ms1 = 0.0
+        if rank == 0:
+            full = torch.randn(m * L, 512, device="cuda", dtype=torch.float16)
+            base1 = torch.arange(m, device="cuda", dtype=torch.int64) * L
+            len1 = torch.full((m,), L, dtype=torch.int32, device="cuda")
+            ns = hk.mla_auto_splits(m, L)
+            ws1 = torch.empty(max(256, hk.mla_partial_bytes(ns, m * 64)), dtype=torch.uint8, device="cuda")
+            ref = torch.empty_like(out)
+            fn1 = lambda: hk.mla_dense_prefill(q, full, ref, m, 0, scale=scale, kv_base=base1, kv_len=len1, n_split=ns,
+                                               workspace=ws1, n_keys_hint=L)
+            for _ in range(3):
+                fn1()
+            torch.cuda.synchronize()
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                fn1()
+            g1.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(30):
+                g1.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ms1 = a.elapsed_time(b) / 30
+            del full, g1
+        ms1 = max_over_ranks(ms1)
+        res["splitkv_decode_262k_b%d" % m] = {
+            "us_per_step": ms * 1e3, "one_gpu_us_per_step": ms1 * 1e3, "speedup_vs_one_gpu": ms1 / ms,
+            "efficiency": ms1 / ms / world, "aggregate_hbm_gbs": m * L * 1024 / (ms * 1e-3) / 1e9,
+            "exchange": dec.form, "device_status": status}
+        del g
+        dec.close()
+        del shard
+        torch.cuda.empty_cache()
+    t_clk1 = time.time()
+    sampler.stop()
+    clk = sampler.summary(t_clk0, t_clk1)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"rank": rank, "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons")})
+    res["per_rank_clocks_during_splitkv"] = gathered
+
+    # ---- KDA prefill sharded by heads: 32 / N heads on every GPU, the same 32,768 tokens ----
+    if H % world == 0:
+        Hl = H // world
+        kd = synth.kda_gates(T, Hl, D, seed=rank)
+        g_l, beta_l = torch.from_numpy(kd["g"]).cuda(), torch.from_numpy(kd["beta"].view(np.int16)).view(torch.bfloat16).cuda()
+        qkv_l = torch.randn(1, T, 3 * Hl * D, device="cuda").to(torch.bfloat16)
+        st_l = torch.zeros(1, 1, Hl, D, D, dtype=torch.float32, device="cuda")
+        out_l = torch.empty(1, T, Hl, D, dtype=torch.bfloat16, device="cuda")
+        ws_l = torch.empty(hk.kda_chunked_workspace_bytes(1, T, Hl), dtype=torch.uint8, device="cuda")
+
+        def kda_step():
+            st_l.zero_()
+            hk.cuda_recurrent_gated_delta_rule(qkv_l, g_l, beta_l, st_l, out_l, 1, T, Hl, Hl, D, D, 1, None, True, False,
+                                               workspace=ws_l)
+        for _ in range(3):
+            kda_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            kda_step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(a.elapsed_time(b) / 10)
+        res["kda_prefill_32k_head_sharded"] = {
+            "heads_per_gpu": Hl, "ms": ms, "tokens_per_s": T / (ms * 1e-3), "ms_32_heads_on_one_gpu": kda_ms_32_heads,
+            "speedup": kda_ms_32_heads / ms, "efficiency": kda_ms_32_heads / ms / world,
+            "note": "one chain per head: with few heads per GPU the step is bound by the 512-chunk chain, not by the SMs"}
+        del qkv_l, g_l, out_l, ws_l
+        torch.cuda.empty_cache()
+
+    # ---- MLA dense decode, 8 sequences x 32,768 tokens, sharded by sequences ----
+    B, L2 = 8, 32768
+    if B % world == 0:
+        Bl = B // world
+        ck = torch.randn(Bl * L2, 512, dtype=torch.float16, device="cuda")
+        qd = torch.randn(Bl, 64, 512, dtype=torch.float16, device="cuda")
+        base = torch.arange(Bl, device="cuda", dtype=torch.int64) * L2
+        lens = torch.full((Bl,), L2, dtype=torch.int32, device="cuda")
+        lo = torch.empty(Bl, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(Bl, L2)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, Bl * 64)), dtype=torch.uint8, device="cuda")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+        def mla_step():
+            hk.mla_dense_prefill(qd, ck, lo, Bl, 0, scale=scale, kv_base=base, kv_len=lens, n_split=ns, workspace=wsb,
+                                 n_keys_hint=L2)
+        for _ in range(3):
+            mla_step()
+        torch.cuda.synchronize()
+        gm = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gm):
+            mla_step()
+        ts = []
+        for _ in range(10):
+            flush.zero_()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            gm.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ms = max_over_ranks(sorted(ts)[len(ts) // 2])
+        res["mla_dense_decode_32k_b8_sequence_sharded"] = {
+            "sequences_per_gpu": Bl, "us_per_layer": ms * 1e3, "aggregate_hbm_gbs": B * L2 * 1024 / (ms * 1e-3) / 1e9,
+            "l2": "256 MB flush before every timed replay"}
+    return res
+
+
+FIGURE_CLOCKS = {}      # label -> SM clock summary sampled while that figure's launch chain ran for 0.3 s
+
+
+def _time_loop(torch, fns, iters=10, warm=2, flush=None, sustain_ms=2.0, label=None, gpu_index=0):
     """median device time, in ms, of ONE pass over the callables of `fns` run back to back.  The chain is
     captured in a CUDA graph after the warm-up and replays are timed, so host launch latency is not in the
     figure; a timed region holds as many replays as fill about `sustain_ms` (a decode loop keeps the GPU
@@ -430,6 +607,17 @@ def _time_loop(torch, fns, iters=10, warm=2, flush=None, sustain_ms=2.0):
 
     reps = max(1, min(200, int(sustain_ms / max(once(1), 1e-3) + 0.999)))
     ts = sorted(once(reps) for _ in range(iters))
+    if label is not None:
+        # the clock record of this figure: the same chain replayed for 0.3 s with the 10 ms sampler running
+        sampler = ClockSampler(gpu_index)
+        t0 = time.time()
+        while time.time() - t0 < 0.3:
+            for _ in range(20):
+                graph.replay()
+            torch.cuda.synchronize()
+        t1 = time.time()
+        sampler.stop()
+        FIGURE_CLOCKS[label] = sampler.summary(t0 + 0.05, t1)
     return ts[len(ts) // 2]
 
 
@@ -442,17 +630,29 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
     res = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     H, D = HEADS, DIM
-    # ---- KDA decode step: 34 layers, each its own 2 MiB fp32 state ----
+    # ---- KDA decode step: 34 layers, each with its own 2 MiB fp32 state and its own conv window; the step includes
+    #      the short convolution: one fused launch per layer, and the reference's two-launch sequence beside it ----
     n_kda = 34
+    dimc = 3 * H * D
     kd = synth.kda_inputs(1, H, D, seed=5)
-    q, g, b = dev_bf16(kd["mixed_qkv"]), dev(kd["g"]), dev_bf16(kd["beta"])
+    g, b = dev(kd["g"]), dev_bf16(kd["beta"])
+    xdec = torch.randn(1, dimc, device="cuda").to(torch.bfloat16)
+    wdec = (0.1 * torch.randn(dimc, 4, device="cuda")).to(torch.bfloat16)
     sts = [torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda") for _ in range(n_kda)]
+    css = [torch.zeros(1, dimc, 4, dtype=torch.bfloat16, device="cuda") for _ in range(n_kda)]
+    qkv1 = torch.empty(1, 1, dimc, dtype=torch.bfloat16, device="cuda")
     o = torch.empty(1, 1, H, D, dtype=torch.bfloat16, device="cuda")
-    fns = [(lambda st=st: hk.cuda_recurrent_gated_delta_rule(q, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)) for st in sts]
-    ms = _time_loop(torch, fns, flush=flush) / n_kda
+    fns = [(lambda st=st, cs=cs: hk.kda_decode_step(xdec, cs, wdec, None, g, b, st, o, 1, H)) for st, cs in zip(sts, css)]
+    ms = _time_loop(torch, fns, flush=flush, label="kda_decode", gpu_index=gpu_index) / n_kda
     res["kda_decode_us_per_layer"] = ms * 1e3
     res["kda_decode_hbm_gbs"] = (2 * H * D * D * 4 + H * 1538) / (ms * 1e-3) / 1e9
-    del sts
+
+    def two_launch(st, cs):
+        hk.cuda_causal_conv1d_update(xdec.view(1, dimc, 1), cs, None, wdec, None, qkv1, 1, dimc, 1, 4, 4, True, False)
+        hk.cuda_recurrent_gated_delta_rule(qkv1, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)
+    fns = [(lambda st=st, cs=cs: two_launch(st, cs)) for st, cs in zip(sts, css)]
+    res["kda_decode_two_launch_us_per_layer"] = 1e3 * _time_loop(torch, fns, flush=flush) / n_kda
+    del sts, css
     # ---- dense MLA decode over 32K latent caches: 11 layers (B=1), 2 alternating layers (B=8) ----
     L = 32768
     for B, n_layers in ((1, 11), (8, 2)):
@@ -465,26 +665,11 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
         wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, B * 64)), dtype=torch.uint8, device="cuda")
         fns = [(lambda ck=ck: hk.mla_dense_prefill(qd, ck, lo, B, 0, scale=512 ** -0.5, kv_base=base, kv_len=lens,
                                                    n_split=ns, workspace=wsb, n_keys_hint=L)) for ck in cks]
-        ms = _time_loop(torch, fns, flush=flush if B * L * 1024 * n_layers < (200 << 20) else None) / n_layers
+        ms = _time_loop(torch, fns, flush=flush if B * L * 1024 * n_layers < (200 << 20) else None,
+                        label="mla_dense_decode_32k_b%d" % B, gpu_index=gpu_index) / n_layers
         res["mla_dense_decode_32k_b%d_us_per_layer" % B] = ms * 1e3
         res["mla_dense_decode_32k_b%d_hbm_gbs" % B] = B * L * 1024 / (ms * 1e-3) / 1e9
         res["mla_dense_decode_32k_b%d_splits" % B] = ns
-        if B == 8:
-            # SM clock under this kernel: a 0.4 s loop of the same chain with the sampler running
-            sampler = ClockSampler(gpu_index)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for f in fns:
-                    f()
-            torch.cuda.synchronize()
-            t0 = time.time()
-            while time.time() - t0 < 0.4:
-                for _ in range(50):
-                    graph.replay()
-                torch.cuda.synchronize()
-            t1 = time.time()
-            sampler.stop()
-            res["mla_dense_decode_32k_b8_clocks"] = sampler.summary(t0 + 0.1, t1)
         del cks
     # ---- indexer -> top-512 -> expand -> sparse MLA at 262,144 tokens of context, 11 layers ----
     npools, L, n_mla = 65536, 262144, 11
@@ -501,14 +686,14 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
     ns = hk.mla_auto_splits(1, 2052)
     wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=torch.uint8, device="cuda")
     f_score = [(lambda pk=pk: hk.indexer_score(qi, pk, w, q_pos, sc, 1, npools)) for pk in pks]
-    ms = _time_loop(torch, f_score, flush=flush) / n_mla
+    ms = _time_loop(torch, f_score, flush=flush, label="indexer_score_262k", gpu_index=gpu_index) / n_mla
     res["indexer_score_262k_us_per_layer"] = ms * 1e3
     res["indexer_score_262k_hbm_gbs"] = npools * 256 / (ms * 1e-3) / 1e9
     f_topk = [lambda: hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)] * n_mla
-    res["topk512_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_topk, flush=flush) / n_mla
+    res["topk512_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_topk, flush=flush, label="topk512_262k", gpu_index=gpu_index) / n_mla
     hk.pool_expand_row(idx, q_pos, raw, 1)
     f_sparse = [(lambda ck=ck: hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)) for ck in ckvs]
-    ms = _time_loop(torch, f_sparse, flush=flush) / n_mla
+    ms = _time_loop(torch, f_sparse, flush=flush, label="mla_sparse_decode_262k", gpu_index=gpu_index) / n_mla
     res["mla_sparse_decode_262k_us_per_layer"] = ms * 1e3
     res["mla_sparse_decode_262k_hbm_gbs"] = 2052 * 1024 / (ms * 1e-3) / 1e9
 
@@ -518,7 +703,8 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
         hk.pool_expand_row(idx, q_pos, raw, 1)
         hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
     f_chain = [(lambda pk=pk, ck=ck: chain(pk, ck)) for pk, ck in zip(pks, ckvs)]
-    res["dsa_sparse_mla_decode_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_chain, flush=flush) / n_mla
+    res["dsa_sparse_mla_decode_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_chain, flush=flush, label="dsa_sparse_mla_decode_262k",
+                                                                        gpu_index=gpu_index) / n_mla
     del pks, ckvs, f_sparse, f_chain
     torch.cuda.empty_cache()
     # ---- one KDA layer of the 32K prefill from the projections' fp32 outputs to the gated, normalised fp16
@@ -559,6 +745,7 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
     res["kda_layer_prefill_32k_reference_call_sequence_ms"] = ms2
     res["kda_layer_prefill_32k_fused_ms"] = ms1
     res["kda_layer_prefill_32k_fused_tokens_per_s"] = T / (ms1 * 1e-3)
+    res["clocks_per_figure"] = dict(FIGURE_CLOCKS)
     return res
 
 

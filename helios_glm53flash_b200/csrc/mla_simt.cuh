@@ -367,17 +367,37 @@ __global__ __launch_bounds__(128) void lse_combine_peers_kernel(
   if (!ready) return;
   const int64_t r = blockIdx.x;
   const int t = threadIdx.x;
-  float gm = -INFINITY;
-  for (int s = 0; s < n_split; s++) gm = fmaxf(gm, __ldcv(ptrs_m[s] + r));
-  float gl = 0.f;
+  float gm = -INFINITY, gl = 0.f;
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (gm != -INFINITY) {
-    for (int s = 0; s < n_split; s++) {
-      const float ms = __ldcv(ptrs_m[s] + r);
-      const float sc = ms == -INFINITY ? 0.f : __expf(ms - gm);
-      gl += sc * __ldcv(ptrs_l[s] + r);
-      const float4 a = __ldcv(reinterpret_cast<const float4*>(ptrs_acc[s] + (size_t)r * LATENT + t * 4));
-      o.x += sc * a.x; o.y += sc * a.y; o.z += sc * a.z; o.w += sc * a.w;
+  // batches of 8 partial sets: every load of a batch is issued before the first one is used, so a batch costs one
+  // round trip over NVLink (a loop that uses each value as it arrives pays one round trip per set and pass)
+  for (int s0 = 0; s0 < n_split; s0 += 8) {
+    float ms[8], ls[8];
+    float4 as[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int s = s0 + u;
+      if (s < n_split) {
+        ms[u] = __ldcv(ptrs_m[s] + r);
+        ls[u] = __ldcv(ptrs_l[s] + r);
+        as[u] = __ldcv(reinterpret_cast<const float4*>(ptrs_acc[s] + (size_t)r * LATENT + t * 4));
+      } else {
+        ms[u] = -INFINITY; ls[u] = 0.f; as[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    float bm = gm;
+#pragma unroll
+    for (int u = 0; u < 8; u++) bm = fmaxf(bm, ms[u]);
+    if (bm != -INFINITY) {
+      const float resc = gm == -INFINITY ? 0.f : __expf(gm - bm);
+      gl *= resc; o.x *= resc; o.y *= resc; o.z *= resc; o.w *= resc;
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const float w = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - bm);
+        gl = fmaf(w, ls[u], gl);
+        o.x = fmaf(w, as[u].x, o.x); o.y = fmaf(w, as[u].y, o.y); o.z = fmaf(w, as[u].z, o.z); o.w = fmaf(w, as[u].w, o.w);
+      }
+      gm = bm;
     }
   }
   const float inv = gl > 0.f ? 1.f / gl : 0.f;

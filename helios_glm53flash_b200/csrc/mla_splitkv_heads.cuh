@@ -108,9 +108,10 @@ __global__ __launch_bounds__(LSE_THREADS) void sk_merge_signal_kernel(
     reinterpret_cast<float*>(set)[r] = gm;
     reinterpret_cast<float*>(set + L.off_l)[r] = gl;
   }
-  __threadfence_system();
+  // the block barrier orders every thread's writes before thread 0's fence, which is cumulative over them
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const int ticket = atomicAdd(hdr + SK_T_MERGE, 1);
     if (ticket == (int)rows - 1) {
       hdr[SK_T_MERGE] = 0;
@@ -180,9 +181,9 @@ __global__ __launch_bounds__(128) void sk_combine_heads_kernel(
     for (int d = 0; d < n_ranks; d++)
       *reinterpret_cast<uint2*>(regions[d] + L.off_out[par] + ((size_t)r * LATENT + t * 4) * 2) = pk;
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const int ticket = atomicAdd(hdr + SK_T_COMB, 1);
     if (ticket == (int)gridDim.x - 1) {
       hdr[SK_T_COMB] = 0;

@@ -1,12 +1,14 @@
 """Long-context MLA decode split over the GPUs of one node (split-KV), one process per GPU.
 
 Rank g owns a contiguous slice of the latent cache.  Two forms of the exchange exist.  The default
-("heads", needs 64 % world == 0) is ``hk_mla_splitkv_heads_step``: every rank merges its local splits
-into one partial set in its exchange region and signals; rank g then combines ONLY heads
-[g * 64 / world, (g + 1) * 64 / world) from all ranks' partial sets and stores the fp16 rows into every
-rank's region; a last kernel waits for all slices and copies them to the caller's tensor.  Bytes over
-NVLink per rank and step are independent of the number of ranks.  The older form ("all") lets every rank
-read every rank's whole partial set.  A decode step of the "all" form is, on every rank:
+("all") lets every rank read every rank's whole partial set (one exchange hop; the loads of all sets are
+in flight together).  The other ("heads", needs 64 % world == 0) is ``hk_mla_splitkv_heads_step``: every
+rank merges its local splits into one partial set in its exchange region and signals; rank g then
+combines ONLY heads [g * 64 / world, (g + 1) * 64 / world) from all ranks' partial sets and stores the
+fp16 rows into every rank's region; a last kernel waits for all slices and copies them to the caller's
+tensor.  Its bytes over NVLink per rank and step are independent of the number of ranks, but it needs two
+exchange hops; measured on 2 and 4 GPUs it is the slower one (78 / 275 us against 64 / 242 us per step
+at batch 1 / 8 on 2 GPUs, 69 / 184 against 47 / 155 on 4).  A decode step of the "all" form is, on every rank:
   1. ``hk_mla_dense_partial`` over the local slice -> un-normalised (m, l, acc) partial in a buffer that
      every peer has mapped (CUDA inter-process handle opened by each peer on its own device; NVLink),
   2. ``hk_peer_signal``: store the step's epoch into this rank's slot of every rank's flag array,
@@ -58,7 +60,9 @@ class SplitKVDecoder:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.m, self.n_heads, self.rows = m, n_heads, m * n_heads
         self.max_wait_ms = max_wait_ms
-        self.form = form or ("heads" if n_heads == 64 and 64 % self.world == 0 else "all")
+        self.form = form or "all"
+        if self.form == "heads" and not (n_heads == 64 and 64 % self.world == 0):
+            raise ValueError("the heads form needs 64 heads and a rank count that divides 64")
         self.lay = region_layout(self.rows, self.world)
         if self.form == "heads":
             self.lay = {"total": hk.load_library().hk_splitkv_region_bytes(m, n_heads)}

@@ -68,6 +68,17 @@ int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* beta, fl
                      int num_v_heads, int k_head_dim, int v_head_dim, int history_stride,
                      const int* slots, int channelwise, int history, void* stream);
 
+/* One KDA decode step with the short convolution inside: what the engine runs per decoded token as
+ * cuda_causal_conv1d_update(seqlen 1, K = state_size = 4, SiLU) followed by cuda_recurrent_gated_delta_rule(seqlen 1,
+ * channelwise) (src/engine/runner.cpp:443-471), in ONE launch and with the same bits.  Head dim 128, Hk == Hv.
+ *   x [bsz][3*H*128] bf16 (the token's pre-conv q|k|v)   conv_state [slots][3*H*128][4] bf16 (in place)
+ *   conv_weight [3*H*128][4] bf16   conv_bias [3*H*128] bf16 or NULL   g [bsz][H][128] f32   beta [bsz][H] bf16
+ *   rec_state [slots][H][128][128] f32 (in place)   out [bsz][H][128] bf16 (rz)   out_f32 optional
+ *   conv_out optional [bsz][3*H*128] bf16: the convolved q|k|v (what the two-kernel sequence leaves in between). */
+int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_weight, const void* conv_bias, const float* g,
+                       const void* beta, float* rec_state, void* out, float* out_f32, void* conv_out, int bsz,
+                       int num_heads, const int* slots, void* stream);
+
 /* Chunked (64-token) KDA prefill on the tensor cores; numerically equivalent to
  * hk_kda_recurrent(channelwise=1, history=0) on the same arguments (the reference has no chunked
  * kernel: prefill calls the recurrence with seqlen = n, src/engine/runner.cpp:468-471).

@@ -258,3 +258,46 @@ def test_chunked_fused_launch_equals_two_kernel_form(T, H, bsz):
     if T * H * bsz <= 8192:
         _, o_32, o_st = orc.kda_recurrent(inp["mixed_qkv"], inp["g"], inp["beta"], s0, bsz, T, H, H, D, D)
         assert max_rel(res[1][1], o_32) < 2e-3 and frob_rel(res[1][2], o_st) < 1e-2
+
+
+@pytest.mark.parametrize("H,bsz", [(32, 1), (4, 2), (64, 3)])
+def test_decode_step_with_conv_inside_equals_the_two_launch_sequence(H, bsz):
+    """hk_kda_decode_step (conv + recurrence of one decoded token in one launch, value slices of a head as a cluster)
+    against cuda_causal_conv1d_update followed by cuda_recurrent_gated_delta_rule on the same buffers, 6 tokens in a
+    row with carried window and state: same bits everywhere; the first token also against the oracle"""
+    D, steps = 128, 6
+    dim = 3 * H * D
+    r = synth.rng(77 + H)
+    x = synth.f32_to_bf16_bits(r.standard_normal((steps, bsz, dim), dtype=np.float32))
+    w = synth.f32_to_bf16_bits((0.1 * r.standard_normal((dim, 4), dtype=np.float32)).astype(np.float32))
+    bias = synth.f32_to_bf16_bits((0.05 * r.standard_normal((dim,), dtype=np.float32)).astype(np.float32))
+    cst0 = synth.f32_to_bf16_bits(r.standard_normal((bsz, dim, 4), dtype=np.float32))
+    gates = synth.kda_gates(steps, H, D, bsz=bsz, seed=3)
+    g_all, beta_all = dev(np.ascontiguousarray(gates["g"].transpose(1, 0, 2, 3))), dev_bf16(np.ascontiguousarray(gates["beta"].transpose(1, 0, 2)))
+    s0 = (0.1 * r.standard_normal((bsz, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    xd, wd, bd = dev_bf16(x), dev_bf16(w), dev_bf16(bias)
+    # two-launch sequence
+    cs_a, st_a = dev_bf16(cst0), dev(s0)
+    qkv_a = torch.empty(steps, bsz, 1, dim, dtype=torch.bfloat16, device="cuda")
+    out_a = torch.empty(steps, bsz, 1, H, D, dtype=torch.bfloat16, device="cuda")
+    # fused
+    cs_b, st_b = dev_bf16(cst0), dev(s0)
+    qkv_b = torch.empty(steps, bsz, dim, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty(steps, bsz, H, D, dtype=torch.bfloat16, device="cuda")
+    o32_b = torch.empty(steps, bsz, H, D, dtype=torch.float32, device="cuda")
+    for s in range(steps):
+        hk.cuda_causal_conv1d_update(xd[s].reshape(bsz, dim, 1), cs_a, None, wd, bd, qkv_a[s], bsz, dim, 1, 4, 4, True, False)
+        hk.cuda_recurrent_gated_delta_rule(qkv_a[s], g_all[s], beta_all[s], st_a, out_a[s], bsz, 1, H, H, D, D, 1, None, True, False)
+        hk.kda_decode_step(xd[s], cs_b, wd, bd, g_all[s], beta_all[s], st_b, out_b[s], bsz, H, out_f32=o32_b[s], conv_out=qkv_b[s])
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(qkv_a.reshape(steps, bsz, dim)), bits(qkv_b)), "convolved q|k|v"
+    assert np.array_equal(bits(cs_a), bits(cs_b)), "rolling window"
+    assert np.array_equal(st_a.cpu().numpy(), st_b.cpu().numpy()), "recurrent state"
+    assert np.array_equal(bits(out_a.reshape(steps, bsz, H, D)), bits(out_b)), "outputs"
+    # first token against the oracle (conv, then recurrence)
+    qkv0, _ = orc.conv1d_update(np.ascontiguousarray(x[0]).reshape(bsz, dim, 1), cst0, w, bias, bsz, dim, 1, 4, 4)
+    assert np.array_equal(qkv0.reshape(bsz, dim), bits(qkv_b[0])) or \
+        bf16_ulp_diff(qkv0.reshape(bsz, dim), bits(qkv_b[0])).max() <= 1
+    _, o_32, _ = orc.kda_recurrent(bits(qkv_b[0]).reshape(bsz, 1, dim), np.ascontiguousarray(gates["g"][:, :1]),
+                                   np.ascontiguousarray(gates["beta"][:, :1]), s0, bsz, 1, H, H, D, D)
+    assert max_rel(o32_b[0].cpu().numpy().reshape(bsz, 1, H, D), o_32) < 2e-3
