@@ -191,6 +191,47 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_trunk_case(args):
+    """The whole hybrid trunk's attention path (34 KDA + 11 MLA layers, shapes of the benchmark configurations) on a
+    synthetic sequence: prefill in 4,096-token chunks, then decode steps; device-timed.  Reports prefill tok/s, decode
+    us per token and the share of every stage (CUDA events around each call, summed over layers and chunks)."""
+    import torch
+    import helios_glm53flash_b200 as hk
+    from helios_glm53flash_b200.trunk import TrunkAttention
+    hk.load_library()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    ctx, B, chunk, steps = args.trunk_ctx, args.trunk_batch, 4096, args.trunk_decode
+    tr = TrunkAttention(n_kda=34, n_mla=11, heads=HEADS, batch=B, max_ctx=ctx + steps + 64, max_chunk=chunk, seed=0, fused=True)
+    tr.run_chunk(0, chunk)                                  # warm-up chunk (its rows are overwritten by the timed run)
+    torch.cuda.synchronize()
+    for st in tr.rec_state + tr.conv_state:
+        st.zero_()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    tr.prefill(ctx, chunk, timed=True)
+    e1.record()
+    shares = tr.stage_shares()
+    for s in range(steps):
+        tr.run_chunk(ctx + s, 1)
+    e2.record()
+    torch.cuda.synchronize()
+    status = hk.read_device_status()
+    pre_ms, dec_ms = e0.elapsed_time(e1), e1.elapsed_time(e2)
+    tot = sum(shares.values())
+    # decode again as one CUDA graph per step position is not possible (positions change); the host-launched figure
+    # is what an engine without graphs sees
+    line = {"metric": "trunk_attention_prefill_tokens_per_s", "value": B * ctx / (pre_ms * 1e-3), "unit": "tok/s", "n_gpus": 1,
+            "higher_is_better": True, "data": "synthetic", "dtype": "bf16 / fp16 in, fp32 accumulate + state",
+            "config": {"workload": "34 KDA + 11 MLA attention layers in the engine's call order, %d sequence(s) x %d tokens, "
+                                   "prefill in %d-token chunks, then %d decode steps" % (B, ctx, chunk, steps)},
+            "prefill_ms": pre_ms, "prefill_ms_per_chunk": pre_ms / (ctx / chunk),
+            "decode_us_per_token_host_launched": 1e3 * dec_ms / max(steps, 1),
+            "stage_share_of_prefill": {k: v / tot for k, v in sorted(shares.items(), key=lambda kv: -kv[1])},
+            "stage_ms_total": {k: v for k, v in sorted(shares.items(), key=lambda kv: -kv[1])},
+            "device_status": status}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,12 +241,22 @@ def main():
     ap.add_argument("--tokens", type=int, default=T_FULL, help="sequence length (default: the benchmark's 32768)")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / MLA side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--case", default="kda_prefill", choices=["kda_prefill", "trunk"],
+                    help="kda_prefill: the headline line (default).  trunk: the 34 KDA + 11 MLA attention stack in the engine's "
+                         "call order, prefill in 4,096-token chunks then decode (one GPU; its own JSON line)")
+    ap.add_argument("--trunk-ctx", type=int, default=32768, help="tokens prefetched by --case trunk (the full configuration is 262144)")
+    ap.add_argument("--trunk-batch", type=int, default=1, help="sequences of --case trunk (the batched configuration is 8 x 32768)")
+    ap.add_argument("--trunk-decode", type=int, default=64, help="decode steps after the prefill of --case trunk")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.case == "trunk":
+        if rank == 0:
+            run_trunk_case(args)
         return
 
     import numpy as np
@@ -276,10 +327,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: nvidia-smi needs a moment to come up
     for _ in range(warmup):
         path = step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -291,7 +342,18 @@ def main():
     barrier()
     t_end = time.time()
     ms_total = e0.elapsed_time(e1)
+    clocks = None
     if sampler:
+        clocks = sampler.summary(t_begin, t_end)
+        if clocks.get("samples", 0) < 3 or "no sample" in clocks.get("note", ""):
+            # the timed region was shorter than a few sampling periods: the same loop runs on, untimed, for 0.4 s
+            t_c0 = time.time()
+            while time.time() - t_c0 < 0.4:
+                for _ in range(10):
+                    step()
+                torch.cuda.synchronize()
+            clocks = sampler.summary(t_c0 + 0.05, time.time())
+            clocks["note"] = "timed region of %.0f ms too short to sample: the same step loop continued untimed for 0.4 s, samples from there" % ms_total
         sampler.stop()
     conv_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / steps
     kda_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / steps
@@ -396,7 +458,7 @@ def main():
                     "pipeline": "%d segments of %d tokens on copy-in / compute / copy-out streams" % (n_seg, seg),
                     "equals_one_launch_result": e2e_matches},
             "gpu_launches": 2 * steps,
-            "clocks": sampler.summary(t_begin, t_end),
+            "clocks": clocks,
             "extras": extras,
         }
         if multi is not None:

@@ -29,7 +29,7 @@ SIGNATURES = {
     "hk_abi_version": (_i, []),
     "hk_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
-    "hk_kda_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "hk_kda_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]),
     "hk_kda_chunked_set_form": (_i, [_i]),
     "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
     "hk_kda_chunked_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
@@ -179,12 +179,23 @@ def cuda_recurrent_gated_delta_rule(mixed_qkv, g, beta, recurrent_state, core_at
     return "recurrent"
 
 
+_decode_tickets = {}
+
+
 def kda_decode_step(x, conv_state, conv_weight, conv_bias, g, beta, rec_state, out, bsz, num_heads, slots=None,
-                    out_f32=None, conv_out=None, stream=None):
+                    out_f32=None, conv_out=None, stream=None, tickets=None):
     """cuda_causal_conv1d_update(seqlen 1, K = 4, SiLU) + cuda_recurrent_gated_delta_rule(seqlen 1, channelwise) of one
-    decoded token (src/engine/runner.cpp:443-471) in one launch; head dim 128."""
+    decoded token (src/engine/runner.cpp:443-471) in one launch; head dim 128.  `tickets`: bsz * num_heads zeroed
+    int32 on the device (one buffer per device is kept here when none is given: single-stream use)."""
+    if tickets is None:
+        torch = _require_cuda()
+        key = (x.device.index, bsz * num_heads)
+        tickets = _decode_tickets.get(key)
+        if tickets is None:
+            tickets = _decode_tickets[key] = torch.zeros(bsz * num_heads, dtype=torch.int32, device=x.device)
     _call("hk_kda_decode_step", _ptr(x), _ptr(conv_state), _ptr(conv_weight), _ptr(conv_bias), _ptr(g), _ptr(beta),
-          _ptr(rec_state), _ptr(out), _ptr(out_f32), _ptr(conv_out), bsz, num_heads, _ptr(slots), _stream(stream))
+          _ptr(rec_state), _ptr(out), _ptr(out_f32), _ptr(conv_out), bsz, num_heads, _ptr(slots), _ptr(tickets),
+          _stream(stream))
 
 
 def kda_chunked_set_form(form):

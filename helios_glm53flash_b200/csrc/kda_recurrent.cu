@@ -141,26 +141,29 @@ __global__ __launch_bounds__(128) void kda_recurrent_kernel(
 // Decode step with the short convolution inside: x -> conv(K = 4) + SiLU -> bf16 q|k|v -> recurrence, one launch.
 // The reference runs cuda_causal_conv1d_update and cuda_recurrent_gated_delta_rule back to back for every decoded
 // token (src/engine/runner.cpp:443-471); at 2-3 us per launch the pair is bound by launch latency, not by the 4 MB
-// of state.  Same grid as the recurrence, (batch, head, value slice), with the slices of a head forming a thread-
-// block CLUSTER: every CTA convolves the head's 128 q and 128 k channels itself (from the window state as it was
-// before the call) and the value channels of its slice; the rolling window of the q / k channels is written back by
-// slice 0 only, after a cluster barrier that tells it the other slices have read the old window.  Arithmetic and
-// rounding are those of the two separate kernels, so results are bit-identical to calling them in turn.
+// of state.  Same grid as the recurrence, (batch, head, value slice): every CTA convolves the head's 128 q and 128 k
+// channels itself (from the window state as it was before the call) and the value channels of its slice; the rolling
+// window of the q / k channels is written back once, by whichever slice of the head is the LAST to have read it (a
+// ticket counter per (batch, head) in caller memory; nobody waits for anybody).  Arithmetic and rounding are those of
+// the two separate kernels, so results are bit-identical to calling them in turn.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float conv4_silu_bf16(const __nv_bfloat16* __restrict__ st, const __nv_bfloat16* __restrict__ w,
-                                                 float bias, float cur) {
+// window and taps of one channel arrive as one 8-byte load each
+__device__ __forceinline__ float conv4_silu_bf16(uint2 st, uint2 w, float bias, float cur) {
   // fp32 fma chain over the window [st1, st2, st3, x], taps ascending; SiLU as a / (1 + exp(-a)); rounded to bf16
   float acc = bias;
-  acc = fmaf(__bfloat162float(w[0]), __bfloat162float(st[1]), acc);
-  acc = fmaf(__bfloat162float(w[1]), __bfloat162float(st[2]), acc);
-  acc = fmaf(__bfloat162float(w[2]), __bfloat162float(st[3]), acc);
-  acc = fmaf(__bfloat162float(w[3]), cur, acc);
+  acc = fmaf(bf16lo(w.x), bf16hi(st.x), acc);
+  acc = fmaf(bf16hi(w.x), bf16lo(st.y), acc);
+  acc = fmaf(bf16lo(w.y), bf16hi(st.y), acc);
+  acc = fmaf(bf16hi(w.y), cur, acc);
   acc = acc * (1.0f / (1.0f + __expf(-acc)));
   return __bfloat162float(__float2bfloat16_rn(acc));
 }
-__device__ __forceinline__ void conv4_roll(__nv_bfloat16* __restrict__ st, __nv_bfloat16 cur) {
-  const __nv_bfloat16 a = st[1], b = st[2], c = st[3];
-  st[0] = a; st[1] = b; st[2] = c; st[3] = cur;
+// new window [st1, st2, st3, x]
+__device__ __forceinline__ uint2 conv4_rolled(uint2 st, __nv_bfloat16 cur) {
+  uint2 r;
+  r.x = (st.x >> 16) | (st.y << 16);
+  r.y = (st.y >> 16) | ((uint32_t)__bfloat16_as_ushort(cur) << 16);
+  return r;
 }
 
 template <int NV>
@@ -168,7 +171,7 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ conv_w,
     const __nv_bfloat16* __restrict__ conv_bias, const float* __restrict__ g, const __nv_bfloat16* __restrict__ beta,
     float* __restrict__ state, __nv_bfloat16* __restrict__ out, float* __restrict__ out_f32,
-    __nv_bfloat16* __restrict__ conv_out, int H, float scale, const int* __restrict__ slots) {
+    __nv_bfloat16* __restrict__ conv_out, int H, float scale, const int* __restrict__ slots, int* __restrict__ tickets) {
   constexpr int D = 128;
   constexpr int KG = 128 / NV, RPT = D / KG;
   const int b = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * NV;
@@ -180,6 +183,7 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
   __shared__ float sh_q[D], sh_k[D], sh_d[D];
   __shared__ float sh_red[2][4];
   __shared__ float sh_part[2][KG][NV];
+  __shared__ int sh_last;
 
   float S[RPT];
 #pragma unroll
@@ -190,14 +194,12 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
   __nv_bfloat16* cs = conv_state + (size_t)slot * dim * 4;
   const int cq = head * D + tid, ck = (H + head) * D + tid, cv = (2 * H + head) * D + v0 + j;
   const __nv_bfloat16 xq = xb[cq], xk = xb[ck], xv = xb[cv];
-  const float q = conv4_silu_bf16(cs + (size_t)cq * 4, conv_w + (size_t)cq * 4, conv_bias ? __bfloat162float(conv_bias[cq]) : 0.f,
-                                  __bfloat162float(xq));
-  const float k = conv4_silu_bf16(cs + (size_t)ck * 4, conv_w + (size_t)ck * 4, conv_bias ? __bfloat162float(conv_bias[ck]) : 0.f,
-                                  __bfloat162float(xk));
-  const float v = conv4_silu_bf16(cs + (size_t)cv * 4, conv_w + (size_t)cv * 4, conv_bias ? __bfloat162float(conv_bias[cv]) : 0.f,
-                                  __bfloat162float(xv));
-  // every slice of the head has now read the old q / k window
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  const uint2 sq4 = *reinterpret_cast<const uint2*>(cs + (size_t)cq * 4), wq4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)cq * 4));
+  const uint2 sk4 = *reinterpret_cast<const uint2*>(cs + (size_t)ck * 4), wk4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)ck * 4));
+  const uint2 sv4 = *reinterpret_cast<const uint2*>(cs + (size_t)cv * 4), wv4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)cv * 4));
+  const float q = conv4_silu_bf16(sq4, wq4, conv_bias ? __bfloat162float(conv_bias[cq]) : 0.f, __bfloat162float(xq));
+  const float k = conv4_silu_bf16(sk4, wk4, conv_bias ? __bfloat162float(conv_bias[ck]) : 0.f, __bfloat162float(xk));
+  const float v = conv4_silu_bf16(sv4, wv4, conv_bias ? __bfloat162float(conv_bias[cv]) : 0.f, __bfloat162float(xv));
   const float gv = g[((size_t)b * H + head) * D + tid];
   const float beta_h = __bfloat162float(beta[(size_t)b * H + head]);
 
@@ -219,10 +221,14 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
     sh_k[tid] = k * rsqrtf(tk + 1e-6f);
     sh_d[tid] = __expf(gv);
   }
+  // every thread of this CTA has read the old q / k window (first barrier): thread 0 takes a ticket now and looks at it
+  // at the end of the kernel, so the round trip of the atomic runs under the recurrence
+  int ticket = 0;
+  if (tid == 0) ticket = atomicAdd(tickets + (size_t)b * H + head, 1);
   __syncthreads();
   // the value window of this slice is private to the CTA: every thread has read it (barrier above)
   if (kg == 0) {
-    conv4_roll(cs + (size_t)cv * 4, xv);
+    *reinterpret_cast<uint2*>(cs + (size_t)cv * 4) = conv4_rolled(sv4, xv);
     if (conv_out) conv_out[(size_t)b * dim + cv] = __float2bfloat16_rn(v);
   }
   float sum = 0.f;
@@ -258,11 +264,17 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
   }
 #pragma unroll
   for (int i = 0; i < RPT; i++) my_state[(size_t)i * D] = S[i];
-  // slice 0 rolls the q / k windows once every slice of the cluster has read them
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (blockIdx.z == 0) {
-    conv4_roll(cs + (size_t)cq * 4, xq);
-    conv4_roll(cs + (size_t)ck * 4, xk);
+  // The slice that drew the last ticket knows that every slice of the head has read the q / k window: it rolls the
+  // window and leaves the counter at zero for the next call.
+  if (tid == 0) {
+    const int last = ticket == (int)gridDim.z - 1;
+    if (last) tickets[(size_t)b * H + head] = 0;
+    sh_last = last;
+  }
+  __syncthreads();
+  if (sh_last) {
+    *reinterpret_cast<uint2*>(cs + (size_t)cq * 4) = conv4_rolled(sq4, xq);
+    *reinterpret_cast<uint2*>(cs + (size_t)ck * 4) = conv4_rolled(sk4, xk);
     if (conv_out) {
       conv_out[(size_t)b * dim + cq] = __float2bfloat16_rn(q);
       conv_out[(size_t)b * dim + ck] = __float2bfloat16_rn(k);
@@ -273,24 +285,10 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
 template <int NV>
 static int launch_decode_conv(const __nv_bfloat16* x, __nv_bfloat16* conv_state, const __nv_bfloat16* w, const __nv_bfloat16* bias,
                               const float* g, const __nv_bfloat16* beta, float* state, __nv_bfloat16* out, float* out_f32,
-                              __nv_bfloat16* conv_out, int bsz, int H, const int* slots, cudaStream_t s) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(bsz, H, 128 / NV);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 128 / NV;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const float scale = 1.0f / sqrtf(128.0f);
-  return cudaLaunchKernelEx(&cfg, kda_decode_conv_kernel<NV>, x, conv_state, w, bias, g, beta, state, out, out_f32, conv_out, H,
-                            scale, slots) == cudaSuccess
-             ? HK_OK
-             : HK_ERR_CUDA;
+                              __nv_bfloat16* conv_out, int bsz, int H, const int* slots, int* tickets, cudaStream_t s) {
+  kda_decode_conv_kernel<NV><<<dim3(bsz, H, 128 / NV), 128, 0, s>>>(x, conv_state, w, bias, g, beta, state, out, out_f32, conv_out,
+                                                                    H, 1.0f / sqrtf(128.0f), slots, tickets);
+  return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 
 template <int D, int NV>
@@ -345,9 +343,9 @@ HK_API int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* b
 
 HK_API int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_weight, const void* conv_bias, const float* g,
                               const void* beta, float* rec_state, void* out, float* out_f32, void* conv_out, int bsz,
-                              int num_heads, const int* slots, void* stream) {
+                              int num_heads, const int* slots, int* tickets, void* stream) {
   using namespace hk;
-  HK_REQUIRE(x && conv_state && conv_weight && g && beta && rec_state && out);
+  HK_REQUIRE(x && conv_state && conv_weight && g && beta && rec_state && out && tickets);
   HK_REQUIRE(bsz > 0 && bsz <= 65535 && num_heads > 0 && num_heads <= 65535);
   auto xb = (const __nv_bfloat16*)x;
   auto cs = (__nv_bfloat16*)conv_state;
@@ -358,6 +356,6 @@ HK_API int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_
   auto co = (__nv_bfloat16*)conv_out;
   cudaStream_t s = as_stream(stream);
   const bool narrow = (long)bsz * num_heads * 4 < sm_count();
-  return narrow ? launch_decode_conv<16>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, s)
-                : launch_decode_conv<32>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, s);
+  return narrow ? launch_decode_conv<16>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, tickets, s)
+                : launch_decode_conv<32>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, tickets, s);
 }

@@ -74,10 +74,13 @@ int hk_kda_recurrent(const void* mixed_qkv, const float* g, const void* beta, fl
  *   x [bsz][3*H*128] bf16 (the token's pre-conv q|k|v)   conv_state [slots][3*H*128][4] bf16 (in place)
  *   conv_weight [3*H*128][4] bf16   conv_bias [3*H*128] bf16 or NULL   g [bsz][H][128] f32   beta [bsz][H] bf16
  *   rec_state [slots][H][128][128] f32 (in place)   out [bsz][H][128] bf16 (rz)   out_f32 optional
- *   conv_out optional [bsz][3*H*128] bf16: the convolved q|k|v (what the two-kernel sequence leaves in between). */
+ *   conv_out optional [bsz][3*H*128] bf16: the convolved q|k|v (what the two-kernel sequence leaves in between).
+ *   tickets: bsz*H device ints, zero before the first call; every call leaves them zero (the slices of a head count
+ *   themselves there to find out which one rolls the head's q / k window).  Calls that share `tickets` must not
+ *   overlap on the GPU.                                                                                          */
 int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_weight, const void* conv_bias, const float* g,
                        const void* beta, float* rec_state, void* out, float* out_f32, void* conv_out, int bsz,
-                       int num_heads, const int* slots, void* stream);
+                       int num_heads, const int* slots, int* tickets, void* stream);
 
 /* Chunked (64-token) KDA prefill on the tensor cores; numerically equivalent to
  * hk_kda_recurrent(channelwise=1, history=0) on the same arguments (the reference has no chunked
