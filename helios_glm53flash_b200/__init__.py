@@ -31,6 +31,7 @@ SIGNATURES = {
     "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "hk_kda_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]),
     "hk_kda_chunked_set_form": (_i, [_i]),
+    "hk_kda_dispatch_is_chunked": (_i, [_i, _i, _i, _i, _i, _i, _i, _i]),
     "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
     "hk_kda_chunked_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "hk_kda_chunked_prefill_gated": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
@@ -46,10 +47,10 @@ SIGNATURES = {
     "hk_pool_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "hk_mla_partial_bytes": (_sz, [_i, _i64]),
     "hk_mla_auto_splits": (_i, [_i, _i]),
-    "hk_mla_sparse": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "hk_mla_sparse": (_i, [_vp, _vp, _i64, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
     "hk_mla_sparse_static_max_slots": (_sz, []),
     "hk_mla_sparse_static": (_i, [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _vp]),
-    "hk_mla_dense": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "hk_mla_dense": (_i, [_vp, _vp, _i64, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp, _sz, _vp]),
     "hk_mla_dense_partial": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "hk_mla_dense_partial_ws": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "hk_lse_combine": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _vp]),
@@ -132,10 +133,15 @@ def _call(name, *args):
         raise HeliosB200Error(name, st)
 
 
-def _scratch(nbytes, device):
-    """A torch-owned scratch buffer (256-byte aligned by the caching allocator)."""
+def _scratch(nbytes, device, stream=None):
+    """A torch-owned scratch buffer (256-byte aligned by the caching allocator).  The kernels that use it run on
+    `stream`; when that is not torch's current stream the block is recorded on it, so that the caching allocator
+    does not hand it out again while they still run."""
     torch = _require_cuda()
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    if stream is not None and stream != torch.cuda.current_stream():
+        ws.record_stream(stream)
+    return ws
 
 
 # ---------------------------------------------------------------------------------------------
@@ -158,12 +164,12 @@ def cuda_recurrent_gated_delta_rule(mixed_qkv, g, beta, recurrent_state, core_at
     As the C++ launcher of this library does, long channelwise calls go to the chunked tensor-core
     kernel; ``force_recurrent`` keeps the per-token kernel.  ``out_f32`` optionally receives the
     output before bf16 rounding."""
-    chunked = (channelwise and not history and seqlen >= 64 and k_head_dim == 128 and
-               v_head_dim == 128 and num_k_heads == num_v_heads and history_stride == 1 and
-               not force_recurrent)
+    chunked = not force_recurrent and load_library().hk_kda_dispatch_is_chunked(
+        seqlen, num_k_heads, num_v_heads, k_head_dim, v_head_dim, history_stride, int(bool(channelwise)),
+        int(bool(history))) != 0
     if chunked:
         nbytes = load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_v_heads)
-        ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device)
+        ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device, stream)
         st = load_library().hk_kda_chunked_prefill(
             _ptr(mixed_qkv), _ptr(g), _ptr(beta), _ptr(recurrent_state), _ptr(core_attn_out),
             _ptr(out_f32), bsz, seqlen, num_v_heads, _ptr(slots), _ptr(ws), ws.numel(),
@@ -213,7 +219,7 @@ def kda_chunked_prefill_gated(mixed_qkv, f, b, dt_bias, a_log, lower_bound, recu
     logit ``b`` and the layer's ``dt_bias`` / ``a_log`` (the arithmetic of helios::glue::kda_gate,
     src/engine/glue2.cu:347-360), head dim 128."""
     nbytes = load_library().hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads)
-    ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device)
+    ws = workspace if workspace is not None else _scratch(nbytes, mixed_qkv.device, stream)
     _call("hk_kda_chunked_prefill_gated", _ptr(mixed_qkv), _ptr(f), _ptr(b), _ptr(dt_bias), _ptr(a_log),
           float(lower_bound), _ptr(recurrent_state), _ptr(core_attn_out), _ptr(out_f32), bsz, seqlen,
           num_heads, _ptr(slots), _ptr(ws), ws.numel(), _stream(stream))
@@ -322,15 +328,23 @@ def mla_partial_bytes(n_split, rows):
     return load_library().hk_mla_partial_bytes(n_split, rows)
 
 
+def _cache_rows(ckv, ckv_rows):
+    """rows of a [rows][512] cache tensor (0 = unknown, for buffers that are not laid out that way)"""
+    if ckv_rows is not None:
+        return int(ckv_rows)
+    return int(ckv.numel() // 512) if ckv.dim() >= 1 and ckv.numel() % 512 == 0 else 0
+
+
 def mla_sparse_decode(q_lat, ckv, raw_idx, kidx, lat_out, m, stream=None, scale=0.0625, n_heads=64,
-                      n_split=0, workspace=None):
-    """helios::attn::mla_sparse_decode (src/cuda/attn/attn.cuh:93-99) with explicit scale / heads."""
+                      n_split=0, workspace=None, ckv_rows=None):
+    """helios::attn::mla_sparse_decode (src/cuda/attn/attn.cuh:93-99) with explicit scale / heads; the cache's row
+    count is taken from the tensor, so row numbers beyond it are skipped instead of read."""
     if n_split <= 0:
         n_split = mla_auto_splits(m, kidx)
     ws = workspace
     if n_split > 1 and ws is None:
-        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device)
-    _call("hk_mla_sparse", _ptr(q_lat), _ptr(ckv), _ptr(raw_idx), kidx, _ptr(lat_out), m, n_heads,
+        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device, stream)
+    _call("hk_mla_sparse", _ptr(q_lat), _ptr(ckv), _cache_rows(ckv, ckv_rows), _ptr(raw_idx), kidx, _ptr(lat_out), m, n_heads,
           float(scale), n_split, _ptr(ws), 0 if ws is None else ws.numel(), _stream(stream))
 
 
@@ -344,15 +358,15 @@ def mla_sparse_decode_static(q_lat, ckv, raw_idx, kidx, lat_out, m, stream=None,
 
 
 def mla_dense_prefill(q_lat, ckv, lat_out, qlen, pos_start, stream=None, scale=0.0625, n_heads=64,
-                      kv_base=None, kv_len=None, n_split=0, workspace=None, n_keys_hint=None):
+                      kv_base=None, kv_len=None, n_split=0, workspace=None, n_keys_hint=None, ckv_rows=None):
     """helios::attn::mla_dense_prefill (src/cuda/attn/attn.cuh:104-108); qlen = 1 is dense decode.
     kv_base / kv_len (device int64 / int32 per row) select per-row cache ranges (batched decode)."""
     if n_split <= 0:
         n_split = mla_auto_splits(qlen, n_keys_hint if n_keys_hint else pos_start + qlen)
     ws = workspace
     if n_split > 1 and ws is None:
-        ws = _scratch(mla_partial_bytes(n_split, qlen * n_heads), q_lat.device)
-    _call("hk_mla_dense", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start,
+        ws = _scratch(mla_partial_bytes(n_split, qlen * n_heads), q_lat.device, stream)
+    _call("hk_mla_dense", _ptr(q_lat), _ptr(ckv), _cache_rows(ckv, ckv_rows), _ptr(kv_base), _ptr(kv_len), pos_start,
           _ptr(lat_out), qlen, n_heads, float(scale), n_split, _ptr(ws),
           0 if ws is None else ws.numel(), _stream(stream))
 
@@ -371,7 +385,7 @@ def mla_dense_partial_ws(q_lat, ckv, kv_base, kv_len, pos_start, part_m, part_l,
         n_split = mla_auto_splits(m, n_keys_hint)
     ws = workspace
     if n_split > 1 and ws is None:
-        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device)
+        ws = _scratch(mla_partial_bytes(n_split, m * n_heads), q_lat.device, stream)
     _call("hk_mla_dense_partial_ws", _ptr(q_lat), _ptr(ckv), _ptr(kv_base), _ptr(kv_len), pos_start, _ptr(part_m),
           _ptr(part_l), _ptr(part_acc), m, n_heads, float(scale), n_split, n_keys_hint, _ptr(ws),
           0 if ws is None else ws.numel(), _stream(stream))

@@ -1334,6 +1334,14 @@ size_t fused_flag_bytes(int n_jobs) {
 }  // namespace
 }  // namespace hk
 
+HK_API int hk_kda_dispatch_is_chunked(int seqlen, int num_k_heads, int num_v_heads, int k_head_dim, int v_head_dim,
+                                      int history_stride, int channelwise, int history) {
+  return (channelwise && !history && seqlen >= hk::KC && k_head_dim == hk::KD && v_head_dim == hk::KD &&
+          num_k_heads == num_v_heads && history_stride == 1)
+             ? 1
+             : 0;
+}
+
 HK_API int hk_kda_chunked_set_form(int form) {
   if (form != 0 && form != 1) return HK_ERR_INVALID;
   hk::g_chunked_form = form;

@@ -7,6 +7,8 @@ namespace hk {
 struct MlaArgs {
   const __half* q_lat;      // [m][n_heads][512]
   const __half* ckv;        // [*][512]
+  int64_t ckv_rows;         // rows the cache holds (0 = not told): gathered indices beyond it count as holes, dense
+                            // ranges are cut there, and the tensor map of the dense path gets this extent
   const int* raw_idx;       // sparse: [m][kidx]; dense: null
   int kidx;
   const int64_t* kv_base;   // dense: per-row first key (null = 0)

@@ -156,16 +156,16 @@ HK_API int hk_mla_auto_splits(int m, int n_keys) {
   return hk::force_simt() ? hk::simt_auto_splits(m, 64, n_keys) : hk::mla_flash_tc_auto_splits(m, n_keys);
 }
 
-HK_API int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx, int kidx,
+HK_API int hk_mla_sparse(const void* q_lat, const void* ckv, int64_t ckv_rows, const int* raw_idx, int kidx,
                          void* lat_out, int m, int n_heads, float scale, int n_split,
                          void* workspace, size_t workspace_bytes, void* stream) {
   using namespace hk;
-  HK_REQUIRE(q_lat && ckv && raw_idx && lat_out);
+  HK_REQUIRE(q_lat && ckv && raw_idx && lat_out && ckv_rows >= 0);
   HK_REQUIRE(m >= 0 && kidx >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
   HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(lat_out, 16));
   if (m == 0) return HK_OK;
   MlaArgs a{};
-  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv; a.ckv_rows = ckv_rows;
   a.raw_idx = raw_idx; a.kidx = kidx;
   a.m = m; a.n_heads = n_heads; a.scale = scale;
   a.out = (__half*)lat_out;
@@ -241,17 +241,19 @@ HK_API int hk_mla_sparse_static(const void* q_lat, const void* ckv, const int* r
   return attend(a, kidx, n_split, scratch, HK_STATIC_SCRATCH_BYTES, as_stream(stream));
 }
 
-HK_API int hk_mla_dense(const void* q_lat, const void* ckv, const int64_t* kv_base,
+HK_API int hk_mla_dense(const void* q_lat, const void* ckv, int64_t ckv_rows, const int64_t* kv_base,
                         const int* kv_len, int pos_start, void* lat_out, int m, int n_heads,
                         float scale, int n_split, void* workspace, size_t workspace_bytes,
                         void* stream) {
   using namespace hk;
-  HK_REQUIRE(q_lat && ckv && lat_out);
+  HK_REQUIRE(q_lat && ckv && lat_out && ckv_rows >= 0);
   HK_REQUIRE(m >= 0 && pos_start >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  // causal form (no per-row arrays): the last row attends rows 0 .. pos_start + m - 1, which must exist
+  if (ckv_rows > 0 && !kv_base && !kv_len) HK_REQUIRE((int64_t)pos_start + m <= ckv_rows);
   HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv, 16) && aligned(lat_out, 16));
   if (m == 0) return HK_OK;
   MlaArgs a{};
-  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv;
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv; a.ckv_rows = ckv_rows;
   a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = pos_start;
   a.m = m; a.n_heads = n_heads; a.scale = scale;
   a.out = (__half*)lat_out;

@@ -129,7 +129,10 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   else {
     n = a.kv_len ? a.kv_len[r] : a.pos_start + r + 1;
     base = a.kv_base ? a.kv_base[r] : 0;
+    if (a.ckv_rows > 0) n = (int)max((int64_t)0, min((int64_t)n, a.ckv_rows - base));   // never past the end of the cache
   }
+  // gathered row numbers beyond the cache are holes
+  auto in_cache = [&](int tk) -> int { return (a.ckv_rows > 0 && (int64_t)tk >= a.ckv_rows) ? -1 : tk; };
   // split boundaries on tile granularity
   const int tiles_total = (n + FT_KEYS - 1) / FT_KEYS;
   const int tiles_per = (tiles_total + a.n_split - 1) / a.n_split;
@@ -216,7 +219,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         for (int half = 0; half < 2; half++) {
           const int pp = q0 + half * 32 + lane;
           if (half * 32 + lane < FT_KEYS && pp < k1) {
-            const int tk = a.raw_idx[(size_t)r * a.kidx + pp];
+            const int tk = in_cache(a.raw_idx[(size_t)r * a.kidx + pp]);
             if (tk >= 0) tc::prefetch_l2(a.ckv + (size_t)tk * LATENT, LATENT * 2);
           }
         }
@@ -230,11 +233,11 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     auto item_index = [&](int tile_i, int j) -> int {      // row number of item j of this warp, -1 = hole
       const int it = lw + j * FT_LOAD_WARPS;
       const int p = k0 + tile_i * FT_KEYS + (it >> 1);
-      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? a.raw_idx[(size_t)r * a.kidx + p] : -1;
+      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? in_cache(a.raw_idx[(size_t)r * a.kidx + p]) : -1;
     };
     auto mask_index = [&](int tile_i, int half) -> int {   // warp 0: row number of key half*32 + lane
       const int p = k0 + tile_i * FT_KEYS + half * 32 + lane;
-      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? a.raw_idx[(size_t)r * a.kidx + p] : -1;
+      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? in_cache(a.raw_idx[(size_t)r * a.kidx + p]) : -1;
     };
     int idx_next = item_index(0, lane), mk0_next = mask_index(0, 0), mk1_next = mask_index(0, 1);
     for (int tile = 0; tile < n_tiles; tile++) {
@@ -563,8 +566,8 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
       return HK_ERR_CUDA;
     attr_set[dev] = true;
   }
-  // tensor map over the latent cache for the dense path: [row][block 8][64 x fp16]; the row extent is
-  // only an upper bound for the copy engine's bounds check (rows are addressed by coordinate)
+  // tensor map over the latent cache for the dense path: [row][block 8][64 x fp16]; the row extent is the cache's
+  // row count when the caller gave it (the copy engine then zero-fills anything past the end), else an upper bound
   alignas(64) CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   int use_tma = 0;
@@ -584,7 +587,7 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
       looked_up = true;
     }
     if (encode) {
-      const cuuint64_t dims[3] = {64, (cuuint64_t)1 << 31, 8};
+      const cuuint64_t dims[3] = {64, a.ckv_rows > 0 ? (cuuint64_t)a.ckv_rows : (cuuint64_t)1 << 31, 8};
       const cuuint64_t strides[2] = {LATENT * 2, 128};
       const cuuint32_t box[3] = {64, FT_KEYS, 8};
       const cuuint32_t estr[3] = {1, 1, 1};

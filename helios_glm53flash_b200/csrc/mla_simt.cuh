@@ -29,6 +29,7 @@ __global__ __launch_bounds__(256) void mla_simt_kernel(MlaArgs a) {
   else {
     n = a.kv_len ? a.kv_len[r] : a.pos_start + r + 1;
     base = a.kv_base ? a.kv_base[r] : 0;
+    if (a.ckv_rows > 0) n = (int)max((int64_t)0, min((int64_t)n, a.ckv_rows - base));
   }
   const int per = (n + a.n_split - 1) / a.n_split;
   const int k0 = sp * per, k1 = min(n, k0 + per);
@@ -57,7 +58,7 @@ __global__ __launch_bounds__(256) void mla_simt_kernel(MlaArgs a) {
   }
   for (int i = k0 + wid; i < k1; i += 8) {
     int64_t tok = sparse ? (int64_t)a.raw_idx[(size_t)r * a.kidx + i] : base + i;
-    if (tok < 0) continue;  // warp-uniform
+    if (tok < 0 || (a.ckv_rows > 0 && tok >= a.ckv_rows)) continue;  // warp-uniform
     const __half* crow = a.ckv + (size_t)tok * LATENT + lane * 16;
     uint4 u0 = *reinterpret_cast<const uint4*>(crow), u1 = *reinterpret_cast<const uint4*>(crow + 8);
     const __half2* p0 = reinterpret_cast<const __half2*>(&u0);

@@ -23,16 +23,26 @@ void check(int status, const char* what) {
 struct Scratch {
   void* ptr = nullptr;
   size_t bytes = 0;
+  bool injected = false;   // memory handed over by the host with set_scratch: never freed or replaced here
 };
 Scratch g_scratch[64];
 
-// Grow-only scratch of the current device.  Growth synchronises the device before freeing the old
-// buffer, so kernels still using it are finished.
+// Scratch of the current device.  Host-provided memory (helios::b200::set_scratch) is used as it is and a request
+// beyond its size aborts with a message.  Otherwise the buffer is grow-only: growth synchronises the device before
+// freeing the old buffer, so kernels still using it are finished.  All launchers of a device share the buffer: they
+// are meant to run on ONE stream (as the engine's layer loop does).
 void* scratch(size_t bytes) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   Scratch& s = g_scratch[dev];
+  if (s.injected) {
+    if (s.bytes < bytes) {
+      std::fprintf(stderr, "helios_b200: the scratch given to set_scratch holds %zu bytes, a launcher needs %zu\n", s.bytes, bytes);
+      std::abort();
+    }
+    return s.ptr;
+  }
   if (s.bytes < bytes) {
     if (s.ptr) {
       cudaDeviceSynchronize();
@@ -55,10 +65,38 @@ void* scratch(size_t bytes) {
 namespace helios {
 
 namespace b200 {
+void set_scratch(void* ptr, size_t bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return;
+  release_scratch();
+  if (ptr && bytes) {
+    g_scratch[dev].ptr = ptr;
+    g_scratch[dev].bytes = bytes;
+    g_scratch[dev].injected = true;
+  }
+}
+size_t scratch_bytes_needed(int max_rows, int kda_heads, int kda_batch) {
+  // the largest request any launcher makes for calls of at most max_rows rows
+  size_t need = hk_kda_chunked_workspace_bytes(kda_batch, max_rows, kda_heads);
+  for (int m : {1, 2, 4, 8, max_rows}) {
+    if (m > max_rows) continue;
+    const int ns_sparse = hk_mla_auto_splits(m, 2052), ns_dense = hk_mla_auto_splits(m, 1 << 20);
+    const size_t a = ns_sparse > 1 ? hk_mla_partial_bytes(ns_sparse, (int64_t)m * attn::N_HEADS) : 0;
+    const size_t b = ns_dense > 1 ? hk_mla_partial_bytes(ns_dense, (int64_t)m * attn::N_HEADS) : 0;
+    need = need > a ? need : a;
+    need = need > b ? need : b;
+  }
+  return (need + 255) / 256 * 256;
+}
 void release_scratch() {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return;
+  if (g_scratch[dev].injected) {
+    g_scratch[dev] = Scratch{};
+    return;
+  }
   if (g_scratch[dev].ptr) {
     cudaDeviceSynchronize();
     cudaFree(g_scratch[dev].ptr);
@@ -118,7 +156,7 @@ void mla_sparse_decode(const half* q_lat, const half* ckv, const int* raw_idx, i
   const int n_split = hk_mla_auto_splits(m, kidx);
   size_t bytes = n_split > 1 ? hk_mla_partial_bytes(n_split, (int64_t)m * N_HEADS) : 0;
   void* ws = bytes ? scratch(bytes) : nullptr;
-  check(hk_mla_sparse(q_lat, ckv, raw_idx, kidx, lat_out, m, N_HEADS, SCALE, n_split, ws, bytes, s),
+  check(hk_mla_sparse(q_lat, ckv, 0, raw_idx, kidx, lat_out, m, N_HEADS, SCALE, n_split, ws, bytes, s),
         "mla_sparse_decode");
 }
 void mla_dense_prefill(const half* q_lat, const half* ckv, half* lat_out, int qlen, int pos_start,
@@ -127,7 +165,7 @@ void mla_dense_prefill(const half* q_lat, const half* ckv, half* lat_out, int ql
   const int n_split = hk_mla_auto_splits(qlen, pos_start + qlen);
   size_t bytes = n_split > 1 ? hk_mla_partial_bytes(n_split, (int64_t)qlen * N_HEADS) : 0;
   void* ws = bytes ? scratch(bytes) : nullptr;
-  check(hk_mla_dense(q_lat, ckv, nullptr, nullptr, pos_start, lat_out, qlen, N_HEADS, SCALE, n_split,
+  check(hk_mla_dense(q_lat, ckv, 0, nullptr, nullptr, pos_start, lat_out, qlen, N_HEADS, SCALE, n_split,
                      ws, bytes, s),
         "mla_dense_prefill");
 }
@@ -142,8 +180,8 @@ void cuda_recurrent_gated_delta_rule(const bfloat16* mixed_qkv, const float* g,
                                      int num_v_heads, int k_head_dim, int v_head_dim,
                                      int history_stride, const int* slots, bool channelwise,
                                      bool history, Stream stream) {
-  const bool chunked = channelwise && !history && seqlen >= 64 && k_head_dim == 128 &&
-                       v_head_dim == 128 && num_k_heads == num_v_heads && history_stride == 1;
+  const bool chunked = hk_kda_dispatch_is_chunked(seqlen, num_k_heads, num_v_heads, k_head_dim, v_head_dim, history_stride,
+                                                  channelwise, history) != 0;
   if (chunked) {
     size_t bytes = hk_kda_chunked_workspace_bytes(bsz, seqlen, num_v_heads);
     int st = hk_kda_chunked_prefill(mixed_qkv, g, beta, recurrent_state, core_attn_out, nullptr, bsz,

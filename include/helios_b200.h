@@ -95,6 +95,10 @@ int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_weight,
  * hk_kda_chunked_set_form(1) selects the two-kernel form for every later call and workspace query of this
  * process, hk_kda_chunked_set_form(0) the automatic choice (default).                              */
 int hk_kda_chunked_set_form(int form);
+/* The rule by which the launcher of the reference's name (helios::aux::cuda_recurrent_gated_delta_rule in the C++
+ * layer, the Python wrapper of the same name) sends a call to the chunked kernels (1) or to hk_kda_recurrent (0).  */
+int hk_kda_dispatch_is_chunked(int seqlen, int num_k_heads, int num_v_heads, int k_head_dim, int v_head_dim,
+                               int history_stride, int channelwise, int history);
 size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads);
 int hk_kda_chunked_prefill(const void* mixed_qkv, const float* g, const void* beta, float* state,
                            void* out, float* out_f32, int bsz, int seqlen, int num_heads,
@@ -204,9 +208,11 @@ int hk_mla_auto_splits(int m, int n_keys);
  * raw_idx >= 0 (duplicates count twice; all skipped -> zeros).
  * Replaces helios::attn::mla_sparse_decode (src/cuda/attn/attn.cuh:89-99, attn.cu:394-617) with an
  * explicit softmax scale and head count (the reference pins 0.0625 and 64).
- *   q_lat [m][n_heads][512] f16, ckv [*][512] f16, lat_out [m][n_heads][512] f16.
+ *   q_lat [m][n_heads][512] f16, ckv [ckv_rows][512] f16, lat_out [m][n_heads][512] f16.
+ * ckv_rows: rows the cache buffer holds; row numbers at or beyond it are treated as holes instead of being read
+ * (0 = not told, as in the reference's signature: every non-negative row number is read).
  * n_split = 0 lets the library choose; workspace may be NULL when the choice is 1.             */
-int hk_mla_sparse(const void* q_lat, const void* ckv, const int* raw_idx, int kidx, void* lat_out,
+int hk_mla_sparse(const void* q_lat, const void* ckv, int64_t ckv_rows, const int* raw_idx, int kidx, void* lat_out,
                   int m, int n_heads, float scale, int n_split, void* workspace,
                   size_t workspace_bytes, void* stream);
 
@@ -227,8 +233,11 @@ int hk_mla_sparse_static(const void* q_lat, const void* ckv, const int* raw_idx,
 /* Dense causal attention: row r attends ckv[kv_base[r] .. kv_base[r] + kv_len[r]).
  * With kv_base == NULL and kv_len == NULL: base 0 and len = pos_start + r + 1, which is
  * helios::attn::mla_dense_prefill (src/cuda/attn/attn.cuh:101-108, attn.cu:621-699); qlen = 1 is
- * dense decode, and per-row base/len arrays give batched decode over concatenated caches.       */
-int hk_mla_dense(const void* q_lat, const void* ckv, const int64_t* kv_base, const int* kv_len,
+ * dense decode, and per-row base/len arrays give batched decode over concatenated caches.
+ * ckv_rows: rows the cache buffer holds (0 = not told).  With it the causal form is checked on the host
+ * (pos_start + m <= ckv_rows, else HK_ERR_INVALID), per-row ranges are cut at the end of the cache on the device, and
+ * the copy engine's tensor map gets the real extent, so that nothing past the buffer is read.               */
+int hk_mla_dense(const void* q_lat, const void* ckv, int64_t ckv_rows, const int64_t* kv_base, const int* kv_len,
                  int pos_start, void* lat_out, int m, int n_heads, float scale, int n_split,
                  void* workspace, size_t workspace_bytes, void* stream);
 

@@ -9,10 +9,14 @@
 // src/cuda/aux/dsa_topk.cuh:15-43, src/cuda/aux/norm.cuh:71-87, src/engine/glue2.cuh:57-67); the bodies forward to the hk_* C ABI (helios_b200.h).
 //
 // Differences a maintainer should know:
-//   * the reference signatures carry no scratch pointers, so this layer keeps one grow-only device
-//     scratch buffer per GPU (cudaMalloc on first use / growth, like the reference's own
-//     dsa_topk workspace, src/cuda/aux/dsa_topk.cu:299-306); helios::b200::release_scratch()
-//     frees it.  The hk_* ABI underneath never allocates.
+//   * the reference signatures carry no scratch pointers, so this layer keeps one device scratch buffer
+//     per GPU, shared by all launchers of that GPU: call them from ONE stream, as the engine's layer
+//     loop does.  By default it is grow-only (cudaMalloc on first use / growth after a device
+//     synchronisation, like the reference's own dsa_topk workspace, src/cuda/aux/dsa_topk.cu:299-306)
+//     and helios::b200::release_scratch() frees it.  An engine that owns all device memory hands over
+//     its own block once with helios::b200::set_scratch(ptr, bytes) (size it with
+//     scratch_bytes_needed): the launchers then never allocate or synchronise, also under stream
+//     capture, and abort with a message if a call needs more.  The hk_* ABI underneath never allocates.
 //   * cuda_recurrent_gated_delta_rule runs the chunked tensor-core kernel when
 //     channelwise && !history && seqlen >= 64 && head dims are 128, and the per-token kernel
 //     otherwise; results agree within the tolerances stated in the test-suite.
@@ -21,6 +25,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <cstddef>
 
 namespace helios {
 
@@ -93,8 +99,14 @@ void layernorm_f16(const half* x, const half* w, const half* b, half* y, int row
 }  // namespace glue
 
 namespace b200 {
-// frees this layer's per-GPU scratch buffer on the current device (it regrows on demand)
+// frees this layer's per-GPU scratch buffer on the current device (it regrows on demand); forgets a host-provided one
 void release_scratch();
+// makes the launchers of the current device use `bytes` bytes at `ptr` (256-byte aligned device memory owned by the
+// host) as their scratch instead of allocating; (nullptr, 0) returns to the grow-only buffer
+void set_scratch(void* ptr, size_t bytes);
+// upper bound of what the launchers ask for when no call has more than max_rows rows (chunk length of the prefill;
+// decode calls are covered), for a KDA side of kda_batch sequences x kda_heads heads
+size_t scratch_bytes_needed(int max_rows, int kda_heads, int kda_batch = 1);
 }  // namespace b200
 
 }  // namespace helios

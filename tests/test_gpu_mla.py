@@ -333,3 +333,37 @@ def test_dense_large_logit_scale():
         assert hk.read_device_status() == 0
         g = synth.f16_bits_to_f32(bits(out))
         assert max_rel(g, o32) < TOL and sum_rel(g, o32) < 3e-3
+
+
+def test_cache_row_count_bounds_gathered_and_dense_reads():
+    """with the cache's row count given, gathered row numbers at or beyond it count as holes (nothing past the
+    buffer is read) and a causal call that would run past the end is refused on the host"""
+    T, m, kidx = 600, 2, 96
+    inp = synth.mla_inputs(T, m, seed=61, cache_std=0.5)
+    r = np.random.RandomState(3)
+    ridx = r.randint(0, T, (m, kidx)).astype(np.int32)
+    bad = ridx.copy()
+    bad[:, 1::5] = T + r.randint(0, 1000, bad[:, 1::5].shape)        # beyond the cache
+    holes = ridx.copy()
+    holes[:, 1::5] = -1
+    _, o32 = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, raw_idx=holes, kidx=kidx)
+    q, c = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    for n_split in (1, 2):
+        out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+        hk.mla_sparse_decode(q, c, dev(bad), kidx, out, m, n_split=n_split)        # ckv_rows = 600 from the tensor
+        torch.cuda.synchronize()
+        assert max_rel(synth.f16_bits_to_f32(bits(out)), o32) < TOL
+    out = torch.empty(4, 64, 512, dtype=torch.float16, device="cuda")
+    q4 = torch.zeros(4, 64, 512, dtype=torch.float16, device="cuda")
+    with pytest.raises(hk.HeliosB200Error) as e:
+        hk.mla_dense_prefill(q4, c, out, 4, T - 2)                                  # rows T-2 .. T+1 would be needed
+    assert e.value.status == hk.HK_ERR_INVALID
+    # per-row ranges are cut at the end of the cache on the device
+    base, lens = np.array([T - 100, 0], dtype=np.int64), np.array([400, 50], dtype=np.int32)
+    cut = np.array([100, 50], dtype=np.int32)
+    _, o32d = orc.mla_attend(inp["q_lat"], inp["ckv"], m, 64, 0.0625, kv_base=base, kv_len=cut)
+    out = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+    hk.mla_dense_prefill(q, c, out, m, 0, kv_base=dev(base), kv_len=dev(lens), n_keys_hint=400)
+    torch.cuda.synchronize()
+    assert hk.read_device_status() == 0
+    assert max_rel(synth.f16_bits_to_f32(bits(out)), o32d) < TOL
