@@ -20,6 +20,8 @@ import sys
 import threading
 import time
 
+import numpy as np
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -191,6 +193,382 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+
+# =====================================================================================================
+# per-kernel cases (one entry point each, small enough for a profiler capture) and the reference's own
+# kernels timed beside this library's on the same buffers
+# =====================================================================================================
+def _bits16(t, dtype):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(t).view(np.int16)).view(dtype).cuda()
+
+
+def build_kernel_case(name):
+    """returns (callable, algorithmic_bytes, needs_flush, description)"""
+    import torch
+    import helios_glm53flash_b200 as hk
+    from helios_glm53flash_b200 import synth
+    H, D = 32, 128
+    if name in ("kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512"):
+        T = {"kda_prefill_8k": 8192, "kda_prefill_32k": 32768, "kda_recurrent_512": 512}[name]
+        gates = synth.kda_gates(T, H, D, seed=1)
+        g, beta = torch.from_numpy(gates["g"]).cuda(), _bits16(gates["beta"], torch.bfloat16)
+        qkv = torch.randn(1, T, 3 * H * D, device="cuda").to(torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(hk.kda_chunked_workspace_bytes(1, T, H), dtype=torch.uint8, device="cuda")
+        force = name == "kda_recurrent_512"
+
+        def fn():
+            hk.cuda_recurrent_gated_delta_rule(qkv, g, beta, st, out, 1, T, H, H, D, D, 1, None, True, False,
+                                               workspace=ws, force_recurrent=force)
+        return fn, T * H * 1538 + 2 * H * D * D * 4, T < 8192, "KDA prefill T=%d H=32 (chunked unless 'recurrent')" % T
+    if name in ("conv_8k", "conv_32k"):
+        T = 8192 if name == "conv_8k" else 32768
+        dim = 3 * H * D
+        x = torch.randn(1, dim, T, device="cuda").to(torch.bfloat16)
+        w = (0.1 * torch.randn(dim, 4, device="cuda")).to(torch.bfloat16)
+        st = torch.zeros(1, dim, 4, dtype=torch.bfloat16, device="cuda")
+        out = torch.empty(1, T, dim, dtype=torch.bfloat16, device="cuda")
+
+        def fn():
+            hk.cuda_causal_conv1d_update(x, st, None, w, None, out, 1, dim, T, 4, 4, True, False)
+        return fn, 4 * dim * T, False, "short conv + SiLU, 12288 channels x %d tokens" % T
+    if name in ("transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k",
+                "transpose_cast_4k", "gate_4k", "gated_norm_4k", "cast_conv_4k"):
+        T = 4096 if name.endswith("_4k") else 32768
+        F = 3 * H * D
+        kind = name.rsplit("_", 1)[0]
+        if kind == "transpose_cast":
+            x = torch.randn(T, F, device="cuda")
+            dst = torch.empty(F, T, dtype=torch.bfloat16, device="cuda")
+
+            def fn():
+                hk.kda_transpose_cast(dst, x, T, F)
+            return fn, 6 * T * F, False, "transpose + cast, %d tokens x 12288 channels (fp32 in, bf16 out)" % T
+        if kind == "cast_conv":
+            x = torch.randn(1, T, F, device="cuda")
+            w = (0.1 * torch.randn(F, 4, device="cuda")).to(torch.bfloat16)
+            st = torch.zeros(1, F, 4, dtype=torch.bfloat16, device="cuda")
+            out = torch.empty(1, T, F, dtype=torch.bfloat16, device="cuda")
+
+            def fn():
+                hk.kda_cast_conv(x, st, None, w, None, out, 1, F, T, True)
+            return fn, 6 * T * F, False, "cast + short conv + SiLU from token-major fp32, %d tokens x 12288 channels" % T
+        raw = synth.kda_raw_gates(T, H, D, seed=2)
+        f, b = torch.from_numpy(raw["f"]).cuda(), torch.from_numpy(raw["b"]).cuda()
+        dtb, al = torch.from_numpy(raw["dt_bias"]).cuda(), torch.from_numpy(raw["a_log"]).cuda()
+        if kind == "gate":
+            beta = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+            g = torch.empty(T, H, D, dtype=torch.float32, device="cuda")
+
+            def fn():
+                hk.kda_gate(b, f, dtb, al, raw["lower_bound"], beta, g, T, H, D)
+            return fn, T * H * (8 * D + 6), False, "gate preparation, %d tokens x 32 heads x 128" % T
+        if kind == "gated_norm":
+            x = torch.randn(T * H, D, device="cuda").to(torch.bfloat16)
+            w = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+            y = torch.empty(T * H, D, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)
+            return fn, T * H * D * 8, False, "gated RMS norm (sigmoid), %d rows of 128 (bf16 in, fp32 gate, fp16 out)" % (T * H)
+        qkv = torch.randn(1, T, F, device="cuda").to(torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, T, H, D, dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(hk.kda_chunked_workspace_bytes(1, T, H), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.kda_chunked_prefill_gated(qkv, f, b, dtb, al, raw["lower_bound"], st, out, 1, T, H, workspace=ws)
+        return fn, T * H * 1538 + 2 * H * D * D * 4, False, "KDA prefill with the gates formed in the kernel, T=%d H=32" % T
+    if name == "kda_decode":
+        kd = synth.kda_inputs(1, H, D, seed=5)
+        q, g, b = _bits16(kd["mixed_qkv"], torch.bfloat16), torch.from_numpy(kd["g"]).cuda(), _bits16(kd["beta"], torch.bfloat16)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        o = torch.empty(1, 1, H, D, dtype=torch.bfloat16, device="cuda")
+
+        def fn():
+            hk.cuda_recurrent_gated_delta_rule(q, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)
+        return fn, 2 * H * D * D * 4 + H * 1538, True, "KDA decode step, 32 heads"
+    if name in ("mla_dense_b1", "mla_dense_b8", "mla_dense_b1_simt"):
+        B = 8 if name == "mla_dense_b8" else 1
+        L = 32768
+        ck = torch.randn(B * L, 512, dtype=torch.float16, device="cuda")
+        qd = torch.randn(B, 64, 512, dtype=torch.float16, device="cuda")
+        base = torch.from_numpy((np.arange(B) * L).astype(np.int64)).cuda()
+        lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        lo = torch.empty(B, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(B, L)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, B * 64)), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.mla_dense_prefill(qd, ck, lo, B, 0, scale=512 ** -0.5, kv_base=base, kv_len=lens, n_split=ns,
+                                 workspace=wsb, n_keys_hint=L)
+        return fn, B * L * 1024, B == 1, "dense MLA decode, batch %d x 32768 latents, %d splits" % (B, ns)
+    if name == "mla_prefill_256":
+        qlen, pos = 256, 32768
+        ck = torch.randn(pos + qlen, 512, dtype=torch.float16, device="cuda")
+        qd = torch.randn(qlen, 64, 512, dtype=torch.float16, device="cuda")
+        lo = torch.empty(qlen, 64, 512, dtype=torch.float16, device="cuda")
+
+        def fn():
+            hk.mla_dense_prefill(qd, ck, lo, qlen, pos, scale=512 ** -0.5, n_split=1)
+        return fn, (pos + qlen) * 1024 + 2 * qlen * 65536, True, "dense causal MLA prefill, 256 rows after 32768"
+    if name in ("indexer_262k", "indexer_prefill_256"):
+        npools = 65536
+        m = 1 if name == "indexer_262k" else 256
+        ix = synth.indexer_inputs(npools, m, seed=7)
+        qi, pk, w = _bits16(ix["q_idx"], torch.float16), _bits16(ix["pool_k"], torch.float16), _bits16(ix["w"], torch.float16)
+        q_pos = torch.full((m,), 4 * npools - 1, dtype=torch.int32, device="cuda")
+        sc = torch.empty(m, npools, dtype=torch.float16, device="cuda")
+
+        def fn():
+            hk.indexer_score(qi, pk, w, q_pos, sc, m, npools)
+        return fn, npools * 256 + m * npools * 2, True, "indexer scores, %d rows x 65536 pools" % m
+    if name in ("q_latent_4096", "o_absorb_4096"):
+        n = 4096
+        kb = (0.05 * torch.randn(32768, 512, device="cuda")).half()
+        if name == "q_latent_4096":
+            qn = torch.randn(n, 64, 256, device="cuda").half()
+            ql = torch.empty(n, 64, 512, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.q_latent(qn, kb, ql, n)
+        else:
+            lo = torch.randn(n, 64, 512, device="cuda").half()
+            o = torch.empty(n, 64, 256, dtype=torch.float16, device="cuda")
+
+            def fn():
+                hk.o_absorb(lo, kb, o, n)
+        return fn, n * 64 * (256 + 512) * 2 + 64 * 256 * 512 * 2, True, "absorbed projection, 4096 rows x 64 heads (68.7 GFLOP)"
+    if name == "topk_262k":
+        npools = 65536
+        sc = torch.randn(1, npools, device="cuda").half()
+        idx = torch.empty(1, 512, dtype=torch.int32, device="cuda")
+
+        def fn():
+            hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)
+        return fn, npools * 2, True, "top-512 of 65536 fp16 scores, one row"
+    if name == "sparse_262k":
+        L = 262144
+        ck = torch.randn(L, 512, dtype=torch.float16, device="cuda")
+        ql = torch.randn(1, 64, 512, dtype=torch.float16, device="cuda")
+        raw = torch.randint(0, L, (1, 2052), dtype=torch.int32, device="cuda")
+        lo = torch.empty(1, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(1, 2052)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
+        return fn, 2052 * 1024, True, "sparse MLA decode, 2052 gathered latents of 262144, %d splits" % ns
+    raise SystemExit("unknown case " + name)
+
+
+KERNEL_CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "q_latent_4096", "o_absorb_4096",
+         "transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k", "transpose_cast_4k",
+         "gate_4k", "gated_norm_4k", "cast_conv_4k"]
+
+
+
+
+def run_kernel_cases(args):
+    """`--kernel-case NAME` (or `all`): median device time of one entry point (CUDA events on the current stream, L2
+    flushed by a 256 MB write between iterations unless the working set exceeds L2 by itself), one JSON line each"""
+    import torch
+    import helios_glm53flash_b200 as hk
+    hk.load_library()
+    names = KERNEL_CASES if args.kernel_case == "all" else [args.kernel_case]
+    for name in names:
+        fn, nbytes, flush, desc = build_kernel_case(name)
+        buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize()
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            call = graph.replay
+        else:
+            call = fn
+        ts = []
+        for _ in range(args.iters):
+            if buf is not None:
+                buf.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            call()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        ms = ts[len(ts) // 2]
+        print(json.dumps({"case": name + ("+graph" if args.graph else ""), "desc": desc, "us": ms * 1e3,
+                          "algorithmic_GBps": nbytes / (ms * 1e-3) / 1e9, "device_status": hk.read_device_status()}), flush=True)
+        del fn, buf
+        torch.cuda.empty_cache()
+
+
+def _timed_us(torch, fn, iters, flush):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e3          # microseconds
+
+
+def reference_kernel_cases(torch, hk, ref, synth):
+    H, D = 32, 128
+    bf = torch.bfloat16
+
+    def bits16(a, dtype):
+        return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(dtype).cuda()
+
+    def kda(T):
+        gates = synth.kda_gates(T, H, D, seed=1)
+        g, beta = torch.from_numpy(gates["g"]).cuda(), bits16(gates["beta"], bf)
+        qkv = torch.randn(1, T, 3 * H * D, device="cuda").to(bf)
+        st = torch.zeros(1, 1, H, D, D, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, T, H, D, dtype=bf, device="cuda")
+        ws = torch.empty(max(256, hk.kda_chunked_workspace_bytes(1, T, H)), dtype=torch.uint8, device="cuda")
+        ours = lambda: hk.cuda_recurrent_gated_delta_rule(qkv, g, beta, st, out, 1, T, H, H, D, D, 1, None, True, False, workspace=ws)
+        theirs = lambda: ref.kda_recurrent(qkv, g, beta, st, out, 1, T, H, H, D, D, 1, None, True, False)
+        return ours, theirs
+
+    def conv(T):
+        dim = 3 * H * D
+        x = torch.randn(1, dim, T, device="cuda").to(bf)
+        w = (0.1 * torch.randn(dim, 4, device="cuda")).to(bf)
+        st = torch.zeros(1, dim, 4, dtype=bf, device="cuda")
+        out = torch.empty(1, T, dim, dtype=bf, device="cuda")
+        ours = lambda: hk.cuda_causal_conv1d_update(x, st, None, w, None, out, 1, dim, T, 4, 4, True, False)
+        theirs = lambda: ref.conv1d_update(x, st, None, w, None, out, 1, dim, T, 4, 4, True, False)
+        return ours, theirs
+
+    def indexer(m):
+        npools = 65536
+        ix = synth.indexer_inputs(npools, m, seed=7)
+        qi, pk, w = bits16(ix["q_idx"], torch.float16), bits16(ix["pool_k"], torch.float16), bits16(ix["w"], torch.float16)
+        q_pos = torch.full((m,), 4 * npools - 1, dtype=torch.int32, device="cuda")
+        sc = torch.empty(m, npools, dtype=torch.float16, device="cuda")
+        ours = lambda: hk.indexer_score(qi, pk, w, q_pos, sc, m, npools)
+        theirs = lambda: ref.indexer_score(qi, pk, w, q_pos, sc, m, npools)
+        return ours, theirs
+
+    def topk():
+        npools = 65536
+        sc = torch.randn(1, npools, device="cuda").half()
+        idx = torch.empty(1, 512, dtype=torch.int32, device="cuda")
+        ours = lambda: hk.dsa_topk(sc, npools, idx, 1, npools, 512, 512)
+        theirs = lambda: ref.dsa_topk(sc, npools, idx, 1, npools, 512, 512)
+        return ours, theirs
+
+    def sparse(m):
+        L, kidx = 262144, 2052
+        ck = torch.randn(L, 512, dtype=torch.float16, device="cuda")
+        q = torch.randn(m, 64, 512, dtype=torch.float16, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(3)
+        raw = torch.randint(0, L, (m, kidx), generator=g, device="cuda", dtype=torch.int32)
+        lo = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+        ours = lambda: hk.mla_sparse_decode(q, ck, raw, kidx, lo, m)
+        theirs = lambda: ref.mla_sparse_decode(q, ck, raw, kidx, lo, m)
+        return ours, theirs
+
+    def dense(qlen, pos):
+        ck = torch.randn(pos + qlen, 512, dtype=torch.float16, device="cuda")
+        q = torch.randn(qlen, 64, 512, dtype=torch.float16, device="cuda")
+        lo = torch.empty(qlen, 64, 512, dtype=torch.float16, device="cuda")
+        ours = lambda: hk.mla_dense_prefill(q, ck, lo, qlen, pos)
+        theirs = lambda: ref.mla_dense_prefill(q, ck, lo, qlen, pos)
+        return ours, theirs
+
+    def absorb(n, which):
+        kb = (0.05 * torch.randn(32768, 512, device="cuda")).half()
+        if which == "q":
+            qn = torch.randn(n, 64, 256, device="cuda").half()
+            ql = torch.empty(n, 64, 512, dtype=torch.float16, device="cuda")
+            return (lambda: hk.q_latent(qn, kb, ql, n)), (lambda: ref.q_latent_t(qn, kb, ql, n))
+        lo = torch.randn(n, 64, 512, device="cuda").half()
+        o = torch.empty(n, 64, 256, dtype=torch.float16, device="cuda")
+        wt = torch.empty(64, 512, 256, dtype=torch.float16, device="cuda")
+        ref.wuv_transpose(kb, wt)
+        return (lambda: hk.o_absorb(lo, kb, o, n)), (lambda: ref.o_absorb_t(lo, wt, o, n))
+
+    def glue(kind, T):
+        F = 3 * H * D
+        if kind == "transpose":
+            x = torch.randn(T, F, device="cuda")
+            dst = torch.empty(F, T, dtype=bf, device="cuda")
+            return (lambda: hk.kda_transpose_cast(dst, x, T, F)), (lambda: ref.kda_transpose_cast(dst, x, T, F))
+        raw = synth.kda_raw_gates(T, H, D, seed=2)
+        f, b = torch.from_numpy(raw["f"]).cuda(), torch.from_numpy(raw["b"]).cuda()
+        dtb, al, lb = torch.from_numpy(raw["dt_bias"]).cuda(), torch.from_numpy(raw["a_log"]).cuda(), raw["lower_bound"]
+        if kind == "gate":
+            beta = torch.empty(T, H, dtype=bf, device="cuda")
+            g = torch.empty(T, H, D, dtype=torch.float32, device="cuda")
+            return (lambda: hk.kda_gate(b, f, dtb, al, lb, beta, g, T, H, D)), (lambda: ref.kda_gate(b, f, dtb, al, lb, beta, g, T, H, D))
+        x = torch.randn(T * H, D, device="cuda").to(bf)
+        w = torch.ones(D, dtype=bf, device="cuda")
+        y = torch.empty(T * H, D, dtype=torch.float16, device="cuda")
+        return ((lambda: hk.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)),
+                (lambda: ref.gated_rms_norm(x, w, y, f, T * H, D, 1e-6, gate_act=1)))
+
+    return {
+        "transpose_cast_32k": (lambda: glue("transpose", 32768), "transpose + cast, 32768 tokens x 12288 channels", 10),
+        "gate_32k": (lambda: glue("gate", 32768), "gate preparation, 32768 tokens x 32 heads x 128", 10),
+        "gated_norm_32k": (lambda: glue("norm", 32768), "gated RMS norm, 1048576 rows of 128", 10),
+        "kda_prefill_32k": (lambda: kda(32768), "KDA layer prefill, T=32768, H=32, d=128 (reference: per-token recurrence)", 3),
+        "kda_prefill_4k": (lambda: kda(4096), "KDA layer prefill, T=4096, H=32", 5),
+        "kda_decode": (lambda: kda(1), "KDA decode step, H=32", 20),
+        "conv_32k": (lambda: conv(32768), "short conv + SiLU, 12288 channels x 32768 tokens", 10),
+        "indexer_m1": (lambda: indexer(1), "indexer scores, 1 row x 65536 pools", 20),
+        "indexer_m256": (lambda: indexer(256), "indexer scores, 256 rows x 65536 pools", 5),
+        "topk_65536": (topk, "top-512 of 65536 scores, 1 row", 20),
+        "sparse_m1": (lambda: sparse(1), "sparse MLA decode, 1 row, 2052 gathered latents of 262144", 20),
+        "sparse_m256": (lambda: sparse(256), "sparse MLA, 256 rows x 2052 gathered latents", 5),
+        "dense_decode_32k": (lambda: dense(1, 32767), "dense MLA decode, 1 row over 32768 latents", 10),
+        "dense_prefill_256": (lambda: dense(256, 32768), "dense causal MLA prefill, 256 rows after 32768", 3),
+        "q_latent_4096": (lambda: absorb(4096, "q"), "absorbed query projection, 4096 rows x 64 heads (reference: q_latent_t)", 5),
+        "o_absorb_4096": (lambda: absorb(4096, "o"), "absorbed output projection, 4096 rows x 64 heads (reference: o_absorb_t on transposed weights)", 5),
+    }
+
+
+
+
+def run_reference_kernel_cases(args):
+    """`--case reference_kernels`: the reference's own CUDA kernels (oracle/_ref/libhelios_ref.so, its sources compiled
+    for sm_100a) and this library's on the same buffers: median device time of each (2 warm-ups, 256 MB L2 flush before
+    every timed call), one JSON line per case; `--kernel-case NAME` selects one"""
+    import torch
+    import helios_glm53flash_b200 as hk
+    from helios_glm53flash_b200 import synth
+    import hk_ref as ref
+    if not ref.available():
+        print(json.dumps({"case": "reference_kernels", "unavailable": "oracle/_ref/libhelios_ref.so is not built (make -C oracle ref)"}))
+        return
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    table = reference_kernel_cases(torch, hk, ref, synth)
+    for name in ([args.kernel_case] if args.kernel_case else list(table)):
+        build, desc, iters = table[name]
+        ours, theirs = build()
+        t_ref = _timed_us(torch, theirs, iters, flush)
+        t_ours = _timed_us(torch, ours, iters, flush)
+        print(json.dumps({"case": name, "desc": desc, "reference_kernel_us": t_ref, "this_library_us": t_ours,
+                          "speedup": t_ref / t_ours, "iters": iters, "device_status": hk.read_device_status()}), flush=True)
+        del ours, theirs
+        torch.cuda.empty_cache()
+
+
 def run_trunk_case(args):
     """The whole hybrid trunk's attention path (34 KDA + 11 MLA layers, shapes of the benchmark configurations) on a
     synthetic sequence: prefill in 4,096-token chunks, then decode steps; device-timed.  Reports prefill tok/s, decode
@@ -241,9 +619,15 @@ def main():
     ap.add_argument("--tokens", type=int, default=T_FULL, help="sequence length (default: the benchmark's 32768)")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / MLA side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--case", default="kda_prefill", choices=["kda_prefill", "trunk"],
+    ap.add_argument("--case", default="kda_prefill", choices=["kda_prefill", "trunk", "reference_kernels"],
                     help="kda_prefill: the headline line (default).  trunk: the 34 KDA + 11 MLA attention stack in the engine's "
-                         "call order, prefill in 4,096-token chunks then decode (one GPU; its own JSON line)")
+                         "call order, prefill in 4,096-token chunks then decode (one GPU; its own JSON line).  reference_kernels: "
+                         "the reference's own kernels timed beside this library's, one JSON line per kernel")
+    ap.add_argument("--kernel-case", default=None,
+                    help="time ONE entry point on a small case (median of --iters) and print its JSON line; 'all' runs every "
+                         "case.  With --case reference_kernels: the one comparison to run")
+    ap.add_argument("--iters", type=int, default=20, help="timed calls of --kernel-case")
+    ap.add_argument("--graph", action="store_true", help="--kernel-case: time the replay of a CUDA graph of the call")
     ap.add_argument("--trunk-ctx", type=int, default=32768, help="tokens prefetched by --case trunk (the full configuration is 262144)")
     ap.add_argument("--trunk-batch", type=int, default=1, help="sequences of --case trunk (the batched configuration is 8 x 32768)")
     ap.add_argument("--trunk-decode", type=int, default=64, help="decode steps after the prefill of --case trunk")
@@ -257,6 +641,14 @@ def main():
     if args.case == "trunk":
         if rank == 0:
             run_trunk_case(args)
+        return
+    if args.case == "reference_kernels":
+        if rank == 0:
+            run_reference_kernel_cases(args)
+        return
+    if args.kernel_case:
+        if rank == 0:
+            run_kernel_cases(args)
         return
 
     import numpy as np

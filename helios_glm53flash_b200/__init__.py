@@ -75,7 +75,6 @@ SIGNATURES = {
     "hk_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "hk_read_device_status": (_i, [_vp, _i]),
     "hk_tc05_selftest": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
-    "hk_tc05_issue_probe": (_i, [_i, _i, _i, _i, _vp, _vp, _vp]),
 }
 
 _lib = None
@@ -500,19 +499,6 @@ def read_device_status(reset=True):
     v = _c.c_int(0)
     _call("hk_read_device_status", _c.byref(v), int(reset))
     return v.value
-
-
-def tc05_issue_probe(M, N, converged, count=512, stream=None):
-    """SM clock ticks (issue, completion) of `count` back-to-back tcgen05 products of shape M x N x 16, issued
-    by one diverged thread (converged=False) or by a converged warp with an elected lane (converged=True)."""
-    torch = _require_cuda()
-    cycles = torch.zeros(2, dtype=torch.int64, device="cuda")
-    status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
-    _call("hk_tc05_issue_probe", M, N, int(bool(converged)), count, _ptr(cycles), _ptr(status), _stream(stream))
-    torch.cuda.synchronize()
-    if int(status[0]) != 0:
-        raise HeliosB200Error("hk_tc05_issue_probe", HK_ERR_TIMEOUT)
-    return int(cycles[0]), int(cycles[1])
 
 
 def tc05_selftest(a, b, M, N, K, b_layout, stream=None):

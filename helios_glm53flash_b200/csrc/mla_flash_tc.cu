@@ -61,9 +61,9 @@ constexpr int FT_POLL_NS = 40;                    // poll back-off of the waitin
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;         // log2 units: P stays below 2^8, fine for fp16
 
-// Optional timeline instrumentation (compile with -DHK_FLASH_TRACE): CTA (0,0) stamps clock64 at the
+// Optional timeline instrumentation (diagnostic build, -DHK_DIAG): CTA (0,0) stamps clock64 at the
 // hand-off points of its first 64 tiles; hk_debug_flash_trace copies the stamps to the host.
-#ifdef HK_FLASH_TRACE
+#ifdef HK_DIAG
 __device__ long long hk_flash_trace[64 * 16];
 __device__ unsigned long long hk_flash_cta[2 * 4096];   // per CTA: globaltimer at start and end
 __device__ __forceinline__ unsigned long long ft_globaltimer() {
@@ -531,7 +531,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   FT_CTA_STAMP(1);
 }
 
-#ifdef HK_FLASH_TRACE
+#ifdef HK_DIAG
 }  // namespace hk
 extern "C" __attribute__((visibility("default"))) int hk_debug_flash_trace(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, hk::hk_flash_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : 3;

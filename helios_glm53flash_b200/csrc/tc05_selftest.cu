@@ -134,6 +134,7 @@ __global__ __launch_bounds__(128) void tc05_selftest_kernel(const __half* __rest
 }
 
 
+#ifdef HK_DIAG   // measurement aid of the diagnostic build only (not part of the product ABI)
 // Issue-rate probe: `count` products (K = 16 each, operands cycling through a zeroed K = 128 tile, all
 // accumulated into one TMEM tile) are issued back to back, then committed and waited for.  cycles[0] = clock64
 // ticks until the last product was issued, cycles[1] = until all had completed.  converged = 0: issued by one
@@ -198,6 +199,8 @@ __global__ __launch_bounds__(128) void tc05_issue_probe_kernel(int M, int N, int
   if (warp == 0) tc::tmem_dealloc(tmem, 256);
 }
 
+#endif  // HK_DIAG
+
 }  // namespace hk
 
 HK_API int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,
@@ -223,7 +226,8 @@ HK_API int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int 
   return HK_OK;
 }
 
-HK_API int hk_tc05_issue_probe(int M, int N, int converged, int count, long long* cycles, int* status, void* stream) {
+#ifdef HK_DIAG
+extern "C" __attribute__((visibility("default"))) int hk_debug_tc05_issue_probe(int M, int N, int converged, int count, long long* cycles, int* status, void* stream) {
   using namespace hk;
   HK_REQUIRE(cycles && status);
   HK_REQUIRE((M == 64 || M == 128) && N >= 16 && N <= 256 && N % 16 == 0 && count >= 8 && count <= 65536 && count % 8 == 0);
@@ -240,3 +244,4 @@ HK_API int hk_tc05_issue_probe(int M, int N, int converged, int count, long long
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
+#endif  // HK_DIAG

@@ -373,12 +373,6 @@ int hk_read_device_status(int* host_out, int reset);
 int hk_tc05_selftest(const void* a_f16, const void* b_f16, float* d, int M, int N, int K,
                      int b_layout, int* status, void* stream);
 
-/* Tensor-core issue-rate probe (measurement aid, no counterpart in the reference): `count` tcgen05 products of
- * shape M x N x 16 are issued back to back by one CTA, either by a single thread inside a diverged branch
- * (converged = 0) or by a converged warp with an elected lane (converged = 1).  cycles[0] (device int64) receives the
- * SM clock ticks until the last product was issued, cycles[1] until all had completed; `status` (device int) 0 or the
- * code of an expired wait.  M in {64,128}; N multiple of 16, <= 256; count multiple of 8, <= 65536.               */
-int hk_tc05_issue_probe(int M, int N, int converged, int count, long long* cycles, int* status, void* stream);
 
 #ifdef __cplusplus
 }

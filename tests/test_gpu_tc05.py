@@ -36,14 +36,6 @@ def test_tc05_gemm_matches_fp32_matmul(M, N, K, b_layout):
     assert torch.allclose(got, want, atol=2e-2, rtol=1e-3), float((got - want).abs().max())
 
 
-def test_issue_probe_runs_in_both_forms():
-    """The issue-rate probe completes in both issue forms; a converged warp never issues slower than a diverged thread."""
-    single = hk.tc05_issue_probe(64, 48, False, 512)
-    conv = hk.tc05_issue_probe(64, 48, True, 512)
-    assert 0 < single[0] <= single[1] and 0 < conv[0] <= conv[1]
-    assert conv[1] <= single[1] * 1.1
-
-
 def test_reference_parity_binary_against_this_library():
     """The reference's own kernel parity test (src/cuda/attn/test/test_attn_parity.cpp), compiled
     from the reference tree and linked against libhelios_b200.so through the helios::attn shim."""
