@@ -108,9 +108,9 @@ constexpr int P1_LD = 132;                               // fp32 row pitch (conf
 constexpr int P1_LDH = 136;                              // 16-bit row pitch of raw k
 constexpr int P1_LDA = 68;                               // fp32 row pitch of the 64x64 matrices
 constexpr uint32_t P1_KP = 0;                            // fp16 K+ = first half of the B operand [K+|V] (16 KB)
-constexpr uint32_t P1_G = 16384;                         // f32 [64][132] cumulative log decay      (later: V half of the B operand)
-constexpr uint32_t P1_KR = P1_G + KC * P1_LD * 4;        // bf16 [64][136] raw k                    (later: X = inverse, f32 [64][68])
-constexpr uint32_t P1_L = P1_KR + KC * P1_LDH * 2;       // tf32 [2][16][132] left operands of ONE 16-row block (later: T operand, 16 KB)
+constexpr uint32_t P1_G = 16384;                         // f32 [64][132] cumulative log decay, then R  (later: V half of the B operand)
+constexpr uint32_t P1_KR = P1_G + KC * P1_LD * 4;        // X = inverse, f32 [64][68]
+constexpr uint32_t P1_L = P1_KR + KC * P1_LDH * 2;       // raw bf16 v rows as loaded (16 KB), then the T operand (16 KB)
 constexpr uint32_t P1_A = P1_L + 2 * 16 * P1_LD * 4;     // f32 [64][68] N = A beta (strictly lower); upper blocks = scratch
 constexpr uint32_t P1_P = P1_A + KC * P1_LDA * 4;     // f32 [4][128] G_last - (sum before each 16-token block)
 constexpr uint32_t P1_EP = P1_P + 2048;                  // f32 [4][128] e^{sum before the block}
@@ -278,17 +278,17 @@ __device__ __forceinline__ void prep_unit(
     float lower_bound) {
   uint8_t* smem = ctx.smem;
   float* sG = reinterpret_cast<float*>(smem + P1_G);
-  uint16_t* sKr = reinterpret_cast<uint16_t*>(smem + P1_KR);
   float* sA = reinterpret_cast<float*>(smem + P1_A);
   float* sGLP = reinterpret_cast<float*>(smem + P1_P);
   float* sTot = reinterpret_cast<float*>(smem + P1_TOT);
   float* sEP = reinterpret_cast<float*>(smem + P1_EP);
   float* sBeta = reinterpret_cast<float*>(smem + P1_BETA);
-  float* sRk = reinterpret_cast<float*>(smem + P1_RK);
   float* sDD = reinterpret_cast<float*>(smem + P1_DD);
-  uint8_t* sKV = smem + P1_KP;                             // [K+ | V]; the V half aliases sG, valid after the A/B stage
+  float* sETot = sTot;                                     // e^{block total}: overwrites the totals once the tables are built
+  float* sEGLN = sGLP;                                     // e^{G_last - (sum up to the END of the block)}
+  uint8_t* sKV = smem + P1_KP;                             // [K+ | V] fp16 B operand; the V half aliases sG, valid after the A/B stage
   float* sX = reinterpret_cast<float*>(smem + P1_KR);      // alias, valid after the A/B stage
-  uint8_t* sT = smem + P1_L;                               // alias, valid after the A/B stage
+  uint8_t* sT = smem + P1_L;                               // raw v rows, then the T operand (valid after the conversion of v)
 
   const int tid = ctx.tid, lane = tid & 31, warp = tid >> 5;
   const int t0 = chunk * KC;
@@ -339,7 +339,9 @@ __device__ __forceinline__ void prep_unit(
     }
     __pipeline_commit();
     // v rows (raw bf16) are parked where the T operand goes later; chunk cc of row t sits at cc ^ (t % 8)
-    // so that the conversion pass (8 rows of one chunk per quarter-warp) is free of bank conflicts
+    // so that the conversion pass (8 rows of one chunk per quarter-warp) is free of bank conflicts.  (The product
+    // T V needs both operands in ONE 16-bit format: a kind::f16 product of an fp16 T with the bf16 rows as they
+    // were loaded is rejected by the hardware as an illegal instruction.)
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int i = tid + 256 * j, t = i >> 4, cc = i & 15;
@@ -357,14 +359,12 @@ __device__ __forceinline__ void prep_unit(
       }
       sBeta[tid] = bv;
     }
-    for (int i = tid; i < KC * P1_LDA; i += 256) sA[i] = 0.f;
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const int t = 16 * ib + g8 + 8 * h;
       float ss = 0.f;
 #pragma unroll
       for (int m = 0; m < 4; m++) {
-        if (!is_q) *reinterpret_cast<uint4*>(sKr + t * P1_LDH + 32 * m + 8 * tig) = raw[h][m];
         const uint32_t w4[4] = {raw[h][m].x, raw[h][m].y, raw[h][m].z, raw[h][m].w};
 #pragma unroll
         for (int e = 0; e < 4; e++) {
@@ -377,7 +377,6 @@ __device__ __forceinline__ void prep_unit(
       ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       ss += __shfl_xor_sync(0xffffffffu, ss, 2);
       const float rn = rsqrtf(ss + 1e-6f);                  // L2 normalisation of the q / k row
-      if (!is_q && tig == 0) sRk[t] = rn;
 #pragma unroll
       for (int e = 0; e < 32; e++) v[h][e] *= rn;
     }
@@ -435,10 +434,15 @@ __device__ __forceinline__ void prep_unit(
     sTot[(b0 + 1) * KD + c] = a1;
   }
   prep_sync<SUB>(ctx);
-  if (tid < KD) {
+  // The k warps (threads 0-127, one channel each) build the per-block tables while the q warps scale their rows by
+  // e^{x}, which needs x only.
+  if (!is_q) {
     const float t0s = sTot[tid], t1s = sTot[KD + tid], t2s = sTot[2 * KD + tid], t3s = sTot[3 * KD + tid];
     const float P1v = t0s, P2v = P1v + t1s, P3v = P2v + t2s, GL = P3v + t3s;
-    sGLP[tid] = GL; sGLP[KD + tid] = GL - P1v; sGLP[2 * KD + tid] = GL - P2v; sGLP[3 * KD + tid] = GL - P3v;
+    // for Kt: decay from a token to the end of ITS block is e^{tot - x} = e^{-x} e^{tot} (each factor within fp32
+    // range for |x| <= 85), the decay over the LATER blocks is e^{G_last - P_next} (may underflow: then Kt is 0)
+    sEGLN[tid] = __expf(GL - P1v); sEGLN[KD + tid] = __expf(GL - P2v); sEGLN[2 * KD + tid] = __expf(GL - P3v); sEGLN[3 * KD + tid] = 1.f;
+    sETot[tid] = __expf(t0s); sETot[KD + tid] = __expf(t1s); sETot[2 * KD + tid] = __expf(t2s); sETot[3 * KD + tid] = __expf(t3s);
     sEP[tid] = 1.f; sEP[KD + tid] = __expf(P1v); sEP[2 * KD + tid] = __expf(P2v); sEP[3 * KD + tid] = __expf(P3v);
     // pair (ib, jb < ib) at index ib (ib - 1) / 2 + jb: e^{P_ib - P_jb}
     sDD[tid] = __expf(t0s);
@@ -446,27 +450,7 @@ __device__ __forceinline__ void prep_unit(
     sDD[3 * KD + tid] = __expf(t0s + t1s + t2s); sDD[4 * KD + tid] = __expf(t1s + t2s); sDD[5 * KD + tid] = __expf(t2s);
     reinterpret_cast<float*>(unit + U_DEC)[tid] = __expf(GL);
   }
-  prep_sync<SUB>(ctx);
-
-  KT_TRACE(3);
-  // ---- stage 3 (two phases; k and q warps swap jobs so that x is read before it is overwritten) ----
-  // phase A: k warps write the Kt^T tile (rows = channels, K = tokens) straight to the workspace;
-  //          q warps scale their rows by e^{x}
-  if (!is_q) {
-    for (int i = warp * 32 + lane; i < KD * (KC / 8); i += 128) {
-      const int c = i & 127, tg = i >> 7;
-      const float glp = sGLP[(tg >> 1) * KD + c];
-      float kt[8];
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int t = tg * 8 + u;
-        kt[u] = sBeta[t] * sRk[t] * bf16_bits_to_f(sKr[t * P1_LDH + c]) * __expf(glp - sG[t * P1_LD + c]);
-      }
-      uint4 p;
-      p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
-      *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
-    }
-  } else {
+  else {
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const float* xr = sG + (16 * ib + g8 + 8 * h) * P1_LD + 8 * tig;
@@ -481,9 +465,12 @@ __device__ __forceinline__ void prep_unit(
     }
   }
   prep_sync<SUB>(ctx);
+
+  KT_TRACE(3);
   KT_TRACE(4);
-  // phase B: k warps turn x into the RIGHT operand R[s][c] = k^_s e^{-x_s} (in place, fp32: up to e^85)
-  //          and scale their own rows by e^{x}; q warps emit Q+ = q^ e^{G_t} (fp16 tile rows 64..127)
+  // ---- stage 3: the q warps have read x; the k warps turn it into the RIGHT operand R[s][c] = k^_s e^{-x_s} (in
+  //      place, fp32: up to e^85) and scale their own rows by e^{x}; the q warps emit Q+ = q^ e^{G_t} (fp16 tile
+  //      rows 64..127) ----
 #pragma unroll
   for (int h = 0; h < 2; h++) {
     const int t = 16 * ib + g8 + 8 * h;
@@ -519,6 +506,21 @@ __device__ __forceinline__ void prep_unit(
   //      block is moved from its own reference P_jb to P_ib by the pair decay while it is loaded.  The
   //      contraction runs over the channels in the order the registers hold them. ----
   prep_ab_block(ib, v, is_q, sG, sDD, sBeta, sA, unit, g8, tig);
+  // Kt^T tile (rows = channels, K = tokens) from R: Kt[t][c] = beta_t R[t][c] e^{tot_blk} e^{G_last - P_next}, no
+  // exponentials; all eight warps, a thread = 8 tokens of one channel = one 16-byte piece of the tile
+  for (int i = tid; i < KD * (KC / 8); i += 256) {
+    const int c = i & 127, tg = i >> 7;
+    const float et = sETot[(tg >> 1) * KD + c], en = sEGLN[(tg >> 1) * KD + c];
+    float kt[8];
+#pragma unroll
+    for (int u8 = 0; u8 < 8; u8++) {
+      const int t = tg * 8 + u8;
+      kt[u8] = sBeta[t] * (sG[t * P1_LD + c] * et) * en;
+    }
+    uint4 p;
+    p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
+    *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
+  }
   if (!is_q) {
     // K+ = k^ e^{G_t}: first half of the [K+ | V] operand
 #pragma unroll
@@ -538,10 +540,11 @@ __device__ __forceinline__ void prep_unit(
   __pipeline_wait_prior(0);                                 // v rows
   prep_sync<SUB>(ctx);
   KT_TRACE(6);
-  // from here on sG, sKr and sL are dead: the V half of sKV, sX and sT take their place
+  // from here on sG is dead: the V half of sKV, sX and (after the conversion) sT take their place
 
-  // ---- stage 5: V -> B operand columns 128..255, then the blocked
-  //      inverse X = (I + N)^-1 in fp32 and its fp16 copy T as the A operand ----
+  // ---- stage 5: V -> B operand columns 128..255 (bf16 -> fp16), then the blocked inverse X = (I + N)^-1 in fp32
+  //      and its fp16 copy T as the A operand.  The conversion needs no barrier of its own: the inverse works on sA
+  //      and sX only, and the T operand is written (5c) after the barriers of the inverse. ----
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = tid + 256 * j;
@@ -552,8 +555,6 @@ __device__ __forceinline__ void prep_unit(
     p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
     *reinterpret_cast<uint4*>(sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
   }
-  for (int i = tid; i < KC * P1_LDA; i += 256) sX[i] = 0.f;
-  prep_sync<SUB>(ctx);
   KT_TRACE(7);
   // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
   if (warp < 4 && lane < 16) {
@@ -602,10 +603,12 @@ __device__ __forceinline__ void prep_unit(
   for (int i = tid; i < 8192 / 16; i += 256) reinterpret_cast<uint4*>(sT + 8192)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < KC * (KC / 8); i += 256) {
     const int t = (i & 7) + ((i >> 6) << 3), jc = (i >> 3) & 7;
-    const float4 v0 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8);
-    const float4 v1 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8 + 4);
-    uint4 p;
-    p.x = pack_h2(v0.x, v0.y); p.y = pack_h2(v0.z, v0.w); p.z = pack_h2(v1.x, v1.y); p.w = pack_h2(v1.z, v1.w);
+    uint4 p = make_uint4(0, 0, 0, 0);                      // blocks above the diagonal are never computed: zeros
+    if ((jc >> 1) <= (t >> 4)) {
+      const float4 v0 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8);
+      const float4 v1 = *reinterpret_cast<const float4*>(sX + t * P1_LDA + jc * 8 + 4);
+      p.x = pack_h2(v0.x, v0.y); p.y = pack_h2(v0.z, v0.w); p.z = pack_h2(v1.x, v1.y); p.w = pack_h2(v1.z, v1.w);
+    }
     *reinterpret_cast<uint4*>(sT + (t >> 3) * SBO_K64 + jc * LBO + (t & 7) * 16) = p;
   }
   tc::fence_async_smem();
