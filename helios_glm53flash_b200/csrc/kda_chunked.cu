@@ -22,7 +22,10 @@
 // order.  The fp32 state slice stays in registers; per chunk it pulls the 60 KB of operands with TMA
 // bulk copies (three stages in flight) and issues three tcgen05 contractions with TMEM accumulators:
 // [W;Q+] S0 (M128 N32 K128), [0;B beta] U (accumulated onto the Q+ S0 rows) and Kt^T U (M128 N32 K64).
+#include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime at first use)
 #include <cuda_pipeline_primitives.h>
+
+#include <cstring>
 
 #include "hk_common.cuh"
 #include "tc05.cuh"
@@ -124,13 +127,18 @@ static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_
 // Optional stage timeline (diagnostic build, -DHK_DIAG): one preparation worker and one scan CTA stamp clock64 at
 // their stage boundaries; hk_debug_kda_trace copies the stamps to the host.
 #ifdef HK_DIAG
-__device__ long long hk_kda_trace[64];
-#define KT_TRACE(slot) do { if (ctx.trace && ctx.tid == 0) hk_kda_trace[slot] = clock64(); } while (0)
+__device__ long long hk_kda_trace[128];
+// stamps go to shared memory and are copied out once per unit: a global store per stamp would sit in the memory pipe
+// in front of the next barrier and inflate the interval that follows it
+__shared__ long long hk_kda_stamps[48];
+#define KT_TRACE(slot) do { if (ctx.trace && ctx.tid == 0) hk_kda_stamps[slot] = clock64(); } while (0)
+#define KT_FLUSH() do { if (ctx.trace && ctx.tid == 0) { for (int q_ = 0; q_ < 16; q_++) hk_kda_trace[q_] = hk_kda_stamps[q_]; for (int q_ = 16; q_ < 48; q_++) hk_kda_trace[q_ + 48] = hk_kda_stamps[q_]; } } while (0)
 #define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #define KS_TRACE_AT(slot, ch, want) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == (want)) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #else
 #define KS_TRACE_AT(slot, ch, want) do { } while (0)
 #define KT_TRACE(slot) do { } while (0)
+#define KT_FLUSH() do { } while (0)
 #define KS_TRACE(slot, ch) do { } while (0)
 #endif
 
@@ -232,6 +240,9 @@ __device__ __forceinline__ void prep_ab_block(const int ib, const float (&v)[2][
         } else {                // B beta, lower including the diagonal, fp16 operand tile
           const float v0 = s0 <= t ? acc[jb][nt][2 * hrow] * b0 : 0.f;
           const float v1 = s0 + 1 <= t ? acc[jb][nt][2 * hrow + 1] * b1 : 0.f;
+#ifdef HK_DIAG_NO_STORES
+          if (v0 == 12345.f)
+#endif
           *reinterpret_cast<uint32_t*>(unit + U_BB + (t >> 3) * SBO_K64 + (s0 >> 3) * LBO + (t & 7) * 16 + (s0 & 7) * 2) =
               pack_h2(v0, v1);
         }
@@ -494,6 +505,9 @@ __device__ __forceinline__ void prep_unit(
         uint4 p;
         p.x = pack_h2(v[h][8 * m + 0] * e0.x, v[h][8 * m + 1] * e0.y); p.y = pack_h2(v[h][8 * m + 2] * e0.z, v[h][8 * m + 3] * e0.w);
         p.z = pack_h2(v[h][8 * m + 4] * e1.x, v[h][8 * m + 5] * e1.y); p.w = pack_h2(v[h][8 * m + 6] * e1.z, v[h][8 * m + 7] * e1.w);
+#ifdef HK_DIAG_NO_STORES
+        if (p.x == 0x12345678u)
+#endif
         *reinterpret_cast<uint4*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (4 * m + tig) * LBO + (t & 7) * 16) = p;
       }
     }
@@ -519,6 +533,9 @@ __device__ __forceinline__ void prep_unit(
     }
     uint4 p;
     p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
+#ifdef HK_DIAG_NO_STORES
+    if (p.x == 0x12345678u)
+#endif
     *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
   }
   if (!is_q) {
@@ -538,13 +555,20 @@ __device__ __forceinline__ void prep_unit(
     }
   }
   __pipeline_wait_prior(0);                                 // v rows
+#ifdef HK_DIAG
+  if (ctx.trace && lane == 0) hk_kda_stamps[16 + warp] = clock64();       // arrival at the barrier that ends stage 4
+#endif
   prep_sync<SUB>(ctx);
   KT_TRACE(6);
+#ifdef HK_DIAG
+  if (ctx.trace && lane == 0) hk_kda_stamps[24 + warp] = clock64();       // release
+#endif
   // from here on sG is dead: the V half of sKV, sX and (after the conversion) sT take their place
 
   // ---- stage 5: V -> B operand columns 128..255 (bf16 -> fp16), then the blocked inverse X = (I + N)^-1 in fp32
   //      and its fp16 copy T as the A operand.  The conversion needs no barrier of its own: the inverse works on sA
   //      and sX only, and the T operand is written (5c) after the barriers of the inverse. ----
+#ifndef HK_DIAG_SKIP_VCONV
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = tid + 256 * j;
@@ -555,6 +579,13 @@ __device__ __forceinline__ void prep_unit(
     p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
     *reinterpret_cast<uint4*>(sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
   }
+#endif
+#ifdef HK_DIAG
+  if (ctx.trace && lane == 0) hk_kda_stamps[32 + warp] = clock64();       // arrival at the next barrier
+  prep_sync<SUB>(ctx);                                     // diagnostic build: a barrier so that the stamp separates the stages
+  KT_TRACE(13);
+  prep_sync<SUB>(ctx);
+#endif
   KT_TRACE(7);
   // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
   if (warp < 4 && lane < 16) {
@@ -980,9 +1011,11 @@ constexpr uint32_t F_DEC = 81920;                         // 512
 constexpr uint32_t F_STAGE = 82432;
 constexpr uint32_t F_S = F_NSTAGE * F_STAGE;              // fp16 B operand: state [128 k][128 v], MN-major, 32 KB
 constexpr uint32_t F_U = F_S + 32768;                     // fp16 B operand: U [64 tokens][128 v], MN-major, 16 KB
-constexpr uint32_t F_O = F_U + 16384;                     // bf16 output rows of one chunk, [64 tokens][272 B] (256 + 16 pad)
-constexpr uint32_t F_OPITCH = 272;
-constexpr uint32_t F_SMEM_SCAN = F_O + KC * F_OPITCH;
+constexpr uint32_t F_O = F_U + 16384;                     // bf16 output rows of one chunk: two swizzled 8 KB boxes for the tiled
+                                                          // stores, or plain [64 tokens][256 B] rows when the kernel stores itself
+constexpr uint32_t F_OPITCH = 256;
+constexpr uint32_t F_SMEM_SCAN = F_O + KC * F_OPITCH + 1024;   // + slack to start the tiles at a 1 KB boundary
+static_assert(F_O % 1024 == 0 && KC * F_OPITCH >= 16384, "the output tile holds two 8 KB swizzled boxes");
 constexpr uint32_t F_SMEM = F_SMEM_SCAN > 2 * P1_SMEM ? F_SMEM_SCAN : 2 * P1_SMEM;
 static_assert(U_KT + 16384 == U_UL && U_UL + 16384 == U_DEC && F_KT + 16384 == F_UL && F_UL + 16384 == F_DEC,
               "Kt^T, Uloc and the decay row travel as one copy");
@@ -993,7 +1026,8 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g, const void* __restrict__ beta_in,
     uint8_t* __restrict__ ring, int* __restrict__ flags, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
     float* __restrict__ out_f32, int seqlen, int H, int n_chunks, int n_jobs, const int* __restrict__ slots, float scale,
-    int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound) {
+    int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound,
+    const __grid_constant__ CUtensorMap tmap_out, int use_tma_out) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[F_NSTAGE];
   // chain: one barrier per contraction group, each completing once per chunk (parity = chunk & 1); the output warps
@@ -1001,6 +1035,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
   __shared__ uint64_t mma_bar;       // chain: [W;Q+] S0;       preparation worker 0: its product
   __shared__ uint64_t mma2_bar;      // chain: Kt^T U (state path)
   __shared__ uint64_t out_bar;       // chain: (B beta) U;      preparation worker 1: its product
+  __shared__ uint64_t u_bar;         // chain: the 256 token-row threads have written U (count 256)
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -1017,6 +1052,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     tc::mbar_init(&mma_bar, 1);
     tc::mbar_init(&mma2_bar, 1);
     tc::mbar_init(&out_bar, 1);
+    tc::mbar_init(&u_bar, 256);
     tc::mbar_fence_init();
     abort_flag = 0;
   }
@@ -1025,11 +1061,16 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
+  uint8_t* const smem_base = smem;
 
   if ((int)blockIdx.x >= n_jobs) {
     // =========================== two preparation workers ===========================
     const int sub = warp >> 3;
+#ifdef HK_DIAG_ONE_WORKER
+    const int worker = (int)blockIdx.x - n_jobs, n_workers = (int)gridDim.x - n_jobs;
+#else
     const int worker = ((int)blockIdx.x - n_jobs) * 2 + sub, n_workers = ((int)gridDim.x - n_jobs) * 2;
+#endif
     const long long n_units = (long long)n_chunks * n_jobs;
     PrepCtx ctx{smem + sub * P1_SMEM, sub ? &out_bar : &mma_bar, 0u, &abort_flag, tmem + sub * 256, tid & 255, 1 + sub, false,
                 nullptr, 0, 0, g_abort};
@@ -1037,13 +1078,15 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     ctx.trace = false;
 #endif
     int it = 0;
+#ifdef HK_DIAG_ONE_WORKER
+    if (sub == 1) goto prep_done;                          // diagnostic: stage times of a worker that has its SM alone
+#endif
     for (long long u = worker; u < n_units; u += n_workers, it++) {
       const int chunk = (int)(u / n_jobs), job = (int)(u % n_jobs);
       const int b = job / H, head = job % H;
 #ifdef HK_DIAG
       ctx.trace = (worker == 7 && it == 20);
 #endif
-      KT_TRACE(13);
       // the slot of this chunk must have been drained by the chain CTA (it held chunk - KR): thread 0 asks now and
       // looks at the answer just before the worker's first write to the unit (prep_unit calls slot_wait there)
       ctx.slot_flag = consumed + job;
@@ -1060,9 +1103,16 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       // release store (which is cumulative over them)
       if (ctx.tid == 0) st_release_gpu(ready + (size_t)job * KR + (chunk % KR), chunk + 1);
       KT_TRACE(15);
+      KT_FLUSH();
     }
+#ifdef HK_DIAG_ONE_WORKER
+  prep_done:;
+#endif
   } else {
     // =========================== one (batch, head) chain ===========================
+    // the chain CTA's tiles start at a 1 KB boundary (the output tile is written in the 128-byte-swizzle pattern,
+    // which is a function of the shared-memory address)
+    uint8_t* const smem = smem_base + ((1024u - (tc::smem_u32(smem_base) & 1023u)) & 1023u);
     const int job = blockIdx.x, b = job / H, head = job % H;
     const int lq = warp & 3, cb = warp >> 2;               // TMEM lane quarter, 32-column block
     const int rowi = lq * 32 + (tid & 31);                       // k row of the state / token row of W S0 / output row - 64
@@ -1116,8 +1166,11 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
 
     const uint32_t idesc = tc::make_idesc(128, KD, tc::FMT_F16, tc::FMT_F16, false, true);
     const uint32_t s_addr = tc::smem_u32(smem + F_S), u_addr = tc::smem_u32(smem + F_U);
-    const bool issue_warp = tc::warp_index_uniform() == 0;
-    const uint32_t leader = issue_warp ? tc::elect_one() : 0u;
+    // two issuing warps: warp 0 the contractions on the chain ([W;Q+] S0 and Kt^T U), warp 2 (an output warp) the
+    // output contraction (B beta) U, so that warp 0 does not spend its issue time before its share of the state update
+    const int warp_u = tc::warp_index_uniform();
+    const bool issue_warp = warp_u == 0, out_issue_warp = warp_u == 2;
+    const uint32_t leader = (issue_warp || out_issue_warp) ? tc::elect_one() : 0u;
 
     // Output rows of chunk c: TMEM lanes 64-127 of that chunk's D1 range = tokens, lane quarters 2 and 3 (eight warps =
     // two token halves x four column blocks).  A thread holds 32 columns of one token; stored directly, a warp-wide
@@ -1125,12 +1178,20 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     // one SM).  The bf16 rows are therefore assembled in shared memory (272-byte pitch: conflict-free both ways) and
     // written out with every warp instruction covering two whole 256-byte rows.  The eight warps meet at a named
     // barrier of their own; the block barriers of the chain separate one chunk's reads from the next chunk's writes.
+    // With a tensor map over the output the rows leave as TWO tiled TMA stores per chunk (64 tokens x 64 channels each,
+    // 128-byte-swizzle boxes; rows past the end of the sequence are clipped by the copy engine): the tile is written
+    // conflict-free (16-byte piece p of row r at p ^ (r % 8)) and one thread hands it over.
     auto emit_outputs = [&](int c, bool valid) {
       const int trow = rowi - 64;
       uint32_t r[32];
       tc::tmem_ld32(tmem + ((c & 1) ? 128u : 0u) + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
       tc::tmem_ld_wait();
-      uint8_t* orow = smem + F_O + trow * F_OPITCH + cb * (KNV * 2);
+      const bool issuer = warp == 2 && (tid & 31) == 0;
+      if (use_tma_out) {
+        if (issuer) tc::bulk_wait_read<0>();               // the previous chunk's tile has been read by the copy engine
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
+      uint8_t* orow = use_tma_out ? smem + F_O + (cb >> 1) * 8192 + trow * 128 : smem + F_O + trow * F_OPITCH + cb * (KNV * 2);
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         uint32_t w[4];
@@ -1141,17 +1202,31 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rz(c2));
           w[e] = lo | (hi << 16);
         }
-        *reinterpret_cast<uint4*>(orow + u * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        const int off = use_tma_out ? ((((cb & 1) * 4 + u) ^ (trow & 7)) << 4) : u * 16;
+        *reinterpret_cast<uint4*>(orow + off) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const int ot = (lq - 2) * 128 + cb * 32 + (tid & 31);   // 0..255 over the eight output warps
+      if (use_tma_out) {
+        tc::fence_async_smem();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (issuer && valid) {
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int piece = ot + 256 * i, prow = piece >> 4, pc = piece & 15;
-        const int ptok = c * KC + prow;
-        if (ptok < seqlen && valid) {
-          const uint4 v = *reinterpret_cast<const uint4*>(smem + F_O + prow * F_OPITCH + pc * 16);
-          *reinterpret_cast<uint4*>(out + (((size_t)b * seqlen + ptok) * H + head) * KD + pc * 8) = v;
+          for (int hb = 0; hb < 2; hb++)
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(&tmap_out),
+                         "r"(hb * 64), "r"(head), "r"(c * KC), "r"(b), "r"(tc::smem_u32(smem + F_O + hb * 8192))
+                         : "memory");
+          tc::bulk_commit();
+        }
+      } else {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int ot = (lq - 2) * 128 + cb * 32 + (tid & 31);   // 0..255 over the eight output warps
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const int piece = ot + 256 * i, prow = piece >> 4, pc = piece & 15;
+          const int ptok = c * KC + prow;
+          if (ptok < seqlen && valid) {
+            const uint4 v = *reinterpret_cast<const uint4*>(smem + F_O + prow * F_OPITCH + pc * 16);
+            *reinterpret_cast<uint4*>(out + (((size_t)b * seqlen + ptok) * H + head) * KD + pc * 8) = v;
+          }
         }
       }
       const int tok = c * KC + trow;
@@ -1224,13 +1299,11 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           *reinterpret_cast<uint4*>(urow + u * 1024) = p;
         }
       }
-      // only the token-row warps (lane quarters 0 and 1, the issuing warp among them) meet here: the output warps
-      // are still writing the previous chunk's rows and join again at the state update
+      // U is complete when all 256 token-row threads have arrived (after their proxy fence); the two issuing warps
+      // wait for that, nobody else does
       if (lq < 2) {
         tc::fence_async_smem();
-        tc::fence_before_sync();
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-        tc::fence_after_sync();
+        tc::mbar_arrive(&u_bar);
       }
       KS_TRACE(3, chunk);
       // The ring protocol runs here, while the producer's warp has nothing to do until the state contraction is
@@ -1248,8 +1321,10 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
         // sampled now, used when this chunk's stage is released at the end of the iteration
         if (issued == chunk + 2 && chunk + 2 < n_chunks) next_flag = ld_acquire_gpu(my_ready + ((chunk + 2) % KR));
       }
-      // ---- D2 = Kt^T U (state path, committed first) ;  D1 rows 64-127 += (B beta) U (outputs, own barrier) ----
+      // ---- D2 = Kt^T U (state path, warp 0) ;  D1 rows 64-127 += (B beta) U (outputs, warp 2, own barrier) ----
       if (issue_warp) {
+        ok = tc::mbar_wait(&u_bar, cpar, &abort_flag, 6) && ok;
+        tc::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < KC / 16; kk++) {
           const uint64_t ad = tc::make_sdesc(stg_addr + F_KT + kk * 2 * LBO, LBO, SBO_K64);
@@ -1257,6 +1332,10 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           tc::mma_f16_if(leader, d2, ad, bd, idesc, kk > 0);
         }
         tc::mma_commit_if(leader, &mma2_bar);
+      }
+      if (out_issue_warp) {
+        ok = tc::mbar_wait(&u_bar, cpar, &abort_flag, 7) && ok;
+        tc::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < KC / 16; kk++) {
           const uint64_t ad = tc::make_sdesc(stg_addr + F_BB + kk * 2 * LBO, LBO, SBO_K64);
@@ -1302,7 +1381,10 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
         issued = chunk + 3;
       }
     }
-    if (lq >= 2 && n_chunks > 0) emit_outputs(n_chunks - 1, prev_ok);
+    if (lq >= 2 && n_chunks > 0) {
+      emit_outputs(n_chunks - 1, prev_ok);
+      if (use_tma_out && warp == 2 && (tid & 31) == 0) tc::bulk_wait_all<0>();
+    }
     if (!abort_flag) {
 #pragma unroll
       for (int u = 0; u < KNV / 4; u++)
@@ -1319,7 +1401,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
 
 #ifdef HK_DIAG
 extern "C" __attribute__((visibility("default"))) int hk_debug_kda_trace(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, hk::hk_kda_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
+  return cudaMemcpyFromSymbol(host_out, hk::hk_kda_trace, sizeof(long long) * 128) == cudaSuccess ? 0 : 3;
 }
 #endif
 
@@ -1408,14 +1490,43 @@ int chunked_prefill_launch(const void* mixed_qkv, const float* g_or_f, const voi
     int* a_flags = (int*)workspace;
     __nv_bfloat16* a_out = (__nv_bfloat16*)out;
     const float a_scale = 1.0f / sqrtf((float)KD);
+    // tensor map over the output [bsz][seqlen][H][128] bf16 for the chain CTAs' tiled stores: box = 64 channels x 1 head x
+    // 64 tokens x 1 sequence, 128-byte swizzle; without the encoder the kernel stores the rows itself
+    alignas(64) CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    int use_tma_out = 0;
+    {
+      typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+      static EncodeFn encode = nullptr;
+      static bool looked_up = false;
+      if (!looked_up) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+          encode = (EncodeFn)fn;
+        looked_up = true;
+      }
+      if (encode) {
+        const cuuint64_t dims[4] = {(cuuint64_t)KD, (cuuint64_t)num_heads, (cuuint64_t)seqlen, (cuuint64_t)bsz};
+        const cuuint64_t strides[3] = {(cuuint64_t)KD * 2, (cuuint64_t)num_heads * KD * 2, (cuuint64_t)seqlen * num_heads * KD * 2};
+        const cuuint32_t box[4] = {64, 1, (cuuint32_t)KC, 1};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+          use_tma_out = 1;
+      }
+    }
     const float* a_dt = gated ? dt_bias : nullptr;
     const float* a_al = gated ? a_log : nullptr;
     const float a_lb = gated ? lower_bound : 0.f;
     cudaError_t e = gated
         ? cudaLaunchKernelEx(&cfg, kda_fused_kernel<true>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
-                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb)
+                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out)
         : cudaLaunchKernelEx(&cfg, kda_fused_kernel<false>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
-                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb);
+                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out);
     return e == cudaSuccess ? HK_OK : HK_ERR_CUDA;
   }
   const dim3 grid(num_heads, n_chunks, bsz);
