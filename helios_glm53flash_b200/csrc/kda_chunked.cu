@@ -128,11 +128,12 @@ static_assert(KC * P1_LD * 4 >= 16384 && 2 * 16 * P1_LD * 4 >= 16384 && KC * P1_
 // their stage boundaries; hk_debug_kda_trace copies the stamps to the host.
 #ifdef HK_DIAG
 __device__ long long hk_kda_trace[128];
-// stamps go to shared memory and are copied out once per unit: a global store per stamp would sit in the memory pipe
-// in front of the next barrier and inflate the interval that follows it
-__shared__ long long hk_kda_stamps[48];
+// stamps go to shared memory and are copied out once per unit.  A stamp placed after a barrier is taken when the
+// stamping warp ARRIVES there (the clock read is not held back by the barrier): the intervals are that warp's own
+// work, not the stage's length - the slowest warp of a stage shows up in the NEXT interval.
+__shared__ long long hk_kda_stamps[16];
 #define KT_TRACE(slot) do { if (ctx.trace && ctx.tid == 0) hk_kda_stamps[slot] = clock64(); } while (0)
-#define KT_FLUSH() do { if (ctx.trace && ctx.tid == 0) { for (int q_ = 0; q_ < 16; q_++) hk_kda_trace[q_] = hk_kda_stamps[q_]; for (int q_ = 16; q_ < 48; q_++) hk_kda_trace[q_ + 48] = hk_kda_stamps[q_]; } } while (0)
+#define KT_FLUSH() do { if (ctx.trace && ctx.tid == 0) { for (int q_ = 0; q_ < 16; q_++) hk_kda_trace[q_] = hk_kda_stamps[q_]; } } while (0)
 #define KS_TRACE(slot, ch) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == 100) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #define KS_TRACE_AT(slot, ch, want) do { if (threadIdx.x == 0 && blockIdx.x == 1 && (ch) == (want)) hk_kda_trace[32 + (slot)] = clock64(); } while (0)
 #else
@@ -240,9 +241,6 @@ __device__ __forceinline__ void prep_ab_block(const int ib, const float (&v)[2][
         } else {                // B beta, lower including the diagonal, fp16 operand tile
           const float v0 = s0 <= t ? acc[jb][nt][2 * hrow] * b0 : 0.f;
           const float v1 = s0 + 1 <= t ? acc[jb][nt][2 * hrow + 1] * b1 : 0.f;
-#ifdef HK_DIAG_NO_STORES
-          if (v0 == 12345.f)
-#endif
           *reinterpret_cast<uint32_t*>(unit + U_BB + (t >> 3) * SBO_K64 + (s0 >> 3) * LBO + (t & 7) * 16 + (s0 & 7) * 2) =
               pack_h2(v0, v1);
         }
@@ -505,9 +503,6 @@ __device__ __forceinline__ void prep_unit(
         uint4 p;
         p.x = pack_h2(v[h][8 * m + 0] * e0.x, v[h][8 * m + 1] * e0.y); p.y = pack_h2(v[h][8 * m + 2] * e0.z, v[h][8 * m + 3] * e0.w);
         p.z = pack_h2(v[h][8 * m + 4] * e1.x, v[h][8 * m + 5] * e1.y); p.w = pack_h2(v[h][8 * m + 6] * e1.z, v[h][8 * m + 7] * e1.w);
-#ifdef HK_DIAG_NO_STORES
-        if (p.x == 0x12345678u)
-#endif
         *reinterpret_cast<uint4*>(unit + U_WQ + ((64 + t) >> 3) * SBO_K128 + (4 * m + tig) * LBO + (t & 7) * 16) = p;
       }
     }
@@ -533,9 +528,6 @@ __device__ __forceinline__ void prep_unit(
     }
     uint4 p;
     p.x = pack_h2(kt[0], kt[1]); p.y = pack_h2(kt[2], kt[3]); p.z = pack_h2(kt[4], kt[5]); p.w = pack_h2(kt[6], kt[7]);
-#ifdef HK_DIAG_NO_STORES
-    if (p.x == 0x12345678u)
-#endif
     *reinterpret_cast<uint4*>(unit + U_KT + (c >> 3) * SBO_K64 + tg * LBO + (c & 7) * 16) = p;
   }
   if (!is_q) {
@@ -555,20 +547,14 @@ __device__ __forceinline__ void prep_unit(
     }
   }
   __pipeline_wait_prior(0);                                 // v rows
-#ifdef HK_DIAG
-  if (ctx.trace && lane == 0) hk_kda_stamps[16 + warp] = clock64();       // arrival at the barrier that ends stage 4
-#endif
   prep_sync<SUB>(ctx);
   KT_TRACE(6);
-#ifdef HK_DIAG
-  if (ctx.trace && lane == 0) hk_kda_stamps[24 + warp] = clock64();       // release
-#endif
+
   // from here on sG is dead: the V half of sKV, sX and (after the conversion) sT take their place
 
   // ---- stage 5: V -> B operand columns 128..255 (bf16 -> fp16), then the blocked inverse X = (I + N)^-1 in fp32
   //      and its fp16 copy T as the A operand.  The conversion needs no barrier of its own: the inverse works on sA
   //      and sX only, and the T operand is written (5c) after the barriers of the inverse. ----
-#ifndef HK_DIAG_SKIP_VCONV
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = tid + 256 * j;
@@ -579,13 +565,6 @@ __device__ __forceinline__ void prep_unit(
     p.z = pack_h2(bf16lo(vr.z), bf16hi(vr.z)); p.w = pack_h2(bf16lo(vr.w), bf16hi(vr.w));
     *reinterpret_cast<uint4*>(sKV + (16 + cc) * 1024 + (t >> 3) * 128 + (t & 7) * 16) = p;
   }
-#endif
-#ifdef HK_DIAG
-  if (ctx.trace && lane == 0) hk_kda_stamps[32 + warp] = clock64();       // arrival at the next barrier
-  prep_sync<SUB>(ctx);                                     // diagnostic build: a barrier so that the stamp separates the stages
-  KT_TRACE(13);
-  prep_sync<SUB>(ctx);
-#endif
   KT_TRACE(7);
   // 5a: the four diagonal 16x16 blocks, one warp each, lane = column: x_r = delta - sum_{s<r} N[r][s] x_s
   if (warp < 4 && lane < 16) {
