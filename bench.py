@@ -992,22 +992,24 @@ def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, 
         del qkv_l, g_l, out_l, ws_l
         torch.cuda.empty_cache()
 
-    # ---- MLA dense decode, 8 sequences x 32,768 tokens, sharded by sequences ----
+    # ---- MLA dense decode, 8 sequences x 32,768 tokens, sharded by sequences: two alternating sets of caches
+    #      (together larger than L2), a timed region = 10 replays of a graph that decodes both ----
     B, L2 = 8, 32768
     if B % world == 0:
         Bl = B // world
-        ck = torch.randn(Bl * L2, 512, dtype=torch.float16, device="cuda")
+        n_sets = 2 if Bl * L2 * 1024 * 2 > (160 << 20) else 4
+        cks = [torch.randn(Bl * L2, 512, dtype=torch.float16, device="cuda") for _ in range(n_sets)]
         qd = torch.randn(Bl, 64, 512, dtype=torch.float16, device="cuda")
         base = torch.arange(Bl, device="cuda", dtype=torch.int64) * L2
         lens = torch.full((Bl,), L2, dtype=torch.int32, device="cuda")
         lo = torch.empty(Bl, 64, 512, dtype=torch.float16, device="cuda")
         ns = hk.mla_auto_splits(Bl, L2)
         wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, Bl * 64)), dtype=torch.uint8, device="cuda")
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
         def mla_step():
-            hk.mla_dense_prefill(qd, ck, lo, Bl, 0, scale=scale, kv_base=base, kv_len=lens, n_split=ns, workspace=wsb,
-                                 n_keys_hint=L2)
+            for ck in cks:
+                hk.mla_dense_prefill(qd, ck, lo, Bl, 0, scale=scale, kv_base=base, kv_len=lens, n_split=ns, workspace=wsb,
+                                     n_keys_hint=L2)
         for _ in range(3):
             mla_step()
         torch.cuda.synchronize()
@@ -1015,19 +1017,19 @@ def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, 
         with torch.cuda.graph(gm):
             mla_step()
         ts = []
-        for _ in range(10):
-            flush.zero_()
+        for _ in range(5):
             dist.barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            gm.replay()
+            for _ in range(10):
+                gm.replay()
             b.record()
             torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
+            ts.append(a.elapsed_time(b) / (10 * n_sets))
         ms = max_over_ranks(sorted(ts)[len(ts) // 2])
         res["mla_dense_decode_32k_b8_sequence_sharded"] = {
             "sequences_per_gpu": Bl, "us_per_layer": ms * 1e3, "aggregate_hbm_gbs": B * L2 * 1024 / (ms * 1e-3) / 1e9,
-            "l2": "256 MB flush before every timed replay"}
+            "l2": "%d alternating cache sets of %d MB per GPU, 10 graph replays per timed region" % (n_sets, Bl * L2 * 1024 >> 20)}
     return res
 
 
