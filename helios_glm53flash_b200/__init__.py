@@ -58,6 +58,10 @@ SIGNATURES = {
     "hk_peer_signal": (_i, [_vp, _i, _i, _i, _vp]),
     "hk_mla_splitkv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _vp, _vp,
                                  _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "hk_mla_splitkv_sparse_step": (_i, [_vp, _vp, _i64, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _sz, _vp,
+                                        _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "hk_dsa_select_region_bytes": (_sz, [_i, _i]),
+    "hk_dsa_select_splitkv": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "hk_splitkv_region_bytes": (_sz, [_i, _i]),
     "hk_splitkv_region_reset": (_i, [_vp, _i, _i, _vp]),
     "hk_mla_splitkv_heads_step": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp, _sz, _vp, _i, _i, _vp, _vp, _i, _i, _vp]),
@@ -417,6 +421,30 @@ def mla_splitkv_step(q_lat, ckv_shard, kv_base, kv_len, parts0, parts1, m, n_hea
           n_split, n_keys_hint, _ptr(workspace), workspace.numel(), _ptr(flag_ptrs), _ptr(ptrs_m), _ptr(ptrs_l),
           _ptr(ptrs_acc), n_ranks, my_rank, _ptr(step_ctr), _ptr(local_flags), _ptr(out), max_wait_ms,
           int(bool(signal)), _stream(stream))
+
+
+def mla_splitkv_sparse_step(q_lat, ckv_shard, ckv_rows, raw_local, kidx, parts0, parts1, m, n_heads, scale, n_split,
+                            workspace, flag_ptrs, ptrs_m, ptrs_l, ptrs_acc, n_ranks, my_rank, step_ctr, local_flags, out,
+                            max_wait_ms=1000, signal=True, stream=None):
+    """mla_splitkv_step over gathered rows of the local slice (raw_local: rows relative to the slice, negative = skipped)"""
+    _call("hk_mla_splitkv_sparse_step", _ptr(q_lat), _ptr(ckv_shard), int(ckv_rows), _ptr(raw_local), kidx, _ptr(parts0[0]),
+          _ptr(parts0[1]), _ptr(parts0[2]), _ptr(parts1[0]), _ptr(parts1[1]), _ptr(parts1[2]), m, n_heads, float(scale),
+          n_split, _ptr(workspace), workspace.numel(), _ptr(flag_ptrs), _ptr(ptrs_m), _ptr(ptrs_l), _ptr(ptrs_acc),
+          n_ranks, my_rank, _ptr(step_ctr), _ptr(local_flags), _ptr(out), max_wait_ms, int(bool(signal)), _stream(stream))
+
+
+def dsa_select_region_bytes(m, n_ranks):
+    return load_library().hk_dsa_select_region_bytes(m, n_ranks)
+
+
+def dsa_select_splitkv(scores, s_stride, n_local_pools, pool_base, local_idx, cand_bases, local_cand_base, n_ranks,
+                       my_rank, m, k, q_pos, row_base, n_local_rows, sel_pools, raw_local, step_ctr, max_wait_ms=1000,
+                       signal=True, phases=3, stream=None):
+    """local top-k -> candidate exchange -> selection over all ranks' candidates -> rows of the local slice;
+    cand_bases = device int64 [n_ranks] (candidate areas as mapped here), local_cand_base = address of the own one"""
+    _call("hk_dsa_select_splitkv", _ptr(scores), s_stride, n_local_pools, pool_base, _ptr(local_idx), _ptr(cand_bases),
+          _c.c_void_p(int(local_cand_base)), n_ranks, my_rank, m, k, _ptr(q_pos), row_base, n_local_rows,
+          _ptr(sel_pools), _ptr(raw_local), _ptr(step_ctr), max_wait_ms, int(bool(signal)), int(phases), _stream(stream))
 
 
 def enable_peer_access(peer_device):

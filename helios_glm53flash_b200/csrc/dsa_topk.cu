@@ -70,13 +70,9 @@ __device__ __forceinline__ void load8(const uint16_t* row, int i8, int T, uint32
   }
 }
 
+// One row by one CTA of TK_THREADS threads; `row` and `row_o` may point to global or shared memory.
 template <bool VEC>
-__global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
-    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k,
-    int k_pad, const int* __restrict__ t_ptr, int t_seq) {
-  if (t_ptr) T = t_seq > 0 ? t_ptr[blockIdx.x / t_seq] : *t_ptr;
-  const uint16_t* row = scores + (size_t)blockIdx.x * s_stride;
-  int* row_o = out + (size_t)blockIdx.x * k_pad;
+__device__ __forceinline__ void topk_row(const uint16_t* row, int* row_o, int T, int k, int k_pad) {
   const int t = threadIdx.x;
   const int n_slots = (T + 7) >> 3;
 
@@ -184,6 +180,14 @@ __global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
   }
   const int emitted = cnt_gt + min(base_eq, n_eq_take);
   for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
+}
+
+template <bool VEC>
+__global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
+    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k,
+    int k_pad, const int* __restrict__ t_ptr, int t_seq) {
+  if (t_ptr) T = t_seq > 0 ? t_ptr[blockIdx.x / t_seq] : *t_ptr;
+  topk_row<VEC>(scores + (size_t)blockIdx.x * s_stride, out + (size_t)blockIdx.x * k_pad, T, k, k_pad);
 }
 
 
@@ -373,8 +377,10 @@ HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, in
   if (R == 0) return HK_OK;
   const bool vec = (s_stride % 8 == 0) && aligned(scores, 16);
   cudaStream_t s = as_stream(stream);
-  if (T <= TKC_MAX_T && !t_ptr) {
-    // rows of up to 65,536 scores: one 8-CTA cluster per row
+  if (T > 16384 && T <= TKC_MAX_T && R <= 16 && !t_ptr) {
+    // a few long rows (decode): one 8-CTA cluster per row.  With many rows (prefill) the clusters queue for
+    // eight free SMs of one GPC each and the one-CTA kernel below is 3 to 20 times faster (measured at
+    // 64 to 4,096 rows); up to 16,384 scores one CTA is as fast as the cluster even for a single row.
     if (vec)
       dsa_topk_cluster_kernel<true><<<R * TKC_CTAS, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad);
     else
@@ -389,3 +395,5 @@ HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, in
   HK_LAUNCH_CHECK();
   return HK_OK;
 }
+
+#include "dsa_select_splitkv.cuh"

@@ -368,35 +368,25 @@ HK_API int hk_lse_combine_peers(const float* const* ptrs_m, const float* const* 
 // bounded-wait combine over all ranks' partial sets.  The step number lives on the device (step_ctr,
 // advanced by the signal kernel), so a captured graph of this call can be replayed: the exchange set
 // written and read in step e is set e & 1, the flags carry e.
-HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
-                               float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
-                               float* part_acc1, int m, int n_heads, float scale, int n_split, int n_keys_hint,
-                               void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
-                               const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
-                               int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
-                               int max_wait_ms, int signal, void* stream) {
-  using namespace hk;
-  HK_REQUIRE(q_lat && ckv_shard && part_m0 && part_l0 && part_acc0 && part_m1 && part_l1 && part_acc1);
-  HK_REQUIRE(flag_ptrs && ptrs_m && ptrs_l && ptrs_acc && step_ctr && local_flags && out_f16 && workspace);
-  HK_REQUIRE(m > 0 && n_heads > 0 && n_heads % SIMT_HG == 0 && n_ranks >= 1 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks);
-  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv_shard, 16) && aligned(part_acc0, 16) && aligned(part_acc1, 16) && aligned(workspace, 256));
-  HK_REQUIRE(max_wait_ms > 0 && max_wait_ms <= 10000);
-  const bool tc = (n_heads == 64) && !force_simt();
+namespace hk {
+// partial over this rank's slice (dense range or gathered rows), local splits merged into the exchange set of the
+// step, signal, bounded-wait combine over all ranks' sets
+static int splitkv_exchange(MlaArgs a, int n_split, int n_keys_hint, void* workspace, size_t workspace_bytes,
+                            float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1, float* part_acc1,
+                            int* const* flag_ptrs, const float* const* ptrs_m, const float* const* ptrs_l,
+                            const float* const* ptrs_acc, int n_ranks, int my_rank, int* step_ctr, const int* local_flags,
+                            void* out_f16, int max_wait_ms, int signal, cudaStream_t s) {
+  const bool tc = (a.n_heads == 64) && !force_simt();
   if (n_split <= 0)
-    n_split = tc ? mla_flash_tc_auto_splits(m, n_keys_hint > 0 ? n_keys_hint : 4096)
-                 : simt_auto_splits(m, n_heads, n_keys_hint > 0 ? n_keys_hint : 4096);
+    n_split = tc ? mla_flash_tc_auto_splits(a.m, n_keys_hint > 0 ? n_keys_hint : 4096)
+                 : simt_auto_splits(a.m, a.n_heads, n_keys_hint > 0 ? n_keys_hint : 4096);
   if (n_split > LSE_MAX_SPLITS) return HK_ERR_UNSUPPORTED;
-  const int64_t rows = (int64_t)m * n_heads;
+  const int64_t rows = (int64_t)a.m * a.n_heads;
   PartialLayout pl = partial_layout(n_split, rows);
   if (workspace_bytes < pl.total) return HK_ERR_WORKSPACE;
   char* ws = (char*)workspace;
-  MlaArgs a{};
-  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv_shard;
-  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = 0;
-  a.m = m; a.n_heads = n_heads; a.scale = scale;
   a.n_split = n_split;
   a.part_m = (float*)ws; a.part_l = (float*)(ws + pl.off_l); a.part_acc = (float*)(ws + pl.off_acc);
-  cudaStream_t s = as_stream(stream);
   int st = HK_ERR_UNSUPPORTED;
   if (tc) st = mla_flash_tc_launch(a, s);
   if (st == HK_ERR_UNSUPPORTED) st = launch_simt(a, s);
@@ -410,6 +400,55 @@ HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const i
                                                           0, (long long)max_wait_ms * 2000000LL, device_status_ptr(), step_ctr);
   HK_LAUNCH_CHECK();
   return HK_OK;
+}
+}  // namespace hk
+
+HK_API int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t* kv_base, const int* kv_len,
+                               float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
+                               float* part_acc1, int m, int n_heads, float scale, int n_split, int n_keys_hint,
+                               void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
+                               const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
+                               int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
+                               int max_wait_ms, int signal, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv_shard && part_m0 && part_l0 && part_acc0 && part_m1 && part_l1 && part_acc1);
+  HK_REQUIRE(flag_ptrs && ptrs_m && ptrs_l && ptrs_acc && step_ctr && local_flags && out_f16 && workspace);
+  HK_REQUIRE(m > 0 && n_heads > 0 && n_heads % SIMT_HG == 0 && n_ranks >= 1 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv_shard, 16) && aligned(part_acc0, 16) && aligned(part_acc1, 16) && aligned(workspace, 256));
+  HK_REQUIRE(max_wait_ms > 0 && max_wait_ms <= 10000);
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv_shard;
+  a.kv_base = kv_base; a.kv_len = kv_len; a.pos_start = 0;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  return splitkv_exchange(a, n_split, n_keys_hint, workspace, workspace_bytes, part_m0, part_l0, part_acc0, part_m1, part_l1,
+                          part_acc1, flag_ptrs, ptrs_m, ptrs_l, ptrs_acc, n_ranks, my_rank, step_ctr, local_flags, out_f16,
+                          max_wait_ms, signal, as_stream(stream));
+}
+
+// The same step over GATHERED rows of this rank's slice (sparse split-KV): raw_local [m][kidx] holds row numbers
+// relative to the slice, negative = not on this rank (skipped); a rank without any selected row contributes an
+// empty partial (m = -inf, l = 0), which the combine weighs with zero.
+HK_API int hk_mla_splitkv_sparse_step(const void* q_lat, const void* ckv_shard, int64_t ckv_rows, const int* raw_local, int kidx,
+                                      float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
+                                      float* part_acc1, int m, int n_heads, float scale, int n_split,
+                                      void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
+                                      const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
+                                      int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
+                                      int max_wait_ms, int signal, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(q_lat && ckv_shard && raw_local && part_m0 && part_l0 && part_acc0 && part_m1 && part_l1 && part_acc1);
+  HK_REQUIRE(flag_ptrs && ptrs_m && ptrs_l && ptrs_acc && step_ctr && local_flags && out_f16 && workspace);
+  HK_REQUIRE(m > 0 && kidx >= 0 && ckv_rows >= 0 && n_heads > 0 && n_heads % SIMT_HG == 0);
+  HK_REQUIRE(n_ranks >= 1 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks);
+  HK_REQUIRE(aligned(q_lat, 16) && aligned(ckv_shard, 16) && aligned(part_acc0, 16) && aligned(part_acc1, 16) && aligned(workspace, 256));
+  HK_REQUIRE(max_wait_ms > 0 && max_wait_ms <= 10000);
+  MlaArgs a{};
+  a.q_lat = (const __half*)q_lat; a.ckv = (const __half*)ckv_shard; a.ckv_rows = ckv_rows;
+  a.raw_idx = raw_local; a.kidx = kidx;
+  a.m = m; a.n_heads = n_heads; a.scale = scale;
+  return splitkv_exchange(a, n_split, kidx, workspace, workspace_bytes, part_m0, part_l0, part_acc0, part_m1, part_l1,
+                          part_acc1, flag_ptrs, ptrs_m, ptrs_l, ptrs_acc, n_ranks, my_rank, step_ctr, local_flags, out_f16,
+                          max_wait_ms, signal, as_stream(stream));
 }
 
 

@@ -160,8 +160,11 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   auto load_acc = [&](int s) -> float4 {
     const float* pa = PTRS ? ptrs_acc[s] : part_acc + (size_t)s * rows * LATENT;
     const float4* ap = reinterpret_cast<const float4*>(pa + (size_t)r * LATENT) + cpart * LANES + cq;
-    return PTRS ? __ldcv(ap) : __ldg(ap);             // peer memory: never through the read-only cache
+    // peer memory: cache-volatile.  Local partials: L2 loads (ld.global.cg), never the non-coherent read-only path:
+    // as a programmatic dependent this kernel's lifetime overlaps the grid that writes the partials.
+    return PTRS ? __ldcv(ap) : __ldcg(ap);
   };
+  auto load_ml = [&](const float* base) -> float { return PTRS ? __ldcv(base + r) : __ldcg(base + r); };
   // All loads that do not depend on the weights go out first: this thread's first PRE accumulator pieces
   // and the (m, l) pair of split t.  The weight phases below then run while they are in flight (one memory
   // round trip on the critical path instead of three).
@@ -173,12 +176,12 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
   }
   float m_first = -INFINITY, l_first = 0.f;
   if (t < n_split) {
-    m_first = (PTRS ? ptrs_m[t] : part_m + (size_t)t * rows)[r];
-    l_first = (PTRS ? ptrs_l[t] : part_l + (size_t)t * rows)[r];
+    m_first = load_ml(PTRS ? ptrs_m[t] : part_m + (size_t)t * rows);
+    l_first = load_ml(PTRS ? ptrs_l[t] : part_l + (size_t)t * rows);
   }
   float mloc = -INFINITY;
   for (int s = t; s < n_split; s += THREADS) {
-    const float m = s == t ? m_first : (PTRS ? ptrs_m[s] : part_m + (size_t)s * rows)[r];
+    const float m = s == t ? m_first : load_ml(PTRS ? ptrs_m[s] : part_m + (size_t)s * rows);
     s_w[s] = m;
     mloc = fmaxf(mloc, m);
   }
@@ -195,7 +198,7 @@ __device__ __forceinline__ void lse_reduce_row(const float* __restrict__ part_m,
     const float m = s_w[s];
     const float w = (m == -INFINITY) ? 0.f : __expf(m - gm);
     s_w[s] = w;
-    lloc += w * (s == t ? l_first : (PTRS ? ptrs_l[s] : part_l + (size_t)s * rows)[r]);
+    lloc += w * (s == t ? l_first : load_ml(PTRS ? ptrs_l[s] : part_l + (size_t)s * rows));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);

@@ -31,7 +31,15 @@ def shard_tokens(n_tokens, rank, world):
     return synth.shard_range(n_tokens, rank, world)
 
 
-def region_layout(rows, world):
+def shard_pools(n_tokens, rank, world):
+    """sparse split-KV: [first pool, end pool) and [first row, end row) of `rank`.  The COMPLETE pools (4 tokens each)
+    are split evenly; a rank's rows are those of its pools, and the last rank also owns the up to 3 tokens of the
+    incomplete pool at the end (they are only ever reached through the 4-token tail of the selection)."""
+    p0, p1 = synth.shard_range(n_tokens // 4, rank, world)
+    return (p0, p1), (4 * p0, n_tokens if rank == world - 1 else 4 * p1)
+
+
+def region_layout(rows, world, cand_bytes=0):
     """byte offsets inside one rank's exchange region: flags | (m | l | acc) x 2.  The partial sets are
     double buffered by step parity: a rank may already write step s+1 while a slower peer still reads
     step s; it cannot reach step s+2 before that peer has signalled s+1, i.e. has finished reading s."""
@@ -44,14 +52,15 @@ def region_layout(rows, world):
         lay["l%d" % par] = off + pad
         lay["acc%d" % par] = off + 2 * pad
         off += 2 * pad + rows * 512 * 4
-    lay["total"] = off
+    lay["cand"] = off                     # candidate area of the sparse selection (hk_dsa_select_splitkv), if any
+    lay["total"] = off + cand_bytes
     return lay
 
 
 class SplitKVDecoder:
     """Owns the peer-mapped exchange region of this rank and the pointer tables of all ranks."""
 
-    def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000, form=None):
+    def __init__(self, m, n_heads=64, group=None, max_wait_ms=1000, form=None, sparse=False):
         import torch
         import torch.distributed as dist
         import helios_glm53flash_b200 as hk
@@ -63,7 +72,11 @@ class SplitKVDecoder:
         self.form = form or "all"
         if self.form == "heads" and not (n_heads == 64 and 64 % self.world == 0):
             raise ValueError("the heads form needs 64 heads and a rank count that divides 64")
-        self.lay = region_layout(self.rows, self.world)
+        self.sparse = bool(sparse)
+        if self.sparse and self.form != "all":
+            raise ValueError("the sparse step uses the 'all' form of the exchange")
+        self.lay = region_layout(self.rows, self.world,
+                                 ((hk.dsa_select_region_bytes(m, self.world) + 255) // 256) * 256 if sparse else 0)
         if self.form == "heads":
             self.lay = {"total": hk.load_library().hk_splitkv_region_bytes(m, n_heads)}
         # The exchange region is library-owned device memory with an inter-process handle; every peer
@@ -96,6 +109,13 @@ class SplitKVDecoder:
         # pointer tables of both exchange sets, [set][rank]
         self.m_ptrs, self.l_ptrs, self.acc_ptrs = [torch.cat([table(k + str(par)) for par in (0, 1)]) for k in ("m", "l", "acc")]
         self._views()
+        if self.sparse:
+            self.cand_ptrs = table("cand")
+            self.local_idx = torch.empty(m, 512, dtype=torch.int32, device="cuda")
+            self.sel_pools = torch.full((m, 512), -1, dtype=torch.int32, device="cuda")
+            self.raw_local = torch.full((m, 2052), -1, dtype=torch.int32, device="cuda")
+            self.qpos_local = torch.empty(m, dtype=torch.int32, device="cuda")
+            self.scores = None
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -149,6 +169,39 @@ class SplitKVDecoder:
                             max_wait_ms=self.max_wait_ms, signal=signal)
 
 
+    def step_sparse(self, q_lat, q_idx, w, q_pos, pool_shard, pool_range, ckv_shard, row_range, out, scale, signal=True,
+                    signal_candidates=True):
+        """one SPARSE decode step of one sequence: q_lat [m, 64, 512] f16, q_idx [m, 32, 128] / w [m, 32] of the
+        indexer, q_pos device int32 [m] (global positions); pool_shard [p1 - p0, 128] = this rank's pooled keys,
+        pool_range = (p0, p1), ckv_shard = this rank's cache rows, row_range = (r0, r1) (see shard_pools).  Scores of
+        the local pools -> selection across ranks (self.sel_pools holds the GLOBAL selection afterwards) -> attention
+        over the selected rows of the local slice -> exchange and combine.  Every rank gets the full result."""
+        import helios_glm53flash_b200 as hk
+        t = self.torch
+        (p0, p1), (r0, r1) = pool_range, row_range
+        npl = p1 - p0
+        self.epoch += 1
+        stride = max(8, ((npl + 7) // 8) * 8)
+        if self.scores is None or self.scores.shape[1] < stride:
+            self.scores = t.empty(self.m, stride, dtype=t.float16, device="cuda")
+        if self.workspace is None or getattr(self, "_n_keys", None) != -2052:
+            self._n_keys = -2052
+            self._n_split = hk.mla_auto_splits(self.m, 2052)
+            self.workspace = t.empty(max(256, hk.mla_partial_bytes(self._n_split, self.rows)), dtype=t.uint8, device="cuda")
+        if npl > 0:
+            t.sub(q_pos, r0, out=self.qpos_local)
+            hk.indexer_score(q_idx, pool_shard, w, self.qpos_local, self.scores, self.m, npl, score_stride=self.scores.shape[1])
+        hk.dsa_select_splitkv(self.scores, self.scores.shape[1], npl, p0, self.local_idx, self.cand_ptrs,
+                              self.local.data_ptr() + self.lay["cand"], self.world, self.rank, self.m, 512, q_pos, r0,
+                              r1 - r0, self.sel_pools, self.raw_local, self.step_ctr, max_wait_ms=self.max_wait_ms,
+                              signal=signal_candidates)
+        hk.mla_splitkv_sparse_step(q_lat, ckv_shard, r1 - r0, self.raw_local, 2052,
+                                   (self.part_m[0], self.part_l[0], self.part_acc[0]),
+                                   (self.part_m[1], self.part_l[1], self.part_acc[1]), self.m, self.n_heads, scale,
+                                   self._n_split, self.workspace, self.flag_ptrs, self.m_ptrs, self.l_ptrs, self.acc_ptrs,
+                                   self.world, self.rank, self.step_ctr, self.flags, out, max_wait_ms=self.max_wait_ms,
+                                   signal=signal)
+
     def resync(self):
         """After a step timed out (device status HK_ERR_TIMEOUT) the ranks are no longer in lock step and a slow peer
         may still read an exchange set: every rank calls this before stepping again.  Host barrier, flags and step
@@ -161,6 +214,8 @@ class SplitKVDecoder:
         else:
             self.flags.zero_()
             self.step_ctr.zero_()
+            if self.sparse:
+                self.local.as_tensor(self.lay["cand"], 256, self.torch.int32).zero_()
         self.epoch = 0
         self.hk.read_device_status(reset=True)
         self.torch.cuda.synchronize()

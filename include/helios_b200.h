@@ -293,6 +293,42 @@ int hk_mla_splitkv_step(const void* q_lat, const void* ckv_shard, const int64_t*
                         int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
                         int max_wait_ms, int signal, void* stream);
 
+/* Sparse split-KV decode across GPUs (one sequence, pools and cache rows split over the ranks), selection part.
+ * Rank g has scored ITS pools (hk_indexer_score with q_pos made relative to its slice): scores [m][s_stride] fp16,
+ * n_local_pools valid entries per row, the first being global pool pool_base.  The call takes the local top-k
+ * (local_idx [m][512], scratch), stores the k candidates (score bits + global pool index, ascending index) into every
+ * rank's candidate area, waits (bounded by max_wait_ms) for all ranks' candidates of the step, selects the k best of
+ * the n_ranks * k candidates with the selection rule of hk_dsa_topk (the result equals hk_dsa_topk over the whole
+ * row: an entry the whole-row selection takes is always among its rank's local top-k), and writes
+ *   sel_pools [m][512]   global pool indices, -1 padded (may be NULL),
+ *   raw_local [m][2052]  cache rows RELATIVE to this rank's slice [row_base, row_base + n_local_rows), -1 for rows of
+ *                        other ranks, pool rows past q_pos[row] and padding; the 4 tail rows q_pos - 3 .. q_pos are
+ *                        appended as hk_pool_expand does.  Feed it to hk_mla_splitkv_sparse_step.
+ * cand_bases: DEVICE array of n_ranks addresses of the ranks' candidate areas (hk_dsa_select_region_bytes(m, n_ranks)
+ * bytes each, zeroed, inside peer-mapped regions) as mapped in THIS process; local_cand_base == cand_bases[my_rank].
+ * The step number is *step_ctr + 1 (the counter that hk_mla_splitkv_sparse_step advances), the candidate sets are
+ * double buffered by its parity.  On a time-out nothing is written and the device status reports HK_ERR_TIMEOUT.
+ * signal == 0 withholds this rank's flag (failure injection in tests).  k <= 512, n_ranks <= 8.  phases: 3 = the whole
+ * call; 1 = local top-k and publication only, 2 = wait and selection only (two calls, e.g. several ranks' regions
+ * driven by one process in turn).
+ * Selection semantics: helios::aux::dsa_topk (src/cuda/aux/dsa_topk.cu:179-267); no multi-GPU counterpart there.  */
+size_t hk_dsa_select_region_bytes(int m, int n_ranks);
+int hk_dsa_select_splitkv(const void* scores, int s_stride, int n_local_pools, int pool_base, int* local_idx,
+                          void* const* cand_bases, const void* local_cand_base, int n_ranks, int my_rank, int m, int k,
+                          const int* q_pos, int row_base, int n_local_rows, int* sel_pools, int* raw_local,
+                          const int* step_ctr, int max_wait_ms, int signal, int phases, void* stream);
+
+/* hk_mla_splitkv_step over GATHERED rows of this rank's slice: raw_local [m][kidx] (negative = skipped),
+ * ckv_rows = rows in ckv_shard (larger indices are skipped).  A rank without any selected row contributes an empty
+ * partial.  All other arguments as in hk_mla_splitkv_step.                                                         */
+int hk_mla_splitkv_sparse_step(const void* q_lat, const void* ckv_shard, int64_t ckv_rows, const int* raw_local, int kidx,
+                               float* part_m0, float* part_l0, float* part_acc0, float* part_m1, float* part_l1,
+                               float* part_acc1, int m, int n_heads, float scale, int n_split,
+                               void* workspace, size_t workspace_bytes, int* const* flag_ptrs,
+                               const float* const* ptrs_m, const float* const* ptrs_l, const float* const* ptrs_acc,
+                               int n_ranks, int my_rank, int* step_ctr, const int* local_flags, void* out_f16,
+                               int max_wait_ms, int signal, void* stream);
+
 /* Split-KV across GPUs with the combine sharded by heads (n_heads = 64, 64 % n_ranks == 0): one decode step of one rank
  * in one call.  Every rank owns an exchange region of hk_splitkv_region_bytes(m, n_heads) bytes (zeroed; allocate it
  * with hk_peer_region_alloc) that every peer has mapped; region_ptrs is a DEVICE array of the n_ranks region addresses

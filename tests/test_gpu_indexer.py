@@ -124,7 +124,7 @@ def _topk_gpu(scores_bits, s_stride, R, T, k, k_pad, fn=None, offset=0):
 @pytest.mark.parametrize("R,T,k,k_pad,stride_pad,offset", [
     (4, 1000, 512, 512, 0, 0), (3, 513, 512, 512, 7, 0), (2, 511, 512, 512, 1, 0), (2, 65536, 512, 512, 0, 0),
     (1, 8, 512, 512, 0, 0), (5, 20000, 512, 520, 0, 3), (2, 4096, 1, 8, 0, 0), (2, 3000, 0, 16, 0, 0),
-    (16, 16384, 512, 512, 0, 0)])
+    (16, 16384, 512, 512, 0, 0), (16, 16392, 512, 512, 0, 0), (17, 16392, 512, 512, 0, 0), (40, 30000, 512, 512, 8, 0)])
 def test_topk_bit_exact_vs_oracle_and_reference(R, T, k, k_pad, stride_pad, offset):
     r = synth.rng(R * 7 + T)
     s_stride = T + stride_pad
@@ -186,3 +186,59 @@ def test_pool_expand_exact(per_row):
             ref.pool_expand(dev(pidx), dev(q_pos), raw2, m, 100)
         torch.cuda.synchronize()
         assert np.array_equal(raw2.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("G,P,k", [(1, 3000, 512), (2, 3000, 512), (3, 1400, 512), (8, 9000, 512), (4, 1000, 200), (2, 300, 512)])
+def test_selection_over_rank_slices_equals_whole_row_selection(G, P, k):
+    """hk_dsa_select_splitkv with the ranks' regions driven in turn by one process (all publications first, then all
+    selections: no kernel ever waits for one that has not been launched): the selected pools equal hk_dsa_topk over the
+    whole row, and the expanded rows of the ranks' slices together equal hk_pool_expand of that selection."""
+    from helios_glm53flash_b200 import splitkv
+    m = 2
+    r = synth.rng(G * 1000 + P)
+    sc = np.round(r.standard_normal((m, P), dtype=np.float32) * 4) / 4            # coarse: many exact ties
+    sc[:, P // 3:] = np.where(r.random((m, P - P // 3)) < 0.2, -np.inf, sc[:, P // 3:])
+    n_tokens = 4 * P + 2
+    q_pos = np.array([n_tokens - 1, 4 * (P // 2) + 1], dtype=np.int32)
+    for row in range(m):
+        sc[row, (q_pos[row] + 1) // 4:] = -np.inf                                   # pools not yet complete for the row
+    scb = synth.f32_to_f16_bits(sc)
+    want = _topk_gpu(scb, P, m, P, k, 512)
+    raw_want = torch.empty(m, 2052, dtype=torch.int32, device="cuda")
+    hk.pool_expand_row(dev(want), dev(q_pos), raw_want, m)
+    raw_want = raw_want.cpu().numpy()
+
+    nbytes = hk.dsa_select_region_bytes(m, G)
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(G)]
+    bases = torch.tensor([x.data_ptr() for x in regions], dtype=torch.int64, device="cuda")
+    ctr = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qp = dev(q_pos)
+    for step in range(3):                                                          # both candidate sets get used
+        state = []
+        for g in range(G):
+            (p0, p1), (r0, r1) = splitkv.shard_pools(n_tokens, g, G)
+            stride = max(8, (p1 - p0 + 7) // 8 * 8)
+            loc = np.full((m, stride), 0x7c00, dtype=np.uint16)                    # +inf beyond the slice: must not be read
+            loc[:, :p1 - p0] = scb[:, p0:p1]
+            st = dict(sc=dev_f16(loc), lidx=torch.empty(m, 512, dtype=torch.int32, device="cuda"),
+                      sel=torch.full((m, 512), -9, dtype=torch.int32, device="cuda"),
+                      raw=torch.full((m, 2052), -9, dtype=torch.int32, device="cuda"), p=(p0, p1), r=(r0, r1), stride=stride)
+            state.append(st)
+            hk.dsa_select_splitkv(st["sc"], stride, p1 - p0, p0, st["lidx"], bases, regions[g].data_ptr(), G, g, m, k, qp, r0,
+                                  r1 - r0, st["sel"], st["raw"], ctr, phases=1)
+        for g, st in enumerate(state):
+            hk.dsa_select_splitkv(st["sc"], st["stride"], st["p"][1] - st["p"][0], st["p"][0], st["lidx"], bases,
+                                  regions[g].data_ptr(), G, g, m, k, qp, st["r"][0], st["r"][1] - st["r"][0], st["sel"],
+                                  st["raw"], ctr, phases=2)
+        torch.cuda.synchronize()
+        assert hk.read_device_status(reset=True) == 0
+        merged = np.full((m, 2052), -1, dtype=np.int64)
+        for g, st in enumerate(state):
+            assert np.array_equal(st["sel"].cpu().numpy(), want), (step, g)
+            raw = st["raw"].cpu().numpy().astype(np.int64)
+            assert ((raw == -1) | ((raw >= 0) & (raw < st["r"][1] - st["r"][0]))).all()
+            here = raw >= 0
+            assert (merged[here] == -1).all()                                      # every row belongs to exactly one rank
+            merged[here] = raw[here] + st["r"][0]
+        assert np.array_equal(merged, raw_want), step
+        ctr += 1                                                                   # what the partial exchange of the step does

@@ -367,3 +367,35 @@ def test_cache_row_count_bounds_gathered_and_dense_reads():
     torch.cuda.synchronize()
     assert hk.read_device_status() == 0
     assert max_rel(synth.f16_bits_to_f32(bits(out)), o32d) < TOL
+
+
+def test_split_decode_replayed_from_a_graph_sees_each_replays_partials():
+    """The combine is a programmatic dependent of the partial kernel: in a replayed graph it must read the partials
+    of THAT replay (the cache changes between replays), not lines of an earlier one."""
+    B, L = 4, 2000
+    inp = synth.mla_inputs(B * L, B, seed=31, cache_std=0.5)
+    base, lens = dev((np.arange(B) * L).astype(np.int64)), dev(np.full(B, L, dtype=np.int32))
+    q, ckv = dev_f16(inp["q_lat"]), dev_f16(inp["ckv"])
+    out = torch.empty(B, 64, 512, dtype=torch.float16, device="cuda")
+    run = lambda: hk.mla_dense_prefill(q, ckv, out, B, 0, kv_base=base, kv_len=lens, n_keys_hint=L)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        run()                                                   # scratch is sized before the capture
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            run()
+    torch.cuda.synchronize()
+    for rep in range(3):
+        ckv.copy_(torch.roll(ckv, 977 * (rep + 1), 0))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        got = out.clone()
+        run()
+        torch.cuda.synchronize()
+        assert torch.equal(got, out), rep
+    host = bits(ckv)
+    o16, o32 = orc.mla_attend(inp["q_lat"], host, B, 64, 0.0625, kv_base=(np.arange(B) * L).astype(np.int64),
+                              kv_len=np.full(B, L, dtype=np.int32))
+    assert max_rel(synth.f16_bits_to_f32(bits(out)), o32) < TOL
