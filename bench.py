@@ -866,6 +866,8 @@ def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, 
     """The partitions of the path across the GPUs of one node, device-timed, max over ranks:
       * split-KV decode over a 262,144-token latent cache (batch 1 and batch 8): every rank attends its slice, the
         partials are combined by peer loads over NVLink; against the same decode on one GPU (rank 0's own time);
+      * the sparse form of it for one sequence (indexer scores of the local pools, selection exchanged between the
+        ranks, attention over the selected rows of the local slice), against the one-GPU chain;
       * KDA prefill sharded by heads (32 / N heads per GPU, same 32,768 tokens): strong scaling of the headline step;
       * MLA dense decode of 8 sequences x 32,768 tokens sharded by sequences (8 / N per GPU); the tensor-core kernel
         keeps all 64 heads of a sequence on one GPU (heads are its accumulator lanes);
@@ -952,6 +954,64 @@ def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, 
         del g
         dec.close()
         del shard
+        torch.cuda.empty_cache()
+    # ---- SPARSE split-KV decode of one 262,144-token sequence: pools and cache rows split over the ranks, selection
+    # exchanged (512 candidates per rank), attention over the selected rows of the local slice, partials combined ----
+    if world <= 8:
+        gen = torch.Generator(device="cuda").manual_seed(99)
+        P = L // 4
+        q = torch.randn(1, 64, 512, generator=gen, device="cuda", dtype=torch.float32).half()
+        q_idx = torch.randn(1, 32, 128, generator=gen, device="cuda", dtype=torch.float32).half()
+        w_idx = torch.rand(1, 32, generator=gen, device="cuda", dtype=torch.float32).half()
+        q_pos = torch.tensor([L - 1], dtype=torch.int32, device="cuda")
+        prange, rrange = splitkv.shard_pools(L, rank, world)
+        pool_l = (torch.randn(prange[1] - prange[0], 128, device="cuda") * 0.5).half()
+        ckv_l = torch.randn(rrange[1] - rrange[0], 512, device="cuda", dtype=torch.float16)
+        out = torch.zeros(1, 64, 512, dtype=torch.float16, device="cuda")
+        dec = splitkv.SplitKVDecoder(1, max_wait_ms=2000, sparse=True)
+        g, ms = graph_time(lambda: dec.step_sparse(q, q_idx, w_idx, q_pos, pool_l, prange, ckv_l, rrange, out, scale))
+        ms = max_over_ranks(ms)
+        status = hk.read_device_status()
+        ms1 = 0.0
+        if rank == 0:
+            pool_f = (torch.randn(P, 128, device="cuda") * 0.5).half()
+            ckv_f = torch.randn(L, 512, device="cuda", dtype=torch.float16)
+            sc = torch.empty(1, P, dtype=torch.float16, device="cuda")
+            topk = torch.empty(1, 512, dtype=torch.int32, device="cuda")
+            raw = torch.empty(1, 2052, dtype=torch.int32, device="cuda")
+            ref = torch.empty_like(out)
+            ns = hk.mla_auto_splits(1, 2052)
+            ws1 = torch.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=torch.uint8, device="cuda")
+
+            def chain():
+                hk.indexer_score(q_idx, pool_f, w_idx, q_pos, sc, 1, P)
+                hk.dsa_topk(sc, P, topk, 1, P, 512, 512)
+                hk.pool_expand_row(topk, q_pos, raw, 1)
+                hk.mla_sparse_decode(q, ckv_f, raw, 2052, ref, 1, scale=scale, n_split=ns, workspace=ws1)
+            for _ in range(3):
+                chain()
+            torch.cuda.synchronize()
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                chain()
+            g1.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(30):
+                g1.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ms1 = a.elapsed_time(b) / 30
+            del pool_f, ckv_f, g1
+        ms1 = max_over_ranks(ms1)
+        res["splitkv_sparse_decode_262k_b1"] = {
+            "us_per_step": ms * 1e3, "one_gpu_us_per_step": ms1 * 1e3, "speedup_vs_one_gpu": ms1 / ms,
+            "note": "latency-bound on one GPU already (16.8 MB of pooled keys + 2.1 MB of selected rows per step): the split "
+                    "buys cache capacity per GPU, not time", "device_status": status}
+        del g
+        dec.close()
+        del pool_l, ckv_l
         torch.cuda.empty_cache()
     t_clk1 = time.time()
     sampler.stop()
