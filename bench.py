@@ -361,11 +361,27 @@ def build_kernel_case(name):
         def fn():
             hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
         return fn, 2052 * 1024, True, "sparse MLA decode, 2052 gathered latents of 262144, %d splits" % ns
+    if name in ("sparse_prefill_4096", "sparse_prefill_1024"):
+        # the trunk's largest prefill stage: every row of a chunk attends its own 2,052 gathered rows of a 32,768-row
+        # cache (32 MB: the gathers hit L2); bytes = gathered bytes, flops = 4 * 64 * 512 per (row, key)
+        L, m = 32768, int(name.split("_")[-1])
+        ck = torch.randn(L, 512, dtype=torch.float16, device="cuda")
+        ql = torch.randn(m, 64, 512, dtype=torch.float16, device="cuda")
+        pos = torch.arange(L - m, L, device="cuda").view(m, 1)
+        raw = (torch.rand(m, 2052, device="cuda") * (pos + 1).float()).int().clamp_(max=L - 1)    # causal: rows <= position
+        lo = torch.empty(m, 64, 512, dtype=torch.float16, device="cuda")
+        ns = hk.mla_auto_splits(m, 2052)
+        wsb = torch.empty(max(256, hk.mla_partial_bytes(ns, m * 64)), dtype=torch.uint8, device="cuda")
+
+        def fn():
+            hk.mla_sparse_decode(ql, ck, raw, 2052, lo, m, n_split=ns, workspace=wsb)
+        return fn, m * 2052 * 1024, False, "sparse MLA prefill, %d rows x 2052 gathered latents of 32768, %d split(s), %.1f GFLOP" % (
+            m, ns, m * 2052 * 4 * 64 * 512 / 1e9)
     raise SystemExit("unknown case " + name)
 
 
 KERNEL_CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
-         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "q_latent_4096", "o_absorb_4096",
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "sparse_prefill_4096", "q_latent_4096", "o_absorb_4096",
          "transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k", "transpose_cast_4k",
          "gate_4k", "gated_norm_4k", "cast_conv_4k"]
 

@@ -95,6 +95,22 @@ __device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap*
       : "memory");
 }
 
+// Four gathered cache rows x one 64-channel block (4 x 128 B) in one tensor copy: the 2-D map covers the cache as
+// [row][512 channels] with a box of {64 channels, 1 row}; the instruction names four row coordinates, the copy engine
+// lays the four 128-byte pieces down one after the other and applies the 128-byte swizzle by destination address, i.e.
+// exactly key slots k .. k+3 of a block of the tile layout.  A negative row is outside the tensor: zero fill.
+__device__ __forceinline__ void tma_gather4_rows(void* smem_dst, const CUtensorMap* tmap, int channel, int r0, int r1, int r2,
+                                                 int r3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(
+          tc::smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(channel), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(tc::smem_u32(bar))
+      : "memory");
+}
+
+constexpr int FT_G4_LANES = 14;                   // lanes 0-13 of each of the 7 loader warps issue one gather each
+static_assert(FT_KEYS % 4 == 0 && FT_LOAD_WARPS * FT_G4_LANES >= (FT_KEYS / 4) * 8, "one gather4 per (key quad, block)");
+
 __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status,
                                                                      const __grid_constant__ CUtensorMap tmap,
                                                                      int use_tma) {
@@ -139,7 +155,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const int k0 = min(n, sp * tiles_per * FT_KEYS), k1 = min(n, (sp + 1) * tiles_per * FT_KEYS);
   const int n_tiles = (k1 - k0 + FT_KEYS - 1) / FT_KEYS;
   // a tile goes through TMA when it is a whole tile of a dense range
-  auto tile_is_tma = [&](int t) { return use_tma && !sparse && (k0 + (t + 1) * FT_KEYS <= k1); };
+  auto tile_is_tma = [&](int t) { return use_tma == 1 && !sparse && (k0 + (t + 1) * FT_KEYS <= k1); };
 
   if (tid == 0) {
 #pragma unroll
@@ -208,13 +224,19 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     uint4 stage[FT_ITEMS];
     // L2 prefetch of the tiles ahead keeps HBM busy while this CTA computes: the register-staged
     // loads below then hit L2.  Dense: one contiguous range per tile; sparse: one 1 KB row per lane.
+    // Gathered rows: the look-ahead costs one bulk prefetch per row, and the unit that takes them serialises the 32
+    // lanes of a warp (measured: about 4,000 cycles per 48-row tile in the warp that issues them).  That is worth it
+    // when a CTA has only a few tiles and its rows come from HBM (decode: about two tiles per CTA); in long gathered
+    // runs (prefill rows: 43 tiles per CTA, rows shared by many queries and mostly in L2) it was the largest part of
+    // the tile period, so it is only done for short runs.
+    const bool pf_rows = n_tiles <= 8 && use_tma != 2;
     auto prefetch_tile = [&](int t) {
       if (lw != 0 || t >= n_tiles) return;
       const int q0 = k0 + t * FT_KEYS;
       if (!sparse) {
         const int cnt = min(FT_KEYS, k1 - q0);
         if (lane == 0 && cnt > 0) tc::prefetch_l2(a.ckv + (size_t)(base + q0) * LATENT, (uint32_t)cnt * LATENT * 2);
-      } else {
+      } else if (pf_rows) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const int pp = q0 + half * 32 + lane;
@@ -226,35 +248,93 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
       }
     };
 #pragma unroll 1
-    for (int t = FT_NBUF - 1; t < FT_PF_AHEAD; t++) prefetch_tile(t);
-    // Gathered rows: the row numbers a warp needs for a tile are fetched one tile AHEAD, one per lane
-    // (lane j: the row of item j; warp 0 also the rows behind the validity mask), and handed out by
-    // shuffle, so the row loads of a tile are not each behind an index load of their own.
+    for (int t = FT_NBUF - 1; t < FT_PF_AHEAD; t++) prefetch_tile(t);   // (nothing for gathered rows through the copy engine)
+    // Gathered rows: the row numbers a warp needs for a tile are fetched TWO tiles ahead, one per lane (lane j: the
+    // row of item j; warp 0 also the rows behind the validity mask), and handed out by shuffle.  The loads are
+    // volatile so that they are issued here and not moved down to their first use: the row list of a query is read
+    // once, from HBM, and a load issued only one tile ahead (or sunk to its use) put its full latency, about 2,000
+    // cycles, into every tile.  Range checks that need the value (in_cache) are applied when it is used.
+    auto ld_idx = [&](int p) -> int {
+      int v;
+      asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(a.raw_idx + (size_t)r * a.kidx + p));
+      return v;
+    };
     auto item_index = [&](int tile_i, int j) -> int {      // row number of item j of this warp, -1 = hole
       const int it = lw + j * FT_LOAD_WARPS;
       const int p = k0 + tile_i * FT_KEYS + (it >> 1);
-      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? in_cache(a.raw_idx[(size_t)r * a.kidx + p]) : -1;
+      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? ld_idx(p) : -1;
     };
     auto mask_index = [&](int tile_i, int half) -> int {   // warp 0: row number of key half*32 + lane
       const int p = k0 + tile_i * FT_KEYS + half * 32 + lane;
-      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? in_cache(a.raw_idx[(size_t)r * a.kidx + p]) : -1;
+      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? ld_idx(p) : -1;
     };
-    int idx_next = item_index(0, lane), mk0_next = mask_index(0, 0), mk1_next = mask_index(0, 1);
+    if (sparse && use_tma == 2) {
+      // ---- gathered rows through the copy engine: 96 gather4 copies per tile, one per (key quad, 64-channel block),
+      // issued by 14 lanes of each loader warp.  Nothing passes through registers or the load/store unit, whose
+      // outstanding-request capacity held the register-staged path to about 13 B per cycle and SM. ----
+      const int u = lw * FT_G4_LANES + lane;
+      const bool issuer = lane < FT_G4_LANES && u < (FT_KEYS / 4) * 8;
+      const int kq = u >> 3, blk = u & 7;
+      auto quad_index = [&](int tile_i, int e) -> int {
+        const int p = k0 + tile_i * FT_KEYS + kq * 4 + e;
+        return (issuer && tile_i < n_tiles && p < k1) ? ld_idx(p) : -1;
+      };
+      int qa[4], qb[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) { qa[e] = quad_index(0, e); qb[e] = quad_index(1, e); }
+      int mk0_n1 = mask_index(0, 0), mk1_n1 = mask_index(0, 1), mk0_n2 = mask_index(1, 0), mk1_n2 = mask_index(1, 1);
+      for (int tile = 0; tile < n_tiles; tile++) {
+        const int buf = tile % FT_NBUF;
+        const int p0 = k0 + tile * FT_KEYS;
+        int rows4[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) { rows4[e] = in_cache(qa[e]); qa[e] = qb[e]; qb[e] = quad_index(tile + 2, e); }
+        const int mk0 = in_cache(mk0_n1), mk1 = in_cache(mk1_n1);
+        mk0_n1 = mk0_n2; mk1_n1 = mk1_n2;
+        mk0_n2 = mask_index(tile + 2, 0);
+        mk1_n2 = mask_index(tile + 2, 1);
+        unsigned long long mk = 0;
+        if (lw == 0) {
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            const int p = p0 + half * 32 + lane;
+            const bool v = half * 32 + lane < FT_KEYS && p < k1 && (half ? mk1 : mk0) >= 0;
+            mk |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
+          }
+        }
+        if (tile >= FT_NBUF) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - FT_NBUF) / FT_NBUF) & 1, &abort_flag, 5) && ok;
+        if (tid == 160) FT_TRACE(0, tile);
+        if (lw == 0 && lane == 0) s_mask[buf] = mk;
+        if (issuer && ok) {
+          tc::mbar_arrive_expect_tx(&k_full[buf], 4 * 128);
+          tma_gather4_rows(smem + FS_K + buf * FT_TILE + blk * FT_BLK + kq * 4 * 128, &tmap, blk * 64,
+                           rows4[0] < 0 ? -1 : rows4[0], rows4[1] < 0 ? -1 : rows4[1], rows4[2] < 0 ? -1 : rows4[2],
+                           rows4[3] < 0 ? -1 : rows4[3], &k_full[buf]);
+        } else {
+          tc::mbar_arrive(&k_full[buf]);
+        }
+        if (tid == 160) FT_TRACE(1, tile);
+      }
+    } else {
+    int idx_n1 = item_index(0, lane), mk0_n1 = mask_index(0, 0), mk1_n1 = mask_index(0, 1);
+    int idx_n2 = item_index(1, lane), mk0_n2 = mask_index(1, 0), mk1_n2 = mask_index(1, 1);
     for (int tile = 0; tile < n_tiles; tile++) {
       const int buf = tile % FT_NBUF;
       const int p0 = k0 + tile * FT_KEYS;
       const bool via_tma = tile_is_tma(tile);
       prefetch_tile(tile + FT_PF_AHEAD);
-      const int idx_cur = idx_next, mk0 = mk0_next, mk1 = mk1_next;
-      idx_next = item_index(tile + 1, lane);
-      mk0_next = mask_index(tile + 1, 0);
-      mk1_next = mask_index(tile + 1, 1);
+      if (tid == 160 && tile >= 2) FT_TRACE(13, tile);   // look-ahead prefetch issued
+      const int idx_cur = idx_n1, mk0 = in_cache(mk0_n1), mk1 = in_cache(mk1_n1);
+      idx_n1 = idx_n2; mk0_n1 = mk0_n2; mk1_n1 = mk1_n2;
+      idx_n2 = item_index(tile + 2, lane);
+      mk0_n2 = mask_index(tile + 2, 0);
+      mk1_n2 = mask_index(tile + 2, 1);
       // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
 #pragma unroll
       for (int j = 0; j < FT_ITEMS; j++) {
         const int it = lw + j * FT_LOAD_WARPS;
         stage[j] = make_uint4(0, 0, 0, 0);
-        const int row_j = __shfl_sync(0xffffffffu, idx_cur, j);
+        const int row_j = in_cache(__shfl_sync(0xffffffffu, idx_cur, j));
         if (!via_tma && it < 2 * FT_KEYS) {
           const int p = p0 + (it >> 1);
           int64_t tok = -1;
@@ -262,6 +342,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
           if (tok >= 0) stage[j] = ld_stream16(a.ckv + (size_t)tok * LATENT + ((it & 1) * 32 + lane) * 8);
         }
       }
+      if (tid == 160 && tile >= 2) FT_TRACE(14, tile);   // this tile's row loads issued
       unsigned long long mk = 0;                       // validity of the key slots of this tile
       if (lw == 0) {
 #pragma unroll
@@ -272,6 +353,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
           mk |= (unsigned long long)__ballot_sync(0xffffffffu, v) << (32 * half);
         }
       }
+      if (tid == 160 && tile >= 2) FT_TRACE(15, tile);   // validity mask built
       if (tile >= FT_NBUF) ok = tc::mbar_wait<FT_POLL_NS>(&t_done[buf], ((tile - FT_NBUF) / FT_NBUF) & 1, &abort_flag, 5) && ok;
       if (tid == 160) FT_TRACE(0, tile);               // buffer free, stores start
       uint8_t* dst0 = smem + FS_K + buf * FT_TILE;
@@ -300,6 +382,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         tc::mbar_arrive(&k_full[buf]);
       }
       if (tid == 160) FT_TRACE(1, tile);               // tile published
+    }
     }
   } else if (mma_warp) {
     // =========================== tensor-core issue (whole warp, one elected lane) ===========================
@@ -572,7 +655,7 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
   memset(&tmap, 0, sizeof(tmap));
   int use_tma = 0;
   static const bool tma_disabled = getenv("HK_MLA_NO_TMA") != nullptr;   // debug switch: vector-load path only
-  if (!a.raw_idx && !tma_disabled) {
+  if (!tma_disabled) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -586,7 +669,17 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
         encode = (EncodeFn)fn;
       looked_up = true;
     }
-    if (encode) {
+    if (encode && a.raw_idx) {
+      // gathered rows: 2-D map [row][512 channels], box {64 channels, 1 row} for the four-row gather copies
+      const cuuint64_t dims[2] = {LATENT, a.ckv_rows > 0 ? (cuuint64_t)a.ckv_rows : (cuuint64_t)1 << 31};
+      const cuuint64_t strides[1] = {LATENT * 2};
+      const cuuint32_t box[2] = {64, 1};
+      const cuuint32_t estr[2] = {1, 1};
+      if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.ckv, dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        use_tma = 2;
+    } else if (encode) {
       const cuuint64_t dims[3] = {64, a.ckv_rows > 0 ? (cuuint64_t)a.ckv_rows : (cuuint64_t)1 << 31, 8};
       const cuuint64_t strides[2] = {LATENT * 2, 128};
       const cuuint32_t box[3] = {64, FT_KEYS, 8};
