@@ -314,9 +314,9 @@ def build_kernel_case(name):
         def fn():
             hk.mla_dense_prefill(qd, ck, lo, qlen, pos, scale=512 ** -0.5, n_split=1)
         return fn, (pos + qlen) * 1024 + 2 * qlen * 65536, True, "dense causal MLA prefill, 256 rows after 32768"
-    if name in ("indexer_262k", "indexer_prefill_256"):
-        npools = 65536
-        m = 1 if name == "indexer_262k" else 256
+    if name in ("indexer_262k", "indexer_prefill_256", "indexer_prefill_1024x8192"):
+        npools = 8192 if name.endswith("x8192") else 65536
+        m = {"indexer_262k": 1, "indexer_prefill_256": 256}.get(name, 1024)
         ix = synth.indexer_inputs(npools, m, seed=7)
         qi, pk, w = _bits16(ix["q_idx"], torch.float16), _bits16(ix["pool_k"], torch.float16), _bits16(ix["w"], torch.float16)
         q_pos = torch.full((m,), 4 * npools - 1, dtype=torch.int32, device="cuda")
@@ -324,7 +324,8 @@ def build_kernel_case(name):
 
         def fn():
             hk.indexer_score(qi, pk, w, q_pos, sc, m, npools)
-        return fn, npools * 256 + m * npools * 2, True, "indexer scores, %d rows x 65536 pools" % m
+        return fn, npools * 256 + m * npools * 2, True, "indexer scores, %d rows x %d pools, %.1f GFLOP" % (
+            m, npools, m * npools * 32 * 128 * 2 / 1e9)
     if name in ("q_latent_4096", "o_absorb_4096"):
         n = 4096
         kb = (0.05 * torch.randn(32768, 512, device="cuda")).half()
@@ -381,7 +382,7 @@ def build_kernel_case(name):
 
 
 KERNEL_CASES = ["kda_prefill_8k", "kda_prefill_32k", "kda_recurrent_512", "conv_8k", "conv_32k", "kda_decode", "mla_dense_b1",
-         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "topk_262k", "sparse_262k", "sparse_prefill_4096", "q_latent_4096", "o_absorb_4096",
+         "mla_dense_b8", "mla_prefill_256", "indexer_262k", "indexer_prefill_256", "indexer_prefill_1024x8192", "topk_262k", "sparse_262k", "sparse_prefill_4096", "q_latent_4096", "o_absorb_4096",
          "transpose_cast_32k", "gate_32k", "gated_norm_32k", "cast_conv_32k", "kda_prefill_gated_32k", "transpose_cast_4k",
          "gate_4k", "gated_norm_4k", "cast_conv_4k"]
 
@@ -612,14 +613,39 @@ def run_trunk_case(args):
     status = hk.read_device_status()
     pre_ms, dec_ms = e0.elapsed_time(e1), e1.elapsed_time(e2)
     tot = sum(shares.values())
-    # decode again as one CUDA graph per step position is not possible (positions change); the host-launched figure
-    # is what an engine without graphs sees
+    # The same decode step as ONE replayed CUDA graph (all launches of the 45 layers at one position; a replay repeats
+    # that position, so the work per replay is that of one token at this context): what an engine that captures its
+    # decode step sees, without the host's launch cost.
+    graph_us = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            tr.run_chunk(ctx + steps, 1)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                tr.run_chunk(ctx + steps, 1)
+            side.synchronize()
+            for _ in range(3):
+                graph.replay()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(max(steps, 8)):
+                graph.replay()
+            g1.record()
+            side.synchronize()
+            graph_us = 1e3 * g0.elapsed_time(g1) / max(steps, 8)
+        status = status or hk.read_device_status()
+    except Exception as exc:   # a capture that fails must not cost the prefill figures
+        graph_us = "capture failed: %s" % str(exc)[:200]
     line = {"metric": "trunk_attention_prefill_tokens_per_s", "value": B * ctx / (pre_ms * 1e-3), "unit": "tok/s", "n_gpus": 1,
             "higher_is_better": True, "data": "synthetic", "dtype": "bf16 / fp16 in, fp32 accumulate + state",
             "config": {"workload": "34 KDA + 11 MLA attention layers in the engine's call order, %d sequence(s) x %d tokens, "
                                    "prefill in %d-token chunks, then %d decode steps" % (B, ctx, chunk, steps)},
             "prefill_ms": pre_ms, "prefill_ms_per_chunk": pre_ms / (ctx / chunk),
             "decode_us_per_token_host_launched": 1e3 * dec_ms / max(steps, 1),
+            "decode_us_per_token_graph_replay": graph_us,
             "stage_share_of_prefill": {k: v / tot for k, v in sorted(shares.items(), key=lambda kv: -kv[1])},
             "stage_ms_total": {k: v for k, v in sorted(shares.items(), key=lambda kv: -kv[1])},
             "device_status": status}

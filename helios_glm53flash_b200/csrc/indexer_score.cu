@@ -10,7 +10,11 @@
 // kernel streams the key plane once from HBM (256 B per pool).  Both operands are K-major exactly
 // as they sit in memory ([pool][128] and [row][head][128]); they are staged with 16-byte cp.async
 // into the no-swizzle core-matrix layout (8 rows x 16 B contiguous per lane group: conflict-free).
+#include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime at first use)
 #include <cuda_pipeline_primitives.h>
+
+#include <cstdlib>
+#include <cstring>
 
 #include "hk_common.cuh"
 #include "tc05.cuh"
@@ -285,6 +289,8 @@ int* device_status_ptr() {
 }
 }  // namespace hk
 
+#include "indexer_prefill.cuh"
+
 HK_API int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void* w,
                             const int* q_pos, void* scores, int m, int npools, int score_stride,
                             int n_heads, int dtype, void* stream) {
@@ -330,6 +336,11 @@ HK_API int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void
       indexer_tc_decode_kernel<1><<<grid_x, 128, smem, sd>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, tiles, cols, std_);
     HK_LAUNCH_CHECK();
     return HK_OK;
+  }
+  if (m >= 32) {
+    // many rows: the pipelined copy-engine kernel
+    const int st = indexer_prefill_launch(q_idx, pool_k_nt, w, q_pos, scores, m, npools, score_stride, dtype, as_stream(stream));
+    if (st != HK_ERR_UNSUPPORTED) return st;
   }
   // enough row groups per CTA to amortise the key tile, enough CTAs to cover the GPU twice
   int row_groups = (m + IX_RG - 1) / IX_RG;

@@ -76,7 +76,8 @@ def _score_case(m, npools, q_pos, bf16=False, seed=0):
 
 
 @pytest.mark.parametrize("m,npools,bf16", [(1, 128, False), (2, 64, False), (3, 600, False), (48, 600, False),
-                                           (1, 4096, True), (9, 1000, True), (1, 65536, False)])
+                                           (1, 4096, True), (9, 1000, True), (1, 65536, False),
+                                           (45, 1100, True), (37, 300, False), (130, 5000, False), (32, 129, False)])
 def test_indexer_score_vs_oracle_and_reference(m, npools, bf16):
     q_pos = np.array([min(npools * 4 - 1, 900 + 37 * r) if m > 1 else npools * 4 - 1 for r in range(m)], dtype=np.int32)
     inp, g = _score_case(m, npools, q_pos, bf16, seed=m + npools)
