@@ -44,6 +44,8 @@ SIGNATURES = {
     "hk_indexer_score": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hk_indexer_score_legacy": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "hk_dsa_topk": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "hk_dsa_topk_expand": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "hk_indexer_select": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "hk_pool_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "hk_mla_partial_bytes": (_sz, [_i, _i64]),
     "hk_mla_auto_splits": (_i, [_i, _i]),
@@ -284,6 +286,22 @@ def dsa_topk(scores, s_stride, indices, R, T, k, k_pad, t_ptr=None, t_seq=0, str
     """helios::aux::dsa_topk (src/cuda/aux/dsa_topk.cuh:15-27)."""
     _call("hk_dsa_topk", _ptr(scores), s_stride, _ptr(indices), R, T, k, k_pad, _ptr(t_ptr), t_seq,
           _stream(stream))
+
+
+def dsa_topk_expand(scores, s_stride, indices, raw_idx, q_pos, R, T, k, after_scorer=False, stream=None):
+    """dsa_topk (k_pad = 512) with pool_expand_row folded in: indices [R, 512] and raw_idx [R, 2052] in one kernel"""
+    _call("hk_dsa_topk_expand", _ptr(scores), s_stride, _ptr(indices), _ptr(raw_idx), _ptr(q_pos), R, T, k,
+          int(bool(after_scorer)), _stream(stream))
+
+
+def indexer_select(q_idx, pool_k_nt, w, q_pos, scores, indices, raw_idx, m, npools, k=512, stream=None, score_stride=None,
+                   n_heads=32):
+    """decode-step selection: indexer_score -> top-k with the expansion folded in, two launches (the second a
+    programmatic dependent of the first); scores = fp16 workspace [m, score_stride]"""
+    torch = _require_cuda()
+    dtype = HK_BF16 if q_idx.dtype == torch.bfloat16 else HK_F16
+    _call("hk_indexer_select", _ptr(q_idx), _ptr(pool_k_nt), _ptr(w), _ptr(q_pos), _ptr(scores), _ptr(indices),
+          _ptr(raw_idx), m, npools, npools if score_stride is None else score_stride, n_heads, dtype, k, _stream(stream))
 
 
 # ---------------------------------------------------------------------------------------------

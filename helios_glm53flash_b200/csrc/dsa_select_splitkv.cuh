@@ -133,7 +133,7 @@ __global__ __launch_bounds__(TK_THREADS) void sel_select_kernel(const char* __re
   for (int j = t; j < n_cand; j += TK_THREADS) s_ci[j] = __ldcv(gi + j);
   for (int j = t; j < n_cand / 2; j += TK_THREADS) reinterpret_cast<uint32_t*>(s_sc)[j] = __ldcv(gs + j);
   __syncthreads();
-  topk_row<true>(s_sc, s_pos, n_cand, k, SEL_K);
+  topk_row<true>(s_sc, TopkSink{s_pos, nullptr, 0}, n_cand, k, SEL_K);
   __syncthreads();
   const int cur = q_pos[row];
   int4* out = reinterpret_cast<int4*>(raw_local + (size_t)row * (SEL_K * 4 + 4));

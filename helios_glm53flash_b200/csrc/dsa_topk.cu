@@ -70,9 +70,32 @@ __device__ __forceinline__ void load8(const uint16_t* row, int i8, int T, uint32
   }
 }
 
-// One row by one CTA of TK_THREADS threads; `row` and `row_o` may point to global or shared memory.
+// Where a selected index goes: the index row and, optionally, the expanded token row of the same slot
+// (helios::attn::pool_expand_row folded in: slot i -> tokens 4 idx .. 4 idx + 3, each kept if <= cur, else -1; the
+// caller appends the four tail tokens in slot k_pad).
+struct TopkSink {
+  int* idx;          // [k_pad] (global or shared)
+  int4* raw;         // [k_pad + 1] or nullptr
+  int cur;
+  __device__ __forceinline__ void put(int slot, int v) const {
+    idx[slot] = v;
+    if (raw) {
+      const int tk = v * POOL;
+      raw[slot] = v < 0 ? make_int4(-1, -1, -1, -1)
+                        : make_int4(tk <= cur ? tk : -1, tk + 1 <= cur ? tk + 1 : -1, tk + 2 <= cur ? tk + 2 : -1,
+                                    tk + 3 <= cur ? tk + 3 : -1);
+    }
+  }
+  __device__ __forceinline__ void put_tail(int k_pad) const {
+    if (raw)
+      raw[k_pad] = make_int4(cur - 3 >= 0 ? cur - 3 : -1, cur - 2 >= 0 ? cur - 2 : -1, cur - 1 >= 0 ? cur - 1 : -1,
+                             cur >= 0 ? cur : -1);
+  }
+};
+
+// One row by one CTA of TK_THREADS threads; `row` and the sink's index row may point to global or shared memory.
 template <bool VEC>
-__device__ __forceinline__ void topk_row(const uint16_t* row, int* row_o, int T, int k, int k_pad) {
+__device__ __forceinline__ void topk_row(const uint16_t* row, const TopkSink row_o, int T, int k, int k_pad) {
   const int t = threadIdx.x;
   const int n_slots = (T + 7) >> 3;
 
@@ -167,27 +190,34 @@ __device__ __forceinline__ void topk_row(const uint16_t* row, int* row_o, int T,
     while (m_gt) {
       const int j = __ffs((int)m_gt) - 1;
       m_gt &= m_gt - 1;
-      row_o[o_gt++] = ibase + j;
+      row_o.put(o_gt++, ibase + j);
     }
     while (m_eq) {
       const int j = __ffs((int)m_eq) - 1;
       m_eq &= m_eq - 1;
-      if (o_eq < n_eq_take) row_o[cnt_gt + o_eq] = ibase + j;
+      if (o_eq < n_eq_take) row_o.put(cnt_gt + o_eq, ibase + j);
       o_eq++;
     }
     base_gt += tot & 0xffff;
     base_eq += tot >> 16;
   }
   const int emitted = cnt_gt + min(base_eq, n_eq_take);
-  for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
+  for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o.put(j, -1);
+  if (t == 0) row_o.put_tail(k_pad);
 }
 
+// raw != nullptr: the expanded token rows [R][4 k_pad + 4] are written as well, row r clipped at q_pos[r]
 template <bool VEC>
 __global__ __launch_bounds__(TK_THREADS) void dsa_topk_kernel(
-    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k,
-    int k_pad, const int* __restrict__ t_ptr, int t_seq) {
+    const uint16_t* scores, int* __restrict__ out, int T, int s_stride, int k,
+    int k_pad, const int* __restrict__ t_ptr, int t_seq, int* __restrict__ raw, const int* __restrict__ q_pos) {
+  // behind a kernel that allowed its dependents to start early (the scorer): wait for its scores
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (t_ptr) T = t_seq > 0 ? t_ptr[blockIdx.x / t_seq] : *t_ptr;
-  topk_row<VEC>(scores + (size_t)blockIdx.x * s_stride, out + (size_t)blockIdx.x * k_pad, T, k, k_pad);
+  TopkSink sink{out + (size_t)blockIdx.x * k_pad,
+                raw ? reinterpret_cast<int4*>(raw + (size_t)blockIdx.x * (4 * k_pad + 4)) : nullptr,
+                raw ? q_pos[blockIdx.x] : 0};
+  topk_row<VEC>(scores + (size_t)blockIdx.x * s_stride, sink, T, k, k_pad);
 }
 
 
@@ -211,13 +241,16 @@ constexpr int TKC_MAX_T = TKC_CTAS * TK_THREADS * 8;      // 65536
 
 template <bool VEC>
 __global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void dsa_topk_cluster_kernel(
-    const uint16_t* __restrict__ scores, int* __restrict__ out, int T, int s_stride, int k, int k_pad) {
+    const uint16_t* scores, int* __restrict__ out, int T, int s_stride, int k, int k_pad,
+    int* __restrict__ raw, const int* __restrict__ q_pos) {
   namespace cg = cooperative_groups;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // see dsa_topk_kernel
   cg::cluster_group cluster = cg::this_cluster();
   const int c = (int)cluster.block_rank();
   const int row_id = blockIdx.x / TKC_CTAS;
   const uint16_t* row = scores + (size_t)row_id * s_stride;
-  int* row_o = out + (size_t)row_id * k_pad;
+  const TopkSink row_o{out + (size_t)row_id * k_pad,
+                       raw ? reinterpret_cast<int4*>(raw + (size_t)row_id * (4 * k_pad + 4)) : nullptr, raw ? q_pos[row_id] : 0};
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 
   __shared__ int hist[2048];       // this CTA's bucket counts
@@ -345,17 +378,18 @@ __global__ __cluster_dims__(TKC_CTAS, 1, 1) __launch_bounds__(TK_THREADS) void d
   while (m_gt) {
     const int j = __ffs((int)m_gt) - 1;
     m_gt &= m_gt - 1;
-    row_o[o_gt++] = ibase + j;
+    row_o.put(o_gt++, ibase + j);
   }
   while (m_eq) {
     const int j = __ffs((int)m_eq) - 1;
     m_eq &= m_eq - 1;
-    if (o_eq < n_eq_take) row_o[cnt_gt + o_eq] = ibase + j;
+    if (o_eq < n_eq_take) row_o.put(cnt_gt + o_eq, ibase + j);
     o_eq++;
   }
   if (c == 0) {
     const int emitted = cnt_gt + min(sh_off[4], n_eq_take);
-    for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o[j] = -1;
+    for (int j = emitted + t; j < k_pad; j += TK_THREADS) row_o.put(j, -1);
+    if (t == 0) row_o.put_tail(k_pad);
   }
   TK_TRACE(6);
   cluster.sync();                  // (4) no CTA leaves while a peer may still read its shared memory
@@ -369,31 +403,55 @@ extern "C" __attribute__((visibility("default"))) int hk_debug_topk_trace(long l
 }
 #endif
 
+namespace hk {
+// common launcher; raw != nullptr adds the expansion, pdl launches the kernel as a programmatic dependent of the
+// kernel before it in the stream (which must have released its dependents: the decode scorer does)
+static int topk_launch(const void* scores, int s_stride, int* indices, int R, int T, int k, int k_pad, const int* t_ptr,
+                       int t_seq, int* raw, const int* q_pos, bool pdl, cudaStream_t s) {
+  const bool vec = (s_stride % 8 == 0) && aligned(scores, 16);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(TK_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  const uint16_t* sc = (const uint16_t*)scores;
+  cudaError_t e;
+  if (T > 16384 && T <= TKC_MAX_T && R <= 16 && !t_ptr) {
+    // a few long rows (decode): one 8-CTA cluster per row.  With many rows (prefill) the clusters queue for
+    // eight free SMs of one GPC each and the one-CTA kernel below is 3 to 20 times faster (measured at
+    // 64 to 4,096 rows); up to 16,384 scores one CTA is as fast as the cluster even for a single row.
+    cfg.gridDim = dim3(R * TKC_CTAS);
+    e = vec ? cudaLaunchKernelEx(&cfg, dsa_topk_cluster_kernel<true>, sc, indices, T, s_stride, k, k_pad, raw, q_pos)
+            : cudaLaunchKernelEx(&cfg, dsa_topk_cluster_kernel<false>, sc, indices, T, s_stride, k, k_pad, raw, q_pos);
+  } else {
+    cfg.gridDim = dim3(R);
+    e = vec ? cudaLaunchKernelEx(&cfg, dsa_topk_kernel<true>, sc, indices, T, s_stride, k, k_pad, t_ptr, t_seq, raw, q_pos)
+            : cudaLaunchKernelEx(&cfg, dsa_topk_kernel<false>, sc, indices, T, s_stride, k, k_pad, t_ptr, t_seq, raw, q_pos);
+  }
+  return e == cudaSuccess && cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
+}
+}  // namespace hk
+
 HK_API int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, int T, int k,
                        int k_pad, const int* t_ptr, int t_seq, void* stream) {
   using namespace hk;
   HK_REQUIRE(scores && indices && R >= 0 && T >= 0 && k >= 0 && k <= k_pad && s_stride >= 0);
   HK_REQUIRE(k <= 32767);  // packed 16-bit counters in the compaction scan
   if (R == 0) return HK_OK;
-  const bool vec = (s_stride % 8 == 0) && aligned(scores, 16);
-  cudaStream_t s = as_stream(stream);
-  if (T > 16384 && T <= TKC_MAX_T && R <= 16 && !t_ptr) {
-    // a few long rows (decode): one 8-CTA cluster per row.  With many rows (prefill) the clusters queue for
-    // eight free SMs of one GPC each and the one-CTA kernel below is 3 to 20 times faster (measured at
-    // 64 to 4,096 rows); up to 16,384 scores one CTA is as fast as the cluster even for a single row.
-    if (vec)
-      dsa_topk_cluster_kernel<true><<<R * TKC_CTAS, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad);
-    else
-      dsa_topk_cluster_kernel<false><<<R * TKC_CTAS, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad);
-    HK_LAUNCH_CHECK();
-    return HK_OK;
-  }
-  if (vec)
-    dsa_topk_kernel<true><<<R, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad, t_ptr, t_seq);
-  else
-    dsa_topk_kernel<false><<<R, TK_THREADS, 0, s>>>((const uint16_t*)scores, indices, T, s_stride, k, k_pad, t_ptr, t_seq);
-  HK_LAUNCH_CHECK();
-  return HK_OK;
+  return topk_launch(scores, s_stride, indices, R, T, k, k_pad, t_ptr, t_seq, nullptr, nullptr, false, as_stream(stream));
+}
+
+HK_API int hk_dsa_topk_expand(const void* scores, int s_stride, int* indices, int* raw_idx, const int* q_pos, int R, int T,
+                              int k, int after_scorer, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(scores && indices && raw_idx && q_pos && R >= 0 && T >= 0 && k >= 0 && k <= 512 && s_stride >= 0);
+  HK_REQUIRE(aligned(raw_idx, 16));
+  if (R == 0) return HK_OK;
+  return topk_launch(scores, s_stride, indices, R, T, k, 512, nullptr, 0, raw_idx, q_pos, after_scorer != 0, as_stream(stream));
 }
 
 #include "dsa_select_splitkv.cuh"

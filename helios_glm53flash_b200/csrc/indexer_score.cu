@@ -165,6 +165,9 @@ __global__ __launch_bounds__(128) void indexer_tc_decode_kernel(
   __shared__ int abort_flag;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane >> 4, chunk = lane & 15;    // a warp instruction covers 2 rows x 16 chunks
+  // a selection kernel launched as this grid's programmatic dependent may be placed now; it waits for this grid's
+  // completion itself before it reads a score
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
     tc::mbar_init(&bar, 1);
@@ -358,4 +361,20 @@ HK_API int hk_indexer_score(const void* q_idx, const void* pool_k_nt, const void
     indexer_tc_kernel<1><<<grid, 128, IX_SMEM, s>>>((const uint16_t*)q_idx, (const uint16_t*)pool_k_nt, (const uint16_t*)w, q_pos, (__half*)scores, m, npools, score_stride, rows_per_cta, st);
   HK_LAUNCH_CHECK();
   return HK_OK;
+}
+
+// Scores, top-k and expansion of a decode step (at most 8 query rows) in one call: the scorer above, then the
+// selection kernel with the expansion folded into its output writes, launched as the scorer's programmatic dependent
+// (its CTAs are resident and waiting when the last score is written).  The reference runs four launches here
+// (indexer_score -> dsa_topk -> pool_expand_row -> ..., src/engine/runner.cpp:620-630); this is two.
+HK_API int hk_indexer_select(const void* q_idx, const void* pool_k_nt, const void* w, const int* q_pos, void* scores,
+                             int* indices, int* raw_idx, int m, int npools, int score_stride, int n_heads, int dtype, int k,
+                             void* stream) {
+  using namespace hk;
+  HK_REQUIRE(indices && raw_idx && m >= 0 && k >= 0 && k <= 512);
+  if (m == 0) return HK_OK;
+  if (npools == 0) return hk_dsa_topk_expand(scores, score_stride, indices, raw_idx, q_pos, m, 0, k, 0, stream);
+  const int st = hk_indexer_score(q_idx, pool_k_nt, w, q_pos, scores, m, npools, score_stride, n_heads, dtype, stream);
+  if (st != HK_OK) return st;
+  return hk_dsa_topk_expand(scores, score_stride, indices, raw_idx, q_pos, m, npools, k, m <= IX_RG ? 1 : 0, stream);
 }

@@ -184,7 +184,14 @@ class TrunkAttention:
             self._mark("mla_q_latent")
         npools = (pos + n) // 4
         ktop = min(512, npools)
-        for off in range(0, n, IDX_BLOCK):
+        if n <= 8 and self.fused and npools > 0:
+            # decode rows: scores, top-k and expansion as two launches
+            sc = self.scores.view(-1)[:n * npools].view(n, npools)
+            hk.indexer_select(mi["q_idx"][:n], pool, mi["w"][:n], self.qpos[:n], sc, self.topk[:n], self.raw_idx[:n], n, npools, k=ktop)
+            blocks = ()
+        else:
+            blocks = range(0, n, IDX_BLOCK)
+        for off in blocks:
             rows = min(IDX_BLOCK, n - off)
             if npools > 0:
                 sc = self.scores.view(-1)[:rows * npools].view(rows, npools)

@@ -183,6 +183,20 @@ int hk_indexer_score_legacy(const void* q_idx, const void* pool_k, const void* w
 int hk_dsa_topk(const void* scores, int s_stride, int* indices, int R, int T, int k, int k_pad,
                 const int* t_ptr, int t_seq, void* stream);
 
+/* hk_dsa_topk with hk_pool_expand folded into the output writes: indices [R][512] as hk_dsa_topk (k_pad = 512) AND
+ * raw_idx [R][2052] as hk_pool_expand(indices, q_pos) would give, in one kernel.  after_scorer != 0: the kernel is
+ * launched as a programmatic dependent of the kernel before it in the stream (use only directly behind
+ * hk_indexer_score of at most 8 rows, which releases its dependents early).                                       */
+int hk_dsa_topk_expand(const void* scores, int s_stride, int* indices, int* raw_idx, const int* q_pos, int R, int T,
+                       int k, int after_scorer, void* stream);
+
+/* Decode-step selection in one call: hk_indexer_score into `scores` (workspace, [m][score_stride] fp16), then
+ * hk_dsa_topk_expand behind it.  Two launches where the reference's decode runs indexer_score, dsa_topk and
+ * pool_expand_row (src/engine/runner.cpp:620-630).  Arguments as in those calls; k <= 512.                        */
+int hk_indexer_select(const void* q_idx, const void* pool_k_nt, const void* w, const int* q_pos, void* scores,
+                      int* indices, int* raw_idx, int m, int npools, int score_stride, int n_heads, int dtype, int k,
+                      void* stream);
+
 /* Pool index -> token index expansion plus the 4 tail tokens, clipped to the row's position.
  * Replaces helios::attn::pool_expand_row (q_pos != NULL) and helios::attn::pool_expand
  * (q_pos == NULL, cur_pos used for every row)  (src/cuda/attn/attn.cuh:57-72, attn.cu:284-327).

@@ -243,3 +243,56 @@ def test_selection_over_rank_slices_equals_whole_row_selection(G, P, k):
             merged[here] = raw[here] + st["r"][0]
         assert np.array_equal(merged, raw_want), step
         ctr += 1                                                                   # what the partial exchange of the step does
+
+
+@pytest.mark.parametrize("R,T,k", [(2, 65536, 512), (1, 20000, 512), (3, 5000, 512), (40, 700, 512), (2, 300, 512), (1, 4096, 77)])
+def test_topk_with_expansion_equals_topk_then_expand(R, T, k):
+    r = synth.rng(R + T)
+    sc = np.round(r.standard_normal((R, T), dtype=np.float32) * 4) / 4
+    sc[:, T // 2:] = np.where(r.random((R, T - T // 2)) < 0.3, -np.inf, sc[:, T // 2:])
+    q_pos = np.array([4 * T - 1 - 5 * i for i in range(R)], dtype=np.int32)
+    scores = dev_f16(synth.f32_to_f16_bits(sc))
+    idx0 = torch.full((R, 512), -7, dtype=torch.int32, device="cuda")
+    raw0 = torch.full((R, 2052), -7, dtype=torch.int32, device="cuda")
+    hk.dsa_topk(scores, T, idx0, R, T, k, 512)
+    hk.pool_expand_row(idx0, dev(q_pos), raw0, R)
+    idx1, raw1 = torch.full_like(idx0, -9), torch.full_like(raw0, -9)
+    hk.dsa_topk_expand(scores, T, idx1, raw1, dev(q_pos), R, T, k)
+    torch.cuda.synchronize()
+    assert torch.equal(idx0, idx1) and torch.equal(raw0, raw1)
+
+
+@pytest.mark.parametrize("m,npools", [(1, 65536), (1, 5000), (3, 600), (8, 20000)])
+def test_indexer_select_equals_the_three_call_chain_also_from_a_graph(m, npools):
+    q_pos = np.array([npools * 4 - 1 - 9 * r for r in range(m)], dtype=np.int32)
+    inp, _ = _score_case(m, npools, q_pos, False, seed=5 + m)
+    qi, pk, w, qp = dev_f16(inp["q_idx"]), dev_f16(inp["pool_k"]), dev_f16(inp["w"]), dev(q_pos)
+    sc0 = torch.empty(m, npools, dtype=torch.float16, device="cuda")
+    idx0 = torch.empty(m, 512, dtype=torch.int32, device="cuda")
+    raw0 = torch.empty(m, 2052, dtype=torch.int32, device="cuda")
+    hk.indexer_score(qi, pk, w, qp, sc0, m, npools)
+    hk.dsa_topk(sc0, npools, idx0, m, npools, min(512, npools), 512)
+    hk.pool_expand_row(idx0, qp, raw0, m)
+    sc1, idx1, raw1 = torch.empty_like(sc0), torch.full_like(idx0, -9), torch.full_like(raw0, -9)
+    run = lambda: hk.indexer_select(qi, pk, w, qp, sc1, idx1, raw1, m, npools, k=min(512, npools))
+    run()
+    torch.cuda.synchronize()
+    assert torch.equal(idx0, idx1) and torch.equal(raw0, raw1)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            run()
+    for rep in range(3):
+        # other keys every replay: the selection kernel must see the scores of THIS replay
+        pk.copy_(torch.roll(pk, 1 + rep, 0))
+        idx1.fill_(-9)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        hk.indexer_score(qi, pk, w, qp, sc0, m, npools)
+        hk.dsa_topk(sc0, npools, idx0, m, npools, min(512, npools), 512)
+        hk.pool_expand_row(idx0, qp, raw0, m)
+        torch.cuda.synchronize()
+        assert torch.equal(idx0, idx1) and torch.equal(raw0, raw1), rep
+    assert hk.read_device_status() == 0
