@@ -27,7 +27,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 T_FULL, HEADS, DIM = 32768, 32, 128
-CPU_SAMPLE_T = 16384
+CPU_SAMPLE_T = 32768
 METRIC = "kda_prefill_tokens_per_s_at_32k_ctx"
 
 
@@ -898,7 +898,7 @@ def main():
         if multi is not None:
             line["multi_gpu"] = multi
         if not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(steps=1)
+            line["cpu_baseline"] = cpu_baseline(steps=3)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -1263,7 +1263,14 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
     f_chain = [(lambda pk=pk, ck=ck: chain(pk, ck)) for pk, ck in zip(pks, ckvs)]
     res["dsa_sparse_mla_decode_262k_us_per_layer"] = 1e3 * _time_loop(torch, f_chain, flush=flush, label="dsa_sparse_mla_decode_262k",
                                                                         gpu_index=gpu_index) / n_mla
-    del pks, ckvs, f_sparse, f_chain
+
+    def chain2(pk, ck):       # the same step with the selection in two launches (scorer, top-k with the expansion inside)
+        hk.indexer_select(qi, pk, w, q_pos, sc, idx, raw, 1, npools)
+        hk.mla_sparse_decode(ql, ck, raw, 2052, lo, 1, n_split=ns, workspace=wsb)
+    f_chain2 = [(lambda pk=pk, ck=ck: chain2(pk, ck)) for pk, ck in zip(pks, ckvs)]
+    res["dsa_sparse_mla_decode_262k_fused_selection_us_per_layer"] = 1e3 * _time_loop(
+        torch, f_chain2, flush=flush, label="dsa_sparse_mla_decode_262k_fused_selection", gpu_index=gpu_index) / n_mla
+    del pks, ckvs, f_sparse, f_chain, f_chain2
     torch.cuda.empty_cache()
     # ---- one KDA layer of the 32K prefill from the projections' fp32 outputs to the gated, normalised fp16
     #      activations: the reference's call sequence (transpose+cast, gate, conv, recurrence, gated norm) and the
