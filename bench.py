@@ -883,7 +883,7 @@ def main():
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          # dram__bytes_read + dram__bytes_write of the fused kernel from the ncu capture of the T = 8,192
                          # case (574 MB), scaled by the chunk count: traffic is linear in T
-                         "traffic": 574.1e6 * (T / 8192.0), "traffic_source": "ncu dram bytes of kda_fused_kernel at T = 8192, scaled by T / 8192",
+                         "traffic": 574.8e6 * (T / 8192.0), "traffic_source": "ncu dram bytes of kda_fused_kernel at T = 8192, scaled by T / 8192",
                          "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "tensor_tflops_dense_chunk_math": (T // 64) * H * 11.71e6 / (kda_ms * 1e-3) / 1e12},
