@@ -111,6 +111,9 @@ __device__ __forceinline__ void tma_gather4_rows(void* smem_dst, const CUtensorM
 constexpr int FT_G4_LANES = 14;                   // lanes 0-13 of each of the 7 loader warps issue one gather each
 static_assert(FT_KEYS % 4 == 0 && FT_LOAD_WARPS * FT_G4_LANES >= (FT_KEYS / 4) * 8, "one gather4 per (key quad, block)");
 
+// G4: gathered rows through the copy engine (use_tma == 2).  A separate instantiation: with both loaders in one
+// kernel the dense paths lost 3-14 % (256-row dense prefill 1.55 -> 1.77 ms) to the register allocation of the whole.
+template <bool G4>
 __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status,
                                                                      const __grid_constant__ CUtensorMap tmap,
                                                                      int use_tma) {
@@ -229,7 +232,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     // when a CTA has only a few tiles and its rows come from HBM (decode: about two tiles per CTA); in long gathered
     // runs (prefill rows: 43 tiles per CTA, rows shared by many queries and mostly in L2) it was the largest part of
     // the tile period, so it is only done for short runs.
-    const bool pf_rows = n_tiles <= 8 && use_tma != 2;
+    const bool pf_rows = n_tiles <= 8 && !G4;
     auto prefetch_tile = [&](int t) {
       if (lw != 0 || t >= n_tiles) return;
       const int q0 = k0 + t * FT_KEYS;
@@ -249,11 +252,9 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     };
 #pragma unroll 1
     for (int t = FT_NBUF - 1; t < FT_PF_AHEAD; t++) prefetch_tile(t);   // (nothing for gathered rows through the copy engine)
-    // Gathered rows: the row numbers a warp needs for a tile are fetched TWO tiles ahead, one per lane (lane j: the
-    // row of item j; warp 0 also the rows behind the validity mask), and handed out by shuffle.  The loads are
-    // volatile so that they are issued here and not moved down to their first use: the row list of a query is read
-    // once, from HBM, and a load issued only one tile ahead (or sunk to its use) put its full latency, about 2,000
-    // cycles, into every tile.  Range checks that need the value (in_cache) are applied when it is used.
+    // Gathered rows through the copy engine: the row numbers a lane needs are fetched TWO tiles ahead with volatile
+    // loads, so that they are issued where they stand and not moved down to their first use (the row list of a query
+    // is read once, from HBM); range checks that need the value (in_cache) are applied when it is used.
     auto ld_idx = [&](int p) -> int {
       int v;
       asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(a.raw_idx + (size_t)r * a.kidx + p));
@@ -262,13 +263,13 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
     auto item_index = [&](int tile_i, int j) -> int {      // row number of item j of this warp, -1 = hole
       const int it = lw + j * FT_LOAD_WARPS;
       const int p = k0 + tile_i * FT_KEYS + (it >> 1);
-      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? ld_idx(p) : -1;
+      return (sparse && tile_i < n_tiles && j < FT_ITEMS && it < 2 * FT_KEYS && p < k1) ? a.raw_idx[(size_t)r * a.kidx + p] : -1;
     };
     auto mask_index = [&](int tile_i, int half) -> int {   // warp 0: row number of key half*32 + lane
       const int p = k0 + tile_i * FT_KEYS + half * 32 + lane;
-      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? ld_idx(p) : -1;
+      return (sparse && lw == 0 && tile_i < n_tiles && half * 32 + lane < FT_KEYS && p < k1) ? (G4 ? ld_idx(p) : a.raw_idx[(size_t)r * a.kidx + p]) : -1;
     };
-    if (sparse && use_tma == 2) {
+    if (G4) {
       // ---- gathered rows through the copy engine: 96 gather4 copies per tile, one per (key quad, 64-channel block),
       // issued by 14 lanes of each loader warp.  Nothing passes through registers or the load/store unit, whose
       // outstanding-request capacity held the register-staged path to about 13 B per cycle and SM. ----
@@ -316,30 +317,33 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
         if (tid == 160) FT_TRACE(1, tile);
       }
     } else {
-    int idx_n1 = item_index(0, lane), mk0_n1 = mask_index(0, 0), mk1_n1 = mask_index(0, 1);
-    int idx_n2 = item_index(1, lane), mk0_n2 = mask_index(1, 0), mk1_n2 = mask_index(1, 1);
+    // (register-staged path: gathered rows only without the copy engine; row numbers one tile ahead, plain loads)
+    int idx_next = item_index(0, lane), mk0_next = mask_index(0, 0), mk1_next = mask_index(0, 1);
     for (int tile = 0; tile < n_tiles; tile++) {
       const int buf = tile % FT_NBUF;
       const int p0 = k0 + tile * FT_KEYS;
       const bool via_tma = tile_is_tma(tile);
       prefetch_tile(tile + FT_PF_AHEAD);
       if (tid == 160 && tile >= 2) FT_TRACE(13, tile);   // look-ahead prefetch issued
-      const int idx_cur = idx_n1, mk0 = in_cache(mk0_n1), mk1 = in_cache(mk1_n1);
-      idx_n1 = idx_n2; mk0_n1 = mk0_n2; mk1_n1 = mk1_n2;
-      idx_n2 = item_index(tile + 2, lane);
-      mk0_n2 = mask_index(tile + 2, 0);
-      mk1_n2 = mask_index(tile + 2, 1);
+      const int idx_cur = idx_next, mk0 = in_cache(mk0_next), mk1 = in_cache(mk1_next);
+      idx_next = item_index(tile + 1, lane);
+      mk0_next = mask_index(tile + 1, 0);
+      mk1_next = mask_index(tile + 1, 1);
       // item = (key, half row): lane copies chunk half*32 + lane of that key's 1 KB latent row
+      // (a tile that arrives as a tensor copy skips all of this: the loader warps' instructions compete with the
+      // softmax warps for issue slots, and the kernel executes about 4 K warp instructions per tile as it is)
+      if (!via_tma) {
 #pragma unroll
-      for (int j = 0; j < FT_ITEMS; j++) {
-        const int it = lw + j * FT_LOAD_WARPS;
-        stage[j] = make_uint4(0, 0, 0, 0);
-        const int row_j = in_cache(__shfl_sync(0xffffffffu, idx_cur, j));
-        if (!via_tma && it < 2 * FT_KEYS) {
-          const int p = p0 + (it >> 1);
-          int64_t tok = -1;
-          if (p < k1) tok = sparse ? (int64_t)row_j : base + p;
-          if (tok >= 0) stage[j] = ld_stream16(a.ckv + (size_t)tok * LATENT + ((it & 1) * 32 + lane) * 8);
+        for (int j = 0; j < FT_ITEMS; j++) {
+          const int it = lw + j * FT_LOAD_WARPS;
+          stage[j] = make_uint4(0, 0, 0, 0);
+          const int row_j = sparse ? in_cache(__shfl_sync(0xffffffffu, idx_cur, j)) : -1;
+          if (it < 2 * FT_KEYS) {
+            const int p = p0 + (it >> 1);
+            int64_t tok = -1;
+            if (p < k1) tok = sparse ? (int64_t)row_j : base + p;
+            if (tok >= 0) stage[j] = ld_stream16(a.ckv + (size_t)tok * LATENT + ((it & 1) * 32 + lane) * 8);
+          }
         }
       }
       if (tid == 160 && tile >= 2) FT_TRACE(14, tile);   // this tile's row loads issued
@@ -645,7 +649,8 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(mla_flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FS_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(mla_flash_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FS_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(mla_flash_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FS_SMEM) != cudaSuccess)
       return HK_ERR_CUDA;
     attr_set[dev] = true;
   }
@@ -691,7 +696,10 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
     }
   }
   dim3 grid(a.n_split, a.m);
-  mla_flash_tc_kernel<<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
+  if (use_tma == 2)
+    mla_flash_tc_kernel<true><<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
+  else
+    mla_flash_tc_kernel<false><<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 
