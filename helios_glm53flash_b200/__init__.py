@@ -30,6 +30,8 @@ SIGNATURES = {
     "hk_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "hk_kda_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "hk_kda_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]),
+    "hk_kda_decode_layer": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _f, _f, _i, _i, _i,
+                                 _vp, _vp, _vp]),
     "hk_kda_chunked_set_form": (_i, [_i]),
     "hk_kda_dispatch_is_chunked": (_i, [_i, _i, _i, _i, _i, _i, _i, _i]),
     "hk_kda_chunked_workspace_bytes": (_sz, [_i, _i, _i]),
@@ -207,6 +209,25 @@ def kda_decode_step(x, conv_state, conv_weight, conv_bias, g, beta, rec_state, o
     _call("hk_kda_decode_step", _ptr(x), _ptr(conv_state), _ptr(conv_weight), _ptr(conv_bias), _ptr(g), _ptr(beta),
           _ptr(rec_state), _ptr(out), _ptr(out_f32), _ptr(conv_out), bsz, num_heads, _ptr(slots), _ptr(tickets),
           _stream(stream))
+
+
+def kda_decode_layer(x32, conv_state, conv_weight, conv_bias, f, b, dt_bias, a_log, lower_bound, rec_state, out, norm_w,
+                     gate_out, y, bsz, num_heads, epsilon=1e-6, gate_act=1, constant_bias=0.0, slots=None, out_f32=None,
+                     stream=None, tickets=None):
+    """The KDA layer of one decoded token in ONE launch (src/engine/runner.cpp:433-489 runs five): x = bf16(x32)
+    (glue::kda_transpose_cast of one row), g / beta from f / b (glue::kda_gate), short conv + SiLU, recurrence, gated RMS
+    norm of the output (aux::gated_rms_norm with gate `gate_out`, weight `norm_w`) -> y.  `out` receives the recurrence
+    output as the separate calls would leave it.  `tickets`: 2 * bsz * num_heads zeroed int32."""
+    if tickets is None:
+        torch = _require_cuda()
+        key = (x32.device.index, -2 * bsz * num_heads)
+        tickets = _decode_tickets.get(key)
+        if tickets is None:
+            tickets = _decode_tickets[key] = torch.zeros(2 * bsz * num_heads, dtype=torch.int32, device=x32.device)
+    _call("hk_kda_decode_layer", _ptr(x32), _ptr(conv_state), _ptr(conv_weight), _ptr(conv_bias), _ptr(f), _ptr(b), _ptr(dt_bias),
+          _ptr(a_log), float(lower_bound), _ptr(rec_state), _ptr(out), _ptr(out_f32), _ptr(norm_w), _dtype_code(norm_w),
+          _ptr(gate_out), _dtype_code(gate_out), _ptr(y), _dtype_code(y), float(epsilon), float(constant_bias), int(gate_act),
+          bsz, num_heads, _ptr(slots), _ptr(tickets), _stream(stream))
 
 
 def kda_chunked_set_form(form):

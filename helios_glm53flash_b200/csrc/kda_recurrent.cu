@@ -10,6 +10,7 @@
 // group kg; the k-reduction is the sum of the KG group sums taken in ascending order, which for
 // D = 128, NV = 32 is exactly the reference's 4 x 32 order (gdn.cu:683-705).
 #include "hk_common.cuh"
+#include "kda_norm_common.cuh"
 
 namespace hk {
 
@@ -282,6 +283,142 @@ __global__ __launch_bounds__(128) void kda_decode_conv_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The whole KDA layer of a decoded token in ONE launch: cast of the projected q|k|v row, gate preparation, short
+// convolution, recurrence, gated RMS norm.  The reference's decode runs kda_transpose_cast, kda_gate,
+// cuda_causal_conv1d_update, cuda_recurrent_gated_delta_rule and gated_rms_norm here (src/engine/runner.cpp:433-489);
+// at 2-3 us per launch, over 34 layers, the launches are most of a decode step.  Same grid and arithmetic as
+// kda_decode_conv_kernel with, in front, x = bf16(x32) and g = gate_value(f), beta = bf16(sigmoid(b)) computed in
+// place, and behind it the norm of the head's 128 outputs, done by whichever value slice of the head is the LAST to
+// have written its outputs (second ticket counter; it reads the other slices' bf16 outputs from L2).  Every value is
+// formed by the same operations as in the separate kernels: results are bit-identical to the five-call sequence.
+// ---------------------------------------------------------------------------------------------
+template <int NV>
+__global__ __launch_bounds__(128) void kda_decode_layer_kernel(
+    const float* __restrict__ x32, __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ conv_w,
+    const __nv_bfloat16* __restrict__ conv_bias, const float* __restrict__ f, const float* __restrict__ bgate,
+    const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound, float* __restrict__ state,
+    __nv_bfloat16* out, float* __restrict__ out_f32, const void* __restrict__ norm_w, int w_bf16,
+    const void* __restrict__ gate_out, int g_bf16, void* __restrict__ y, int y_f16, float eps, float cbias, int gate_act, int H,
+    float scale, const int* __restrict__ slots, int* __restrict__ tickets) {
+  constexpr int D = 128;
+  constexpr int KG = 128 / NV, RPT = D / KG;
+  const int b = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * NV;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j = tid % NV, kg = tid / NV;
+  const int dim = 3 * H * D;
+  const int slot = slots ? slots[b] : b;
+  const size_t bh = (size_t)b * H + head;
+  float* my_state = state + ((size_t)slot * H + head) * D * D + (size_t)(kg * RPT) * D + v0 + j;
+  __shared__ float sh_q[D], sh_k[D], sh_d[D];
+  __shared__ float sh_red[2][4];
+  __shared__ float sh_part[2][KG][NV];
+  __shared__ int sh_last, sh_last2;
+
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; i++) S[i] = my_state[(size_t)i * D];
+
+  const float* xb = x32 + (size_t)b * dim;
+  __nv_bfloat16* cs = conv_state + (size_t)slot * dim * 4;
+  const int cq = head * D + tid, ck = (H + head) * D + tid, cv = (2 * H + head) * D + v0 + j;
+  const __nv_bfloat16 xq = __float2bfloat16(xb[cq]), xk = __float2bfloat16(xb[ck]), xv = __float2bfloat16(xb[cv]);
+  const uint2 sq4 = *reinterpret_cast<const uint2*>(cs + (size_t)cq * 4), wq4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)cq * 4));
+  const uint2 sk4 = *reinterpret_cast<const uint2*>(cs + (size_t)ck * 4), wk4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)ck * 4));
+  const uint2 sv4 = *reinterpret_cast<const uint2*>(cs + (size_t)cv * 4), wv4 = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)cv * 4));
+  const float q = conv4_silu_bf16(sq4, wq4, conv_bias ? __bfloat162float(conv_bias[cq]) : 0.f, __bfloat162float(xq));
+  const float k = conv4_silu_bf16(sk4, wk4, conv_bias ? __bfloat162float(conv_bias[ck]) : 0.f, __bfloat162float(xk));
+  const float v = conv4_silu_bf16(sv4, wv4, conv_bias ? __bfloat162float(conv_bias[cv]) : 0.f, __bfloat162float(xv));
+  const float gv = gate_value(f[bh * D + tid], __ldg(dt_bias + head * D + tid), __expf(__ldg(a_log + head)), lower_bound);
+  const float beta_h = __bfloat162float(__float2bfloat16(1.0f / (1.0f + __expf(-bgate[bh]))));
+
+  float sq = warp_sum(q * q), sk = warp_sum(k * k);
+  if (lane == 0) {
+    sh_red[0][warp] = sq;
+    sh_red[1][warp] = sk;
+  }
+  __syncthreads();
+  {
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      tq += sh_red[0][w];
+      tk += sh_red[1][w];
+    }
+    sh_q[tid] = q * rsqrtf(tq + 1e-6f);
+    sh_k[tid] = k * rsqrtf(tk + 1e-6f);
+    sh_d[tid] = __expf(gv);
+  }
+  int ticket = 0;
+  if (tid == 0) ticket = atomicAdd(tickets + bh, 1);
+  __syncthreads();
+  if (kg == 0) *reinterpret_cast<uint2*>(cs + (size_t)cv * 4) = conv4_rolled(sv4, xv);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < RPT; i++) {
+    const int c = kg * RPT + i;
+    sum = sum + sh_k[c] * sh_d[c] * S[i];
+  }
+  sh_part[0][kg][j] = sum;
+  __syncthreads();
+  float kv = 0.f;
+#pragma unroll
+  for (int p = 0; p < KG; p++) kv = __fadd_rn(kv, sh_part[0][p][j]);
+  const float vp = v - kv;
+  float o = 0.f;
+#pragma unroll
+  for (int i = 0; i < RPT; i++) {
+    const int c = kg * RPT + i;
+    const float st = S[i] * sh_d[c] + sh_k[c] * vp * beta_h;
+    S[i] = st;
+    o = o + sh_q[c] * st;
+  }
+  sh_part[1][kg][j] = o;
+  __syncthreads();
+  if (kg == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int p = 0; p < KG; p++) tot = __fadd_rn(tot, sh_part[1][p][j]);
+    tot *= scale;
+    const size_t oi = bh * D + v0 + j;
+    out[oi] = __float2bfloat16_rz(tot);
+    if (out_f32) out_f32[oi] = tot;
+    __threadfence();                       // the outputs of this slice are visible before its second ticket is drawn
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; i++) my_state[(size_t)i * D] = S[i];
+  __syncthreads();
+  if (tid == 0) {
+    const int last = ticket == (int)gridDim.z - 1;
+    if (last) tickets[bh] = 0;
+    sh_last = last;
+    int* t2 = tickets + (size_t)gridDim.x * H + bh;
+    const int last2 = atomicAdd(t2, 1) == (int)gridDim.z - 1;
+    if (last2) *t2 = 0;
+    sh_last2 = last2;
+  }
+  __syncthreads();
+  if (sh_last) {
+    *reinterpret_cast<uint2*>(cs + (size_t)cq * 4) = conv4_rolled(sq4, xq);
+    *reinterpret_cast<uint2*>(cs + (size_t)ck * 4) = conv4_rolled(sk4, xk);
+  }
+  if (sh_last2 && warp == 0) {
+    // gated RMS norm of the head's 128 outputs: lane = four channels, as the one-warp-per-row norm kernel
+    __threadfence();
+    const uint2 xr = __ldcg(reinterpret_cast<const uint2*>(out + bh * D) + lane);
+    const float4 xa = make_float4(bf16lo(xr.x), bf16hi(xr.x), bf16lo(xr.y), bf16hi(xr.y));
+    const float4 ga = g_bf16 ? load4(reinterpret_cast<const __nv_bfloat16*>(gate_out) + bh * D + 4 * lane)
+                             : load4(reinterpret_cast<const float*>(gate_out) + bh * D + 4 * lane);
+    const float4 w4 = w_bf16 ? load4(reinterpret_cast<const __nv_bfloat16*>(norm_w) + 4 * lane)
+                             : load4(reinterpret_cast<const float*>(norm_w) + 4 * lane);
+    float s = warp_sum(sum_squares(0.f, xa));
+    const float rmf = rsqrtf(s / (float)D + eps);
+    const float4 r = finish4(xa, w4, ga, rmf, cbias, false, gate_act);
+    if (y_f16) store4(reinterpret_cast<__half*>(y) + bh * D + 4 * lane, r);
+    else store4(reinterpret_cast<float*>(y) + bh * D + 4 * lane, r);
+  }
+}
+
 template <int NV>
 static int launch_decode_conv(const __nv_bfloat16* x, __nv_bfloat16* conv_state, const __nv_bfloat16* w, const __nv_bfloat16* bias,
                               const float* g, const __nv_bfloat16* beta, float* state, __nv_bfloat16* out, float* out_f32,
@@ -358,4 +495,32 @@ HK_API int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_
   const bool narrow = (long)bsz * num_heads * 4 < sm_count();
   return narrow ? launch_decode_conv<16>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, tickets, s)
                 : launch_decode_conv<32>(xb, cs, cw, cb, g, bt, rec_state, o, out_f32, co, bsz, num_heads, slots, tickets, s);
+}
+
+HK_API int hk_kda_decode_layer(const float* x32, void* conv_state, const void* conv_weight, const void* conv_bias, const float* f,
+                               const float* b, const float* dt_bias, const float* a_log, float lower_bound, float* rec_state,
+                               void* out, float* out_f32, const void* norm_w, int w_type, const void* gate_out, int g_type, void* y,
+                               int y_type, float epsilon, float constant_bias, int gate_act, int bsz, int num_heads,
+                               const int* slots, int* tickets, void* stream) {
+  using namespace hk;
+  HK_REQUIRE(x32 && conv_state && conv_weight && f && b && dt_bias && a_log && rec_state && out && norm_w && gate_out && y && tickets);
+  HK_REQUIRE(bsz > 0 && bsz <= 65535 && num_heads > 0 && num_heads <= 65535);
+  HK_REQUIRE(w_type == HK_F32 || w_type == HK_BF16);
+  HK_REQUIRE(y_type == HK_F32 || y_type == HK_F16);
+  HK_REQUIRE(g_type == HK_F32 || g_type == HK_BF16);
+  HK_REQUIRE(gate_act == 0 || gate_act == 1);
+  HK_REQUIRE(aligned(out, 8) && aligned(norm_w, w_type == HK_F32 ? 16 : 8) && aligned(y, y_type == HK_F32 ? 16 : 8) &&
+             aligned(gate_out, g_type == HK_F32 ? 16 : 8));
+  cudaStream_t s = as_stream(stream);
+  const float scale = 1.0f / sqrtf(128.0f);
+  const bool narrow = (long)bsz * num_heads * 4 < sm_count();
+#define HK_DL(NV)                                                                                                          \
+  kda_decode_layer_kernel<NV><<<dim3(bsz, num_heads, 128 / NV), 128, 0, s>>>(                                              \
+      x32, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)conv_weight, (const __nv_bfloat16*)conv_bias, f, b, dt_bias, a_log,  \
+      lower_bound, rec_state, (__nv_bfloat16*)out, out_f32, norm_w, w_type == HK_BF16, gate_out, g_type == HK_BF16, y,        \
+      y_type == HK_F16, epsilon, constant_bias, gate_act, num_heads, scale, slots, tickets)
+  if (narrow) HK_DL(16); else HK_DL(32);
+#undef HK_DL
+  HK_LAUNCH_CHECK();
+  return HK_OK;
 }

@@ -121,10 +121,14 @@ class TrunkAttention:
             x32, f, b = x32.contiguous(), f.contiguous(), b.contiguous()
         qkv, rec = self.qkv.view(-1)[:B * n * dim].view(B, n, dim), self.rec_out.view(-1)[:B * n * H * D].view(B, n, H, D)
         if n == 1 and self.fused:
-            for s in range(B):
-                hk.kda_transpose_cast(self.x16[s], x32[s], 1, dim)
-            g = self._decode_gate(f, b)
-            hk.kda_decode_step(self.x16, self.conv_state[L], ki["conv_w"], None, g[0], g[1], self.rec_state[L], rec, B, H)
+            # a decoded token: the whole layer (cast, gates, conv, recurrence, gated norm) is one launch
+            y = self.kda_y[:B * H]
+            hk.kda_decode_layer(x32.reshape(B, dim), self.conv_state[L], ki["conv_w"], None, f.reshape(B, H, D), b.reshape(B, H),
+                                ki["dt_bias"], ki["a_log"], ki["lower_bound"], self.rec_state[L], rec, ki["norm_w"],
+                                ki["gate_out"][:B * H], y, B, H, epsilon=1e-6, gate_act=1)
+            if self.keep:
+                self.kept.setdefault(("kda", L), []).append((rec.clone(), y.clone()))
+            return
         elif self.fused:
             hk.kda_cast_conv(x32, self.conv_state[L], None, ki["conv_w"], None, qkv, B, dim, n, True)
             if timed:

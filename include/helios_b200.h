@@ -82,6 +82,20 @@ int hk_kda_decode_step(const void* x, void* conv_state, const void* conv_weight,
                        const void* beta, float* rec_state, void* out, float* out_f32, void* conv_out, int bsz,
                        int num_heads, const int* slots, int* tickets, void* stream);
 
+/* The whole KDA layer of ONE decoded token per sequence in one launch: cast of the projected row x32 [bsz][3*H*128] fp32
+ * to bf16 (glue::kda_transpose_cast of one row), g = lower_bound * sigmoid(exp(a_log[h]) * (f + dt_bias)) and
+ * beta = sigmoid(b) (glue::kda_gate; f [bsz][H][128] fp32, b [bsz][H] fp32), hk_kda_decode_step, and the gated RMS norm
+ * of the output (hk_gated_rms_norm with w_groups 1, gate after the norm): y [bsz*H][128] of y_type (HK_F16 / HK_F32),
+ * norm_w [128] of w_type (HK_F32 / HK_BF16), gate_out [bsz*H][128] of g_type (HK_F32 / HK_BF16).  `out` (bf16) and
+ * out_f32 (optional) receive the recurrence output.  The reference's decode runs five launches here
+ * (src/engine/runner.cpp:433-489); results are bit-identical to calling the five in turn.
+ * tickets: 2 * bsz * H zeroed ints of caller memory, left zeroed; calls sharing them must not overlap on the GPU.   */
+int hk_kda_decode_layer(const float* x32, void* conv_state, const void* conv_weight, const void* conv_bias, const float* f,
+                        const float* b, const float* dt_bias, const float* a_log, float lower_bound, float* rec_state,
+                        void* out, float* out_f32, const void* norm_w, int w_type, const void* gate_out, int g_type, void* y,
+                        int y_type, float epsilon, float constant_bias, int gate_act, int bsz, int num_heads,
+                        const int* slots, int* tickets, void* stream);
+
 /* Chunked (64-token) KDA prefill on the tensor cores; numerically equivalent to
  * hk_kda_recurrent(channelwise=1, history=0) on the same arguments (the reference has no chunked
  * kernel: prefill calls the recurrence with seqlen = n, src/engine/runner.cpp:468-471).

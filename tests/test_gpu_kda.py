@@ -301,3 +301,50 @@ def test_decode_step_with_conv_inside_equals_the_two_launch_sequence(H, bsz):
     _, o_32, _ = orc.kda_recurrent(bits(qkv_b[0]).reshape(bsz, 1, dim), np.ascontiguousarray(gates["g"][:, :1]),
                                    np.ascontiguousarray(gates["beta"][:, :1]), s0, bsz, 1, H, H, D, D)
     assert max_rel(o32_b[0].cpu().numpy().reshape(bsz, 1, H, D), o_32) < 2e-3
+
+
+@pytest.mark.parametrize("H,bsz,w_bf16,g_bf16,y_f16", [(32, 1, True, False, True), (4, 3, False, True, False), (64, 2, True, True, True)])
+def test_decode_layer_in_one_launch_equals_the_five_call_sequence(H, bsz, w_bf16, g_bf16, y_f16):
+    """hk_kda_decode_layer (cast, gate preparation, conv, recurrence, gated RMS norm of one decoded token in ONE launch)
+    against kda_transpose_cast -> kda_gate -> cuda_causal_conv1d_update -> cuda_recurrent_gated_delta_rule ->
+    gated_rms_norm on the same buffers, 5 tokens in a row with carried window and state: the same bits everywhere"""
+    D, steps = 128, 5
+    dim = 3 * H * D
+    r = synth.rng(5 + H)
+    x32 = dev(r.standard_normal((steps, bsz, dim), dtype=np.float32))
+    raw = synth.kda_raw_gates(steps * bsz, H, D, seed=9)
+    f = dev(raw["f"]).reshape(steps, bsz, H, D).contiguous()
+    b = dev(raw["b"]).reshape(steps, bsz, H).contiguous()
+    dtb, alog, lb = dev(raw["dt_bias"]), dev(raw["a_log"]), raw["lower_bound"]
+    w = dev_bf16(synth.f32_to_bf16_bits((0.1 * r.standard_normal((dim, 4), dtype=np.float32)).astype(np.float32)))
+    cst0 = synth.f32_to_bf16_bits(r.standard_normal((bsz, dim, 4), dtype=np.float32))
+    s0 = (0.1 * r.standard_normal((bsz, 1, H, D, D), dtype=np.float32)).astype(np.float32)
+    nw = (1.0 + 0.1 * torch.randn(D, device="cuda"))
+    nw = nw.to(torch.bfloat16) if w_bf16 else nw
+    go = torch.randn(steps, bsz * H, D, device="cuda")
+    go = go.to(torch.bfloat16) if g_bf16 else go
+    ydt = torch.float16 if y_f16 else torch.float32
+    cs_a, st_a, cs_b, st_b = dev_bf16(cst0), dev(s0), dev_bf16(cst0), dev(s0)
+    x16 = torch.empty(bsz, dim, 1, dtype=torch.bfloat16, device="cuda")
+    g = torch.empty(bsz, H, D, dtype=torch.float32, device="cuda")
+    beta = torch.empty(bsz, H, dtype=torch.bfloat16, device="cuda")
+    qkv = torch.empty(bsz, 1, dim, dtype=torch.bfloat16, device="cuda")
+    out_a = torch.empty(steps, bsz, 1, H, D, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty(steps, bsz, H, D, dtype=torch.bfloat16, device="cuda")
+    y_a = torch.empty(steps, bsz * H, D, dtype=ydt, device="cuda")
+    y_b = torch.empty(steps, bsz * H, D, dtype=ydt, device="cuda")
+    for s in range(steps):
+        for q in range(bsz):
+            hk.kda_transpose_cast(x16[q], x32[s, q:q + 1], 1, dim)
+        hk.kda_gate(b[s], f[s], dtb, alog, lb, beta, g, bsz, H, D)
+        hk.cuda_causal_conv1d_update(x16, cs_a, None, w, None, qkv, bsz, dim, 1, 4, 4, True, False)
+        hk.cuda_recurrent_gated_delta_rule(qkv, g, beta, st_a, out_a[s], bsz, 1, H, H, D, D, 1, None, True, False)
+        hk.gated_rms_norm(out_a[s], nw, y_a[s], go[s], bsz * H, D, 1e-6, gate_act=1)
+        hk.kda_decode_layer(x32[s], cs_b, w, None, f[s], b[s], dtb, alog, lb, st_b, out_b[s], nw, go[s], y_b[s], bsz, H,
+                            epsilon=1e-6, gate_act=1)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(cs_a), bits(cs_b)), "rolling window"
+    assert np.array_equal(st_a.cpu().numpy(), st_b.cpu().numpy()), "recurrent state"
+    assert np.array_equal(bits(out_a.reshape(steps, bsz, H, D)), bits(out_b)), "recurrence outputs"
+    assert torch.equal(y_a, y_b), "normalised outputs"
+    assert torch.isfinite(y_b.float()).all()
