@@ -1210,6 +1210,31 @@ def side_measurements(hk, synth, torch, np, gpu_index=0):
         hk.cuda_recurrent_gated_delta_rule(qkv1, g, b, st, o, 1, 1, H, H, D, D, 1, None, True, False)
     fns = [(lambda st=st, cs=cs: two_launch(st, cs)) for st, cs in zip(sts, css)]
     res["kda_decode_two_launch_us_per_layer"] = 1e3 * _time_loop(torch, fns, flush=flush) / n_kda
+    # the whole layer of a decoded token, from the projections' fp32 row to the gated, normalised fp16 activations: one
+    # launch (hk_kda_decode_layer), and the reference's five-call sequence (cast, gate, conv, recurrence, gated norm)
+    rawg = synth.kda_raw_gates(1, H, D, seed=4)
+    f1, b1 = dev(rawg["f"]), dev(rawg["b"])
+    dtb1, alog1, lb1 = dev(rawg["dt_bias"]), dev(rawg["a_log"]), rawg["lower_bound"]
+    x32d = torch.randn(1, dimc, device="cuda")
+    nw1 = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    go1 = torch.randn(H, D, device="cuda")
+    y1 = torch.empty(H, D, dtype=torch.float16, device="cuda")
+    o1 = torch.empty(1, H, D, dtype=torch.bfloat16, device="cuda")
+    g1, bt1 = torch.empty(1, H, D, device="cuda"), torch.empty(1, H, dtype=torch.bfloat16, device="cuda")
+    x16d = torch.empty(dimc, 1, dtype=torch.bfloat16, device="cuda")
+    fns = [(lambda st=st, cs=cs: hk.kda_decode_layer(x32d, cs, wdec, None, f1, b1, dtb1, alog1, lb1, st, o1, nw1, go1, y1, 1, H))
+           for st, cs in zip(sts, css)]
+    res["kda_decode_layer_one_launch_us_per_layer"] = 1e3 * _time_loop(torch, fns, flush=flush, label="kda_decode_layer",
+                                                                       gpu_index=gpu_index) / n_kda
+
+    def five_calls(st, cs):
+        hk.kda_transpose_cast(x16d, x32d, 1, dimc)
+        hk.kda_gate(b1, f1, dtb1, alog1, lb1, bt1, g1, 1, H, D)
+        hk.cuda_causal_conv1d_update(x16d.view(1, dimc, 1), cs, None, wdec, None, qkv1, 1, dimc, 1, 4, 4, True, False)
+        hk.cuda_recurrent_gated_delta_rule(qkv1, g1, bt1, st, o, 1, 1, H, H, D, D, 1, None, True, False)
+        hk.gated_rms_norm(o, nw1, y1, go1, H, D, 1e-6, gate_act=1)
+    fns = [(lambda st=st, cs=cs: five_calls(st, cs)) for st, cs in zip(sts, css)]
+    res["kda_decode_layer_five_call_sequence_us_per_layer"] = 1e3 * _time_loop(torch, fns, flush=flush) / n_kda
     del sts, css
     # ---- dense MLA decode over 32K latent caches: 11 layers (B=1), 2 alternating layers (B=8) ----
     L = 32768
