@@ -81,6 +81,7 @@ SIGNATURES = {
     "hk_o_absorb_t": (_i, [_vp, _vp, _vp, _i, _vp]),
     "hk_mla_cache_append": (_i, [_vp, _vp, _vp, _vp, _c.c_longlong, _i, _f, _vp]),
     "hk_layernorm_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "hk_mla_decode_prologue": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp]),
     "hk_read_device_status": (_i, [_vp, _i]),
     "hk_tc05_selftest": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
@@ -294,6 +295,15 @@ def gated_rms_norm(x, w, y, g, rows, dim, epsilon, constant_bias=0.0, w_groups=1
 def layernorm_f16(x, w, b, y, rows, dim, eps, stream=None):
     """helios::glue::layernorm_f16 (src/engine/glue2.cuh:73-75)."""
     _call("hk_layernorm_f16", _ptr(x), _ptr(w), _ptr(b), _ptr(y), rows, dim, float(eps), _stream(stream))
+
+
+def mla_decode_prologue(kv_pre, ln_w, ckv, eps_rms, idx_k, knorm_w, knorm_b, idx_kn, eps_ln, idx_g, raw_ring, raw_rows,
+                        pool_k_nt, ape, pos, q_pos_out=None, stream=None):
+    """cache append + indexer key layer norm + pooled-key write of ONE new token (src/engine/runner.cpp:569-584) in one
+    launch; q_pos_out (device int32[1], optional) receives pos"""
+    _call("hk_mla_decode_prologue", _ptr(kv_pre), _ptr(ln_w), _ptr(ckv), float(eps_rms), _ptr(idx_k), _ptr(knorm_w),
+          _ptr(knorm_b), _ptr(idx_kn), float(eps_ln), _ptr(idx_g), _ptr(raw_ring), raw_rows, _ptr(pool_k_nt), _ptr(ape),
+          int(pos), _ptr(q_pos_out), _stream(stream))
 
 
 def mla_cache_append(kv_pre, ln_w, ckv, pos, n, eps, ckv_new=None, stream=None):

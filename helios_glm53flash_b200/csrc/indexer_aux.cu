@@ -2,56 +2,16 @@
 // cross-check scorer.  Interfaces of helios::attn::kpool_write / pool_expand / pool_expand_row /
 // indexer_score_legacy (reference: src/cuda/attn/attn.cu:134-158, :284-390).
 #include "hk_common.cuh"
+#include "kpool_common.cuh"
 
 namespace hk {
 
-// One CTA per pool touched by this call, one thread per channel.  A pool key is produced by the
-// call that writes the pool's LAST member; members written by earlier calls are read back from the
-// ring, members of this call straight from the inputs (and copied into the ring for later calls).
+// One CTA per pool touched by this call, one thread per channel (body: kpool_common.cuh).
 __global__ __launch_bounds__(128) void kpool_write_kernel(
     const __half* __restrict__ ik, const __half* __restrict__ ig, __half* __restrict__ ring,
     int raw_rows, __half* __restrict__ pk_nt, const float* __restrict__ ape, int pos_start,
     int n_new, int first_pool) {
-  const int p = first_pool + blockIdx.x;
-  const int c = threadIdx.x;
-  const int t0 = p * POOL;
-  const int last = t0 + POOL - 1;
-  const bool complete = last >= pos_start && last < pos_start + n_new;
-  float kk[POOL], gg[POOL];
-  float mx = -1e30f;
-#pragma unroll
-  for (int i = 0; i < POOL; i++) {
-    const int pos = t0 + i, src = pos - pos_start;
-    __half* r = ring + (size_t)(pos % raw_rows) * 256;
-    __half hk_, hg_;
-    if (src >= 0 && src < n_new) {
-      hk_ = ik[(size_t)src * 128 + c];
-      hg_ = ig[(size_t)src * 128 + c];
-      r[c] = hk_;
-      r[128 + c] = hg_;
-    } else if (complete && src < 0) {
-      hk_ = r[c];
-      hg_ = r[128 + c];
-    } else {
-      hk_ = __float2half(0.f);
-      hg_ = __float2half(0.f);
-    }
-    kk[i] = __half2float(hk_);
-    gg[i] = __half2float(hg_) + ape[i * 128 + c];
-    mx = fmaxf(mx, gg[i]);
-  }
-  if (!complete) return;
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < POOL; i++) {
-    gg[i] = __expf(gg[i] - mx);
-    sum += gg[i];
-  }
-  float o = 0.f;
-#pragma unroll
-  for (int i = 0; i < POOL; i++) o += (gg[i] / sum) * kk[i];
-  o *= 0.25f;
-  pk_nt[(size_t)p * 128 + c] = __float2half_rn(o);
+  kpool_one(ik, ig, ring, raw_rows, pk_nt, ape, pos_start, n_new, first_pool + blockIdx.x, threadIdx.x);
 }
 
 // raw[r][4i+j] = 4*pool_i + j if <= cur else -1; raw[r][4*n_sel + i] = cur-3+i (>= 0) - the tail

@@ -177,12 +177,18 @@ class TrunkAttention:
     def mla_layer(self, L, n, pos, seq=0, timed=False):
         hk, mi, t = self.hk, self.mla_in, self.torch
         ckv, pool, ring = self.ckv[seq][L], self.pool[seq][L], self.ring[seq][L]
-        hk.mla_cache_append(mi["kv_pre"][:n], mi["ln_w"], ckv, pos, n, 1e-6)
-        hk.layernorm_f16(mi["idx_k"][:n], mi["knorm_w"], mi["knorm_b"], self.idx_kn[:n], n, 128, 1e-5)
-        hk.kpool_write(self.idx_kn[:n], mi["idx_g"][:n], ring, self.ring_rows, pool, mi["ape"], pos, n)
+        if n == 1 and self.fused:
+            # a decoded token: append, key layer norm, pooled-key write and the position in one launch
+            hk.mla_decode_prologue(mi["kv_pre"][:1], mi["ln_w"], ckv, 1e-6, mi["idx_k"][:1], mi["knorm_w"], mi["knorm_b"],
+                                   self.idx_kn[:1], 1e-5, mi["idx_g"][:1], ring, self.ring_rows, pool, mi["ape"], pos,
+                                   q_pos_out=self.qpos[:1])
+        else:
+            hk.mla_cache_append(mi["kv_pre"][:n], mi["ln_w"], ckv, pos, n, 1e-6)
+            hk.layernorm_f16(mi["idx_k"][:n], mi["knorm_w"], mi["knorm_b"], self.idx_kn[:n], n, 128, 1e-5)
+            hk.kpool_write(self.idx_kn[:n], mi["idx_g"][:n], ring, self.ring_rows, pool, mi["ape"], pos, n)
+            t.arange(pos, pos + n, dtype=t.int32, device="cuda", out=self.qpos[:n])
         if timed:
             self._mark("mla_append_kpool")
-        t.arange(pos, pos + n, dtype=t.int32, device="cuda", out=self.qpos[:n])
         hk.q_latent(mi["q_nope"][:n], mi["kv_b"], self.q_lat[:n], n)
         if timed:
             self._mark("mla_q_latent")

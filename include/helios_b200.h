@@ -420,6 +420,16 @@ int hk_mla_cache_append(const float* kv_pre, const void* ln_w_f16, void* ckv, vo
 int hk_layernorm_f16(const void* x, const void* w, const void* b, void* y, int rows, int dim,
                      float epsilon, void* stream);
 
+/* Everything an MLA layer does with ONE new token before its attention, in one launch: hk_mla_cache_append of the row
+ * (kv_pre [512] fp32 -> ckv[pos]), hk_layernorm_f16 of the indexer key row idx_k [128] (result also to idx_kn if not
+ * NULL), hk_kpool_write of (normalised key, idx_g) at position pos (ring row, and the pooled key if pos completes its
+ * pool), and *q_pos_out = pos (optional device int).  The reference's decode runs rms_norm + copy, layernorm_f16 and
+ * kpool_write here (src/engine/runner.cpp:569-584); results are bit-identical to those calls in turn.           */
+int hk_mla_decode_prologue(const float* kv_pre, const void* ln_w_f16, void* ckv, float eps_rms, const void* idx_k,
+                           const void* knorm_w, const void* knorm_b, void* idx_kn, float eps_ln, const void* idx_g,
+                           void* raw_ring, int raw_rows, void* pool_k_nt, const float* ape, int pos, int* q_pos_out,
+                           void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * diagnostics
  * ------------------------------------------------------------------------------------------- */

@@ -227,3 +227,38 @@ def test_layernorm_f16(rows, dim):
     hk.layernorm_f16(dx, dw, db, dx, rows, dim, 1e-5)
     torch.cuda.synchronize()
     assert torch.equal(dx, y)
+
+
+def test_mla_decode_prologue_equals_append_layernorm_kpool_in_turn():
+    """hk_mla_decode_prologue (one launch per decoded token) against hk_mla_cache_append -> hk_layernorm_f16 ->
+    hk_kpool_write on separate copies of the caches, 11 consecutive positions (three pools complete on the way):
+    cache rows, normalised keys, ring rows, pooled keys and the position word are the same bits"""
+    r = synth.rng(404)
+    pos0, steps, ring_rows = 1021, 11, 64
+    cap = pos0 + steps + 2
+    lw = dev_f16(synth.f32_to_f16_bits((1 + 0.1 * r.standard_normal(512, dtype=np.float32)).astype(np.float32)))
+    kw = dev_f16(synth.f32_to_f16_bits((1 + 0.1 * r.standard_normal(128, dtype=np.float32)).astype(np.float32)))
+    kb = dev_f16(synth.f32_to_f16_bits((0.1 * r.standard_normal(128, dtype=np.float32)).astype(np.float32)))
+    ape = dev((0.1 * r.standard_normal((4, 128), dtype=np.float32)).astype(np.float32))
+    cache0 = synth.f32_to_f16_bits(r.standard_normal((cap, 512), dtype=np.float32))
+    ring0 = synth.f32_to_f16_bits(r.standard_normal((ring_rows, 256), dtype=np.float32))
+    pool0 = synth.f32_to_f16_bits(r.standard_normal((cap // 4 + 1, 128), dtype=np.float32))
+    ck_a, ck_b = dev_f16(cache0), dev_f16(cache0)
+    rg_a, rg_b = dev_f16(ring0), dev_f16(ring0)
+    pl_a, pl_b = dev_f16(pool0), dev_f16(pool0)
+    kn_a = torch.zeros(1, 128, dtype=torch.float16, device="cuda")
+    kn_b = torch.zeros(1, 128, dtype=torch.float16, device="cuda")
+    qp = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    for s in range(steps):
+        pos = pos0 + s
+        kv = dev((3 * r.standard_normal((1, 512), dtype=np.float32)).astype(np.float32))
+        ik = dev_f16(synth.f32_to_f16_bits((2 * r.standard_normal((1, 128), dtype=np.float32) + 0.3).astype(np.float32)))
+        ig = dev_f16(synth.f32_to_f16_bits(r.standard_normal((1, 128), dtype=np.float32)))
+        hk.mla_cache_append(kv, lw, ck_a, pos, 1, 1e-6)
+        hk.layernorm_f16(ik, kw, kb, kn_a, 1, 128, 1e-5)
+        hk.kpool_write(kn_a, ig, rg_a, ring_rows, pl_a, ape, pos, 1)
+        hk.mla_decode_prologue(kv, lw, ck_b, 1e-6, ik, kw, kb, kn_b, 1e-5, ig, rg_b, ring_rows, pl_b, ape, pos, q_pos_out=qp)
+        torch.cuda.synchronize()
+        assert torch.equal(kn_a, kn_b) and int(qp.item()) == pos, s
+    assert torch.equal(ck_a, ck_b) and torch.equal(rg_a, rg_b) and torch.equal(pl_a, pl_b)
+    assert not np.array_equal(bits(pl_b), pool0), "pools were completed on the way"
