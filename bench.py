@@ -989,10 +989,48 @@ def multi_gpu_measurements(hk, synth, torch, dist, np, rank, local_rank, world, 
             ms1 = a.elapsed_time(b) / 30
             del full, g1
         ms1 = max_over_ranks(ms1)
+        # the library baseline for the exchange: the same local partial, then ncclAllGather of the partial sets and
+        # the local combine over the gathered sets (host-launched: a collective cannot sit in this graph replay loop
+        # together with the bounded waits; so the figure includes NCCL's launch cost, as an engine would see it)
+        rows_ = m * 64
+        pad_ = ((rows_ * 4 + 255) // 256) * 256
+        set_bytes = 2 * pad_ + rows_ * 512 * 4
+        mine = torch.empty(set_bytes, dtype=torch.uint8, device="cuda")
+        allsets = torch.empty(world * set_bytes, dtype=torch.uint8, device="cuda")
+        pm = mine[:rows_ * 4].view(torch.float32)
+        plv = mine[pad_:pad_ + rows_ * 4].view(torch.float32)
+        pa = mine[2 * pad_:].view(torch.float32)
+        base_all = allsets.data_ptr()
+        tm = torch.tensor([base_all + r_ * set_bytes for r_ in range(world)], dtype=torch.int64, device="cuda")
+        tl = tm + pad_
+        ta = tm + 2 * pad_
+        lens_ = torch.full((m,), e0 - b0, dtype=torch.int32, device="cuda")
+        ns_ = hk.mla_auto_splits(m, max(1, e0 - b0))
+        wsn = torch.empty(max(256, hk.mla_partial_bytes(ns_, rows_)), dtype=torch.uint8, device="cuda")
+        out_n = torch.zeros_like(out)
+
+        def nccl_step():
+            hk.mla_dense_partial_ws(q, shard, shard_base, lens_, 0, pm, plv, pa, m, e0 - b0, scale=scale, n_split=ns_, workspace=wsn)
+            dist.all_gather_into_tensor(allsets, mine)
+            hk.lse_combine_ptrs(tm, tl, ta, world, rows_, out_n)
+        for _ in range(5):
+            nccl_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_.record()
+        for _ in range(30):
+            nccl_step()
+        b_.record()
+        torch.cuda.synchronize()
+        ms_nccl = max_over_ranks(a_.elapsed_time(b_) / 30)
+        agree = float((out_n.float() - out.float()).abs().max())
         res["splitkv_decode_262k_b%d" % m] = {
             "us_per_step": ms * 1e3, "one_gpu_us_per_step": ms1 * 1e3, "speedup_vs_one_gpu": ms1 / ms,
             "efficiency": ms1 / ms / world, "aggregate_hbm_gbs": m * L * 1024 / (ms * 1e-3) / 1e9,
-            "exchange": dec.form, "device_status": status}
+            "exchange": dec.form, "device_status": status,
+            "nccl_allgather_baseline_us_per_step": ms_nccl * 1e3, "nccl_baseline_max_abs_diff": agree}
+        del mine, allsets, wsn
         del g
         dec.close()
         del shard
