@@ -83,3 +83,64 @@ def test_shard_and_region_layout():
         assert all(lay[k + str(par)] % 256 == 0 for k in ("m", "l", "acc"))
     assert lay["m0"] >= 256 and lay["m1"] == lay["acc0"] + 64 * 2048      # two partial sets, one per step parity
     assert lay["total"] == lay["acc1"] + 64 * 2048
+
+
+def _sparse_worker(rank, world, port, ret):
+    """gloo rank of the sparse split-KV selection: local top-k of the own pools with the oracle, candidates gathered,
+    selection over the candidates in ascending global index (the host statement of hk_dsa_select_splitkv)"""
+    import datetime
+    import hk_oracle as orc
+    from helios_glm53flash_b200 import splitkv, synth
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        n_tokens, m, k = 4 * 1500 + 3, 2, 512
+        P = n_tokens // 4
+        r = synth.rng(11)                                          # the same scores on every rank
+        sc = np.round(r.standard_normal((m, P), dtype=np.float32) * 4) / 4     # coarse: many exact ties at the threshold
+        sc[:, P // 2:] = np.where(r.random((m, P - P // 2)) < 0.25, -np.inf, sc[:, P // 2:])
+        bits = synth.f32_to_f16_bits(sc)
+        (p0, p1), _ = splitkv.shard_pools(n_tokens, rank, world)
+        local = np.ascontiguousarray(bits[:, p0:p1])
+        idx = orc.dsa_topk(local, p1 - p0, m, p1 - p0, min(k, p1 - p0), 512)       # local selection, -1 padded
+        cand = []
+        for row in range(m):
+            sel = np.sort(idx[row][idx[row] >= 0])                  # ascending local index
+            cand.append((sel + p0, local[row][sel]))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, cand)
+        got = np.full((m, 512), -1, dtype=np.int32)
+        for row in range(m):
+            gidx = np.concatenate([g[row][0] for g in gathered])    # rank by rank = ascending global index
+            gsc = np.concatenate([g[row][1] for g in gathered])
+            assert np.all(np.diff(gidx) > 0)
+            pos = orc.dsa_topk(gsc.reshape(1, -1), gsc.size, 1, gsc.size, min(k, gsc.size), 512)[0]
+            got[row] = np.where(pos >= 0, gidx[np.maximum(pos, 0)], -1)
+        want = orc.dsa_topk(bits, P, m, P, k, 512)
+        ret[rank] = bool(np.array_equal(got, want))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sparse_selection_over_rank_slices_equals_whole_row_selection_on_cpu():
+    """the property the GPU kernels rely on, with two gloo ranks and the oracle's top-k: the union of the ranks' local
+    selections contains the whole-row selection, and selecting among the candidates in ascending global index breaks
+    ties as the whole-row selection does"""
+    world, port = 2, 29655
+    ret = mp.Manager().dict()
+    mp.spawn(_sparse_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: True, 1: True}
+
+
+def test_shard_pools_partitions_pools_and_rows():
+    from helios_glm53flash_b200 import splitkv
+    for n_tokens in (4, 7, 1000, 1003, 262144):
+        for world in (1, 2, 3, 8):
+            prev_p, prev_r = 0, 0
+            for rank in range(world):
+                (p0, p1), (r0, r1) = splitkv.shard_pools(n_tokens, rank, world)
+                assert p0 == prev_p and r0 == prev_r and r0 == 4 * p0 and p1 >= p0
+                assert r1 == (n_tokens if rank == world - 1 else 4 * p1)
+                prev_p, prev_r = p1, r1
+            assert prev_p == n_tokens // 4 and prev_r == n_tokens
