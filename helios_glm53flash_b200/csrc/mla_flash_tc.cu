@@ -21,7 +21,7 @@
 //
 // Warp roles (416 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
 // S = Q K^T, warp 12 issues O^T += V^T P^T (each as a converged warp with an elected lane, tc05.cuh),
-// warps 5-11 stage the key tiles.  S and P are double buffered, so QK^T of tile i+1 runs on the tensor
+// warps 5-11 stage the key tiles (the instantiation for gathered rows has 512 threads: warps 13-15 issue copies too).  S and P are double buffered, so QK^T of tile i+1 runs on the tensor
 // pipe while tile i is in the softmax, and the copies of the next tiles are in flight during both.  The
 // copies of the first three dense tiles leave at kernel entry; all warps stage the queries.  All
 // hand-offs are mbarriers with bounded waits, executed by every lane of the waiting warp.
@@ -108,13 +108,17 @@ __device__ __forceinline__ void tma_gather4_rows(void* smem_dst, const CUtensorM
       : "memory");
 }
 
-constexpr int FT_G4_LANES = 14;                   // lanes 0-13 of each of the 7 loader warps issue one gather each
-static_assert(FT_KEYS % 4 == 0 && FT_LOAD_WARPS * FT_G4_LANES >= (FT_KEYS / 4) * 8, "one gather4 per (key quad, block)");
+// The gather instantiation runs three more loader warps (warps 13-15): a warp gets one copy out per about 90 cycles
+// whichever lanes issue them, so the 96 copies of a tile are spread over 10 warps x 10 lanes.
+constexpr int FT_G4_THREADS = 512;
+constexpr int FT_G4_WARPS = FT_LOAD_WARPS + 3;
+constexpr int FT_G4_LANES = 10;
+static_assert(FT_KEYS % 4 == 0 && FT_G4_WARPS * FT_G4_LANES >= (FT_KEYS / 4) * 8, "one gather4 per (key quad, block)");
 
 // G4: gathered rows through the copy engine (use_tma == 2).  A separate instantiation: with both loaders in one
 // kernel the dense paths lost 3-14 % (256-row dense prefill 1.55 -> 1.77 ms) to the register allocation of the whole.
 template <bool G4>
-__global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status,
+__global__ __launch_bounds__(G4 ? FT_G4_THREADS : FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, int* __restrict__ status,
                                                                      const __grid_constant__ CUtensorMap tmap,
                                                                      int use_tma) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -163,7 +167,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   if (tid == 0) {
 #pragma unroll
     for (int b = 0; b < FT_NBUF; b++) {
-      tc::mbar_init(&k_full[b], FT_LOADERS);
+      tc::mbar_init(&k_full[b], G4 ? FT_G4_WARPS * 32 : FT_LOADERS);
       tc::mbar_init(&t_done[b], 1);
     }
 #pragma unroll
@@ -190,7 +194,7 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   if (n_tiles > 0) {
     // Q [64 heads][512] -> K-major operand tile, staged by ALL warps with every load of a thread in flight at
     // once.  item = (head group, chunk quad); lanes = 8 heads x 4 chunks -> one 128-byte core matrix per octet
-    constexpr int NW = FT_THREADS / 32, QI = (128 + NW - 1) / NW;
+    constexpr int NW = (G4 ? FT_G4_THREADS : FT_THREADS) / 32, QI = (128 + NW - 1) / NW;
     const __half* q = a.q_lat + (size_t)r * FT_HEADS * LATENT;
     uint4 qs[QI];
 #pragma unroll
@@ -218,12 +222,12 @@ __global__ __launch_bounds__(FT_THREADS, 1) void mla_flash_tc_kernel(MlaArgs a, 
   const uint32_t tS = tmem, tO = tmem + 128;   // S: 2 x 64 columns; O^T: 4 x 64 columns
   bool ok = true;
 
-  if (!mma_warp && warp >= 5) {   // warps 5-11
+  if (!mma_warp && warp >= 5) {   // warps 5-11 (and 13-15 of the gather instantiation)
     // =========================== loaders: the key tiles ===========================
     // Register-staged copies: every loader warp first issues all of its 16-byte loads of the NEXT
     // tile (they fly while the tensor pipe still owns the buffer), then waits for the buffer, then
     // stores.  Plain vector loads: the per-thread cp.async path sustains far fewer bytes in flight.
-    const int lw = warp - 5;
+    const int lw = (G4 && warp >= 12) ? warp - 6 : warp - 5;
     uint4 stage[FT_ITEMS];
     // L2 prefetch of the tiles ahead keeps HBM busy while this CTA computes: the register-staged
     // loads below then hit L2.  Dense: one contiguous range per tile; sparse: one 1 KB row per lane.
@@ -697,7 +701,7 @@ int mla_flash_tc_launch(const MlaArgs& a, cudaStream_t s) {
   }
   dim3 grid(a.n_split, a.m);
   if (use_tma == 2)
-    mla_flash_tc_kernel<true><<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
+    mla_flash_tc_kernel<true><<<grid, FT_G4_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
   else
     mla_flash_tc_kernel<false><<<grid, FT_THREADS, FS_SMEM, s>>>(a, device_status_ptr(), tmap, use_tma);
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
