@@ -17,11 +17,14 @@
 // the B operand of Q K^T; the same bytes read MN-major (64 contiguous channels per key) are the A
 // operand V^T.  Whole tiles of a dense range arrive with ONE TMA tensor copy each (3-D box
 // {64 channels, 48 keys, 8 blocks} over the cache viewed as [row][block][64], 128-byte swizzle);
-// gathered rows and ragged tails go through register-staged vector loads into the same layout.
+// gathered rows arrive as gather4 tensor copies (four cache rows x one 64-channel block each, 96 per tile; a separate
+// instantiation of the kernel); ragged tails, and everything when the copy engine is not available, go through
+// register-staged vector loads into the same layout.
 //
 // Warp roles (416 threads): warps 0-3 softmax + epilogue (one per TMEM lane quarter), warp 4 issues
 // S = Q K^T, warp 12 issues O^T += V^T P^T (each as a converged warp with an elected lane, tc05.cuh),
-// warps 5-11 stage the key tiles (the instantiation for gathered rows has 512 threads: warps 13-15 issue copies too).  S and P are double buffered, so QK^T of tile i+1 runs on the tensor
+// warps 5-11 stage the key tiles (the instantiation for gathered rows has 512 threads: warps 13-15 issue copies
+// too).  S and P are double buffered, so QK^T of tile i+1 runs on the tensor
 // pipe while tile i is in the softmax, and the copies of the next tiles are in flight during both.  The
 // copies of the first three dense tiles leave at kernel entry; all warps stage the queries.  All
 // hand-offs are mbarriers with bounded waits, executed by every lane of the waiting warp.
