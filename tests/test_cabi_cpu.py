@@ -67,3 +67,22 @@ def test_product_does_not_reference_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".hpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "liboracle" not in text and "hk_oracle" not in text and "oracle/" not in text, f
+
+
+def test_host_only_answers_of_the_abi(built):
+    """entry points that compute on the host: sizes, layouts and the dispatch rule (no device needed)"""
+    from helios_glm53flash_b200 import splitkv
+    lib = hk.load_library()
+    # candidate area of the sparse split-KV selection: 256 B of flags + two sets of (int32 index, fp16 score) x 512 x ranks x rows
+    for m, g in ((1, 1), (1, 8), (3, 2), (8, 8)):
+        assert lib.hk_dsa_select_region_bytes(m, g) == 256 + 2 * m * g * 512 * 6
+    assert lib.hk_dsa_select_region_bytes(1, 9) == 0 and lib.hk_dsa_select_region_bytes(0, 2) == 0
+    lay = splitkv.region_layout(64, 2, cand_bytes=lib.hk_dsa_select_region_bytes(1, 2))
+    assert lay["cand"] % 256 == 0 and lay["total"] == lay["cand"] + lib.hk_dsa_select_region_bytes(1, 2)
+    # the dispatch rule of the recurrence launcher: chunked path for channelwise decay, no history, 128-wide heads, >= 64 tokens
+    rule = lambda seqlen, dk, dv, cw, hist: lib.hk_kda_dispatch_is_chunked(seqlen, 32, 32, dk, dv, 1, cw, hist)
+    assert rule(64, 128, 128, 1, 0) == 1 and rule(32768, 128, 128, 1, 0) == 1
+    assert rule(63, 128, 128, 1, 0) == 0 and rule(1, 128, 128, 1, 0) == 0
+    assert rule(4096, 128, 128, 1, 1) == 0 and rule(4096, 128, 128, 0, 0) == 0 and rule(4096, 64, 64, 1, 0) == 0
+    # static no-allocation entry: 64 (split, row) slots
+    assert lib.hk_mla_sparse_static_max_slots() == 64
