@@ -25,6 +25,8 @@ recurrence launcher), the form the unchanged engine would call.
 
 There is no CPU path: the module drives libhelios_b200 only.
 """
+from types import SimpleNamespace
+
 import numpy as np
 
 from . import synth
@@ -97,6 +99,7 @@ class TrunkAttention:
         self.kept = {}
         self.stage_ms = {}
         self._events = []
+        self._dec = None                                                  # per-sequence decode buffers and streams (batch > 1)
 
     # ------------------------------------------------------------------------------------------
     def _mark(self, name):
@@ -174,61 +177,77 @@ class TrunkAttention:
             self.hk.kda_gate(b[s], f[s], ki["dt_bias"], ki["a_log"], ki["lower_bound"], beta[s], g[s], n, H, D)
         self.hk.cuda_recurrent_gated_delta_rule(qkv, g, beta, self.rec_state[L], rec, B, n, H, H, D, D, 1, None, True, False)
 
-    def mla_layer(self, L, n, pos, seq=0, timed=False):
+    def _decode_bufs(self):
+        """one set of single-row work buffers and one stream per sequence, so that the sequences' MLA layers of a decode
+        step can run side by side (their caches are separate; the shared work buffers of a chunk are not)"""
+        if self._dec is None:
+            t, hk = self.torch, self.hk
+            ns = hk.mla_auto_splits(1, KIDX)
+            self._dec = [SimpleNamespace(
+                idx_kn=t.empty(1, 128, dtype=t.float16, device="cuda"), q_lat=t.empty(1, 64, 512, dtype=t.float16, device="cuda"),
+                qpos=t.empty(1, dtype=t.int32, device="cuda"), scores=t.empty(1, self.scores.shape[1], dtype=t.float16, device="cuda"),
+                topk=t.empty(1, 512, dtype=t.int32, device="cuda"), raw_idx=t.empty(1, KIDX, dtype=t.int32, device="cuda"),
+                lat_out=t.empty(1, 64, 512, dtype=t.float16, device="cuda"), o_abs=t.empty(1, 64, 256, dtype=t.float16, device="cuda"),
+                sparse_ws=t.empty(max(256, hk.mla_partial_bytes(ns, 64)), dtype=t.uint8, device="cuda"),
+                stream=t.cuda.Stream()) for _ in range(self.B)]
+        return self._dec
+
+    def mla_layer(self, L, n, pos, seq=0, timed=False, bufs=None):
         hk, mi, t = self.hk, self.mla_in, self.torch
         ckv, pool, ring = self.ckv[seq][L], self.pool[seq][L], self.ring[seq][L]
+        wb = self if bufs is None else bufs                    # work buffers: the chunk's shared ones, or this sequence's own
         if n == 1 and self.fused:
             # a decoded token: append, key layer norm, pooled-key write and the position in one launch
             hk.mla_decode_prologue(mi["kv_pre"][:1], mi["ln_w"], ckv, 1e-6, mi["idx_k"][:1], mi["knorm_w"], mi["knorm_b"],
-                                   self.idx_kn[:1], 1e-5, mi["idx_g"][:1], ring, self.ring_rows, pool, mi["ape"], pos,
-                                   q_pos_out=self.qpos[:1])
+                                   wb.idx_kn[:1], 1e-5, mi["idx_g"][:1], ring, self.ring_rows, pool, mi["ape"], pos,
+                                   q_pos_out=wb.qpos[:1])
         else:
             hk.mla_cache_append(mi["kv_pre"][:n], mi["ln_w"], ckv, pos, n, 1e-6)
-            hk.layernorm_f16(mi["idx_k"][:n], mi["knorm_w"], mi["knorm_b"], self.idx_kn[:n], n, 128, 1e-5)
-            hk.kpool_write(self.idx_kn[:n], mi["idx_g"][:n], ring, self.ring_rows, pool, mi["ape"], pos, n)
-            t.arange(pos, pos + n, dtype=t.int32, device="cuda", out=self.qpos[:n])
+            hk.layernorm_f16(mi["idx_k"][:n], mi["knorm_w"], mi["knorm_b"], wb.idx_kn[:n], n, 128, 1e-5)
+            hk.kpool_write(wb.idx_kn[:n], mi["idx_g"][:n], ring, self.ring_rows, pool, mi["ape"], pos, n)
+            t.arange(pos, pos + n, dtype=t.int32, device="cuda", out=wb.qpos[:n])
         if timed:
             self._mark("mla_append_kpool")
-        hk.q_latent(mi["q_nope"][:n], mi["kv_b"], self.q_lat[:n], n)
+        hk.q_latent(mi["q_nope"][:n], mi["kv_b"], wb.q_lat[:n], n)
         if timed:
             self._mark("mla_q_latent")
         npools = (pos + n) // 4
         ktop = min(512, npools)
         if n <= 8 and self.fused and npools > 0:
             # decode rows: scores, top-k and expansion as two launches
-            sc = self.scores.view(-1)[:n * npools].view(n, npools)
-            hk.indexer_select(mi["q_idx"][:n], pool, mi["w"][:n], self.qpos[:n], sc, self.topk[:n], self.raw_idx[:n], n, npools, k=ktop)
+            sc = wb.scores.view(-1)[:n * npools].view(n, npools)
+            hk.indexer_select(mi["q_idx"][:n], pool, mi["w"][:n], wb.qpos[:n], sc, wb.topk[:n], wb.raw_idx[:n], n, npools, k=ktop)
             blocks = ()
         else:
             blocks = range(0, n, IDX_BLOCK)
         for off in blocks:
             rows = min(IDX_BLOCK, n - off)
             if npools > 0:
-                sc = self.scores.view(-1)[:rows * npools].view(rows, npools)
-                hk.indexer_score(mi["q_idx"][off:off + rows], pool, mi["w"][off:off + rows], self.qpos[off:off + rows], sc, rows, npools)
+                sc = wb.scores.view(-1)[:rows * npools].view(rows, npools)
+                hk.indexer_score(mi["q_idx"][off:off + rows], pool, mi["w"][off:off + rows], wb.qpos[off:off + rows], sc, rows, npools)
                 if timed:
                     self._mark("mla_indexer_score")
-                hk.dsa_topk(sc, npools, self.topk[off:off + rows], rows, npools, ktop, 512)
+                hk.dsa_topk(sc, npools, wb.topk[off:off + rows], rows, npools, ktop, 512)
             else:
-                self.topk[off:off + rows].fill_(-1)
+                wb.topk[off:off + rows].fill_(-1)
             if timed:
                 self._mark("mla_topk")
-            hk.pool_expand_row(self.topk[off:off + rows], self.qpos[off:off + rows], self.raw_idx[off:off + rows], rows)
+            hk.pool_expand_row(wb.topk[off:off + rows], wb.qpos[off:off + rows], wb.raw_idx[off:off + rows], rows)
         if timed:
             self._mark("mla_expand")
         ns = hk.mla_auto_splits(n, KIDX)
         need = hk.mla_partial_bytes(ns, n * 64) if ns > 1 else 0
-        if need > self.sparse_ws.numel():
-            self.sparse_ws = t.empty(need, dtype=t.uint8, device="cuda")
-        hk.mla_sparse_decode(self.q_lat[:n], ckv, self.raw_idx[:n], KIDX, self.lat_out[:n], n, n_split=ns, workspace=self.sparse_ws)
+        if need > wb.sparse_ws.numel():
+            wb.sparse_ws = t.empty(need, dtype=t.uint8, device="cuda")
+        hk.mla_sparse_decode(wb.q_lat[:n], ckv, wb.raw_idx[:n], KIDX, wb.lat_out[:n], n, n_split=ns, workspace=wb.sparse_ws)
         if timed:
             self._mark("mla_sparse_attention")
-        hk.o_absorb(self.lat_out[:n], mi["kv_b"], self.o_abs[:n], n)
+        hk.o_absorb(wb.lat_out[:n], mi["kv_b"], wb.o_abs[:n], n)
         if timed:
             self._mark("mla_o_absorb")
         if self.keep:
-            self.kept.setdefault(("mla", L, seq), []).append((pos, n, self.topk[:n].clone(), self.raw_idx[:n].clone(),
-                                                              self.lat_out[:n].clone(), self.o_abs[:n].clone()))
+            self.kept.setdefault(("mla", L, seq), []).append((pos, n, wb.topk[:n].clone(), wb.raw_idx[:n].clone(),
+                                                              wb.lat_out[:n].clone(), wb.o_abs[:n].clone()))
 
     def run_chunk(self, pos, n, timed=False):
         """all layers over rows pos .. pos + n - 1 (prefill chunk, or a decode step with n = 1).  The model interleaves
@@ -238,6 +257,19 @@ class TrunkAttention:
             self._mark("begin")
         for L in range(self.n_kda):
             self.kda_layer(L, n, timed)
+        if n == 1 and self.B > 1 and self.fused and not timed:
+            # a decode step of several sequences: their MLA layers touch separate caches, so every sequence gets a stream
+            # and single-row work buffers of its own and the chains run side by side (also inside a captured graph)
+            t = self.torch
+            cur = t.cuda.current_stream()
+            for seq, bufs in enumerate(self._decode_bufs()):
+                bufs.stream.wait_stream(cur)
+                with t.cuda.stream(bufs.stream):
+                    for L in range(self.n_mla):
+                        self.mla_layer(L, n, pos, seq, False, bufs)
+            for bufs in self._dec:
+                cur.wait_stream(bufs.stream)
+            return
         for seq in range(self.B):
             for L in range(self.n_mla):
                 self.mla_layer(L, n, pos, seq, timed)

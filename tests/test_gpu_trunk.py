@@ -171,3 +171,33 @@ def test_cut_down_hybrid_stack_two_chunks_then_decode(fused):
         assert max_rel(g_lat, o_lat32) < 2e-3, "sparse attention rows of call %d" % ci
         want_o = f16(orc.o_absorb(np.ascontiguousarray(bits(lat)[rows]), kv_b, len(rows)))
         assert max_rel(oab.float().cpu().numpy()[rows], want_o) < 2e-3
+
+
+def test_decode_step_of_two_sequences_on_their_own_streams_equals_sequence_by_sequence():
+    """batch 2: the MLA layers of a decode step run on one stream per sequence with single-row work buffers of their
+    own (fused driver); the same stack run sequence by sequence on one stream (unfused driver: the reference's call
+    sequence) must leave the same selections, attention rows, caches and states"""
+    n_tok, chunk, steps, H = 1024, 512, 5, 4
+    runs = []
+    for fused in (True, False):
+        tr = TrunkAttention(n_kda=2, n_mla=2, heads=H, batch=2, max_ctx=n_tok + 64, max_chunk=chunk, seed=9, fused=fused,
+                            keep_outputs=True)
+        tr.prefill(n_tok, chunk)
+        for s in range(steps):
+            tr.run_chunk(n_tok + s, 1)
+        torch.cuda.synchronize()
+        assert hk.read_device_status() == 0
+        runs.append(tr)
+    a, b = runs
+    for seq in range(2):
+        for L in range(2):
+            assert torch.equal(a.ckv[seq][L], b.ckv[seq][L]) and torch.equal(a.pool[seq][L], b.pool[seq][L])
+            ka, kb = a.kept[("mla", L, seq)], b.kept[("mla", L, seq)]
+            assert len(ka) == len(kb) == 2 + steps
+            for (pa, na, ta, ra, la, oa), (pb, nb, tb, rb, lb, ob) in zip(ka[-steps:], kb[-steps:]):
+                assert (pa, na) == (pb, nb) and torch.equal(ta, tb) and torch.equal(ra, rb), "selection of a decoded token"
+                assert max_rel(la.float().cpu().numpy(), lb.float().cpu().numpy()) < 2e-3
+                assert max_rel(oa.float().cpu().numpy(), ob.float().cpu().numpy()) < 2e-3
+    for L in range(2):
+        assert frob_rel(a.rec_state[L].cpu().numpy(), b.rec_state[L].cpu().numpy()) < 1e-2
+        assert torch.equal(a.conv_state[L], b.conv_state[L])
