@@ -262,7 +262,7 @@ def test_topk_with_expansion_equals_topk_then_expand(R, T, k):
     assert torch.equal(idx0, idx1) and torch.equal(raw0, raw1)
 
 
-@pytest.mark.parametrize("m,npools", [(1, 65536), (1, 5000), (3, 600), (8, 20000)])
+@pytest.mark.parametrize("m,npools", [(1, 65536), (1, 5000), (3, 600), (8, 20000), (20, 3000), (40, 2500)])
 def test_indexer_select_equals_the_three_call_chain_also_from_a_graph(m, npools):
     q_pos = np.array([npools * 4 - 1 - 9 * r for r in range(m)], dtype=np.int32)
     inp, _ = _score_case(m, npools, q_pos, False, seed=5 + m)
