@@ -44,6 +44,7 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
 template <bool B_MN>
 __global__ __launch_bounds__(AB_THREADS, 1) void absorb_gemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const __grid_constant__ CUtensorMap tmap_o, int use_tma_out,
     __half* __restrict__ out, int n_rows, int K, int n_out, int b_rows_per_head, int b_row_off,
     int* __restrict__ status) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -117,7 +118,43 @@ __global__ __launch_bounds__(AB_THREADS, 1) void absorb_gemm_tc_kernel(
     const int row = row0 + q * 32 + lane;
     const bool ok = tc::mbar_wait<64>(&done_bar, 0, &abort_flag, 3);
     tc::fence_after_sync();
-    if (ok) {
+    if (ok && use_tma_out) {
+      // The fp16 tile leaves through the copy engine: every thread lays its row into the (now idle) operand stages as
+      // four 128-row x 64-column boxes in the 128-byte-swizzle pattern (16-byte piece c of row r at c ^ (r % 8):
+      // conflict-free), one thread hands the four boxes over as tiled stores (rows past the end are clipped).  Direct
+      // stores put 32 different rows into every warp instruction.
+      const int r = q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < AB_BN; c0 += 32) {
+        uint32_t rr[32];
+        tc::tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, rr);
+        tc::tmem_ld_wait();
+        uint8_t* box = smem + (c0 >> 6) * 16384 + r * 128;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          uint4 p;
+          __half2 h0 = __floats2half2_rn(__uint_as_float(rr[8 * u + 0]), __uint_as_float(rr[8 * u + 1]));
+          __half2 h1 = __floats2half2_rn(__uint_as_float(rr[8 * u + 2]), __uint_as_float(rr[8 * u + 3]));
+          __half2 h2 = __floats2half2_rn(__uint_as_float(rr[8 * u + 4]), __uint_as_float(rr[8 * u + 5]));
+          __half2 h3 = __floats2half2_rn(__uint_as_float(rr[8 * u + 6]), __uint_as_float(rr[8 * u + 7]));
+          p.x = *reinterpret_cast<uint32_t*>(&h0); p.y = *reinterpret_cast<uint32_t*>(&h1);
+          p.z = *reinterpret_cast<uint32_t*>(&h2); p.w = *reinterpret_cast<uint32_t*>(&h3);
+          const int cc = ((c0 & 63) >> 3) + u;
+          *reinterpret_cast<uint4*>(box + ((cc ^ (r & 7)) << 4)) = p;
+        }
+      }
+      tc::fence_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+#pragma unroll
+        for (int j = 0; j < AB_BN / 64; j++)
+          asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&tmap_o),
+                       "r"(nt * AB_BN + j * 64), "r"(h), "r"(row0), "r"(tc::smem_u32(smem + j * 16384))
+                       : "memory");
+        tc::bulk_commit();
+        tc::bulk_wait_read<0>();                  // the boxes have been read: the CTA may leave
+      }
+    } else if (ok) {
       __half* orow = out + ((size_t)row * 64 + h) * n_out + nt * AB_BN;
 #pragma unroll 1
       for (int c0 = 0; c0 < AB_BN; c0 += 32) {
@@ -187,6 +224,20 @@ int absorb_gemm_tc(const void* a, const void* b, void* out, int n_rows, int K, i
   memset(&mb, 0, sizeof(mb));
   if (!make_map_2d(&ma, a, (uint64_t)n_rows, (uint64_t)64 * K, AB_BM, AB_BK)) return HK_ERR_UNSUPPORTED;
   if (!make_map_2d(&mb, b, b_rows, b_cols, b_mn ? AB_BK : AB_BN, 64)) return HK_ERR_UNSUPPORTED;
+  // output as [row][head][n_out]: boxes of 64 columns x 1 head x 128 rows for the tiled stores of the epilogue
+  alignas(64) CUtensorMap mo;
+  memset(&mo, 0, sizeof(mo));
+  int use_tma_out = 0;
+  {
+    EncodeTiledFn enc = encode_tiled_fn();
+    const cuuint64_t dims[3] = {(cuuint64_t)n_out, 64, (cuuint64_t)n_rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)n_out * 2, (cuuint64_t)64 * n_out * 2};
+    const cuuint32_t box[3] = {64, 1, AB_BM};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if (enc && enc(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+      use_tma_out = 1;
+  }
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -198,9 +249,9 @@ int absorb_gemm_tc(const void* a, const void* b, void* out, int n_rows, int K, i
   }
   const dim3 grid(n_out / AB_BN, (n_rows + AB_BM - 1) / AB_BM, 64);
   if (b_mn)
-    absorb_gemm_tc_kernel<true><<<grid, AB_THREADS, AB_SMEM, s>>>(ma, mb, (__half*)out, n_rows, K, n_out, b_rows_per_head, b_row_off, device_status_ptr());
+    absorb_gemm_tc_kernel<true><<<grid, AB_THREADS, AB_SMEM, s>>>(ma, mb, mo, use_tma_out, (__half*)out, n_rows, K, n_out, b_rows_per_head, b_row_off, device_status_ptr());
   else
-    absorb_gemm_tc_kernel<false><<<grid, AB_THREADS, AB_SMEM, s>>>(ma, mb, (__half*)out, n_rows, K, n_out, b_rows_per_head, b_row_off, device_status_ptr());
+    absorb_gemm_tc_kernel<false><<<grid, AB_THREADS, AB_SMEM, s>>>(ma, mb, mo, use_tma_out, (__half*)out, n_rows, K, n_out, b_rows_per_head, b_row_off, device_status_ptr());
   return cudaPeekAtLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA;
 }
 
