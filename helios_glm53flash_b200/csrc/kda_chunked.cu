@@ -966,14 +966,16 @@ __global__ __launch_bounds__(128, 1) void kda_chunk_scan_kernel(
 
 
 // =================================================================================================
-// fused form: preparation and scan in ONE persistent launch, for calls with few (batch, head) chains
+// fused form: preparation and scan in ONE persistent launch
 //
-// One CTA of 512 threads per SM.  The first n_jobs CTAs each walk the chunks of one (batch, head) chain: the whole
-// 128-column state of the head, sixteen warps = four TMEM lane quarters x four 32-column blocks.  Every other CTA
+// One CTA of 512 threads per SM.  The first n_slots CTAs are chain slots: each walks the chunks of one (batch, head)
+// chain - or, when the call has more than 48 chains, of n_jobs / n_slots chains one after the other (the state is
+// swapped at the chain boundary; ring, flags and barrier parities go by the slot's running chunk number) - with the
+// whole 128-column state of the head, sixteen warps = four TMEM lane quarters x four 32-column blocks.  Every other CTA
 // hosts two preparation workers of 256 threads (its two halves, each with its own shared memory, TMEM columns and
-// named barrier), which take the units (chunk-major) round robin.  A unit travels through a ring of KR chunk slots
-// per chain in global memory - a few tens of MB that stay in L2 - instead of a per-chunk workspace in HBM:
-//   ready[job][slot]  = chunk + 1 once the unit of that chunk is complete (release store after the worker's writes),
+// named barrier), which take the units round robin in the order the slots need them.  A unit travels through a ring
+// of KR chunk slots per chain slot in global memory - a few tens of MB that stay in L2 - instead of a per-chunk workspace in HBM:
+//   ready[slot][v % KR] = v + 1 once the unit of that chunk is complete (release store after the worker's writes),
 //   consumed[job]     = number of chunks whose unit has landed in the chain CTA's shared memory (the slot of chunk c
 //                       may be rewritten once consumed > c).
 // A worker that finds its slot still occupied, and a chain CTA that finds its unit not yet written, poll with a
@@ -1004,9 +1006,9 @@ template <bool GATED>
 __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ g, const void* __restrict__ beta_in,
     uint8_t* __restrict__ ring, int* __restrict__ flags, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
-    float* __restrict__ out_f32, int seqlen, int H, int n_chunks, int n_jobs, const int* __restrict__ slots, float scale,
-    int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log, float lower_bound,
-    const __grid_constant__ CUtensorMap tmap_out, int use_tma_out) {
+    float* __restrict__ out_f32, int seqlen, int H, int n_chunks, int n_jobs, int n_slots, const int* __restrict__ slots,
+    float scale, int* __restrict__ status, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+    float lower_bound, const __grid_constant__ CUtensorMap tmap_out, int use_tma_out) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[F_NSTAGE];
   // chain: one barrier per contraction group, each completing once per chunk (parity = chunk & 1); the output warps
@@ -1023,8 +1025,11 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
   if (tid == 0 && blockIdx.x == 1) hk_kda_trace[32 + 11] = clock64();
 #endif
   int* g_abort = flags;
-  int* ready = flags + F_FLAG_INTS;                        // [n_jobs][KR]
-  int* consumed = ready + (size_t)n_jobs * KR;             // [n_jobs]
+  // A chain CTA ("slot") walks n_jobs / n_slots chains one after the other: its running chunk number v counts through
+  // all of them (chain v / n_chunks of the slot, chunk v % n_chunks), and ring, flags and barrier parities go by v.
+  int* ready = flags + F_FLAG_INTS;                        // [n_slots][KR]
+  int* consumed = ready + (size_t)n_slots * KR;            // [n_slots]
+  const int n_virtual = (n_jobs / n_slots) * n_chunks;     // chunks a slot walks
 
   if (tid == 0) {
     for (int i = 0; i < F_NSTAGE; i++) tc::mbar_init(&full_bar[i], 1);
@@ -1042,13 +1047,13 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
   const uint32_t tmem = tmem_slot;
   uint8_t* const smem_base = smem;
 
-  if ((int)blockIdx.x >= n_jobs) {
+  if ((int)blockIdx.x >= n_slots) {
     // =========================== two preparation workers ===========================
     const int sub = warp >> 3;
 #ifdef HK_DIAG_ONE_WORKER
-    const int worker = (int)blockIdx.x - n_jobs, n_workers = (int)gridDim.x - n_jobs;
+    const int worker = (int)blockIdx.x - n_slots, n_workers = (int)gridDim.x - n_slots;
 #else
-    const int worker = ((int)blockIdx.x - n_jobs) * 2 + sub, n_workers = ((int)gridDim.x - n_jobs) * 2;
+    const int worker = ((int)blockIdx.x - n_slots) * 2 + sub, n_workers = ((int)gridDim.x - n_slots) * 2;
 #endif
     const long long n_units = (long long)n_chunks * n_jobs;
     PrepCtx ctx{smem + sub * P1_SMEM, sub ? &out_bar : &mma_bar, 0u, &abort_flag, tmem + sub * 256, tid & 255, 1 + sub, false,
@@ -1061,26 +1066,31 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     if (sub == 1) goto prep_done;                          // diagnostic: stage times of a worker that has its SM alone
 #endif
     for (long long u = worker; u < n_units; u += n_workers, it++) {
-      const int chunk = (int)(u / n_jobs), job = (int)(u % n_jobs);
+      // units in the order the slots need them: running chunk v of every slot, then v + 1, ...
+      const int v = (int)(u / n_slots), slot = (int)(u % n_slots);
+      const int chunk = v % n_chunks, job = slot + n_slots * (v / n_chunks);
       const int b = job / H, head = job % H;
 #ifdef HK_DIAG
       ctx.trace = (worker == 7 && it == 20);
 #endif
       // the slot of this chunk must have been drained by the chain CTA (it held chunk - KR): thread 0 asks now and
       // looks at the answer just before the worker's first write to the unit (prep_unit calls slot_wait there)
-      ctx.slot_flag = consumed + job;
-      ctx.slot_want = chunk >= KR ? chunk - KR + 1 : 0;
+      ctx.slot_flag = consumed + slot;
+      ctx.slot_want = v >= KR ? v - KR + 1 : 0;
       ctx.slot_seen = (ctx.tid == 0 && ctx.slot_want > 0) ? ld_relaxed_gpu(ctx.slot_flag) : 0;
-      uint8_t* unit = ring + ((size_t)(chunk % KR) * n_jobs + job) * U_BYTES;
+      uint8_t* unit = ring + ((size_t)(v % KR) * n_slots + slot) * U_BYTES;
       const long long pu = u + n_workers;
       int pf_head = 0, pf_chunk = -1;
-      if (pu < n_units && (int)(pu % n_jobs) / H == b) { pf_chunk = (int)(pu / n_jobs); pf_head = (int)(pu % n_jobs) % H; }
+      if (pu < n_units) {
+        const int pv = (int)(pu / n_slots), pjob = (int)(pu % n_slots) + n_slots * (pv / n_chunks);
+        if (pjob / H == b) { pf_chunk = pv % n_chunks; pf_head = pjob % H; }
+      }
       ctx.bar_parity = it & 1;
       KT_TRACE(14);
       prep_unit<GATED, true>(ctx, qkv, g, beta_in, unit, seqlen, H, head, chunk, b, pf_head, pf_chunk, dt_bias, a_log, lower_bound);
       // publish: prep_unit ends with the worker's barrier, so every thread's writes of this unit precede this
       // release store (which is cumulative over them)
-      if (ctx.tid == 0) st_release_gpu(ready + (size_t)job * KR + (chunk % KR), chunk + 1);
+      if (ctx.tid == 0) st_release_gpu(ready + (size_t)slot * KR + (v % KR), v + 1);
       KT_TRACE(15);
       KT_FLUSH();
     }
@@ -1092,13 +1102,18 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     // the chain CTA's tiles start at a 1 KB boundary (the output tile is written in the 128-byte-swizzle pattern,
     // which is a function of the shared-memory address)
     uint8_t* const smem = smem_base + ((1024u - (tc::smem_u32(smem_base) & 1023u)) & 1023u);
-    const int job = blockIdx.x, b = job / H, head = job % H;
+    const int cslot = blockIdx.x;                           // this CTA's chain slot
     const int lq = warp & 3, cb = warp >> 2;               // TMEM lane quarter, 32-column block
     const int rowi = lq * 32 + (tid & 31);                       // k row of the state / token row of W S0 / output row - 64
     const int v0 = cb * KNV;
-    const int slot = slots ? slots[b] : b;
-    float* st = state + ((size_t)slot * H + head) * KD * KD + (size_t)rowi * KD + v0;
-    const int* my_ready = ready + (size_t)job * KR;
+    // chain number `ci` of this slot: (batch, head) = job cslot + n_slots * ci; its state rows for this thread
+    auto chain_state = [&](int ci) -> float* {
+      const int job = cslot + n_slots * ci, jb = job / H, jh = job % H;
+      const int sl = slots ? slots[jb] : jb;
+      return state + ((size_t)sl * H + jh) * KD * KD + (size_t)rowi * KD + v0;
+    };
+    float* st = chain_state(0);
+    const int* my_ready = ready + (size_t)cslot * KR;
 
     for (int i = tid; i < 8192 / 16; i += 512)
       for (int s_i = 0; s_i < F_NSTAGE; s_i++) reinterpret_cast<uint4*>(smem + s_i * F_STAGE + F_BB)[i] = make_uint4(0, 0, 0, 0);
@@ -1128,7 +1143,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     int issued = 0;                                        // producer only: chunks whose copies have been issued
     auto issue_loads = [&](int chunk) {
       uint8_t* stg = smem + (chunk % F_NSTAGE) * F_STAGE;
-      const uint8_t* u = ring + ((size_t)(chunk % KR) * n_jobs + job) * U_BYTES;
+      const uint8_t* u = ring + ((size_t)(chunk % KR) * n_slots + cslot) * U_BYTES;
       uint64_t* bar = &full_bar[chunk % F_NSTAGE];
       fence_proxy_async_all();
       tc::mbar_arrive_expect_tx(bar, U_BYTES);
@@ -1137,7 +1152,7 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       tc::bulk_g2s(stg + F_KT, u + U_KT, 16384 + 16384 + 512, bar);
     };
     if (producer) {
-      for (; issued < F_NSTAGE && issued < n_chunks; issued++) {
+      for (; issued < F_NSTAGE && issued < n_virtual; issued++) {
         poll_flag_ge(my_ready + (issued % KR), issued + 1, &abort_flag, g_abort, 21);
         issue_loads(issued);
       }
@@ -1160,10 +1175,11 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     // With a tensor map over the output the rows leave as TWO tiled TMA stores per chunk (64 tokens x 64 channels each,
     // 128-byte-swizzle boxes; rows past the end of the sequence are clipped by the copy engine): the tile is written
     // conflict-free (16-byte piece p of row r at p ^ (r % 8)) and one thread hands it over.
-    auto emit_outputs = [&](int c, bool valid) {
+    auto emit_outputs = [&](int vc, bool valid) {          // vc: running chunk number of the slot
+      const int c = vc % n_chunks, ejob = cslot + n_slots * (vc / n_chunks), b = ejob / H, head = ejob % H;
       const int trow = rowi - 64;
       uint32_t r[32];
-      tc::tmem_ld32(tmem + ((c & 1) ? 128u : 0u) + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
+      tc::tmem_ld32(tmem + ((vc & 1) ? 128u : 0u) + (uint32_t)v0 + ((uint32_t)(lq * 32) << 16), r);
       tc::tmem_ld_wait();
       const bool issuer = warp == 2 && (tid & 31) == 0;
       if (use_tma_out) {
@@ -1219,7 +1235,28 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
     };
     bool prev_ok = true;
 
-    for (int chunk = 0; chunk < n_chunks; chunk++) {
+    // `chunk` is the slot's RUNNING chunk number over all of its chains
+    for (int chunk = 0; chunk < n_virtual; chunk++) {
+      if (chunk > 0 && chunk % n_chunks == 0) {
+        // the next chain of this slot: its state replaces the previous one (stored at the end of the last iteration)
+        st = chain_state(chunk / n_chunks);
+#pragma unroll
+        for (int u = 0; u < KNV / 4; u++) {
+          const float4 v = *reinterpret_cast<const float4*>(st + u * 4);
+          S[4 * u] = v.x; S[4 * u + 1] = v.y; S[4 * u + 2] = v.z; S[4 * u + 3] = v.w;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          uint4 p;
+          p.x = pack_h2(S[8 * u], S[8 * u + 1]); p.y = pack_h2(S[8 * u + 2], S[8 * u + 3]);
+          p.z = pack_h2(S[8 * u + 4], S[8 * u + 5]); p.w = pack_h2(S[8 * u + 6], S[8 * u + 7]);
+          *reinterpret_cast<uint4*>(sS_row + u * 2048) = p;
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        tc::fence_after_sync();
+      }
       const int sidx = chunk % F_NSTAGE;
       uint8_t* stg = smem + sidx * F_STAGE;
       const uint32_t stg_addr = tc::smem_u32(stg);
@@ -1291,14 +1328,14 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       if (producer) {
         // the unit of this chunk has landed in shared memory: its slot may be rewritten.  A relaxed store is enough:
         // the copy engine's reads are complete, nothing this thread wrote is handed over with the flag.
-        st_relaxed_gpu(consumed + job, chunk + 1);
+        st_relaxed_gpu(consumed + cslot, chunk + 1);
         // catch-up: the other stage is free while the next chunk's copies have not been issued
-        if (issued == chunk + 1 && chunk + 1 < n_chunks && ld_acquire_gpu(my_ready + ((chunk + 1) % KR)) >= chunk + 2) {
+        if (issued == chunk + 1 && chunk + 1 < n_virtual && ld_acquire_gpu(my_ready + ((chunk + 1) % KR)) >= chunk + 2) {
           issue_loads(chunk + 1);
           issued = chunk + 2;
         }
         // sampled now, used when this chunk's stage is released at the end of the iteration
-        if (issued == chunk + 2 && chunk + 2 < n_chunks) next_flag = ld_acquire_gpu(my_ready + ((chunk + 2) % KR));
+        if (issued == chunk + 2 && chunk + 2 < n_virtual) next_flag = ld_acquire_gpu(my_ready + ((chunk + 2) % KR));
       }
       // ---- D2 = Kt^T U (state path, warp 0) ;  D1 rows 64-127 += (B beta) U (outputs, warp 2, own barrier) ----
       if (issue_warp) {
@@ -1342,6 +1379,12 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
           *reinterpret_cast<uint4*>(sS_row + u * 2048) = p;
         }
       }
+      if (chunk % n_chunks == n_chunks - 1 && !abort_flag) {
+        // last chunk of a chain: its final state goes back to memory
+#pragma unroll
+        for (int u = 0; u < KNV / 4; u++)
+          *reinterpret_cast<float4*>(st + u * 4) = make_float4(S[4 * u], S[4 * u + 1], S[4 * u + 2], S[4 * u + 3]);
+      }
       KS_TRACE(5, chunk);
       // the output contraction must be complete before the block barrier: the stage and the U tile it reads are
       // rewritten after it; the rows themselves are read in the next iteration
@@ -1355,19 +1398,14 @@ __global__ __launch_bounds__(512, 1) void kda_fused_kernel(
       tc::fence_after_sync();
       KS_TRACE(6, chunk);
       // refill of this stage, if the unit two chunks ahead was already complete when its flag was sampled
-      if (producer && issued == chunk + 2 && chunk + 2 < n_chunks && next_flag >= chunk + 3) {
+      if (producer && issued == chunk + 2 && chunk + 2 < n_virtual && next_flag >= chunk + 3) {
         issue_loads(chunk + 2);
         issued = chunk + 3;
       }
     }
-    if (lq >= 2 && n_chunks > 0) {
-      emit_outputs(n_chunks - 1, prev_ok);
+    if (lq >= 2 && n_virtual > 0) {
+      emit_outputs(n_virtual - 1, prev_ok);
       if (use_tma_out && warp == 2 && (tid & 31) == 0) tc::bulk_wait_all<0>();
-    }
-    if (!abort_flag) {
-#pragma unroll
-      for (int u = 0; u < KNV / 4; u++)
-        *reinterpret_cast<float4*>(st + u * 4) = make_float4(S[4 * u], S[4 * u + 1], S[4 * u + 2], S[4 * u + 3]);
     }
   }
   tc::fence_before_sync();
@@ -1389,11 +1427,21 @@ namespace {
 // The fused launch serves calls with few (batch, head) chains: every chain occupies one SM, the rest prepare.
 // hk_kda_chunked_set_form(1) keeps the two-kernel form for every call (cross-check of the two forms in the tests).
 int g_chunked_form = 0;
-bool fused_eligible(int n_jobs) {
-  return g_chunked_form == 0 && n_jobs <= 48 && sm_count() - n_jobs >= 64;
+// Number of chain CTAs ("slots") of the fused launch for n_jobs (batch, head) chains, 0 = use the two-kernel form.  Up to
+// 48 chains get a slot each; more chains share slots (a slot walks its chains one after the other), which needs a slot
+// count that divides n_jobs: the largest divisor in [16, 48] that leaves at least 64 SMs to the preparation.
+int fused_slots(long long n_jobs) {
+  if (g_chunked_form != 0 || n_jobs <= 0) return 0;
+  const int room = sm_count() - 64;
+  for (int d = 48; d >= 1; d--) {
+    if (d > room || n_jobs % d != 0) continue;
+    if (d == n_jobs || d >= 16) return d;
+    break;
+  }
+  return 0;
 }
-size_t fused_flag_bytes(int n_jobs) {
-  return (((size_t)F_FLAG_INTS + (size_t)n_jobs * (KR + 1)) * sizeof(int) + 255) / 256 * 256;
+size_t fused_flag_bytes(int n_slots) {
+  return (((size_t)F_FLAG_INTS + (size_t)n_slots * (KR + 1)) * sizeof(int) + 255) / 256 * 256;
 }
 }  // namespace
 }  // namespace hk
@@ -1415,8 +1463,8 @@ HK_API int hk_kda_chunked_set_form(int form) {
 HK_API size_t hk_kda_chunked_workspace_bytes(int bsz, int seqlen, int num_heads) {
   if (bsz <= 0 || seqlen <= 0 || num_heads <= 0) return 0;
   const long long n_jobs = (long long)bsz * num_heads;
-  if (n_jobs <= 48 && hk::fused_eligible((int)n_jobs))
-    return hk::fused_flag_bytes((int)n_jobs) + (size_t)hk::KR * n_jobs * hk::U_BYTES;
+  if (const int n_slots = hk::fused_slots(n_jobs))
+    return hk::fused_flag_bytes(n_slots) + (size_t)hk::KR * n_slots * hk::U_BYTES;
   const size_t n_chunks = ((size_t)seqlen + hk::KC - 1) / hk::KC;
   return (size_t)bsz * num_heads * n_chunks * hk::U_BYTES;
 }
@@ -1449,10 +1497,10 @@ int chunked_prefill_launch(const void* mixed_qkv, const float* g_or_f, const voi
   }
   cudaStream_t s = as_stream(stream);
   int* st = device_status_ptr();
-  if ((long long)bsz * num_heads <= 48 && fused_eligible(bsz * num_heads)) {
-    // one cooperative launch: chains on the first n_jobs CTAs, preparation workers on all others
+  if (const int n_slots = fused_slots((long long)bsz * num_heads)) {
+    // one cooperative launch: chain slots on the first n_slots CTAs, preparation workers on all others
     const int n_jobs = bsz * num_heads;
-    const size_t flag_bytes = fused_flag_bytes(n_jobs);
+    const size_t flag_bytes = fused_flag_bytes(n_slots);
     if (cudaMemsetAsync(workspace, 0, flag_bytes, s) != cudaSuccess) return HK_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count());
@@ -1503,9 +1551,9 @@ int chunked_prefill_launch(const void* mixed_qkv, const float* g_or_f, const voi
     const float a_lb = gated ? lower_bound : 0.f;
     cudaError_t e = gated
         ? cudaLaunchKernelEx(&cfg, kda_fused_kernel<true>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
-                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out)
+                             seqlen, num_heads, n_chunks, n_jobs, n_slots, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out)
         : cudaLaunchKernelEx(&cfg, kda_fused_kernel<false>, a_qkv, g_or_f, beta_or_b, a_ring, a_flags, state, a_out, out_f32,
-                             seqlen, num_heads, n_chunks, n_jobs, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out);
+                             seqlen, num_heads, n_chunks, n_jobs, n_slots, slots, a_scale, st, a_dt, a_al, a_lb, tmap, use_tma_out);
     return e == cudaSuccess ? HK_OK : HK_ERR_CUDA;
   }
   const dim3 grid(num_heads, n_chunks, bsz);

@@ -220,11 +220,12 @@ def test_chunked_batch_and_slots():
     assert max_rel(o32.cpu().numpy(), o_32) < 2e-3 and frob_rel(st.cpu().numpy(), o_st) < 1e-2
 
 
-@pytest.mark.parametrize("T,H,bsz", [(2100, 3, 1), (1500, 2, 2), (4096, 32, 1)])
+@pytest.mark.parametrize("T,H,bsz", [(2100, 3, 1), (1500, 2, 2), (4096, 32, 1), (1200, 64, 1), (1100, 32, 3), (1100, 17, 3)])
 def test_chunked_fused_launch_equals_two_kernel_form(T, H, bsz):
     """the persistent fused launch (chains + preparation workers through the L2 ring; T spans more chunks than the
     ring has slots, so slots are reused) against the two-kernel form on the same inputs: same bits; the short
-    cases also against the oracle"""
+    cases also against the oracle.  The last three cases have more than 48 chains: 32, 48 and 17 chain CTAs walk two,
+    two and three chains each, one after the other."""
     D = 128
     inp = synth.kda_inputs(T, H, D, bsz=bsz, seed=200 + T)
     s0 = (0.1 * synth.rng(8).standard_normal((bsz, 1, H, D, D), dtype=np.float32)).astype(np.float32)
