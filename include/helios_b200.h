@@ -102,10 +102,11 @@ int hk_kda_decode_layer(const float* x32, void* conv_state, const void* conv_wei
  * Requires dk = dv = 128, Hk == Hv.  seqlen may be any positive length (a ragged tail shorter
  * than a chunk is processed by the same kernels).  `workspace` must hold at least
  * hk_kda_chunked_workspace_bytes(bsz, seqlen, num_heads) bytes, 256-byte aligned.
- * Two forms.  Calls with at most 48 (batch, head) chains run as ONE persistent cooperative launch: a chain
- * per SM, the other SMs prepare the chunks and hand them over through a ring of 16 chunk slots per chain
- * (workspace = bsz * num_heads * 16 * 74,240 B + flags, independent of seqlen; it stays in L2).  Larger
- * calls run as two kernels with one 74,240-byte workspace unit per (batch, head, chunk).
+ * Two forms.  ONE persistent cooperative launch when the chains fit its chain CTAs (at most 48 chains: a chain per SM;
+ * more chains when a number of chain CTAs in [16, 48] divides their count, e.g. 64 heads or 8 x 32: a chain CTA then
+ * walks several chains one after the other); the other SMs prepare the chunks and hand them over through a ring of 16
+ * chunk slots per chain CTA (workspace = chain CTAs * 16 * 74,240 B + flags, independent of seqlen; it stays in L2).
+ * Other calls run as two kernels with one 74,240-byte workspace unit per (batch, head, chunk).
  * hk_kda_chunked_set_form(1) selects the two-kernel form for every later call and workspace query of this
  * process, hk_kda_chunked_set_form(0) the automatic choice (default).                              */
 int hk_kda_chunked_set_form(int form);
